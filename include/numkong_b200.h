@@ -1,0 +1,132 @@
+/**
+ *  @file numkong_b200.h
+ *  @brief C ABI of libnumkong_b200.so: NumKong's packed-contraction entry points, executed on an
+ *         NVIDIA B200 (sm_100a). Plain pointers and sizes only.
+ *
+ *  The `nk_*` functions below keep the exact names, argument order and argument meaning of
+ *  NumKong v7.6.0, so a binding that resolves them by symbol (Rust `extern "C"`, Swift, cgo,
+ *  ctypes) or through `nk_find_kernel_punned` needs no source change. The reference declaration
+ *  each one stands in for is cited next to it (paths inside the NumKong tree).
+ *
+ *  Conventions kept from the reference:
+ *   - row-major matrices, `C[i,j] = sum_l A[i,l] * B[j,l]`, all strides in BYTES (dots.h:60-72);
+ *   - the caller owns every buffer; `packed_size` is a pure function of (width, depth);
+ *   - the packed blob is opaque and position independent (it may be memcpy'd, moved, saved);
+ *   - functions return void; on failure the output is filled with 0xFF bytes (c/numkong.c:78-81)
+ *     and `nkb_last_error()` explains why; `packed_size` returns 0 for an unsupported call.
+ *
+ *  Pointer kinds: every pointer may be device memory, managed memory, pinned host memory or
+ *  ordinary host memory, mixed freely. Device/managed operands are used in place and the call is
+ *  asynchronous on the thread's stream (`nkb_set_stream`); when any operand lives in host memory
+ *  the library stages it through device buffers it owns and the call returns with the result
+ *  complete. A host-resident packed blob is uploaded once and its device copy is reused by later
+ *  calls ("pack once, query many").
+ *
+ *  Element types: nk_bf16_t / nk_f16_t are 16-bit storage words, e4m3 / e5m2 / e2m3 / e3m2 one
+ *  byte per value (FP6 as 0b00SEEMMM / 0b00SEEEMM, types.h:785-861). They are `void` here so the
+ *  header stands alone; the dtype codes equal nk_dtype_t (types.h:923-953).
+ */
+#ifndef NUMKONG_B200_H_
+#define NUMKONG_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define NKB_API __attribute__((visibility("default")))
+#else
+#define NKB_API
+#endif
+
+typedef uint64_t nk_size_t; /* types.h:854-856 */
+
+/* dtype codes, numerically nk_dtype_t (types.h:923-953) */
+#define NKB_DTYPE_I8 (1u << 2)
+#define NKB_DTYPE_U8 (1u << 6)
+#define NKB_DTYPE_F32 (1u << 11)
+#define NKB_DTYPE_F16 (1u << 12)
+#define NKB_DTYPE_BF16 (1u << 13)
+#define NKB_DTYPE_E4M3 (1u << 14)
+#define NKB_DTYPE_E5M2 (1u << 15)
+#define NKB_DTYPE_E2M3 (1u << 18)
+#define NKB_DTYPE_E3M2 (1u << 19)
+
+/* ---- packed GEMM: size / pack / multiply ------------------------------------------------------
+ * nk_dots_packed_size_<t>  replaces include/numkong/dots.h:177-201   (wrappers c/numkong.c:628-644)
+ * nk_dots_pack_<t>         replaces include/numkong/dots.h:211-246   (wrappers c/numkong.c:646-665)
+ * nk_dots_packed_<t>       replaces include/numkong/dots.h:259-296   (wrappers c/numkong.c:667-694)
+ * Output cell type: i32 (i8), u32 (u8), f64 (f32), f32 otherwise (include/numkong/dot.h:633-654).
+ * nk_angulars_packed_<t> / nk_euclideans_packed_<t> replace include/numkong/spatials.h:72-
+ * (wrappers c/numkong.c:696-736); output f64 for f32 inputs, f32 otherwise (spatial.h:836-890).
+ */
+#define NKB_DECLARE_PACKED_FAMILY(T)                                                                                   \
+    NKB_API nk_size_t nk_dots_packed_size_##T(nk_size_t width, nk_size_t depth);                                       \
+    NKB_API void nk_dots_pack_##T(void const *b, nk_size_t width, nk_size_t depth, nk_size_t b_stride,                 \
+                                  void *b_packed);                                                                     \
+    NKB_API void nk_dots_packed_##T(void const *a, void const *b_packed, void *c, nk_size_t height, nk_size_t width,   \
+                                    nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride);                          \
+    NKB_API void nk_angulars_packed_##T(void const *a, void const *b_packed, void *c, nk_size_t height,                \
+                                        nk_size_t width, nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride);     \
+    NKB_API void nk_euclideans_packed_##T(void const *a, void const *b_packed, void *c, nk_size_t height,              \
+                                          nk_size_t width, nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride);
+
+NKB_DECLARE_PACKED_FAMILY(i8)
+NKB_DECLARE_PACKED_FAMILY(u8)
+NKB_DECLARE_PACKED_FAMILY(bf16)
+NKB_DECLARE_PACKED_FAMILY(f16)
+NKB_DECLARE_PACKED_FAMILY(e4m3)
+NKB_DECLARE_PACKED_FAMILY(e5m2)
+NKB_DECLARE_PACKED_FAMILY(e2m3)
+NKB_DECLARE_PACKED_FAMILY(e3m2)
+NKB_DECLARE_PACKED_FAMILY(f32)
+
+/* ---- MaxSim late interaction -------------------------------------------------------------------
+ * replaces include/numkong/maxsim.h:72-114 (wrappers c/numkong.c:738-765). Both sides are packed
+ * with the same function. result: f32 for bf16/f16, f64 for f32 (maxsim.h:350-357):
+ *   sum_i max(0, 1 - (max_j q_i . d_j) / (|q_i| |d_j*|)),  j* = first argmax of the raw dot.
+ */
+#define NKB_DECLARE_MAXSIM_FAMILY(T)                                                                                   \
+    NKB_API nk_size_t nk_maxsim_packed_size_##T(nk_size_t vector_count, nk_size_t depth);                              \
+    NKB_API void nk_maxsim_pack_##T(void const *vectors, nk_size_t vector_count, nk_size_t depth, nk_size_t stride,    \
+                                    void *packed);                                                                     \
+    NKB_API void nk_maxsim_packed_##T(void const *query_packed, void const *document_packed, nk_size_t query_count,    \
+                                      nk_size_t document_count, nk_size_t depth, void *result);
+
+NKB_DECLARE_MAXSIM_FAMILY(bf16)
+NKB_DECLARE_MAXSIM_FAMILY(f16)
+NKB_DECLARE_MAXSIM_FAMILY(f32)
+
+/* ---- run-time lookup ---------------------------------------------------------------------------
+ * replaces nk_find_kernel_punned (c/numkong.c:848-913) for the kernel kinds of this path:
+ * 'P' packed size, 'Q' pack, 'G' dots_packed, 'N' angulars_packed, 'E' euclideans_packed,
+ * 'L' / 'l' / 'T' MaxSim size / pack / compute (capabilities.h:229-249). Unknown combinations give
+ * *kernel_output = NULL and *capability_output = 0, which callers already treat as "no kernel".
+ */
+#define NKB_CAPABILITY_B200 (1ull << 40)
+NKB_API void nk_find_kernel_punned(int kind, uint32_t dtype, uint64_t viable_capabilities, void **kernel_output,
+                                   uint64_t *capability_output);
+NKB_API uint64_t nk_capabilities(void);            /* c/numkong.c:832-843: here NKB_CAPABILITY_B200 or 0 */
+NKB_API int nk_configure_thread(uint64_t caps);    /* capabilities.h:909: nothing to set up per thread here; returns 1 */
+
+/* ---- additions (no counterpart in the reference) -------------------------------------------- */
+/** Last error of the calling thread, "" when the last call succeeded. The string stays valid until the next call. */
+NKB_API char const *nkb_last_error(void);
+/** Stream (a cudaStream_t) the calling thread's next calls are enqueued on. NULL selects the default stream. */
+NKB_API void nkb_set_stream(void *cuda_stream);
+/** Waits for the calling thread's stream and returns the device error word (0 = no pipeline wait ever gave up). */
+NKB_API uint32_t nkb_synchronize(void);
+/** Kernels launched by this library in this process so far (for launch accounting in benchmarks). */
+NKB_API uint64_t nkb_launch_count(void);
+/** Forces a GEMM tile configuration for testing/tuning: 0 = choose by shape. */
+NKB_API void nkb_set_gemm_variant(int variant);
+/** Drops the cached device copies of host-resident packed blobs and the staging buffers of the calling thread. */
+NKB_API void nkb_release_caches(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NUMKONG_B200_H_ */

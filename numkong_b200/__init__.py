@@ -1,0 +1,319 @@
+"""Host-side mirror of NumKong's Python interface for the packed-contraction path, running on a B200.
+
+Same names and argument meaning as the reference's module (python/numkong.c:1135-1146,
+python/numkong/__init__.pyi:999-1074):
+
+    dots_pack(b, dtype=None) -> PackedMatrix
+    dots_packed / angulars_packed / euclideans_packed(a, packed, *, out=None) -> matrix
+    maxsim_pack(vectors, dtype=None) -> MaxSimPackedMatrix
+    maxsim_packed(q_packed, d_packed) -> float ;  maxsim(q, d, dtype=None) -> float
+
+Every call goes through the C ABI of libnumkong_b200.so with plain pointers. Inputs may be
+NumPy arrays (host memory: the library stages them) or torch tensors (host or CUDA: CUDA
+tensors are used in place and the result is a CUDA tensor). Element types NumPy cannot name
+(bf16, e4m3, e5m2, e2m3, e3m2) are passed as uint16 / uint8 storage with `dtype="bf16"` etc.,
+or as ml_dtypes / torch low-precision dtypes.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Optional, Tuple
+
+import numpy as np
+
+from . import _lib
+from ._lib import DTYPE_BYTES, DTYPE_CODES, MAXSIM_DTYPES, PACKED_DTYPES, check, last_error, lib
+
+__all__ = [
+    "PackedMatrix", "MaxSimPackedMatrix", "dots_pack", "dots_packed", "angulars_packed", "euclideans_packed",
+    "maxsim_pack", "maxsim_packed", "maxsim", "maxsims_packed", "angulars_packed_topk", "euclideans_packed_topk",
+    "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error",
+]
+
+_NUMPY_NAMES = {
+    "int8": "i8", "uint8": "u8", "float32": "f32", "float16": "f16", "bfloat16": "bf16",
+    "float8_e4m3fn": "e4m3", "float8_e5m2": "e5m2", "float6_e2m3fn": "e2m3", "float6_e3m2fn": "e3m2",
+}
+_TORCH_NAMES = {
+    "torch.int8": "i8", "torch.uint8": "u8", "torch.float32": "f32", "torch.float16": "f16",
+    "torch.bfloat16": "bf16", "torch.float8_e4m3fn": "e4m3", "torch.float8_e5m2": "e5m2",
+}
+_OUT_NUMPY = {"i8": np.int32, "u8": np.uint32, "f32": np.float64}
+
+
+def _is_torch(x: Any) -> bool:
+    return type(x).__module__.startswith("torch")
+
+
+class _View:
+    """Pointer, shape and byte strides of a 2-D matrix, plus where it lives."""
+
+    def __init__(self, x: Any, dtype: Optional[str]):
+        self.obj = x
+        if _is_torch(x):
+            if x.dim() != 2:
+                raise ValueError("expected a 2-D matrix")
+            if x.stride(1) != 1 and x.shape[1] > 1:
+                raise ValueError("rows must be contiguous (column-major inputs are not supported)")
+            name = dtype or _TORCH_NAMES.get(str(x.dtype))
+            if name is None:
+                raise TypeError(f"unsupported torch dtype {x.dtype}")
+            self.is_cuda = x.is_cuda
+            self.ptr = x.data_ptr()
+            self.rows, self.cols = int(x.shape[0]), int(x.shape[1])
+            self.stride = int(x.stride(0)) * x.element_size() if self.rows > 1 else self.cols * x.element_size()
+            item = x.element_size()
+        else:
+            x = np.asarray(x)
+            self.obj = x
+            if x.ndim != 2:
+                raise ValueError("expected a 2-D matrix")
+            if x.shape[1] > 1 and x.strides[1] != x.itemsize:
+                raise ValueError("rows must be contiguous (column-major inputs are not supported)")
+            name = dtype or _NUMPY_NAMES.get(x.dtype.name)
+            if name is None:
+                raise TypeError(f"unsupported numpy dtype {x.dtype}; pass dtype='bf16' etc. with uint16/uint8 storage")
+            self.is_cuda = False
+            self.ptr = x.ctypes.data
+            self.rows, self.cols = int(x.shape[0]), int(x.shape[1])
+            self.stride = int(x.strides[0]) if self.rows > 1 else self.cols * x.itemsize
+            item = x.itemsize
+        if name not in DTYPE_CODES:
+            raise TypeError(f"unknown dtype name {name!r}")
+        if item != DTYPE_BYTES[name]:
+            raise TypeError(f"dtype {name!r} needs {DTYPE_BYTES[name]}-byte elements, got {item}-byte storage")
+        self.dtype = name
+
+
+def _alloc_bytes(nbytes: int, cuda: bool):
+    if cuda:
+        import torch
+        return torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    return np.empty(nbytes, dtype=np.uint8)
+
+
+def _ptr(buf: Any) -> int:
+    return buf.data_ptr() if _is_torch(buf) else buf.ctypes.data
+
+
+class PackedMatrix:
+    """Opaque pre-packed B matrix (the counterpart of the reference's PackedMatrix object,
+    python/matrix.h): the blob lives where the source matrix lived (host or CUDA)."""
+
+    kind = "dots"
+
+    def __init__(self, buffer: Any, dtype: str, width: int, depth: int):
+        self.buffer, self.dtype, self.width, self.depth = buffer, dtype, width, depth
+
+    @property
+    def nbytes(self) -> int:
+        return int(self.buffer.numel()) if _is_torch(self.buffer) else int(self.buffer.nbytes)
+
+    @property
+    def is_cuda(self) -> bool:
+        return _is_torch(self.buffer) and self.buffer.is_cuda
+
+    @staticmethod
+    def packed_size(width: int, depth: int, dtype: str) -> int:
+        if dtype not in PACKED_DTYPES:
+            raise LookupError(f"no packed kernels for dtype {dtype!r}")
+        return int(getattr(lib, f"nk_dots_packed_size_{dtype}")(width, depth))
+
+    def __repr__(self) -> str:
+        return f"PackedMatrix(dtype={self.dtype}, width={self.width}, depth={self.depth}, nbytes={self.nbytes})"
+
+
+class MaxSimPackedMatrix(PackedMatrix):
+    """Packed token vectors of one query or one document (python/maxsim.h of the reference)."""
+
+    kind = "maxsim"
+
+    @staticmethod
+    def packed_size(count: int, depth: int, dtype: str) -> int:
+        if dtype not in MAXSIM_DTYPES:
+            raise LookupError(f"MaxSim supports {MAXSIM_DTYPES}, not {dtype!r}")
+        return int(getattr(lib, f"nk_maxsim_packed_size_{dtype}")(count, depth))
+
+
+def dots_pack(b: Any, dtype: Optional[str] = None) -> PackedMatrix:
+    """Packs B (width x depth, row-major) once for repeated multiplication. Mirrors nk.dots_pack."""
+    v = _View(b, dtype)
+    if v.dtype not in PACKED_DTYPES:
+        raise LookupError(f"no packed kernels for dtype {v.dtype!r}")
+    size = PackedMatrix.packed_size(v.rows, v.cols, v.dtype)
+    buf = _alloc_bytes(size, v.is_cuda)
+    getattr(lib, f"nk_dots_pack_{v.dtype}")(v.ptr, v.rows, v.cols, v.stride, _ptr(buf))
+    check("dots_pack")
+    return PackedMatrix(buf, v.dtype, v.rows, v.cols)
+
+
+def _out_matrix(v: _View, width: int, out: Any, dtype_name: str):
+    """Allocates (or validates) the result matrix; returns (object, ptr, stride)."""
+    if out is not None:
+        if _is_torch(out):
+            if tuple(out.shape) != (v.rows, width) or out.element_size() != (8 if dtype_name == "f32" else 4):
+                raise ValueError("out has the wrong shape or cell size")
+            return out, out.data_ptr(), (int(out.stride(0)) * out.element_size() if v.rows > 1 else width * out.element_size())
+        if out.shape != (v.rows, width) or out.itemsize != (8 if dtype_name == "f32" else 4):
+            raise ValueError("out has the wrong shape or cell size")
+        return out, out.ctypes.data, (int(out.strides[0]) if v.rows > 1 else width * out.itemsize)
+    return None, 0, 0
+
+
+def _packed_call(op: str, a: Any, packed: PackedMatrix, out: Any, dtype: Optional[str]):
+    if not isinstance(packed, PackedMatrix) or packed.kind != "dots":
+        raise TypeError("second argument must be a PackedMatrix produced by dots_pack")
+    v = _View(a, dtype or packed.dtype)
+    if v.dtype != packed.dtype:
+        raise TypeError(f"dtype mismatch: a is {v.dtype}, packed matrix is {packed.dtype}")
+    if v.cols != packed.depth:
+        raise ValueError(f"depth mismatch: a has {v.cols} columns, packed matrix has depth {packed.depth}")
+    t = v.dtype
+    obj, ptr, stride = _out_matrix(v, packed.width, out, t)
+    if obj is None:
+        if v.is_cuda:
+            import torch
+            tdt = torch.float64 if t == "f32" else (torch.int32 if (t in ("i8", "u8") and op == "dots") else torch.float32)
+            obj = torch.empty((v.rows, packed.width), dtype=tdt, device=v.obj.device)
+            ptr, stride = obj.data_ptr(), packed.width * obj.element_size()
+        else:
+            ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if op == "dots" else np.float32)
+            obj = np.empty((v.rows, packed.width), dtype=ndt)
+            ptr, stride = obj.ctypes.data, packed.width * obj.itemsize
+    getattr(lib, f"nk_{op}_packed_{t}")(v.ptr, _ptr(packed.buffer), ptr, v.rows, packed.width, v.cols, v.stride, stride)
+    check(f"{op}_packed")
+    return obj
+
+
+def dots_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Optional[str] = None):
+    """C = A . B^T with widening accumulation (i8->i32, u8->u32, f32->f64, else f32). Mirrors nk.dots_packed."""
+    return _packed_call("dots", a, packed, out, dtype)
+
+
+def angulars_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Optional[str] = None):
+    """Batched angular (cosine) distances. Mirrors nk.angulars_packed."""
+    return _packed_call("angulars", a, packed, out, dtype)
+
+
+def euclideans_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Optional[str] = None):
+    """Batched Euclidean distances. Mirrors nk.euclideans_packed."""
+    return _packed_call("euclideans", a, packed, out, dtype)
+
+
+def maxsim_pack(vectors: Any, dtype: Optional[str] = None) -> MaxSimPackedMatrix:
+    """Packs the token vectors of a query or a document. Mirrors nk.maxsim_pack."""
+    v = _View(vectors, dtype)
+    if v.dtype not in MAXSIM_DTYPES:
+        raise TypeError(f"MaxSim supports {MAXSIM_DTYPES}, not {v.dtype!r}")
+    size = MaxSimPackedMatrix.packed_size(v.rows, v.cols, v.dtype)
+    buf = _alloc_bytes(size, v.is_cuda)
+    getattr(lib, f"nk_maxsim_pack_{v.dtype}")(v.ptr, v.rows, v.cols, v.stride, _ptr(buf))
+    check("maxsim_pack")
+    return MaxSimPackedMatrix(buf, v.dtype, v.rows, v.cols)
+
+
+def maxsim_packed(q: MaxSimPackedMatrix, d: MaxSimPackedMatrix) -> float:
+    """sum_i min_j angular(q_i, d_j) with the argmax taken on the raw dot. Mirrors nk.maxsim_packed."""
+    if not isinstance(q, MaxSimPackedMatrix) or not isinstance(d, MaxSimPackedMatrix):
+        raise TypeError("both arguments must be MaxSimPackedMatrix objects")
+    if q.dtype != d.dtype:
+        raise TypeError("query and document were packed with different dtypes")
+    if q.depth != d.depth:
+        raise ValueError("query and document depths differ")
+    res = (ctypes.c_double if q.dtype == "f32" else ctypes.c_float)()
+    getattr(lib, f"nk_maxsim_packed_{q.dtype}")(_ptr(q.buffer), _ptr(d.buffer), q.width, d.width, q.depth, ctypes.addressof(res))
+    check("maxsim_packed")
+    return float(res.value)
+
+
+def maxsim(q: Any, d: Any, dtype: Optional[str] = None) -> float:
+    """Packs both sides and scores them. Mirrors nk.maxsim."""
+    return maxsim_packed(maxsim_pack(q, dtype), maxsim_pack(d, dtype))
+
+
+# ---- additions that the reference API cannot express (results too large to materialise) ----
+
+def _topk_call(op: str, a: Any, packed: PackedMatrix, top: int, id_base: int, dtype: Optional[str]):
+    v = _View(a, dtype or packed.dtype)
+    if v.dtype != packed.dtype or v.dtype not in ("f16", "bf16"):
+        raise TypeError("top-k distances are available for f16 and bf16")
+    if v.cols != packed.depth:
+        raise ValueError("depth mismatch")
+    if v.is_cuda:
+        import torch
+        dist = torch.empty((v.rows, top), dtype=torch.float32, device=v.obj.device)
+        ids = torch.empty((v.rows, top), dtype=torch.int64, device=v.obj.device)
+    else:
+        dist = np.empty((v.rows, top), dtype=np.float32)
+        ids = np.empty((v.rows, top), dtype=np.int64)
+    getattr(lib, f"nkb_{op}_packed_topk_{v.dtype}")(v.ptr, _ptr(packed.buffer), v.rows, packed.width, v.cols, v.stride,
+                                                    top, _ptr(dist), _ptr(ids), id_base)
+    check(f"{op}_packed_topk")
+    return dist, ids
+
+
+def angulars_packed_topk(a: Any, packed: PackedMatrix, top: int, *, id_base: int = 0, dtype: Optional[str] = None):
+    """The `top` nearest packed rows per row of `a` by angular distance, ascending: (distances, ids)."""
+    return _topk_call("angulars", a, packed, top, id_base, dtype)
+
+
+def euclideans_packed_topk(a: Any, packed: PackedMatrix, top: int, *, id_base: int = 0, dtype: Optional[str] = None):
+    """The `top` nearest packed rows per row of `a` by Euclidean distance, ascending: (distances, ids)."""
+    return _topk_call("euclideans", a, packed, top, id_base, dtype)
+
+
+def maxsims_packed(q: MaxSimPackedMatrix, q_offsets: Any, d: MaxSimPackedMatrix, d_offsets: Any):
+    """All-pairs MaxSim between many queries and many documents whose token vectors were packed
+    together: `q_offsets` / `d_offsets` (int64, length count+1) delimit each query's / document's
+    tokens. Returns the (queries x documents) matrix of the values maxsim_packed would return."""
+    if q.dtype != d.dtype or q.dtype not in ("bf16", "f16"):
+        raise TypeError("batched MaxSim is available for bf16 and f16")
+    if q.depth != d.depth:
+        raise ValueError("query and document depths differ")
+    nq, nd = len(q_offsets) - 1, len(d_offsets) - 1
+    cuda = d.is_cuda
+    if cuda:
+        import torch
+        qo = torch.as_tensor(q_offsets, dtype=torch.int64, device="cuda").contiguous()
+        do = torch.as_tensor(d_offsets, dtype=torch.int64, device="cuda").contiguous()
+        scores = torch.empty((nq, nd), dtype=torch.float32, device="cuda")
+    else:
+        qo = np.ascontiguousarray(q_offsets, dtype=np.int64)
+        do = np.ascontiguousarray(d_offsets, dtype=np.int64)
+        scores = np.empty((nq, nd), dtype=np.float32)
+    getattr(lib, f"nkb_maxsims_packed_{q.dtype}")(_ptr(q.buffer), _ptr(qo), nq, _ptr(d.buffer), _ptr(do), nd, q.depth,
+                                                  _ptr(scores), nd * 4)
+    check("maxsims_packed")
+    return scores
+
+
+def topk_smallest(scores: Any, top: int, *, id_base: int = 0):
+    """Per row, the `top` smallest values (ascending, ties by lower column) and their columns + id_base."""
+    if _is_torch(scores):
+        import torch
+        rows, cols = scores.shape
+        vals = torch.empty((rows, top), dtype=torch.float32, device=scores.device)
+        ids = torch.empty((rows, top), dtype=torch.int64, device=scores.device)
+        stride = scores.stride(0) * 4
+    else:
+        scores = np.ascontiguousarray(scores, dtype=np.float32)
+        rows, cols = scores.shape
+        vals = np.empty((rows, top), dtype=np.float32)
+        ids = np.empty((rows, top), dtype=np.int64)
+        stride = scores.strides[0]
+    lib.nkb_topk_smallest_f32(_ptr(scores), rows, cols, stride, top, id_base, _ptr(vals), _ptr(ids))
+    check("topk_smallest")
+    return vals, ids
+
+
+def synchronize() -> int:
+    """Waits for this thread's stream; returns the device error word (0 = healthy)."""
+    return int(lib.nkb_synchronize())
+
+
+def set_stream(cuda_stream: int) -> None:
+    lib.nkb_set_stream(ctypes.c_void_p(cuda_stream))
+
+
+def launch_count() -> int:
+    return int(lib.nkb_launch_count())

@@ -1,0 +1,465 @@
+// Host side of the C ABI declared in include/numkong_b200.h: argument checks, pointer
+// classification, staging of host-resident operands, the device cache of host-resident packed
+// blobs, and the NumKong failure convention (fill the output with 0xFF, c/numkong.c:78-81).
+// It plays the role of NumKong's dispatch layer (c/numkong.c:347-380, 628-765): one indirection
+// between the exported nk_* symbol and the kernel that does the work.
+#include <atomic>
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/numkong_b200.h"
+#include "nkb_host.h"
+
+namespace nkb {
+
+std::atomic<uint64_t> g_launches{0};
+
+namespace {
+
+std::atomic<int> g_variant{0};
+std::atomic<uint64_t> g_nonce_counter{0};
+
+// ---------------------------------------------------------------- per-thread context
+struct Scratch {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+    int device = -1;
+};
+
+struct ThreadCtx {
+    cudaStream_t stream = nullptr;
+    std::string error;
+    Scratch slots[kScratchSlots];
+    ~ThreadCtx() {}  // device memory is reclaimed with the context at process exit
+};
+thread_local ThreadCtx t_ctx;
+
+// ---------------------------------------------------------------- per-device state
+struct DeviceState {
+    unsigned int *error_word = nullptr;
+};
+std::mutex g_state_mutex;
+DeviceState g_devices[64];
+
+// ---------------------------------------------------------------- cache of host-resident blobs
+struct CachedBlob {
+    uint64_t nonce = 0, bytes = 0;
+    int device = -1;
+    void *dev_ptr = nullptr;
+    uint64_t last_use = 0;
+};
+std::mutex g_cache_mutex;
+std::vector<CachedBlob> g_cache;
+uint64_t g_cache_clock = 0;
+constexpr size_t kCacheMaxEntries = 8;
+
+uint64_t fresh_nonce() {
+    uint64_t t = (uint64_t)std::chrono::steady_clock::now().time_since_epoch().count();
+    uint64_t c = g_nonce_counter.fetch_add(1) + 1;
+    uint64_t x = t ^ (c * 0x9E3779B97F4A7C15ull) ^ (uint64_t)(uintptr_t)&t_ctx;
+    x ^= x >> 31; x *= 0xBF58476D1CE4E5B9ull; x ^= x >> 29;
+    return x ? x : 1;
+}
+
+} // namespace
+
+// ---------------------------------------------------------------- helpers shared with other host files
+void set_error(const char *fmt, const char *detail) {
+    char buf[512];
+    std::snprintf(buf, sizeof buf, fmt, detail ? detail : "");
+    t_ctx.error = buf;
+}
+void clear_error() { t_ctx.error.clear(); }
+cudaStream_t current_stream() { return t_ctx.stream; }
+int current_variant() { return g_variant.load(); }
+
+bool cuda_ok(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return true;
+    char buf[512];
+    std::snprintf(buf, sizeof buf, "%s: %s", what, cudaGetErrorString(e));
+    t_ctx.error = buf;
+    cudaGetLastError();  // clear the sticky-less error state
+    return false;
+}
+
+MemKind classify(const void *p) {
+    if (!p) return kMemHost;
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, p);
+    if (e != cudaSuccess) { cudaGetLastError(); return kMemHost; }
+    if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) return kMemDevice;
+    return kMemHost;
+}
+
+void *scratch(int slot, size_t bytes) {
+    Scratch &s = t_ctx.slots[slot];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (s.ptr && s.device == dev && s.bytes >= bytes) return s.ptr;
+    if (s.ptr) {
+        cudaStreamSynchronize(t_ctx.stream);
+        cudaFree(s.ptr);
+        s.ptr = nullptr; s.bytes = 0;
+    }
+    size_t want = bytes < 256 ? 256 : bytes;
+    void *p = nullptr;
+    if (!cuda_ok(cudaMalloc(&p, want), "cudaMalloc(staging)")) return nullptr;
+    s.ptr = p; s.bytes = want; s.device = dev;
+    return p;
+}
+
+unsigned int *device_error_word() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    DeviceState &st = g_devices[dev];
+    if (!st.error_word) {
+        unsigned int *p = nullptr;
+        if (cudaMalloc(&p, 256) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        cudaMemset(p, 0, 256);
+        st.error_word = p;
+    }
+    return st.error_word;
+}
+
+uint32_t read_device_error() {
+    unsigned int *w = device_error_word();
+    if (!w) return 0;
+    unsigned int v = 0;
+    if (cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return 0xffffffffu; }
+    return v;
+}
+
+void fill_error_output(void *out, MemKind kind, uint64_t rows, uint64_t row_bytes, uint64_t stride) {
+    if (!out || rows == 0 || row_bytes == 0) return;
+    if (kind == kMemHost) {
+        for (uint64_t r = 0; r < rows; ++r) std::memset(static_cast<uint8_t *>(out) + r * stride, 0xFF, row_bytes);
+    } else {
+        cudaMemset2DAsync(out, stride, 0xFF, row_bytes, rows, t_ctx.stream);
+        cudaGetLastError();
+    }
+}
+
+// Device pointer of a packed blob. Host-resident blobs are uploaded once and found again by nonce.
+const uint8_t *resident_blob(const void *blob, MemKind kind, uint32_t magic, uint32_t dtype, uint64_t rows,
+                             uint64_t depth, PackedHeader *header_out) {
+    if (kind == kMemDevice) {
+        // Geometry is a pure function of (dtype, rows, depth); the header is not read back, which
+        // keeps device-resident calls free of synchronisation.
+        PackedGeometry g = packed_geometry(dtype, rows, depth);
+        if (header_out) {
+            std::memset(header_out, 0, sizeof *header_out);
+            header_out->magic = magic; header_out->dtype = dtype; header_out->rows = rows; header_out->depth = depth;
+            header_out->rows_padded = g.rows_padded; header_out->depth_padded_bytes = g.depth_padded_bytes;
+            header_out->payload_offset = g.payload_offset; header_out->norms_offset = g.norms_offset;
+            header_out->total_bytes = g.total_bytes;
+        }
+        if (reinterpret_cast<uintptr_t>(blob) & 15u) { set_error("packed blob in device memory must be 16-byte aligned%s", ""); return nullptr; }
+        return static_cast<const uint8_t *>(blob);
+    }
+    PackedHeader h;
+    std::memcpy(&h, blob, sizeof h);
+    if (h.magic != magic) { set_error("packed blob was not produced by the matching pack function of this library%s", ""); return nullptr; }
+    if (h.dtype != dtype) { set_error("packed blob holds a different element type%s", ""); return nullptr; }
+    if (h.rows != rows || h.depth != depth) { set_error("packed blob was packed for a different width/depth%s", ""); return nullptr; }
+    PackedGeometry g = packed_geometry(dtype, rows, depth);
+    if (h.total_bytes != g.total_bytes) { set_error("packed blob header is inconsistent%s", ""); return nullptr; }
+    if (header_out) *header_out = h;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    for (auto &e : g_cache)
+        if (e.nonce == h.nonce && e.bytes == h.total_bytes && e.device == dev) { e.last_use = ++g_cache_clock; return static_cast<const uint8_t *>(e.dev_ptr); }
+    if (g_cache.size() >= kCacheMaxEntries) {
+        size_t victim = 0;
+        for (size_t i = 1; i < g_cache.size(); ++i) if (g_cache[i].last_use < g_cache[victim].last_use) victim = i;
+        cudaDeviceSynchronize();
+        cudaFree(g_cache[victim].dev_ptr);
+        g_cache.erase(g_cache.begin() + victim);
+    }
+    void *d = nullptr;
+    if (!cuda_ok(cudaMalloc(&d, h.total_bytes), "cudaMalloc(packed blob copy)")) return nullptr;
+    if (!cuda_ok(cudaMemcpyAsync(d, blob, h.total_bytes, cudaMemcpyHostToDevice, t_ctx.stream), "upload of packed blob")) { cudaFree(d); return nullptr; }
+    CachedBlob e; e.nonce = h.nonce; e.bytes = h.total_bytes; e.device = dev; e.dev_ptr = d; e.last_use = ++g_cache_clock;
+    g_cache.push_back(e);
+    return static_cast<const uint8_t *>(d);
+}
+
+void remember_blob(uint64_t nonce, uint64_t bytes, void *dev_ptr) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    if (g_cache.size() >= kCacheMaxEntries) {
+        size_t victim = 0;
+        for (size_t i = 1; i < g_cache.size(); ++i) if (g_cache[i].last_use < g_cache[victim].last_use) victim = i;
+        cudaDeviceSynchronize();
+        cudaFree(g_cache[victim].dev_ptr);
+        g_cache.erase(g_cache.begin() + victim);
+    }
+    CachedBlob e; e.nonce = nonce; e.bytes = bytes; e.device = dev; e.dev_ptr = dev_ptr; e.last_use = ++g_cache_clock;
+    g_cache.push_back(e);
+}
+
+__global__ void write_header_kernel(PackedHeader *dst, PackedHeader h) { *dst = h; }
+
+// Brings a strided matrix into device memory that TMA can address (16-byte aligned base and pitch).
+// Returns the device pointer and pitch; uses `slot` when a copy is needed.
+const void *resident_matrix(const void *src, MemKind kind, uint64_t rows, uint64_t row_bytes, uint64_t stride,
+                            int slot, uint64_t *pitch_out) {
+    if (rows <= 1 && stride < row_bytes) stride = row_bytes;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) && ((stride & 15u) == 0);
+    if (kind == kMemDevice && aligned) { *pitch_out = stride; return src; }
+    uint64_t pitch = round_up(row_bytes, 16);
+    void *dst = scratch(slot, rows * pitch + 16);
+    if (!dst) return nullptr;
+    if (kind == kMemHost) {
+        if (pitch != row_bytes) {
+            if (!cuda_ok(cudaMemsetAsync(dst, 0, rows * pitch, t_ctx.stream), "clear staging")) return nullptr;
+        }
+        if (!cuda_ok(cudaMemcpy2DAsync(dst, pitch, src, stride, row_bytes, rows, cudaMemcpyHostToDevice, t_ctx.stream), "upload of input matrix")) return nullptr;
+    } else {
+        if (!cuda_ok(launch_restride(src, rows, row_bytes, stride, dst, pitch, t_ctx.stream), "restride kernel")) return nullptr;
+        g_launches++;
+    }
+    *pitch_out = pitch;
+    return dst;
+}
+
+namespace {
+
+// ---------------------------------------------------------------- the three entry-point bodies
+uint64_t packed_size_impl(uint32_t dt, uint64_t rows, uint64_t depth) {
+    if (!dtype_supported(dt)) return 0;
+    return packed_geometry(dt, rows, depth).total_bytes;
+}
+
+void pack_impl(uint32_t magic, uint32_t dt, const void *b, uint64_t rows, uint64_t depth, uint64_t stride, void *packed,
+               bool inverse_norms) {
+    clear_error();
+    if (!dtype_supported(dt) || !packed) { set_error("pack: unsupported element type or null output%s", ""); return; }
+    if (rows && depth && !b) { set_error("pack: null input%s", ""); return; }
+    const PackedGeometry g = packed_geometry(dt, rows, depth);
+    const MemKind out_kind = classify(packed), in_kind = classify(b);
+    cudaStream_t stream = t_ctx.stream;
+
+    PackedHeader h;
+    std::memset(&h, 0, sizeof h);
+    h.magic = magic; h.dtype = dt; h.element_bytes = dtype_bytes(dt); h.norm_bytes = norm_bytes(dt);
+    h.rows = rows; h.depth = depth; h.rows_padded = g.rows_padded; h.depth_padded_bytes = g.depth_padded_bytes;
+    h.payload_offset = g.payload_offset; h.norms_offset = g.norms_offset; h.total_bytes = g.total_bytes;
+    h.nonce = fresh_nonce();
+
+    uint8_t *dev_blob = nullptr;
+    bool owned = false;
+    if (out_kind == kMemDevice) {
+        if (reinterpret_cast<uintptr_t>(packed) & 15u) { set_error("pack: device output must be 16-byte aligned%s", ""); return; }
+        dev_blob = static_cast<uint8_t *>(packed);
+    } else {
+        void *d = nullptr;
+        if (!cuda_ok(cudaMalloc(&d, g.total_bytes), "cudaMalloc(packed blob)")) { std::memset(packed, 0xFF, g.total_bytes); return; }
+        dev_blob = static_cast<uint8_t *>(d);
+        owned = true;
+    }
+    bool ok = true;
+    const void *b_dev = b;
+    uint64_t b_pitch = stride;
+    if (rows && depth) {
+        if (in_kind == kMemHost) {
+            // Dense upload; the pack kernel reads any alignment, so no re-pitching is needed.
+            uint64_t row_bytes = depth * dtype_bytes(dt);
+            void *stage = scratch(kSlotA, rows * row_bytes + 16);
+            ok = stage && cuda_ok(cudaMemcpy2DAsync(stage, row_bytes, b, stride < row_bytes ? row_bytes : stride, row_bytes, rows,
+                                                    cudaMemcpyHostToDevice, stream), "upload of matrix to pack");
+            b_dev = stage; b_pitch = row_bytes;
+        }
+        if (ok) {
+            ok = cuda_ok(launch_pack_payload(dt, b_dev, rows, depth, b_pitch, dev_blob + g.payload_offset, g.rows_padded,
+                                             g.depth_padded_bytes, stream), "pack kernel");
+            g_launches++;
+        }
+        if (ok) {
+            ok = cuda_ok(launch_row_sumsq(dt, b_dev, rows, depth, b_pitch, dev_blob + g.norms_offset, false, inverse_norms, stream), "norm kernel");
+            g_launches++;
+        }
+    } else if (ok) {
+        ok = cuda_ok(cudaMemsetAsync(dev_blob + g.payload_offset, 0, g.total_bytes - g.payload_offset, stream), "clear blob");
+    }
+    if (ok) {
+        write_header_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<PackedHeader *>(dev_blob), h);
+        ok = cuda_ok(cudaGetLastError(), "header kernel");
+        g_launches++;
+    }
+    if (out_kind == kMemHost) {
+        if (ok) ok = cuda_ok(cudaMemcpyAsync(packed, dev_blob, g.total_bytes, cudaMemcpyDeviceToHost, stream), "download of packed blob");
+        if (ok) ok = cuda_ok(cudaStreamSynchronize(stream), "pack");
+        if (ok) remember_blob(h.nonce, g.total_bytes, dev_blob);  // later calls with this host blob skip the upload
+        else { if (owned) cudaFree(dev_blob); std::memset(packed, 0xFF, g.total_bytes); }
+    } else if (!ok) {
+        cudaMemsetAsync(dev_blob, 0xFF, g.total_bytes, stream);
+        cudaGetLastError();
+    } else if (in_kind == kMemHost) {
+        cuda_ok(cudaStreamSynchronize(stream), "pack");
+    }
+}
+
+void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed, void *c, uint64_t m, uint64_t n,
+                 uint64_t k, uint64_t a_stride, uint64_t c_stride) {
+    clear_error();
+    const uint32_t out_bytes = dot_out_bytes(dt);  // distances share the cell width of the dots
+    const uint64_t c_row_bytes = n * out_bytes;
+    if (m == 0 || n == 0) return;
+    const MemKind c_kind = classify(c);
+    auto fail = [&]() { fill_error_output(c, c_kind, m, c_row_bytes, c_stride < c_row_bytes ? c_row_bytes : c_stride); };
+    if (!dtype_supported(dt) || !a || !b_packed || !c) { set_error("packed: unsupported element type or null pointer%s", ""); fail(); return; }
+    if (m > 1 && c_stride < c_row_bytes) { set_error("packed: c_stride is smaller than a row of the result%s", ""); fail(); return; }
+    if (c_stride % out_bytes) { set_error("packed: c_stride must be a multiple of the output cell size%s", ""); fail(); return; }
+    cudaStream_t stream = t_ctx.stream;
+    const MemKind a_kind = classify(a), b_kind = classify(b_packed);
+
+    PackedHeader h;
+    const uint8_t *blob = resident_blob(b_packed, b_kind, kMagicDots, dt, n, k, &h);
+    if (!blob) { fail(); return; }
+    unsigned int *err = device_error_word();
+    if (!err) { set_error("could not allocate the device error word%s", ""); fail(); return; }
+
+    // Output: in place when it is device memory with 4-byte aligned rows, else a dense device copy.
+    uint8_t *c_dev = static_cast<uint8_t *>(c);
+    uint64_t c_pitch = c_stride;
+    const bool c_direct = c_kind == kMemDevice && (reinterpret_cast<uintptr_t>(c) % out_bytes) == 0;
+    if (!c_direct) {
+        c_pitch = round_up(c_row_bytes, 16);
+        c_dev = static_cast<uint8_t *>(scratch(kSlotC, m * c_pitch));
+        if (!c_dev) { fail(); return; }
+    }
+    bool ok = true;
+    if (k == 0) {
+        ok = cuda_ok(cudaMemset2DAsync(c_dev, c_pitch, 0, c_row_bytes, m, stream), "clear result");
+    } else if (dt == kF32) {
+        const void *a_dev = a;
+        uint64_t a_pitch = a_stride;
+        if (a_kind == kMemHost || (reinterpret_cast<uintptr_t>(a) & 3u) || (a_stride & 3u)) {
+            a_dev = resident_matrix(a, a_kind, m, k * 4, a_stride, kSlotA, &a_pitch);
+            if (!a_dev) { fail(); return; }
+        }
+        double *a_norms = nullptr;
+        if (epilogue != kEpiDot) {
+            a_norms = static_cast<double *>(scratch(kSlotNorms, m * 8));
+            ok = a_norms && cuda_ok(launch_row_sumsq(dt, a_dev, m, k, a_pitch, a_norms, false, false, stream), "row norm kernel");
+            g_launches++;
+        }
+        if (ok) {
+            ok = cuda_ok(launch_gemm_f32(epilogue, static_cast<const float *>(a_dev), a_pitch,
+                                         reinterpret_cast<const float *>(blob + h.payload_offset), h.depth_padded_bytes,
+                                         reinterpret_cast<const double *>(blob + h.norms_offset), a_norms,
+                                         reinterpret_cast<double *>(c_dev), c_pitch, m, n, k, stream), "f32 GEMM kernel");
+            g_launches++;
+        }
+    } else {
+        uint64_t a_pitch = 0;
+        const void *a_dev = resident_matrix(a, a_kind, m, k * dtype_bytes(dt), a_stride, kSlotA, &a_pitch);
+        if (!a_dev) { fail(); return; }
+        float *a_norms = nullptr;
+        if (epilogue != kEpiDot) {
+            a_norms = static_cast<float *>(scratch(kSlotNorms, m * 4));
+            ok = a_norms && cuda_ok(launch_row_sumsq(dt, a_dev, m, k, a_pitch, a_norms, true, false, stream), "row norm kernel");
+            g_launches++;
+        }
+        if (ok) {
+            GemmArgs g;
+            g.dtype = dt; g.epilogue = epilogue; g.a = a_dev; g.a_stride = a_pitch;
+            g.b_payload = blob + h.payload_offset; g.b_norms = blob + h.norms_offset; g.a_norms = a_norms;
+            g.c = c_dev; g.c_stride = c_pitch; g.m = m; g.n = n; g.k = k;
+            g.depth_padded_bytes = h.depth_padded_bytes; g.error_word = err; g.variant = g_variant.load();
+            ok = cuda_ok(launch_gemm_tc(g, stream), "tensor-core GEMM kernel");
+            g_launches += gemm_tc_launch_count(g);
+        }
+    }
+    if (ok && !c_direct) {
+        cudaMemcpyKind kind = c_kind == kMemHost ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+        ok = cuda_ok(cudaMemcpy2DAsync(c, c_stride < c_row_bytes ? c_row_bytes : c_stride, c_dev, c_pitch, c_row_bytes, m, kind, stream), "download of result");
+    }
+    const bool must_sync = a_kind == kMemHost || b_kind == kMemHost || c_kind == kMemHost;
+    if (ok && must_sync) {
+        ok = cuda_ok(cudaStreamSynchronize(stream), "packed call");
+        if (ok) {
+            uint32_t w = read_device_error();
+            if (w) { char buf[64]; std::snprintf(buf, sizeof buf, "0x%08x", w); set_error("a pipeline wait inside the GEMM kernel gave up (error word %s)", buf); ok = false; }
+        }
+    }
+    if (!ok) fail();
+}
+
+} // namespace
+} // namespace nkb
+
+using namespace nkb;
+
+extern "C" {
+
+#define NKB_DEFINE_PACKED_FAMILY(T, DT)                                                                                \
+    NKB_API nk_size_t nk_dots_packed_size_##T(nk_size_t width, nk_size_t depth) { return packed_size_impl(DT, width, depth); } \
+    NKB_API void nk_dots_pack_##T(void const *b, nk_size_t width, nk_size_t depth, nk_size_t b_stride, void *b_packed) { \
+        pack_impl(kMagicDots, DT, b, width, depth, b_stride, b_packed, false);                                        \
+    }                                                                                                                  \
+    NKB_API void nk_dots_packed_##T(void const *a, void const *b_packed, void *c, nk_size_t height, nk_size_t width,   \
+                                    nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride) {                         \
+        packed_impl(DT, kEpiDot, a, b_packed, c, height, width, depth, a_stride, c_stride);                            \
+    }                                                                                                                  \
+    NKB_API void nk_angulars_packed_##T(void const *a, void const *b_packed, void *c, nk_size_t height,                \
+                                        nk_size_t width, nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride) {    \
+        packed_impl(DT, kEpiAngular, a, b_packed, c, height, width, depth, a_stride, c_stride);                        \
+    }                                                                                                                  \
+    NKB_API void nk_euclideans_packed_##T(void const *a, void const *b_packed, void *c, nk_size_t height,              \
+                                          nk_size_t width, nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride) {  \
+        packed_impl(DT, kEpiEuclidean, a, b_packed, c, height, width, depth, a_stride, c_stride);                      \
+    }
+
+NKB_DEFINE_PACKED_FAMILY(i8, kI8)
+NKB_DEFINE_PACKED_FAMILY(u8, kU8)
+NKB_DEFINE_PACKED_FAMILY(bf16, kBF16)
+NKB_DEFINE_PACKED_FAMILY(f16, kF16)
+NKB_DEFINE_PACKED_FAMILY(e4m3, kE4M3)
+NKB_DEFINE_PACKED_FAMILY(e5m2, kE5M2)
+NKB_DEFINE_PACKED_FAMILY(e2m3, kE2M3)
+NKB_DEFINE_PACKED_FAMILY(e3m2, kE3M2)
+NKB_DEFINE_PACKED_FAMILY(f32, kF32)
+
+NKB_API char const *nkb_last_error(void) { return t_ctx.error.c_str(); }
+NKB_API void nkb_set_stream(void *cuda_stream) { t_ctx.stream = static_cast<cudaStream_t>(cuda_stream); }
+NKB_API uint32_t nkb_synchronize(void) {
+    clear_error();
+    if (!cuda_ok(cudaStreamSynchronize(t_ctx.stream), "nkb_synchronize")) return 0xffffffffu;
+    return read_device_error();
+}
+NKB_API uint64_t nkb_launch_count(void) { return g_launches.load(); }
+NKB_API void nkb_set_gemm_variant(int variant) { g_variant.store(variant); }
+NKB_API void nkb_release_caches(void) {
+    cudaDeviceSynchronize();
+    {
+        std::lock_guard<std::mutex> lock(g_cache_mutex);
+        for (auto &e : g_cache) cudaFree(e.dev_ptr);
+        g_cache.clear();
+    }
+    for (auto &s : t_ctx.slots) {
+        if (s.ptr) cudaFree(s.ptr);
+        s = Scratch();
+    }
+    cudaGetLastError();
+}
+
+NKB_API uint64_t nk_capabilities(void) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) { cudaGetLastError(); return 0; }
+    int dev = 0, major = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    return major == 10 ? NKB_CAPABILITY_B200 : 0;
+}
+NKB_API int nk_configure_thread(uint64_t) { return 1; }
+
+} // extern "C"

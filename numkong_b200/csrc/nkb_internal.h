@@ -1,0 +1,141 @@
+// Internal declarations shared by the translation units of libnumkong_b200.so:
+// dtype codes (numerically equal to NumKong's nk_dtype_t, include/numkong/types.h:923-953),
+// the packed-blob header, and the launchers each .cu file provides.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace nkb {
+
+enum Dtype : uint32_t {
+    kI8 = 1u << 2,
+    kU8 = 1u << 6,
+    kF32 = 1u << 11,
+    kF16 = 1u << 12,
+    kBF16 = 1u << 13,
+    kE4M3 = 1u << 14,
+    kE5M2 = 1u << 15,
+    kE2M3 = 1u << 18,
+    kE3M2 = 1u << 19,
+};
+
+// What the accumulators are turned into before they are stored.
+enum Epilogue : int { kEpiDot = 0, kEpiAngular = 1, kEpiEuclidean = 2 };
+
+constexpr uint32_t kMagicDots = 0x32424B4Eu;    // "NKB2"
+constexpr uint32_t kMagicMaxsim = 0x4D424B4Eu;  // "NKBM"
+constexpr uint32_t kHeaderBytes = 128;
+constexpr uint32_t kChunkRows = 128;            // rows per pre-swizzled chunk
+constexpr uint32_t kChunkRowBytes = 128;        // bytes of depth per chunk row (one swizzle span)
+constexpr uint32_t kChunkBytes = kChunkRows * kChunkRowBytes;  // 16 KiB
+constexpr uint32_t kRowPad = 256;               // rows are padded to a multiple of this
+
+// 128-byte header at the start of every packed blob. The blob is position independent:
+// it holds offsets only, so callers may memcpy, move or serialise it freely.
+//
+// Tensor-core dtypes: the payload is a grid of 16 KiB chunks ordered [row_block][depth_block];
+// a chunk is 128 rows x 128 bytes of depth in exactly the shared-memory image tcgen05.mma
+// reads for a K-major, 128-byte-swizzled operand (row r at (r/8)*1024 + (r%8)*128, its
+// 16-byte piece c stored at piece position c ^ (r%8)). One untiled bulk copy brings a
+// chunk into shared memory with no further rearrangement.
+// f32: the payload is plain row-major f32 with rows padded to `depth_padded_bytes`.
+// After the payload: one norm per row (squared norm for dots blobs, inverse norm for MaxSim blobs).
+struct PackedHeader {
+    uint32_t magic;
+    uint32_t dtype;
+    uint32_t element_bytes;
+    uint32_t norm_bytes;
+    uint64_t rows;                // n (vectors)
+    uint64_t depth;               // k (logical dimensions)
+    uint64_t rows_padded;         // multiple of 256
+    uint64_t depth_padded_bytes;  // multiple of 128
+    uint64_t payload_offset;
+    uint64_t norms_offset;
+    uint64_t total_bytes;
+    uint64_t nonce;               // changes with every pack call; keys the device-side cache of host blobs
+    uint64_t reserved[6];
+};
+static_assert(sizeof(PackedHeader) == 128, "header must be 128 bytes");
+
+inline uint32_t dtype_bytes(uint32_t dt) {
+    switch (dt) {
+    case kF32: return 4;
+    case kF16: case kBF16: return 2;
+    default: return 1;
+    }
+}
+// Bytes of one stored norm: u32 for integers, f64 for f32, f32 otherwise.
+inline uint32_t norm_bytes(uint32_t dt) { return dt == kF32 ? 8 : 4; }
+// Bytes of one output cell of dots_packed: f64 for f32 inputs, 4 bytes otherwise.
+inline uint32_t dot_out_bytes(uint32_t dt) { return dt == kF32 ? 8 : 4; }
+inline bool dtype_supported(uint32_t dt) {
+    switch (dt) {
+    case kI8: case kU8: case kF32: case kF16: case kBF16: case kE4M3: case kE5M2: case kE2M3: case kE3M2: return true;
+    default: return false;
+    }
+}
+
+inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
+
+struct PackedGeometry {
+    uint64_t rows_padded, depth_padded_bytes, payload_offset, norms_offset, total_bytes;
+};
+inline PackedGeometry packed_geometry(uint32_t dt, uint64_t rows, uint64_t depth) {
+    PackedGeometry g;
+    g.rows_padded = round_up(rows ? rows : 1, kRowPad);
+    g.depth_padded_bytes = round_up((depth ? depth : 1) * dtype_bytes(dt), kChunkRowBytes);
+    g.payload_offset = kHeaderBytes;
+    g.norms_offset = g.payload_offset + g.rows_padded * g.depth_padded_bytes;
+    g.total_bytes = g.norms_offset + round_up(rows * norm_bytes(dt), 128);
+    return g;
+}
+
+// ---- launchers (all asynchronous on `stream`; return a cudaError_t from the launch) ----
+
+// Sum of squares of every row. `out` is f32 (float dtypes), u32 (i8/u8) or f64 (f32 input);
+// `as_f32` forces an f32 result for integers (the batched-distance epilogues read f32 norms).
+// `inverse` stores 1/sqrt(sumsq) (0 for a zero row) instead, as MaxSim blobs do.
+cudaError_t launch_row_sumsq(uint32_t dt, const void *x, uint64_t rows, uint64_t depth, uint64_t stride_bytes,
+                             void *out, bool as_f32, bool inverse, cudaStream_t stream);
+
+// Writes the pre-swizzled chunk grid (or padded row-major f32) of a packed blob.
+cudaError_t launch_pack_payload(uint32_t dt, const void *b, uint64_t rows, uint64_t depth, uint64_t stride_bytes,
+                                void *payload, uint64_t rows_padded, uint64_t depth_padded_bytes, cudaStream_t stream);
+
+// Copies a strided matrix into a 16-byte-aligned, 16-byte-pitched scratch copy (for TMA).
+cudaError_t launch_restride(const void *src, uint64_t rows, uint64_t row_bytes, uint64_t src_stride,
+                            void *dst, uint64_t dst_stride, cudaStream_t stream);
+
+struct GemmArgs {
+    uint32_t dtype;
+    int epilogue;                 // Epilogue
+    const void *a;                // device, 16-byte aligned, stride multiple of 16
+    uint64_t a_stride;
+    const void *b_payload;        // device, chunk grid
+    const void *b_norms;          // device (epilogue != dot)
+    const float *a_norms;         // device f32 (epilogue != dot)
+    void *c;
+    uint64_t c_stride;
+    uint64_t m, n, k;
+    uint64_t depth_padded_bytes;
+    unsigned int *error_word;     // device
+    int variant;                  // 0 = default for the shape; otherwise forces a tile configuration (testing/tuning)
+};
+cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream);
+// Number of kernels launch_gemm_tc enqueues for these arguments (for launch accounting).
+int gemm_tc_launch_count(const GemmArgs &args);
+
+// f32 x f32 -> f64 on CUDA cores. `b` is the padded row-major f32 payload.
+cudaError_t launch_gemm_f32(int epilogue, const float *a, uint64_t a_stride, const float *b, uint64_t b_stride,
+                            const double *b_norms, const double *a_norms, double *c, uint64_t c_stride,
+                            uint64_t m, uint64_t n, uint64_t k, cudaStream_t stream);
+
+// Resolves cuTensorMapEncodeTiled through the runtime (no link-time dependency on libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_tiled();
+
+} // namespace nkb

@@ -1,0 +1,192 @@
+// Bandwidth-bound helpers around the GEMM: the B pre-packer, row norms and a re-striding copy.
+//
+// launch_pack_payload replaces the copy loop of NumKong's nk_dots_pack_<t>
+// (include/numkong/dots/serial.h:286-333): instead of a padded row-major copy it writes B
+// directly in the shared-memory image tcgen05.mma consumes (see PackedHeader).
+// launch_row_sumsq replaces the nk_reduce_moments_<t> calls that append per-row squared norms
+// (include/numkong/dots/serial.h:114-180, 326-332) and the per-query norm pass of the batched
+// distances (include/numkong/dots/serial.h:2775-2778); with `inverse` it produces the
+// 1/sqrt(sumsq) MaxSim stores (include/numkong/maxsim/serial.h:263).
+#include "nkb_internal.h"
+#include "nkb_decode.cuh"
+
+namespace nkb {
+
+namespace {
+
+// 16 bytes from a possibly unaligned, possibly short source. Bytes at and past `valid` read as zero.
+__device__ __forceinline__ uint4 load16_guarded(const uint8_t *src, int64_t valid) {
+    if (valid >= 16 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) return __ldg(reinterpret_cast<const uint4 *>(src));
+    uint32_t w[4] = {0, 0, 0, 0};
+    if (valid > 16) valid = 16;
+    for (int i = 0; i < valid; ++i) w[i >> 2] |= (uint32_t)src[i] << ((i & 3) * 8);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// One thread per 16-byte piece of the payload.
+template <bool kSwizzled>
+__global__ void pack_payload_kernel(const uint8_t *__restrict__ b, uint64_t rows, uint64_t row_bytes, uint64_t stride,
+                                    uint4 *__restrict__ payload, uint64_t pieces, uint32_t kblocks) {
+    for (uint64_t o = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; o < pieces; o += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t row, byte_off;
+        if constexpr (kSwizzled) {
+            uint64_t chunk = o >> 10;            // 1024 pieces per 16 KiB chunk
+            uint32_t within = (uint32_t)(o & 1023u);
+            uint32_t r = within >> 3;            // row inside the chunk
+            uint32_t pos = within & 7u;          // stored piece position
+            uint32_t piece = pos ^ (r & 7u);     // logical piece of the 128-byte span
+            uint64_t row_block = chunk / kblocks;
+            uint64_t kb = chunk % kblocks;
+            row = row_block * kChunkRows + r;
+            byte_off = kb * kChunkRowBytes + piece * 16u;
+        } else {
+            uint64_t pieces_per_row = (uint64_t)kblocks * (kChunkRowBytes / 16);
+            row = o / pieces_per_row;
+            byte_off = (o % pieces_per_row) * 16u;
+        }
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < rows && byte_off < row_bytes) v = load16_guarded(b + row * stride + byte_off, (int64_t)(row_bytes - byte_off));
+        payload[o] = v;
+    }
+}
+
+__global__ void restride_kernel(const uint8_t *__restrict__ src, uint64_t rows, uint64_t row_bytes, uint64_t src_stride,
+                                uint4 *__restrict__ dst, uint64_t dst_pieces_per_row) {
+    uint64_t total = rows * dst_pieces_per_row;
+    for (uint64_t o = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; o < total; o += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t row = o / dst_pieces_per_row;
+        uint64_t byte_off = (o % dst_pieces_per_row) * 16u;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (byte_off < row_bytes) v = load16_guarded(src + row * src_stride + byte_off, (int64_t)(row_bytes - byte_off));
+        dst[o] = v;
+    }
+}
+
+template <uint32_t kDtype>
+struct SumSq {
+    using Acc = double;
+    static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) {
+        float v = decode<kDtype>(p);
+        acc += (double)v * (double)v;
+    }
+};
+template <>
+struct SumSq<kI8> {
+    using Acc = unsigned long long;
+    static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) {
+        int v = (int8_t)*p;
+        acc += (unsigned long long)(v * v);
+    }
+};
+template <>
+struct SumSq<kU8> {
+    using Acc = unsigned long long;
+    static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) {
+        unsigned v = *p;
+        acc += (unsigned long long)(v * v);
+    }
+};
+
+// One warp per row; 16-byte vector loads when the row start allows it.
+template <uint32_t kDtype>
+__global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, uint64_t depth, uint64_t stride,
+                                 void *__restrict__ out, int out_mode /*0 native, 1 f32*/, int inverse) {
+    constexpr uint32_t eb = kDtype == kF32 ? 4 : (kDtype == kF16 || kDtype == kBF16) ? 2 : 1;
+    constexpr uint32_t per16 = 16 / eb;
+    using Acc = typename SumSq<kDtype>::Acc;
+    const int lane = threadIdx.x & 31;
+    const uint64_t warps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+    for (uint64_t row = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < rows; row += warps) {
+        const uint8_t *p = x + row * stride;
+        Acc acc = 0;
+        uint64_t done = 0;
+        if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+            uint64_t vecs = depth / per16;
+            for (uint64_t v = lane; v < vecs; v += 32) {
+                uint4 q = __ldg(reinterpret_cast<const uint4 *>(p) + v);
+                const uint8_t *qb = reinterpret_cast<const uint8_t *>(&q);
+#pragma unroll
+                for (uint32_t e = 0; e < per16; ++e) SumSq<kDtype>::add(acc, qb + e * eb);
+            }
+            done = vecs * per16;
+        }
+        for (uint64_t i = done + lane; i < depth; i += 32) {
+            uint8_t tmp[4];
+            for (uint32_t bidx = 0; bidx < eb; ++bidx) tmp[bidx] = p[i * eb + bidx];
+            SumSq<kDtype>::add(acc, tmp);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) {
+            if constexpr (kDtype == kI8 || kDtype == kU8) {
+                if (inverse) {
+                    float s = (float)acc;
+                    static_cast<float *>(out)[row] = s > 0.0f ? (float)(1.0 / sqrt((double)s)) : 0.0f;
+                } else if (out_mode == 1) static_cast<float *>(out)[row] = (float)(uint32_t)acc;
+                else static_cast<uint32_t *>(out)[row] = (uint32_t)acc;
+            } else if constexpr (kDtype == kF32) {
+                if (inverse) static_cast<double *>(out)[row] = acc > 0.0 ? 1.0 / sqrt(acc) : 0.0;
+                else static_cast<double *>(out)[row] = acc;
+            } else {
+                float s = (float)acc;
+                if (inverse) static_cast<float *>(out)[row] = s > 0.0f ? (float)(1.0 / sqrt((double)s)) : 0.0f;
+                else static_cast<float *>(out)[row] = s;
+            }
+        }
+    }
+}
+
+inline int grid_for(uint64_t work_items, int block, int cap = 148 * 16) {
+    uint64_t g = (work_items + block - 1) / block;
+    if (g < 1) g = 1;
+    if (g > (uint64_t)cap) g = cap;
+    return (int)g;
+}
+
+} // namespace
+
+cudaError_t launch_row_sumsq(uint32_t dt, const void *x, uint64_t rows, uint64_t depth, uint64_t stride_bytes,
+                             void *out, bool as_f32, bool inverse, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    const int block = 256;
+    const int grid = grid_for(rows * 32, block);
+    const uint8_t *p = static_cast<const uint8_t *>(x);
+    const int mode = as_f32 ? 1 : 0, inv = inverse ? 1 : 0;
+#define NKB_CASE(DT) case DT: row_sumsq_kernel<DT><<<grid, block, 0, stream>>>(p, rows, depth, stride_bytes, out, mode, inv); break
+    switch (dt) {
+        NKB_CASE(kI8); NKB_CASE(kU8); NKB_CASE(kF32); NKB_CASE(kF16); NKB_CASE(kBF16);
+        NKB_CASE(kE4M3); NKB_CASE(kE5M2); NKB_CASE(kE2M3); NKB_CASE(kE3M2);
+    default: return cudaErrorInvalidValue;
+    }
+#undef NKB_CASE
+    return cudaGetLastError();
+}
+
+cudaError_t launch_pack_payload(uint32_t dt, const void *b, uint64_t rows, uint64_t depth, uint64_t stride_bytes,
+                                void *payload, uint64_t rows_padded, uint64_t depth_padded_bytes, cudaStream_t stream) {
+    const uint64_t pieces = rows_padded * depth_padded_bytes / 16;
+    const uint32_t kblocks = (uint32_t)(depth_padded_bytes / kChunkRowBytes);
+    const int block = 256;
+    const int grid = grid_for(pieces, block, 148 * 32);
+    const uint64_t row_bytes = depth * dtype_bytes(dt);
+    if (dt == kF32)
+        pack_payload_kernel<false><<<grid, block, 0, stream>>>(static_cast<const uint8_t *>(b), rows, row_bytes, stride_bytes,
+                                                               static_cast<uint4 *>(payload), pieces, kblocks);
+    else
+        pack_payload_kernel<true><<<grid, block, 0, stream>>>(static_cast<const uint8_t *>(b), rows, row_bytes, stride_bytes,
+                                                              static_cast<uint4 *>(payload), pieces, kblocks);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_restride(const void *src, uint64_t rows, uint64_t row_bytes, uint64_t src_stride, void *dst,
+                            uint64_t dst_stride, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    const uint64_t per_row = dst_stride / 16;
+    const int block = 256;
+    const int grid = grid_for(rows * per_row, block, 148 * 32);
+    restride_kernel<<<grid, block, 0, stream>>>(static_cast<const uint8_t *>(src), rows, row_bytes, src_stride,
+                                                static_cast<uint4 *>(dst), per_row);
+    return cudaGetLastError();
+}
+
+} // namespace nkb

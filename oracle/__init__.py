@@ -1,0 +1,220 @@
+"""TEST INFRASTRUCTURE ONLY: Python face of the CPU oracle.
+
+`oracle.*` wraps oracle/nk_oracle.c (our scalar restatement of NumKong's packed-contraction path);
+`oracle.ref` / `oracle.ref_serial` wrap the reference itself when it has been compiled from its own
+sources into oracle/_ref/ (see oracle/Makefile). Only tests/, __graft_entry__.smoke() and bench.py's
+CPU-baseline leg may import this package; the product never does.
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from pathlib import Path
+from typing import Optional
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_SO = _HERE / "liboracle.so"
+REF_SO = _HERE / "_ref" / "libnumkong.so"
+REF_SERIAL_SO = _HERE / "_ref" / "libnkref_serial.so"
+
+CODES = {"i8": 1 << 2, "u8": 1 << 6, "f32": 1 << 11, "f16": 1 << 12, "bf16": 1 << 13,
+         "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19}
+BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1}
+STORAGE = {"i8": np.int8, "u8": np.uint8, "f32": np.float32, "f16": np.uint16, "bf16": np.uint16,
+           "e4m3": np.uint8, "e5m2": np.uint8, "e2m3": np.uint8, "e3m2": np.uint8}
+
+
+def build(force: bool = False) -> Path:
+    """Compiles oracle/nk_oracle.c into liboracle.so (gcc, a second or two)."""
+    if force or not _SO.exists() or _SO.stat().st_mtime < (_HERE / "nk_oracle.c").stat().st_mtime:
+        subprocess.run(["make", "-s", "-C", str(_HERE), "all"], check=True)
+    return _SO
+
+
+def build_ref(reference_root: str = "/root/reference") -> bool:
+    """Compiles the reference from its own sources into oracle/_ref/ when the source tree is present."""
+    if not Path(reference_root, "c", "numkong.c").exists():
+        return False
+    subprocess.run(["make", "-s", "-C", str(_HERE), "ref", f"REF={reference_root}", "-j8"], check=True)
+    return True
+
+
+def _load() -> ctypes.CDLL:
+    build()
+    lib = ctypes.CDLL(str(_SO))
+    u64, vp, i32 = ctypes.c_uint64, ctypes.c_void_p, ctypes.c_int
+    lib.orc_decode.restype, lib.orc_decode.argtypes = None, [i32, vp, u64, vp]
+    lib.orc_dots.restype, lib.orc_dots.argtypes = None, [i32, vp, u64, vp, u64, vp, u64, u64, u64, u64]
+    lib.orc_spatials.restype, lib.orc_spatials.argtypes = None, [i32, i32, vp, u64, vp, u64, vp, u64, u64, u64, u64]
+    lib.orc_sumsq.restype, lib.orc_sumsq.argtypes = ctypes.c_double, [i32, vp, u64]
+    lib.orc_rsqrt_f32.restype, lib.orc_rsqrt_f32.argtypes = ctypes.c_float, [ctypes.c_float]
+    for name in ("orc_maxsim_argmax_dot", "orc_maxsim_coarse_i8"):
+        f = getattr(lib, name)
+        f.restype, f.argtypes = ctypes.c_double, [i32, vp, u64, u64, vp, u64, u64, u64, vp]
+    lib.orc_maxsim_exhaustive.restype = ctypes.c_double
+    lib.orc_maxsim_exhaustive.argtypes = [i32, vp, u64, u64, vp, u64, u64, u64]
+    return lib
+
+
+_lib = _load()
+
+
+def _as_storage(x: np.ndarray, dtype: str) -> np.ndarray:
+    x = np.asarray(x)
+    if x.ndim != 2:
+        raise ValueError("expected a 2-D matrix")
+    if x.itemsize != BYTES[dtype]:
+        raise TypeError(f"{dtype} needs {BYTES[dtype]}-byte elements")
+    if x.shape[1] > 1 and x.strides[1] != x.itemsize:
+        x = np.ascontiguousarray(x)
+    return x
+
+
+def _stride(x: np.ndarray) -> int:
+    return x.strides[0] if x.shape[0] > 1 else x.shape[1] * x.itemsize
+
+
+def decode(x: np.ndarray, dtype: str) -> np.ndarray:
+    """Exact f32 values of a storage array."""
+    x = np.ascontiguousarray(x)
+    out = np.empty(x.shape, dtype=np.float32)
+    _lib.orc_decode(CODES[dtype], x.ctypes.data, x.size, out.ctypes.data)
+    return out
+
+
+def out_dtype(dtype: str, op: str = "dots"):
+    if dtype == "f32":
+        return np.float64
+    if op == "dots" and dtype == "i8":
+        return np.int32
+    if op == "dots" and dtype == "u8":
+        return np.uint32
+    return np.float32
+
+
+def dots(a: np.ndarray, b: np.ndarray, dtype: str) -> np.ndarray:
+    a, b = _as_storage(a, dtype), _as_storage(b, dtype)
+    c = np.empty((a.shape[0], b.shape[0]), dtype=out_dtype(dtype))
+    _lib.orc_dots(CODES[dtype], a.ctypes.data, _stride(a), b.ctypes.data, _stride(b), c.ctypes.data,
+                  c.shape[1] * c.itemsize, a.shape[0], b.shape[0], a.shape[1])
+    return c
+
+
+def _spatials(kind: int, a, b, dtype):
+    a, b = _as_storage(a, dtype), _as_storage(b, dtype)
+    c = np.empty((a.shape[0], b.shape[0]), dtype=out_dtype(dtype, "spatial"))
+    _lib.orc_spatials(kind, CODES[dtype], a.ctypes.data, _stride(a), b.ctypes.data, _stride(b), c.ctypes.data,
+                      c.shape[1] * c.itemsize, a.shape[0], b.shape[0], a.shape[1])
+    return c
+
+
+def angulars(a, b, dtype):
+    return _spatials(0, a, b, dtype)
+
+
+def euclideans(a, b, dtype):
+    return _spatials(1, a, b, dtype)
+
+
+def sumsq(x: np.ndarray, dtype: str) -> np.ndarray:
+    x = _as_storage(x, dtype)
+    return np.array([_lib.orc_sumsq(CODES[dtype], x[i:i + 1].ctypes.data, x.shape[1]) for i in range(x.shape[0])])
+
+
+def _maxsim(fn, q, d, dtype, want_best):
+    q, d = _as_storage(q, dtype), _as_storage(d, dtype)
+    best = np.zeros(q.shape[0], dtype=np.uint32)
+    total = fn(CODES[dtype], q.ctypes.data, _stride(q), q.shape[0], d.ctypes.data, _stride(d), d.shape[0], q.shape[1],
+               best.ctypes.data)
+    value = float(total) if dtype == "f32" else float(np.float32(total))
+    return (value, best) if want_best else value
+
+
+def maxsim(q, d, dtype, want_best: bool = False):
+    """Fused semantics (argmax of the raw dot, winner normalised) - what the CUDA kernel implements."""
+    return _maxsim(_lib.orc_maxsim_argmax_dot, q, d, dtype, want_best)
+
+
+def maxsim_coarse_i8(q, d, dtype, want_best: bool = False):
+    """The reference's serial back end (i8 screening, full-precision refinement)."""
+    return _maxsim(_lib.orc_maxsim_coarse_i8, q, d, dtype, want_best)
+
+
+def maxsim_exhaustive(q, d, dtype) -> float:
+    q, d = _as_storage(q, dtype), _as_storage(d, dtype)
+    return float(_lib.orc_maxsim_exhaustive(CODES[dtype], q.ctypes.data, _stride(q), q.shape[0], d.ctypes.data,
+                                            _stride(d), d.shape[0], q.shape[1]))
+
+
+def exact_dots_f64(a: np.ndarray, b: np.ndarray, dtype: str) -> np.ndarray:
+    """Ground truth the reference's tests use: exactly decoded inputs, f64 accumulation."""
+    return decode(a, dtype).astype(np.float64) @ decode(b, dtype).astype(np.float64).T
+
+
+# ---------------------------------------------------------------- the reference itself, when compiled
+class _Ref:
+    """ctypes view of a reference build: `prefix` is 'nk_' (dispatch library) or 'ref_' (scalar shim)."""
+
+    def __init__(self, path: Path, prefix: str):
+        self.lib = ctypes.CDLL(str(path))
+        self.prefix = prefix
+        if prefix == "nk_":
+            self.lib.nk_capabilities.restype = ctypes.c_uint64
+            self.lib.nk_configure_thread.argtypes = [ctypes.c_uint64]
+            self.configure_thread()
+
+    def configure_thread(self):
+        if self.prefix == "nk_":
+            self.lib.nk_configure_thread(self.lib.nk_capabilities())
+
+    def _fn(self, name, restype, argtypes):
+        f = getattr(self.lib, self.prefix + name)
+        f.restype, f.argtypes = restype, argtypes
+        return f
+
+    def pack(self, b: np.ndarray, dtype: str, family: str = "dots") -> np.ndarray:
+        b = _as_storage(b, dtype)
+        u64, vp = ctypes.c_uint64, ctypes.c_void_p
+        size = self._fn(f"{family}_packed_size_{dtype}", u64, [u64, u64])(b.shape[0], b.shape[1])
+        blob = np.zeros(size + 64, dtype=np.uint8)
+        self._fn(f"{family}_pack_{dtype}", None, [vp, u64, u64, u64, vp])(b.ctypes.data, b.shape[0], b.shape[1], _stride(b), blob.ctypes.data)
+        return blob
+
+    def packed(self, op: str, a: np.ndarray, blob: np.ndarray, n: int, dtype: str, out: Optional[np.ndarray] = None,
+               rows: Optional[slice] = None) -> np.ndarray:
+        a = _as_storage(a, dtype)
+        u64, vp = ctypes.c_uint64, ctypes.c_void_p
+        c = out if out is not None else np.empty((a.shape[0], n), dtype=out_dtype(dtype, op))
+        f = self._fn(f"{op}_packed_{dtype}", None, [vp, vp, vp, u64, u64, u64, u64, u64])
+        lo, hi = (0, a.shape[0]) if rows is None else (rows.start, rows.stop)
+        f(a[lo:hi].ctypes.data, blob.ctypes.data, c[lo:hi].ctypes.data, hi - lo, n, a.shape[1], _stride(a), c.strides[0])
+        return c
+
+    def dots(self, a, b, dtype):
+        return self.packed("dots", a, self.pack(b, dtype), np.asarray(b).shape[0], dtype)
+
+    def angulars(self, a, b, dtype):
+        return self.packed("angulars", a, self.pack(b, dtype), np.asarray(b).shape[0], dtype)
+
+    def euclideans(self, a, b, dtype):
+        return self.packed("euclideans", a, self.pack(b, dtype), np.asarray(b).shape[0], dtype)
+
+    def maxsim(self, q, d, dtype) -> float:
+        q, d = _as_storage(q, dtype), _as_storage(d, dtype)
+        u64, vp = ctypes.c_uint64, ctypes.c_void_p
+        qp, dp = self.pack(q, dtype, "maxsim"), self.pack(d, dtype, "maxsim")
+        res = (ctypes.c_double if dtype == "f32" else ctypes.c_float)()
+        self._fn(f"maxsim_packed_{dtype}", None, [vp, vp, u64, u64, u64, vp])(qp.ctypes.data, dp.ctypes.data, q.shape[0], d.shape[0], q.shape[1], ctypes.addressof(res))
+        return float(res.value)
+
+
+def ref() -> Optional[_Ref]:
+    """The reference's dispatch library (best SIMD back end of this CPU), or None when it was not compiled."""
+    return _Ref(REF_SO, "nk_") if REF_SO.exists() else None
+
+
+def ref_serial() -> Optional[_Ref]:
+    """The reference's scalar back end, or None when it was not compiled."""
+    return _Ref(REF_SERIAL_SO, "ref_") if REF_SERIAL_SO.exists() else None

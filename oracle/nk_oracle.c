@@ -1,0 +1,384 @@
+/*
+ *  TEST INFRASTRUCTURE ONLY. CPU restatement of NumKong v7.6.0's packed-contraction path, used as the
+ *  checker for the CUDA kernels. Nothing the library ships imports, links or runs this file; only
+ *  tests/, __graft_entry__.smoke() and bench.py's CPU-baseline leg do.
+ *
+ *  Parity status: PINNED. tests/test_oracle_pins.py checks every function below against
+ *  (a) golden vectors generated from the reference's own kernels (tests/golden/, script committed
+ *  beside them) and (b), when oracle/_ref/libnumkong.so is present, the reference library itself
+ *  on fresh seeded inputs: bit-exact against its *_serial kernels wherever those are deterministic
+ *  functions of the inputs (all dots, distances, norms), within a stated tolerance where the
+ *  reference routes through run-time dispatched helpers (MaxSim refinement).
+ *
+ *  Each function cites the reference source it restates (paths inside the NumKong tree).
+ *  Plain scalar C, compiled with -ffp-contract=off so no product is fused into a sum behind our back.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ORC_API __attribute__((visibility("default")))
+
+/* dtype codes, numerically nk_dtype_t (include/numkong/types.h:923-953) */
+enum {
+    ORC_I8 = 1 << 2, ORC_U8 = 1 << 6, ORC_F32 = 1 << 11, ORC_F16 = 1 << 12, ORC_BF16 = 1 << 13,
+    ORC_E4M3 = 1 << 14, ORC_E5M2 = 1 << 15, ORC_E2M3 = 1 << 18, ORC_E3M2 = 1 << 19,
+};
+
+static float bits_to_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static uint32_t f32_to_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+
+/* ---- element decoders: value semantics of include/numkong/cast/serial.h ---------------------- */
+
+/* bf16 is the upper half of an f32 (cast/serial.h:750-760). */
+static float dec_bf16(const uint8_t *p) { return bits_to_f32(((uint32_t)p[0] << 16) | ((uint32_t)p[1] << 24)); }
+
+/* IEEE binary16 (cast/serial.h:586-). */
+static float dec_f16(const uint8_t *p) {
+    uint32_t h = (uint32_t)p[0] | ((uint32_t)p[1] << 8);
+    uint32_t sign = (h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+    if (exp == 0) {
+        float v = ldexpf((float)man, -24);
+        return sign ? -v : v;
+    }
+    if (exp == 31) return bits_to_f32(sign | 0x7f800000u | (man << 13));
+    return bits_to_f32(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+/* e4m3fn: bias 7, subnormals m/512, no infinities, NaN only at 0x7F / 0xFF (cast/serial.h:810-839). */
+static float dec_e4m3(const uint8_t *p) {
+    uint32_t b = p[0], exp = (b >> 3) & 0xfu, man = b & 7u;
+    float v;
+    if (exp == 15 && man == 7) return bits_to_f32(0x7fc00000u);
+    if (exp == 0) v = ldexpf((float)man, -9);
+    else v = ldexpf(1.0f + (float)man / 8.0f, (int)exp - 7);
+    return (b & 0x80u) ? -v : v;
+}
+
+/* e5m2: the top byte of a binary16, inf/NaN included (cast/serial.h:1042-). */
+static float dec_e5m2(const uint8_t *p) {
+    uint8_t h[2] = {0, p[0]};
+    return dec_f16(h);
+}
+
+/* e2m3: 0b00SEEMMM, bias 1, subnormals m/8, max 7.5, no inf/NaN (cast/serial.h:1318-1330). */
+static float dec_e2m3(const uint8_t *p) {
+    uint32_t b = p[0], exp = (b >> 3) & 3u, man = b & 7u;
+    float v = exp == 0 ? (float)man / 8.0f : ldexpf(1.0f + (float)man / 8.0f, (int)exp - 1);
+    return (b & 0x20u) ? -v : v;
+}
+
+/* e3m2: 0b00SEEEMM, bias 3, subnormals m/16, max 28, no inf/NaN (cast/serial.h:1455-1471). */
+static float dec_e3m2(const uint8_t *p) {
+    uint32_t b = p[0], exp = (b >> 2) & 7u, man = b & 3u;
+    float v = exp == 0 ? (float)man / 16.0f : ldexpf(1.0f + (float)man / 4.0f, (int)exp - 3);
+    return (b & 0x20u) ? -v : v;
+}
+
+static int elem_bytes(int dt) { return dt == ORC_F32 ? 4 : (dt == ORC_F16 || dt == ORC_BF16) ? 2 : 1; }
+
+static float dec(int dt, const uint8_t *p) {
+    switch (dt) {
+    case ORC_BF16: return dec_bf16(p);
+    case ORC_F16: return dec_f16(p);
+    case ORC_E4M3: return dec_e4m3(p);
+    case ORC_E5M2: return dec_e5m2(p);
+    case ORC_E2M3: return dec_e2m3(p);
+    case ORC_E3M2: return dec_e3m2(p);
+    case ORC_I8: return (float)(int8_t)p[0];
+    case ORC_U8: return (float)p[0];
+    default: { float f; memcpy(&f, p, 4); return f; }
+    }
+}
+
+ORC_API void orc_decode(int dt, const void *src, uint64_t count, float *dst) {
+    const uint8_t *p = (const uint8_t *)src;
+    int eb = elem_bytes(dt);
+    for (uint64_t i = 0; i < count; ++i) dst[i] = dec(dt, p + i * eb);
+}
+
+/* ---- scalar helpers --------------------------------------------------------------------------- */
+
+/* Bit-trick reciprocal square root with three Newton steps (include/numkong/scalar/serial.h:22-31). */
+static float rsqrt_f32(float x) {
+    float y = bits_to_f32(0x5F375A86u - (f32_to_bits(x) >> 1));
+    y = y * (1.5f - 0.5f * x * y * y);
+    y = y * (1.5f - 0.5f * x * y * y);
+    y = y * (1.5f - 0.5f * x * y * y);
+    return y;
+}
+/* scalar/serial.h:33 */
+static float sqrt_f32(float x) { return x > 0 ? x * rsqrt_f32(x) : 0; }
+
+/* scalar/serial.h:35-46: four Newton steps in f64 */
+static double rsqrt_f64(double x) {
+    uint64_t u; memcpy(&u, &x, 8);
+    u = 0x5FE6EB50C7B537A9ull - (u >> 1);
+    double y; memcpy(&y, &u, 8);
+    for (int i = 0; i < 4; ++i) y = y * (1.5 - 0.5 * x * y * y);
+    return y;
+}
+static double sqrt_f64(double x) { return x > 0 ? x * rsqrt_f64(x) : 0; }
+
+ORC_API float orc_rsqrt_f32(float x) { return rsqrt_f32(x); }
+
+/* ---- one dot product with the serial kernels' accumulation order ------------------------------
+ * Sub-32-bit floats: four f32 lanes, lane (l mod 4) takes element l in order, lanes added 0+1+2+3
+ * (include/numkong/dot/serial.h:341-374 f16, :376-404 through-f32, :406-439 bf16, :522-680 fp8/fp6).
+ * f32: same with f64 lanes (dot/serial.h:305-335). i8/u8: two i64 lanes (even/odd), truncated to 32 bits
+ * (dot/serial.h:445-479, :481-516). Zero padding of the packed depth adds exact zeros and is omitted.
+ */
+static float dot_f32lanes(int dt, const uint8_t *a, const uint8_t *b, uint64_t k) {
+    int eb = elem_bytes(dt);
+    float s[4] = {0, 0, 0, 0};
+    for (uint64_t l = 0; l < k; ++l) s[l & 3] += dec(dt, a + l * eb) * dec(dt, b + l * eb);
+    return s[0] + s[1] + s[2] + s[3];
+}
+static double dot_f64lanes(const uint8_t *a, const uint8_t *b, uint64_t k) {
+    double s[4] = {0, 0, 0, 0};
+    for (uint64_t l = 0; l < k; ++l) {
+        float x, y; memcpy(&x, a + 4 * l, 4); memcpy(&y, b + 4 * l, 4);
+        s[l & 3] += (double)x * y;
+    }
+    return s[0] + s[1] + s[2] + s[3];
+}
+static int64_t dot_int(int dt, const uint8_t *a, const uint8_t *b, uint64_t k) {
+    int64_t s = 0;
+    if (dt == ORC_I8) for (uint64_t l = 0; l < k; ++l) s += (int64_t)(int8_t)a[l] * (int8_t)b[l];
+    else for (uint64_t l = 0; l < k; ++l) s += (int64_t)a[l] * b[l];
+    return s;
+}
+
+/* C = A . B^T, overwriting C (include/numkong/dots/serial.h:520-1085; output types dot.h:633-654). */
+ORC_API void orc_dots(int dt, const void *a, uint64_t a_stride, const void *b, uint64_t b_stride, void *c,
+                      uint64_t c_stride, uint64_t m, uint64_t n, uint64_t k) {
+    const uint8_t *ap = (const uint8_t *)a, *bp = (const uint8_t *)b;
+    for (uint64_t i = 0; i < m; ++i) {
+        uint8_t *row = (uint8_t *)c + i * c_stride;
+        for (uint64_t j = 0; j < n; ++j) {
+            const uint8_t *x = ap + i * a_stride, *y = bp + j * b_stride;
+            if (dt == ORC_I8 || dt == ORC_U8) ((int32_t *)row)[j] = (int32_t)dot_int(dt, x, y, k);
+            else if (dt == ORC_F32) ((double *)row)[j] = dot_f64lanes(x, y, k);
+            else ((float *)row)[j] = dot_f32lanes(dt, x, y, k);
+        }
+    }
+}
+
+/* ---- squared norms as the serial pack stores them ---------------------------------------------
+ * Floats below 32 bits: compensated (Neumaier) f32 running sum of v*v
+ * (include/numkong/reduce/serial.h:248-272 and siblings). f32: the same in f64. i8/u8: exact, truncated to u32
+ * (dots/serial.h:159-170). Used for the norms appended by pack (dots/serial.h:326-332) and for the
+ * per-query norm of the batched distances (dots/serial.h:2775-2778).
+ */
+static float sumsq_f32_neumaier(int dt, const uint8_t *x, uint64_t k) {
+    int eb = elem_bytes(dt);
+    float run = 0, comp = 0;
+    for (uint64_t l = 0; l < k; ++l) {
+        float v = dec(dt, x + l * eb), sq = v * v, t = run + sq;
+        if (run >= sq) comp += (run - t) + sq; else comp += (sq - t) + run;
+        run = t;
+    }
+    return run + comp;
+}
+ORC_API double orc_sumsq(int dt, const void *x, uint64_t k) {
+    const uint8_t *p = (const uint8_t *)x;
+    if (dt == ORC_I8 || dt == ORC_U8) return (double)(uint32_t)(uint64_t)dot_int(dt, p, p, k);
+    if (dt == ORC_F32) {
+        /* the same compensated sum carried in f64 (reduce/serial.h:50-70) */
+        double run = 0, comp = 0;
+        for (uint64_t l = 0; l < k; ++l) {
+            float v; memcpy(&v, p + 4 * l, 4);
+            double sq = (double)v * (double)v, t = run + sq;
+            if (run >= sq) comp += (run - t) + sq; else comp += (sq - t) + run;
+            run = t;
+        }
+        return run + comp;
+    }
+    return (double)sumsq_f32_neumaier(dt, p, k);
+}
+
+/* ---- batched distances: GEMM, then the from-dot finalisers ------------------------------------
+ * include/numkong/dots/serial.h:2756-2800 drives; formulas include/numkong/spatial/serial.h:257-350.
+ * kind 0 = angular, 1 = euclidean. Output f32 (f64 for f32 inputs).
+ */
+static float angular_from_dot_f32(float dot, float an, float bn) {
+    float product = an * bn;
+    if (product > 0) {
+        float r = 1.0f - dot * rsqrt_f32(product);
+        return r > 0 ? r : 0;
+    }
+    return dot == 0 ? 0.0f : 1.0f;
+}
+static float euclidean_from_dot_f32(float dot, float an, float bn) {
+    float d2 = an + bn - 2.0f * dot;
+    return d2 > 0 ? sqrt_f32(d2) : 0.0f;
+}
+ORC_API void orc_spatials(int kind, int dt, const void *a, uint64_t a_stride, const void *b, uint64_t b_stride, void *c,
+                          uint64_t c_stride, uint64_t m, uint64_t n, uint64_t k) {
+    const uint8_t *ap = (const uint8_t *)a, *bp = (const uint8_t *)b;
+    double *bn = (double *)malloc(sizeof(double) * (n ? n : 1));
+    for (uint64_t j = 0; j < n; ++j) bn[j] = orc_sumsq(dt, bp + j * b_stride, k);
+    for (uint64_t i = 0; i < m; ++i) {
+        uint8_t *row = (uint8_t *)c + i * c_stride;
+        const uint8_t *x = ap + i * a_stride;
+        double an = orc_sumsq(dt, x, k);
+        for (uint64_t j = 0; j < n; ++j) {
+            const uint8_t *y = bp + j * b_stride;
+            if (dt == ORC_F32) {
+                double dot = dot_f64lanes(x, y, k), r;
+                if (kind == 0) {
+                    double product = an * bn[j];
+                    if (product > 0) { r = 1.0 - dot * rsqrt_f64(product); r = r > 0 ? r : 0; }
+                    else r = dot == 0 ? 0.0 : 1.0;
+                } else {
+                    double d2 = an + bn[j] - 2.0 * dot;
+                    r = d2 > 0 ? sqrt_f64(d2) : 0.0;
+                }
+                ((double *)row)[j] = r;
+            } else {
+                float dot, fa, fb;
+                if (dt == ORC_I8) { dot = (float)(int32_t)dot_int(dt, x, y, k); fa = (float)(int32_t)(uint32_t)an; fb = (float)(int32_t)(uint32_t)bn[j]; }
+                else if (dt == ORC_U8) { dot = (float)(uint32_t)dot_int(dt, x, y, k); fa = (float)(uint32_t)an; fb = (float)(uint32_t)bn[j]; }
+                else { dot = dot_f32lanes(dt, x, y, k); fa = (float)an; fb = (float)bn[j]; }
+                ((float *)row)[j] = kind == 0 ? angular_from_dot_f32(dot, fa, fb) : euclidean_from_dot_f32(dot, fa, fb);
+            }
+        }
+    }
+    free(bn);
+}
+
+/* ---- MaxSim ------------------------------------------------------------------------------------
+ * Inverse norm stored by pack: plain f32 running sum of v*v, then the bit-trick rsqrt, 0 for a zero
+ * vector (include/numkong/maxsim/serial.h:122-141, :263).
+ */
+static float inverse_norm(int dt, const uint8_t *x, uint64_t k) {
+    int eb = elem_bytes(dt);
+    float s = 0;
+    for (uint64_t l = 0; l < k; ++l) { float v = dec(dt, x + l * eb); s += v * v; }
+    return s > 0 ? rsqrt_f32(s) : 0.0f;
+}
+
+/* Fused semantics of the tensor-engine back end (include/numkong/maxsim/sapphireamx.h:716-861), which the
+ * CUDA kernel follows: for every query vector the FIRST document vector with the largest raw dot wins
+ * (strict >, running maximum starts at the lowest finite f32); only the winner is normalised:
+ * cosine = dot * inv|q| * inv|d|, angular = max(0, 1 - cosine); angulars are added in f64 and the sum is
+ * returned (callers cast to f32 for bf16/f16). `best` (optional) receives the winning document indices.
+ */
+ORC_API double orc_maxsim_argmax_dot(int dt, const void *q, uint64_t q_stride, uint64_t nq, const void *d,
+                                     uint64_t d_stride, uint64_t nd, uint64_t k, uint32_t *best) {
+    const uint8_t *qp = (const uint8_t *)q, *dp = (const uint8_t *)d;
+    float *inv_d = (float *)malloc(sizeof(float) * (nd ? nd : 1));
+    for (uint64_t j = 0; j < nd; ++j) inv_d[j] = inverse_norm(dt, dp + j * d_stride, k);
+    double total = 0;
+    for (uint64_t i = 0; i < nq; ++i) {
+        const uint8_t *x = qp + i * q_stride;
+        uint32_t arg = 0;
+        if (dt == ORC_F32) {
+            /* f32 inputs keep the dot, the cosine and the angular in f64 (maxsim/serial.h:443-455). */
+            double run = -1.7976931348623157e308;
+            for (uint64_t j = 0; j < nd; ++j) {
+                double dot = dot_f64lanes(x, dp + j * d_stride, k);
+                if (dot > run) { run = dot; arg = (uint32_t)j; }
+            }
+            double angular = 1.0 - run * (double)inverse_norm(dt, x, k) * (double)inv_d[arg];
+            total += angular < 0 ? 0 : angular;
+        } else {
+            float run = -3.402823466e+38f;
+            for (uint64_t j = 0; j < nd; ++j) {
+                float dot = dot_f32lanes(dt, x, dp + j * d_stride, k);
+                if (dot > run) { run = dot; arg = (uint32_t)j; }
+            }
+            float cosine = run * inverse_norm(dt, x, k) * inv_d[arg];
+            float angular = 1.0f - cosine;
+            if (angular < 0) angular = 0;
+            total += (double)angular;
+        }
+        if (best) best[i] = arg;
+    }
+    free(inv_d);
+    return total;
+}
+
+/* Exhaustive definition the reference tests compare against (include/numkong/maxsim.hpp:82-110):
+ * sum over queries of the minimum true angular distance, everything in f64. */
+ORC_API double orc_maxsim_exhaustive(int dt, const void *q, uint64_t q_stride, uint64_t nq, const void *d,
+                                     uint64_t d_stride, uint64_t nd, uint64_t k) {
+    const uint8_t *qp = (const uint8_t *)q, *dp = (const uint8_t *)d;
+    int eb = elem_bytes(dt);
+    double total = 0;
+    for (uint64_t i = 0; i < nq; ++i) {
+        double best = 1.7976931348623157e308;
+        for (uint64_t j = 0; j < nd; ++j) {
+            double ab = 0, aa = 0, bb = 0;
+            for (uint64_t l = 0; l < k; ++l) {
+                double x = dec(dt, qp + i * q_stride + l * eb), y = dec(dt, dp + j * d_stride + l * eb);
+                ab += x * y; aa += x * x; bb += y * y;
+            }
+            double ang;
+            if (aa == 0 && bb == 0) ang = 0;
+            else if (ab == 0) ang = 1;
+            else { ang = 1.0 - ab / (sqrt(aa) * sqrt(bb)); if (ang < 0) ang = 0; }
+            if (ang < best) best = ang;
+        }
+        total += best;
+    }
+    return total;
+}
+
+/* Serial back end of MaxSim (include/numkong/maxsim/serial.h:122-167 quantiser, :331-390 coarse argmax,
+ * :392-424 refinement): per-vector symmetric i8 quantisation (scale = absmax/127, round half away from
+ * zero), argmax of the i8 dot (strict >, first wins), winner re-scored with the full-precision dot. The
+ * reference refines with its run-time dispatched 1-to-1 dot, so only the winners are bit-pinned; the
+ * returned sum is compared with a tolerance. `best` receives the winners.
+ */
+ORC_API double orc_maxsim_coarse_i8(int dt, const void *q, uint64_t q_stride, uint64_t nq, const void *d,
+                                    uint64_t d_stride, uint64_t nd, uint64_t k, uint32_t *best) {
+    const uint8_t *qp = (const uint8_t *)q, *dp = (const uint8_t *)d;
+    int eb = elem_bytes(dt);
+    int8_t *qi = (int8_t *)malloc((nq ? nq : 1) * (k ? k : 1)), *di = (int8_t *)malloc((nd ? nd : 1) * (k ? k : 1));
+    for (int side = 0; side < 2; ++side) {
+        const uint8_t *src = side ? dp : qp;
+        uint64_t cnt = side ? nd : nq, stride = side ? d_stride : q_stride;
+        int8_t *dst = side ? di : qi;
+        for (uint64_t v = 0; v < cnt; ++v) {
+            float absmax = 0;
+            for (uint64_t l = 0; l < k; ++l) { float x = fabsf(dec(dt, src + v * stride + l * eb)); if (x > absmax) absmax = x; }
+            float scale = absmax / 127.0f;
+            if (scale == 0) scale = 1.0f;
+            for (uint64_t l = 0; l < k; ++l) {
+                float s = dec(dt, src + v * stride + l * eb) / scale;
+                int32_t z = s >= 0 ? (int32_t)(s + 0.5f) : (int32_t)(s - 0.5f);
+                if (z > 127) z = 127;
+                if (z < -127) z = -127;
+                dst[v * k + l] = (int8_t)z;
+            }
+        }
+    }
+    double total = 0;
+    for (uint64_t i = 0; i < nq; ++i) {
+        int32_t run = INT32_MIN;
+        uint32_t arg = 0;
+        for (uint64_t j = 0; j < nd; ++j) {
+            int32_t acc = 0;
+            for (uint64_t l = 0; l < k; ++l) acc += (int32_t)qi[i * k + l] * (int32_t)di[j * k + l];
+            if (acc > run) { run = acc; arg = (uint32_t)j; }
+        }
+        const uint8_t *x = qp + i * q_stride, *y = dp + arg * d_stride;
+        if (dt == ORC_F32) {
+            double angular = 1.0 - dot_f64lanes(x, y, k) * (double)inverse_norm(dt, x, k) * (double)inverse_norm(dt, y, k);
+            total += angular < 0 ? 0 : angular;
+        } else {
+            float cosine = dot_f32lanes(dt, x, y, k) * inverse_norm(dt, x, k) * inverse_norm(dt, y, k);
+            float angular = 1.0f - cosine;
+            if (angular < 0) angular = 0;
+            total += (double)angular;
+        }
+        if (best) best[i] = arg;
+    }
+    free(qi); free(di);
+    return total;
+}
+
+/* ---- multi-threaded driver for the CPU-baseline timing (rows of A split across threads, as the
+ * reference's callers do: README.md:199-212) is in Python (threads release the GIL inside ctypes). */

@@ -1,0 +1,55 @@
+/*
+ *  TEST INFRASTRUCTURE ONLY. Compiled against the upstream NumKong headers where they lie (never copied):
+ *  exports the header-only *_serial kernels of the packed-contraction path under ref_* names, so the tests
+ *  can pin oracle/nk_oracle.c bit-for-bit against the reference's own scalar back end. Built by
+ *  `make -C oracle ref` into oracle/_ref/libnkref_serial.so.
+ */
+#include <numkong/numkong.h>
+
+#define REF_API __attribute__((visibility("default")))
+
+#define REF_PACKED_FAMILY(T, IN, OUT, DOUT)                                                                          \
+    REF_API nk_size_t ref_dots_packed_size_##T(nk_size_t n, nk_size_t k) { return nk_dots_packed_size_##T##_serial(n, k); } \
+    REF_API void ref_dots_pack_##T(IN const *b, nk_size_t n, nk_size_t k, nk_size_t s, void *p) {                     \
+        nk_dots_pack_##T##_serial(b, n, k, s, p);                                                                     \
+    }                                                                                                                 \
+    REF_API void ref_dots_packed_##T(IN const *a, void const *p, OUT *c, nk_size_t m, nk_size_t n, nk_size_t k,       \
+                                     nk_size_t as, nk_size_t cs) {                                                    \
+        nk_dots_packed_##T##_serial(a, p, c, m, n, k, as, cs);                                                        \
+    }                                                                                                                 \
+    REF_API void ref_angulars_packed_##T(IN const *a, void const *p, DOUT *c, nk_size_t m, nk_size_t n, nk_size_t k,  \
+                                         nk_size_t as, nk_size_t cs) {                                                \
+        nk_angulars_packed_##T##_serial(a, p, c, m, n, k, as, cs);                                                    \
+    }                                                                                                                 \
+    REF_API void ref_euclideans_packed_##T(IN const *a, void const *p, DOUT *c, nk_size_t m, nk_size_t n,             \
+                                           nk_size_t k, nk_size_t as, nk_size_t cs) {                                 \
+        nk_euclideans_packed_##T##_serial(a, p, c, m, n, k, as, cs);                                                  \
+    }
+
+REF_PACKED_FAMILY(i8, nk_i8_t, nk_i32_t, nk_f32_t)
+REF_PACKED_FAMILY(u8, nk_u8_t, nk_u32_t, nk_f32_t)
+REF_PACKED_FAMILY(bf16, nk_bf16_t, nk_f32_t, nk_f32_t)
+REF_PACKED_FAMILY(f16, nk_f16_t, nk_f32_t, nk_f32_t)
+REF_PACKED_FAMILY(e4m3, nk_e4m3_t, nk_f32_t, nk_f32_t)
+REF_PACKED_FAMILY(e5m2, nk_e5m2_t, nk_f32_t, nk_f32_t)
+REF_PACKED_FAMILY(e2m3, nk_e2m3_t, nk_f32_t, nk_f32_t)
+REF_PACKED_FAMILY(e3m2, nk_e3m2_t, nk_f32_t, nk_f32_t)
+REF_PACKED_FAMILY(f32, nk_f32_t, nk_f64_t, nk_f64_t)
+
+#define REF_MAXSIM_FAMILY(T, IN, OUT)                                                                                \
+    REF_API nk_size_t ref_maxsim_packed_size_##T(nk_size_t n, nk_size_t k) { return nk_maxsim_packed_size_##T##_serial(n, k); } \
+    REF_API void ref_maxsim_pack_##T(IN const *v, nk_size_t n, nk_size_t k, nk_size_t s, void *p) {                   \
+        nk_maxsim_pack_##T##_serial(v, n, k, s, p);                                                                   \
+    }                                                                                                                 \
+    REF_API void ref_maxsim_packed_##T(void const *q, void const *d, nk_size_t nq, nk_size_t nd, nk_size_t k, OUT *r) { \
+        nk_maxsim_packed_##T##_serial(q, d, nq, nd, k, r);                                                            \
+    }
+
+REF_MAXSIM_FAMILY(bf16, nk_bf16_t, nk_f32_t)
+REF_MAXSIM_FAMILY(f16, nk_f16_t, nk_f32_t)
+REF_MAXSIM_FAMILY(f32, nk_f32_t, nk_f64_t)
+
+REF_API float ref_rsqrt_f32(float x) { return nk_f32_rsqrt_serial(x); }
+REF_API void ref_sumsq_bf16(nk_bf16_t const *x, nk_size_t n, float *out) { float s; nk_reduce_moments_bf16_serial(x, n, 2, &s, out); }
+REF_API void ref_sumsq_f16(nk_f16_t const *x, nk_size_t n, float *out) { float s; nk_reduce_moments_f16_serial(x, n, 2, &s, out); }
+REF_API void ref_sumsq_e4m3(nk_e4m3_t const *x, nk_size_t n, float *out) { float s; nk_reduce_moments_e4m3_serial(x, n, 1, &s, out); }
