@@ -112,6 +112,39 @@ NKB_API void nk_find_kernel_punned(int kind, uint32_t dtype, uint64_t viable_cap
 NKB_API uint64_t nk_capabilities(void);            /* c/numkong.c:832-843: here NKB_CAPABILITY_B200 or 0 */
 NKB_API int nk_configure_thread(uint64_t caps);    /* capabilities.h:909: nothing to set up per thread here; returns 1 */
 
+/* ---- results too large to return whole (no counterpart in the reference) -----------------------
+ * Each of these equals "call the reference function, then reduce": the tests check them that way.
+ *
+ * nkb_<metric>s_packed_topk_<t>: for every row of A the `top` (<= 1024) nearest rows of the packed
+ *   matrix, ascending by distance, ties by lower id: distances[height x top] f32, ids[height x top] i64
+ *   (= id_base + row index inside the packed matrix; unused slots hold +inf / -1). Equivalent to
+ *   nk_<metric>s_packed_<t> followed by a per-row selection, without ever storing height x width values.
+ * nkb_maxsims_packed_<t>: all-pairs MaxSim. `q_packed` / `d_packed` hold the token vectors of all queries /
+ *   all documents back to back (one nk_maxsim_pack_<t> call each); q_offsets[n_queries+1] and
+ *   d_offsets[n_documents+1] (u64, ascending, starting at 0) delimit them; every document needs at least
+ *   one vector. scores[q * score_stride/4 + d] receives what nk_maxsim_packed_<t> returns for that pair.
+ * nkb_topk_smallest_f32: per row of a score matrix, the `top` smallest values and their columns + id_base.
+ */
+#define NKB_DECLARE_TOPK_FAMILY(T)                                                                                     \
+    NKB_API void nkb_angulars_packed_topk_##T(void const *a, void const *b_packed, nk_size_t height, nk_size_t width,  \
+                                              nk_size_t depth, nk_size_t a_stride, nk_size_t top, void *distances,     \
+                                              void *ids, nk_size_t id_base);                                           \
+    NKB_API void nkb_euclideans_packed_topk_##T(void const *a, void const *b_packed, nk_size_t height, nk_size_t width, \
+                                                nk_size_t depth, nk_size_t a_stride, nk_size_t top, void *distances,   \
+                                                void *ids, nk_size_t id_base);
+NKB_DECLARE_TOPK_FAMILY(f16)
+NKB_DECLARE_TOPK_FAMILY(bf16)
+
+#define NKB_DECLARE_MAXSIMS_FAMILY(T)                                                                                  \
+    NKB_API void nkb_maxsims_packed_##T(void const *q_packed, void const *q_offsets, nk_size_t n_queries,              \
+                                        void const *d_packed, void const *d_offsets, nk_size_t n_documents,            \
+                                        nk_size_t depth, void *scores, nk_size_t score_stride);
+NKB_DECLARE_MAXSIMS_FAMILY(bf16)
+NKB_DECLARE_MAXSIMS_FAMILY(f16)
+
+NKB_API void nkb_topk_smallest_f32(void const *scores, nk_size_t rows, nk_size_t cols, nk_size_t stride, nk_size_t top,
+                                   nk_size_t id_base, void *out_values, void *out_ids);
+
 /* ---- additions (no counterpart in the reference) -------------------------------------------- */
 /** Last error of the calling thread, "" when the last call succeeded. The string stays valid until the next call. */
 NKB_API char const *nkb_last_error(void);
@@ -123,6 +156,12 @@ NKB_API uint32_t nkb_synchronize(void);
 NKB_API uint64_t nkb_launch_count(void);
 /** Forces a GEMM tile configuration for testing/tuning: 0 = choose by shape. */
 NKB_API void nkb_set_gemm_variant(int variant);
+/** How e2m3 / e3m2 operands reach the tensor cores: 0 (default) = recoded to the e4m3 code of the same value,
+ *  1 = packed 6-bit operands with the native e2m3 / e3m2 MMA formats. Applies to later pack AND multiply calls;
+ *  a blob packed under one setting must be multiplied under the same one. */
+NKB_API void nkb_set_fp6_native(int native);
+/** Packed rows handled per panel by the distance top-k (rounded up to 256); 0 = sized from the scratch budget. */
+NKB_API void nkb_set_topk_panel_rows(nk_size_t rows);
 /** Drops the cached device copies of host-resident packed blobs and the staging buffers of the calling thread. */
 NKB_API void nkb_release_caches(void);
 

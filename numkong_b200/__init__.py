@@ -85,6 +85,19 @@ class _View:
         self.dtype = name
 
 
+def _view_like(x: Any, dtype: Optional[str], packed_dtype: str) -> _View:
+    """View of `x` for use against a matrix packed as `packed_dtype`. Unsigned storage words (uint8 /
+    uint16 / int16) stand for the 8/6-bit and 16-bit float types NumPy and torch cannot name."""
+    if dtype is None:
+        name = (_TORCH_NAMES.get(str(x.dtype)) if _is_torch(x) else _NUMPY_NAMES.get(np.asarray(x).dtype.name))
+        container = name in (None, "u8") and packed_dtype not in ("i8", "u8", "f32")
+        dtype = packed_dtype if container else name
+    v = _View(x, dtype)
+    if v.dtype != packed_dtype:
+        raise TypeError(f"dtype mismatch: matrix is {v.dtype}, packed matrix is {packed_dtype}")
+    return v
+
+
 def _alloc_bytes(nbytes: int, cuda: bool):
     if cuda:
         import torch
@@ -163,9 +176,7 @@ def _out_matrix(v: _View, width: int, out: Any, dtype_name: str):
 def _packed_call(op: str, a: Any, packed: PackedMatrix, out: Any, dtype: Optional[str]):
     if not isinstance(packed, PackedMatrix) or packed.kind != "dots":
         raise TypeError("second argument must be a PackedMatrix produced by dots_pack")
-    v = _View(a, dtype or packed.dtype)
-    if v.dtype != packed.dtype:
-        raise TypeError(f"dtype mismatch: a is {v.dtype}, packed matrix is {packed.dtype}")
+    v = _view_like(a, dtype, packed.dtype)
     if v.cols != packed.depth:
         raise ValueError(f"depth mismatch: a has {v.cols} columns, packed matrix has depth {packed.depth}")
     t = v.dtype
@@ -234,8 +245,8 @@ def maxsim(q: Any, d: Any, dtype: Optional[str] = None) -> float:
 # ---- additions that the reference API cannot express (results too large to materialise) ----
 
 def _topk_call(op: str, a: Any, packed: PackedMatrix, top: int, id_base: int, dtype: Optional[str]):
-    v = _View(a, dtype or packed.dtype)
-    if v.dtype != packed.dtype or v.dtype not in ("f16", "bf16"):
+    v = _view_like(a, dtype, packed.dtype)
+    if v.dtype not in ("f16", "bf16"):
         raise TypeError("top-k distances are available for f16 and bf16")
     if v.cols != packed.depth:
         raise ValueError("depth mismatch")

@@ -24,7 +24,7 @@ MAXSIM_DTYPES = ("bf16", "f16", "f32")
 def _load() -> ctypes.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m numkong_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python numkong_b200/build.py` "
             "(nvcc, sm_100a). There is no CPU fallback."
         )
     lib = ctypes.CDLL(str(LIB_PATH), mode=ctypes.RTLD_LOCAL)
@@ -38,18 +38,15 @@ def _load() -> ctypes.CDLL:
             f = getattr(lib, f"nk_{op}_packed_{t}")
             f.restype, f.argtypes = None, [vp, vp, vp, sz, sz, sz, sz, sz]
     for t in MAXSIM_DTYPES:
-        if not hasattr(lib, f"nk_maxsim_packed_size_{t}"):
-            continue
         f = getattr(lib, f"nk_maxsim_packed_size_{t}")
         f.restype, f.argtypes = sz, [sz, sz]
         f = getattr(lib, f"nk_maxsim_pack_{t}")
         f.restype, f.argtypes = None, [vp, sz, sz, sz, vp]
         f = getattr(lib, f"nk_maxsim_packed_{t}")
         f.restype, f.argtypes = None, [vp, vp, sz, sz, sz, vp]
-    if hasattr(lib, "nk_find_kernel_punned"):
-        lib.nk_find_kernel_punned.restype = None
-        lib.nk_find_kernel_punned.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64,
-                                              ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_uint64)]
+    lib.nk_find_kernel_punned.restype = None
+    lib.nk_find_kernel_punned.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_uint64,
+                                          ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_uint64)]
     lib.nk_capabilities.restype, lib.nk_capabilities.argtypes = ctypes.c_uint64, []
     lib.nk_configure_thread.restype, lib.nk_configure_thread.argtypes = ctypes.c_int, [ctypes.c_uint64]
     lib.nkb_last_error.restype, lib.nkb_last_error.argtypes = ctypes.c_char_p, []
@@ -58,20 +55,17 @@ def _load() -> ctypes.CDLL:
     lib.nkb_launch_count.restype, lib.nkb_launch_count.argtypes = ctypes.c_uint64, []
     lib.nkb_set_gemm_variant.restype, lib.nkb_set_gemm_variant.argtypes = None, [ctypes.c_int]
     lib.nkb_release_caches.restype, lib.nkb_release_caches.argtypes = None, []
+    lib.nkb_set_fp6_native.restype, lib.nkb_set_fp6_native.argtypes = None, [ctypes.c_int]
+    lib.nkb_set_topk_panel_rows.restype, lib.nkb_set_topk_panel_rows.argtypes = None, [sz]
     for t in ("f16", "bf16"):
         for op in ("angulars", "euclideans"):
-            if not hasattr(lib, f"nkb_{op}_packed_topk_{t}"):
-                continue
             f = getattr(lib, f"nkb_{op}_packed_topk_{t}")
             f.restype, f.argtypes = None, [vp, vp, sz, sz, sz, sz, sz, vp, vp, sz]
     for t in ("bf16", "f16"):
-        if not hasattr(lib, f"nkb_maxsims_packed_{t}"):
-            continue
         f = getattr(lib, f"nkb_maxsims_packed_{t}")
         f.restype, f.argtypes = None, [vp, vp, sz, vp, vp, sz, sz, vp, sz]
-    if hasattr(lib, "nkb_topk_smallest_f32"):
-        lib.nkb_topk_smallest_f32.restype = None
-        lib.nkb_topk_smallest_f32.argtypes = [vp, sz, sz, sz, sz, sz, vp, vp]
+    lib.nkb_topk_smallest_f32.restype = None
+    lib.nkb_topk_smallest_f32.argtypes = [vp, sz, sz, sz, sz, sz, vp, vp]
     return lib
 
 

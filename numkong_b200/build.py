@@ -1,7 +1,7 @@
 """Builds libnumkong_b200.so in-tree with nvcc for sm_100a.
 
-    python -m numkong_b200.build            # incremental
-    python -m numkong_b200.build --force    # rebuild everything
+    python numkong_b200/build.py            # incremental (run as a script: importing the package needs the library)
+    python numkong_b200/build.py --force    # rebuild everything
 
 Every .cu file under csrc/ is compiled to an object (in parallel) and linked into one shared
 library next to this file. The CUDA runtime is linked statically, so the library depends only

@@ -21,6 +21,7 @@ std::atomic<uint64_t> g_launches{0};
 namespace {
 
 std::atomic<int> g_variant{0};
+std::atomic<int> g_fp6_native{0};
 std::atomic<uint64_t> g_nonce_counter{0};
 
 // ---------------------------------------------------------------- per-thread context
@@ -76,6 +77,7 @@ void set_error(const char *fmt, const char *detail) {
 void clear_error() { t_ctx.error.clear(); }
 cudaStream_t current_stream() { return t_ctx.stream; }
 int current_variant() { return g_variant.load(); }
+int fp6_native() { return g_fp6_native.load(); }
 
 bool cuda_ok(cudaError_t e, const char *what) {
     if (e == cudaSuccess) return true;
@@ -210,10 +212,10 @@ __global__ void write_header_kernel(PackedHeader *dst, PackedHeader h) { *dst = 
 // Brings a strided matrix into device memory that TMA can address (16-byte aligned base and pitch).
 // Returns the device pointer and pitch; uses `slot` when a copy is needed.
 const void *resident_matrix(const void *src, MemKind kind, uint64_t rows, uint64_t row_bytes, uint64_t stride,
-                            int slot, uint64_t *pitch_out) {
+                            int slot, int piece_mode, uint64_t *pitch_out) {
     if (rows <= 1 && stride < row_bytes) stride = row_bytes;
     const bool aligned = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) && ((stride & 15u) == 0);
-    if (kind == kMemDevice && aligned) { *pitch_out = stride; return src; }
+    if (kind == kMemDevice && aligned && piece_mode == kPieceNone) { *pitch_out = stride; return src; }
     uint64_t pitch = round_up(row_bytes, 16);
     void *dst = scratch(slot, rows * pitch + 16);
     if (!dst) return nullptr;
@@ -222,8 +224,12 @@ const void *resident_matrix(const void *src, MemKind kind, uint64_t rows, uint64
             if (!cuda_ok(cudaMemsetAsync(dst, 0, rows * pitch, t_ctx.stream), "clear staging")) return nullptr;
         }
         if (!cuda_ok(cudaMemcpy2DAsync(dst, pitch, src, stride, row_bytes, rows, cudaMemcpyHostToDevice, t_ctx.stream), "upload of input matrix")) return nullptr;
+        if (piece_mode != kPieceNone) {  // in place: every piece is read and written by the same thread
+            if (!cuda_ok(launch_restride(dst, rows, pitch, pitch, dst, pitch, piece_mode, t_ctx.stream), "operand rewrite kernel")) return nullptr;
+            g_launches++;
+        }
     } else {
-        if (!cuda_ok(launch_restride(src, rows, row_bytes, stride, dst, pitch, t_ctx.stream), "restride kernel")) return nullptr;
+        if (!cuda_ok(launch_restride(src, rows, row_bytes, stride, dst, pitch, piece_mode, t_ctx.stream), "restride kernel")) return nullptr;
         g_launches++;
     }
     *pitch_out = pitch;
@@ -279,7 +285,7 @@ void pack_impl(uint32_t magic, uint32_t dt, const void *b, uint64_t rows, uint64
         }
         if (ok) {
             ok = cuda_ok(launch_pack_payload(dt, b_dev, rows, depth, b_pitch, dev_blob + g.payload_offset, g.rows_padded,
-                                             g.depth_padded_bytes, stream), "pack kernel");
+                                             g.depth_padded_bytes, piece_mode_for(dt), stream), "pack kernel");
             g_launches++;
         }
         if (ok) {
@@ -343,7 +349,7 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
         const void *a_dev = a;
         uint64_t a_pitch = a_stride;
         if (a_kind == kMemHost || (reinterpret_cast<uintptr_t>(a) & 3u) || (a_stride & 3u)) {
-            a_dev = resident_matrix(a, a_kind, m, k * 4, a_stride, kSlotA, &a_pitch);
+            a_dev = resident_matrix(a, a_kind, m, k * 4, a_stride, kSlotA, kPieceNone, &a_pitch);
             if (!a_dev) { fail(); return; }
         }
         double *a_norms = nullptr;
@@ -360,13 +366,39 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
             g_launches++;
         }
     } else {
+        // FP6 operands are rewritten for the tensor cores (see transform_piece); their norms are taken
+        // from the caller's bytes first.
+        const int piece_mode = piece_mode_for(dt);
         uint64_t a_pitch = 0;
-        const void *a_dev = resident_matrix(a, a_kind, m, k * dtype_bytes(dt), a_stride, kSlotA, &a_pitch);
-        if (!a_dev) { fail(); return; }
+        const void *a_dev = nullptr;
         float *a_norms = nullptr;
         if (epilogue != kEpiDot) {
             a_norms = static_cast<float *>(scratch(kSlotNorms, m * 4));
-            ok = a_norms && cuda_ok(launch_row_sumsq(dt, a_dev, m, k, a_pitch, a_norms, true, false, stream), "row norm kernel");
+            if (!a_norms) { fail(); return; }
+        }
+        if (piece_mode == kPieceNone) {
+            a_dev = resident_matrix(a, a_kind, m, k * dtype_bytes(dt), a_stride, kSlotA, kPieceNone, &a_pitch);
+            if (!a_dev) { fail(); return; }
+            if (a_norms) {
+                ok = cuda_ok(launch_row_sumsq(dt, a_dev, m, k, a_pitch, a_norms, true, false, stream), "row norm kernel");
+                g_launches++;
+            }
+        } else if (a_kind == kMemDevice) {
+            if (a_norms) {
+                ok = cuda_ok(launch_row_sumsq(dt, a, m, k, a_stride, a_norms, true, false, stream), "row norm kernel");
+                g_launches++;
+            }
+            a_dev = resident_matrix(a, a_kind, m, k, a_stride, kSlotA, piece_mode, &a_pitch);
+            if (!a_dev) { fail(); return; }
+        } else {
+            a_dev = resident_matrix(a, a_kind, m, k, a_stride, kSlotA, kPieceNone, &a_pitch);
+            if (!a_dev) { fail(); return; }
+            if (a_norms) {
+                ok = cuda_ok(launch_row_sumsq(dt, a_dev, m, k, a_pitch, a_norms, true, false, stream), "row norm kernel");
+                g_launches++;
+            }
+            // In place: each 16-byte piece is read and written by the same thread.
+            ok = ok && cuda_ok(launch_restride(a_dev, m, a_pitch, a_pitch, const_cast<void *>(a_dev), a_pitch, piece_mode, stream), "operand rewrite kernel");
             g_launches++;
         }
         if (ok) {
@@ -395,6 +427,12 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
 }
 
 } // namespace
+
+void maxsim_pack_impl(uint32_t dt, const void *vectors, uint64_t count, uint64_t depth, uint64_t stride, void *packed) {
+    if (dt != kBF16 && dt != kF16 && dt != kF32) { clear_error(); set_error("maxsim_pack: unsupported element type%s", ""); return; }
+    pack_impl(kMagicMaxsim, dt, vectors, count, depth, stride, packed, true);
+}
+
 } // namespace nkb
 
 using namespace nkb;
@@ -438,6 +476,7 @@ NKB_API uint32_t nkb_synchronize(void) {
 }
 NKB_API uint64_t nkb_launch_count(void) { return g_launches.load(); }
 NKB_API void nkb_set_gemm_variant(int variant) { g_variant.store(variant); }
+NKB_API void nkb_set_fp6_native(int native) { g_fp6_native.store(native ? 1 : 0); }
 NKB_API void nkb_release_caches(void) {
     cudaDeviceSynchronize();
     {

@@ -9,8 +9,9 @@
 //   warp 0      producer: TMA tiled loads of A (128-byte swizzle) and untiled bulk copies of the
 //               pre-swizzled B chunks into a multi-stage shared-memory ring (mbarrier full/empty pairs)
 //   warp 1      allocates TMEM and issues tcgen05.mma from one thread; accumulators live in TMEM,
-//               two of them, so the read-out of tile t overlaps the main loop of tile t+1
-//   warps 2..5  epilogue: tcgen05.ld of their 32-lane quarter, finalisation, global stores
+//               two of them, so reading one out overlaps the MMAs that fill the other
+//   warps 2..9  epilogue: tcgen05.ld of their 32-lane quarter and column half, f32/i32 summation of the
+//               accumulation spans in registers, finalisation, global stores
 #include "nkb_internal.h"
 #include "nkb_ptx.cuh"
 
@@ -21,7 +22,8 @@ namespace {
 constexpr int kBM = 128;          // rows of A per tile = TMEM lanes
 constexpr int kBKBytes = 128;     // bytes of depth per pipeline stage (one swizzle span)
 constexpr int kUmmaKBytes = 32;   // bytes of depth one tcgen05.mma consumes
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kGroupM = 8;        // tile rasterisation: walk 8 row-tiles before moving to the next column-tile
 
 struct GemmDev {
@@ -36,6 +38,7 @@ struct GemmDev {
     uint32_t tiles_m, tiles_n;
     uint32_t idesc;
     uint32_t int_mode;            // 0 float accumulators, 1 signed i32, 2 unsigned u32
+    uint32_t flush_kblocks;       // stages per accumulation span (see the MMA issuer)
     unsigned int *error_word;
 };
 
@@ -80,10 +83,11 @@ __device__ __forceinline__ float finalize(float dot, float a_norm, float b_norm)
 }
 
 template <int kKind, int kBN, int kStages, int kEpi>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __maxnreg__(200)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
     using Plan = SmemPlan<kBN, kStages>;
-    constexpr int kTmemCols = 2 * kBN;  // two accumulators
+    constexpr int kTmemCols = 2 * kBN;        // two accumulator buffers
+    constexpr int kColsPerThread = kBN / 2;   // each epilogue thread owns one row x half the tile's columns
     static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
 
     extern __shared__ uint8_t smem_raw[];
@@ -109,7 +113,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tmem_full_bar(a), 1);
-            mbar_init(tmem_empty_bar(a), 128);
+            mbar_init(tmem_empty_bar(a), kEpilogueWarps * 32);
         }
         fence_mbar_init();
     }
@@ -152,85 +156,105 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
+        // The depth is cut into spans of `flush_kblocks` stages. Each span accumulates in one of the two
+        // TMEM buffers and is handed to the epilogue warps, which add the spans up in registers with
+        // round-to-nearest f32 adds. The tensor cores truncate when they accumulate; short spans keep
+        // that error at the level of NumKong's own f32 kernels. Integer kinds use a single span.
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            uint32_t local = 0;
+            uint32_t seq = 0;  // spans issued so far, across tiles
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-                const uint32_t acc = local & 1u;
-                const uint32_t acc_phase = (local >> 1) & 1u;
-                if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, 2, p.error_word)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + acc * kBN;
-                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
+            for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
+                    const uint32_t buf = seq & 1u;
+                    const uint32_t buf_phase = (seq >> 1) & 1u;
+                    if (!mbar_wait(tmem_empty_bar(buf), buf_phase ^ 1u, 2, p.error_word)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t a_src = smem_base + stage * Plan::kStageBytes;
-                    const uint64_t a_desc = make_smem_desc_sw128(a_src);
-                    const uint64_t b_desc = make_smem_desc_sw128(a_src + Plan::kABytes);
+                    const uint32_t d_tmem = tmem_base + buf * kBN;
+                    const uint32_t kb1 = min(kb0 + p.flush_kblocks, p.kblocks);
+                    for (uint32_t kb = kb0; kb < kb1; ++kb) {
+                        if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        const uint32_t a_src = smem_base + stage * Plan::kStageBytes;
+                        const uint64_t a_desc = make_smem_desc_sw128(a_src);
+                        const uint64_t b_desc = make_smem_desc_sw128(a_src + Plan::kABytes);
 #pragma unroll
-                    for (int k = 0; k < kBKBytes / kUmmaKBytes; ++k) {
-                        // Stepping 32 bytes along depth inside the 128-byte swizzle span = +2 in the (addr >> 4) field.
-                        umma<kKind, 1>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb | (uint32_t)k) != 0u);
+                        for (int k = 0; k < kBKBytes / kUmmaKBytes; ++k) {
+                            // Stepping 32 bytes along depth inside the 128-byte swizzle span = +2 in the (addr >> 4) field.
+                            umma<kKind, 1>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, ((kb - kb0) | (uint32_t)k) != 0u);
+                        }
+                        umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
                     }
-                    umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (ok) umma_commit(tmem_full_bar(buf));
                 }
-                if (ok) umma_commit(tmem_full_bar(acc));
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
-        const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may read: 32*quarter .. +31
-        uint32_t local = 0;
+        // ------------------------------------------------------------ epilogue (warps 2..9)
+        const uint32_t quarter = warp & 3u;               // TMEM lanes this warp may read: 32*quarter .. +31
+        const uint32_t half = (uint32_t)(warp - 2) >> 2;  // which half of the tile's columns
+        uint32_t seq = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             uint32_t mt, nt;
             tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
-            const uint32_t acc = local & 1u;
-            const uint32_t acc_phase = (local >> 1) & 1u;
-            if (!mbar_wait(tmem_full_bar(acc), acc_phase, 4, p.error_word)) { ok = false; break; }
-            tc_fence_after_sync();
+            uint32_t acc[kColsPerThread];
+#pragma unroll
+            for (int j = 0; j < kColsPerThread; ++j) acc[j] = 0u;
+            for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
+                const uint32_t buf = seq & 1u;
+                const uint32_t buf_phase = (seq >> 1) & 1u;
+                if (!mbar_wait(tmem_full_bar(buf), buf_phase, 4, p.error_word)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < kColsPerThread / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if constexpr (kKind == kKindI8) acc[c * 32 + j] += v[j];
+                        else acc[c * 32 + j] = __float_as_uint(__uint_as_float(acc[c * 32 + j]) + __uint_as_float(v[j]));
+                    }
+                }
+                tc_fence_before_sync();
+                mbar_arrive(tmem_empty_bar(buf));
+            }
+            if (!ok) break;
             const uint32_t row = mt * kBM + quarter * 32u + lane;
-            const bool row_ok = row < p.m;
+            if (row >= p.m) continue;
             uint8_t *c_row = p.c + (uint64_t)row * p.c_stride;
             float a_norm = 0.0f;
-            if constexpr (kEpi != kEpiDot) a_norm = row_ok ? p.a_norms[row] : 0.0f;
-#pragma unroll 1
-            for (int chunk = 0; chunk < kBN / 32; ++chunk) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * kBN + chunk * 32, v);
-                tmem_ld_wait();
-                const uint32_t col0 = nt * kBN + chunk * 32;
-                if (col0 >= p.n) continue;  // uniform across the CTA
+            if constexpr (kEpi != kEpiDot) a_norm = p.a_norms[row];
+#pragma unroll
+            for (int c = 0; c < kColsPerThread / 32; ++c) {
+                const uint32_t col0 = nt * kBN + half * kColsPerThread + c * 32;
+                if (col0 >= p.n) break;
                 if constexpr (kEpi != kEpiDot) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        float dot = p.int_mode == 0 ? __uint_as_float(v[j])
-                                  : p.int_mode == 1 ? (float)(int32_t)v[j] : (float)v[j];
+                        const uint32_t raw = acc[c * 32 + j];
+                        float dot = p.int_mode == 0 ? __uint_as_float(raw) : p.int_mode == 1 ? (float)(int32_t)raw : (float)raw;
                         float b_norm = 0.0f;
                         if (col0 + j < p.n)
                             b_norm = p.int_mode == 0 ? __ldg(reinterpret_cast<const float *>(p.b_norms) + col0 + j)
                                                      : (float)__ldg(reinterpret_cast<const uint32_t *>(p.b_norms) + col0 + j);
-                        v[j] = __float_as_uint(finalize<kEpi>(dot, a_norm, b_norm));
+                        acc[c * 32 + j] = __float_as_uint(finalize<kEpi>(dot, a_norm, b_norm));
                     }
                 }
-                if (row_ok) {
-                    uint32_t *dst = reinterpret_cast<uint32_t *>(c_row) + col0;
-                    if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                uint32_t *dst = reinterpret_cast<uint32_t *>(c_row) + col0;
+                if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<uint4 *>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<uint4 *>(dst + j) = make_uint4(acc[c * 32 + j], acc[c * 32 + j + 1], acc[c * 32 + j + 2], acc[c * 32 + j + 3]);
+                } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.n) dst[j] = v[j];
-                    }
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.n) dst[j] = acc[c * 32 + j];
                 }
             }
-            tc_fence_before_sync();
-            mbar_arrive(tmem_empty_bar(acc));
         }
     }
 
@@ -255,8 +279,9 @@ bool kind_info(uint32_t dt, KindInfo &ki) {
     case kF16: ki = {kKindF16, 1, 0, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 0}; return true;
     case kE4M3: ki = {kKindF8F6F4, 1, 0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 0}; return true;
     case kE5M2: ki = {kKindF8F6F4, 1, 1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 0}; return true;
-    case kE2M3: ki = {kKindF8F6F4, 1, 3, CU_TENSOR_MAP_DATA_TYPE_UINT8, 0}; return true;
-    case kE3M2: ki = {kKindF8F6F4, 1, 4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 0}; return true;
+    // FP6 operands arrive already rewritten (see transform_piece): as e4m3 codes, or packed for the native formats.
+    case kE2M3: ki = {kKindF8F6F4, 1, fp6_native() ? 3u : 0u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 0}; return true;
+    case kE3M2: ki = {kKindF8F6F4, 1, fp6_native() ? 4u : 0u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 0}; return true;
     case kI8: ki = {kKindI8, 2, 1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1}; return true;
     case kU8: ki = {kKindI8, 2, 0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2}; return true;
     default: return false;
@@ -335,8 +360,8 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
 
     const uint32_t eb = dtype_bytes(args.dtype);
     int bn = 256;
-    if (args.variant == 1) bn = 256;
-    else if (args.variant == 2) bn = 128;
+    if ((args.variant & 0xff) == 1) bn = 256;
+    else if ((args.variant & 0xff) == 2) bn = 128;
     else {
         uint64_t tiles256 = ((args.m + kBM - 1) / kBM) * ((args.n + 255) / 256);
         if (args.n <= 128 || tiles256 < (uint64_t)device_sm_count()) bn = 128;
@@ -368,6 +393,10 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     dev.tiles_n = (uint32_t)((args.n + bn - 1) / bn);
     dev.idesc = make_idesc(ki.c_fmt, ki.ab_fmt, kBM, bn);
     dev.int_mode = ki.int_mode;
+    // Float kinds: spans of 8 stages (512 16-bit or 1024 8-bit values). Integers are exact: one span.
+    const uint32_t forced_flush = (uint32_t)args.variant >> 8;
+    dev.flush_kblocks = ki.kind == kKindI8 ? dev.kblocks : (forced_flush ? forced_flush : 8u);
+    if (dev.flush_kblocks == 0) dev.flush_kblocks = 1;
     dev.error_word = args.error_word;
 
     switch (ki.kind) {

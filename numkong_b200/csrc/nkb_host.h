@@ -29,6 +29,6 @@ const uint8_t *resident_blob(const void *blob, MemKind kind, uint32_t magic, uin
                              uint64_t depth, PackedHeader *header_out);
 void remember_blob(uint64_t nonce, uint64_t bytes, void *dev_ptr);
 const void *resident_matrix(const void *src, MemKind kind, uint64_t rows, uint64_t row_bytes, uint64_t stride,
-                            int slot, uint64_t *pitch_out);
+                            int slot, int piece_mode, uint64_t *pitch_out);
 
 } // namespace nkb

@@ -100,13 +100,25 @@ inline PackedGeometry packed_geometry(uint32_t dt, uint64_t rows, uint64_t depth
 cudaError_t launch_row_sumsq(uint32_t dt, const void *x, uint64_t rows, uint64_t depth, uint64_t stride_bytes,
                              void *out, bool as_f32, bool inverse, cudaStream_t stream);
 
+// Rewrites applied to each 16-byte piece of an FP6 operand on its way to the tensor cores.
+enum PieceMode : int { kPieceNone = 0, kPieceE2M3ToE4M3 = 1, kPieceE3M2ToE4M3 = 2, kPieceFp6Pack = 3 };
+// How FP6 operands are fed to tcgen05.mma: 0 = recoded to e4m3 (exact), 1 = native 6-bit operand formats.
+int fp6_native();
+inline int piece_mode_for(uint32_t dt) {
+    if (dt != kE2M3 && dt != kE3M2) return kPieceNone;
+    if (fp6_native()) return kPieceFp6Pack;
+    return dt == kE2M3 ? kPieceE2M3ToE4M3 : kPieceE3M2ToE4M3;
+}
+
 // Writes the pre-swizzled chunk grid (or padded row-major f32) of a packed blob.
 cudaError_t launch_pack_payload(uint32_t dt, const void *b, uint64_t rows, uint64_t depth, uint64_t stride_bytes,
-                                void *payload, uint64_t rows_padded, uint64_t depth_padded_bytes, cudaStream_t stream);
+                                void *payload, uint64_t rows_padded, uint64_t depth_padded_bytes, int piece_mode,
+                                cudaStream_t stream);
 
-// Copies a strided matrix into a 16-byte-aligned, 16-byte-pitched scratch copy (for TMA).
+// Copies a strided matrix into a 16-byte-aligned, 16-byte-pitched scratch copy (for TMA),
+// applying `piece_mode` to every 16-byte piece.
 cudaError_t launch_restride(const void *src, uint64_t rows, uint64_t row_bytes, uint64_t src_stride,
-                            void *dst, uint64_t dst_stride, cudaStream_t stream);
+                            void *dst, uint64_t dst_stride, int piece_mode, cudaStream_t stream);
 
 struct GemmArgs {
     uint32_t dtype;

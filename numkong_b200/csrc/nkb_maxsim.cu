@@ -1,0 +1,498 @@
+// MaxSim late interaction, fused: the query-token x document-token similarity tile lives only in
+// TMEM; the epilogue keeps a running (max, argmax) per query token and document, normalises the
+// winner, and adds the per-query sums. The full similarity matrix is never written to memory.
+//
+// Replaces NumKong's nk_maxsim_packed_<t> (include/numkong/maxsim.h:106-114). Semantics follow the
+// reference's tensor-engine back end (include/numkong/maxsim/sapphireamx.h:716-861): the argmax is
+// taken over the RAW dot with a strict comparison (first document token wins ties), only the winner
+// is normalised with the inverse norms stored at pack time, the angular is clamped at 0, and the sum
+// over query tokens is carried in f64.
+//
+// One kernel serves both the single (query, document) call of the reference API and the all-pairs
+// batch (many queries x many ragged documents packed back to back): a CTA owns one tile of 128 query
+// tokens and one contiguous run of whole documents, walks that run 256 document tokens at a time
+// with the same producer / MMA / epilogue warp roles as the packed GEMM, and adds each finished
+// (query, document) sum into the output with one atomic per warp.
+#include <cstdio>
+#include <cstring>
+#include "nkb_internal.h"
+#include "nkb_host.h"
+#include "nkb_ptx.cuh"
+#include "../../include/numkong_b200.h"
+
+namespace nkb {
+
+namespace {
+
+constexpr int kMsBM = 128;
+constexpr int kMsBN = 256;
+constexpr int kMsStages = 4;
+constexpr int kMsThreads = 192;
+constexpr int kMsABytes = kMsBM * 128;
+constexpr int kMsBBytes = kMsBN * 128;
+constexpr int kMsStageBytes = kMsABytes + kMsBBytes;
+constexpr int kMsBarrierOffset = kMsStages * kMsStageBytes;
+constexpr int kMsSmemTotal = kMsBarrierOffset + 256 + 1024;
+
+struct MaxsimDev {
+    const uint8_t *q_payload, *d_payload;
+    const float *q_inv, *d_inv;          // inverse norms per token
+    const uint64_t *q_offsets, *d_offsets;  // token offsets per query / document (device), length count+1
+    uint64_t n_queries, n_docs;
+    uint64_t q_tokens, d_tokens;
+    uint32_t kblocks;
+    uint32_t q_tiles, segments;
+    uint32_t idesc;
+    float *scores_f32;                   // batch: n_queries x n_docs
+    uint64_t score_stride;               // in floats
+    double *total_f64;                   // single pair: one accumulator
+    unsigned int *error_word;
+};
+
+// First index i in [0, n] with offsets[i] >= x (offsets ascending, offsets[n] = total).
+__device__ __forceinline__ uint64_t lower_bound_offsets(const uint64_t *offsets, uint64_t n, uint64_t x) {
+    uint64_t lo = 0, hi = n;
+    while (lo < hi) {
+        uint64_t mid = (lo + hi) >> 1;
+        if (offsets[mid] < x) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+template <int kKind>
+__global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p) {
+    constexpr int kTmemCols = 2 * kMsBN;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + kMsBarrierOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kMsStages + s); };
+    auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kMsStages + a); };
+    auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMsStages + 2 + a); };
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kMsBarrierOffset + 8 * (2 * kMsStages + 4));
+    volatile uint64_t *seg_slot = reinterpret_cast<volatile uint64_t *>(smem_gen + kMsBarrierOffset + 8 * (2 * kMsStages + 6));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t q_tile = blockIdx.x % p.q_tiles;
+    const uint32_t segment = blockIdx.x / p.q_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMsStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), 128); }
+        fence_mbar_init();
+        // This CTA's run of whole documents: documents whose first token falls in its share of the tokens.
+        uint64_t per_seg = (p.d_tokens + p.segments - 1) / p.segments;
+        uint64_t t0 = (uint64_t)segment * per_seg, t1 = t0 + per_seg;
+        uint64_t d0 = lower_bound_offsets(p.d_offsets, p.n_docs, t0);
+        uint64_t d1 = (segment + 1 == p.segments) ? p.n_docs : lower_bound_offsets(p.d_offsets, p.n_docs, t1);
+        seg_slot[0] = d0;
+        seg_slot[1] = d1;
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint64_t doc_begin = seg_slot[0], doc_end = seg_slot[1];
+    const bool has_work = doc_begin < doc_end;
+    const uint64_t tok_begin = has_work ? p.d_offsets[doc_begin] : 0;
+    const uint64_t tok_end = has_work ? p.d_offsets[doc_end] : 0;
+    const uint64_t tile_begin = tok_begin / kMsBN;
+    const uint64_t tile_end = has_work ? (tok_end + kMsBN - 1) / kMsBN : tile_begin;  // empty documents only -> no tiles
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            const uint8_t *a_tile = p.q_payload + (uint64_t)q_tile * p.kblocks * kChunkBytes;
+            for (uint64_t t = tile_begin; t < tile_end && ok; ++t) {
+                const uint8_t *b_tile = p.d_payload + t * (kMsBN / kChunkRows) * p.kblocks * kChunkBytes;
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
+                    uint32_t a_dst = smem_base + stage * kMsStageBytes;
+                    mbar_expect_tx(full_bar(stage), kMsStageBytes);
+                    bulk_load(a_dst, a_tile + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
+#pragma unroll
+                    for (int j = 0; j < kMsBN / (int)kChunkRows; ++j)
+                        bulk_load(a_dst + kMsABytes + j * kChunkBytes, b_tile + ((uint64_t)j * p.kblocks + kb) * kChunkBytes,
+                                  kChunkBytes, full_bar(stage));
+                    if (++stage == kMsStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0, local = 0;
+            bool ok = true;
+            for (uint64_t t = tile_begin; t < tile_end && ok; ++t, ++local) {
+                const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
+                if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, 2, p.error_word)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kMsBN;
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_src = smem_base + stage * kMsStageBytes;
+                    const uint64_t a_desc = make_smem_desc_sw128(a_src);
+                    const uint64_t b_desc = make_smem_desc_sw128(a_src + kMsABytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma<kKind, 1>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb | (uint32_t)k) != 0u);
+                    umma_commit(empty_bar(stage));
+                    if (++stage == kMsStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(tmem_full_bar(acc));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue: one query token per thread
+        const uint32_t quarter = warp & 3u;
+        const uint64_t row = (uint64_t)q_tile * kMsBM + quarter * 32u + lane;
+        const bool row_ok = row < p.q_tokens;
+        const float q_inv = row_ok ? p.q_inv[row] : 0.0f;
+        // Query this token belongs to (-1 for padding rows).
+        long long qid = -1;
+        if (row_ok) qid = (long long)lower_bound_offsets(p.q_offsets, p.n_queries, row + 1) - 1;
+        const long long qid_above = __shfl_up_sync(0xffffffffu, qid, 1);
+        const bool segment_head = qid >= 0 && (lane == 0 || qid_above != qid);
+
+        uint64_t cur_doc = doc_begin;
+        uint64_t cur_end = has_work ? p.d_offsets[cur_doc + 1] : 0;
+        float run = -3.402823466e+38f;
+        uint32_t arg = 0;
+
+        // Closes the current document: normalise the winner, add up the angulars of each query's tokens.
+        auto finish_doc = [&]() {
+            float angular = 0.0f;
+            if (row_ok) {
+                float cosine = run * q_inv * __ldg(p.d_inv + arg);
+                angular = 1.0f - cosine;
+                if (!(angular > 0.0f)) angular = angular < 0.0f ? 0.0f : angular;  // clamp, keep NaN
+            }
+            double sum = (double)angular;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                double other = __shfl_down_sync(0xffffffffu, sum, off);
+                long long other_q = __shfl_down_sync(0xffffffffu, qid, off);
+                if (lane + off < 32 && other_q == qid) sum += other;
+            }
+            if (segment_head) {
+                if (p.total_f64) atomicAdd(p.total_f64, sum);
+                else atomicAdd(p.scores_f32 + (uint64_t)qid * p.score_stride + cur_doc, (float)sum);
+            }
+            run = -3.402823466e+38f;
+            arg = 0;
+        };
+
+        uint32_t local = 0;
+        bool ok = true;
+        for (uint64_t t = tile_begin; t < tile_end && ok; ++t, ++local) {
+            const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
+            if (!mbar_wait(tmem_full_bar(acc), acc_phase, 4, p.error_word)) { ok = false; break; }
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int chunk = 0; chunk < kMsBN / 32; ++chunk) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * kMsBN + chunk * 32, v);
+                tmem_ld_wait();
+                const uint64_t col0 = t * kMsBN + (uint64_t)chunk * 32;
+                if (col0 + 32 <= tok_begin || col0 >= tok_end) continue;
+                if (col0 >= tok_begin && col0 + 32 <= cur_end) {
+                    // The whole chunk lies inside the current document.
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x = __uint_as_float(v[j]);
+                        if (x > run) { run = x; arg = (uint32_t)(col0 + j); }
+                    }
+                } else {
+#pragma unroll 1
+                    for (int j = 0; j < 32; ++j) {
+                        const uint64_t col = col0 + j;
+                        if (col < tok_begin) continue;
+                        if (col >= tok_end) break;
+                        while (col >= cur_end) {  // document boundaries are the same for every thread
+                            finish_doc();
+                            ++cur_doc;
+                            cur_end = p.d_offsets[cur_doc + 1];
+                        }
+                        float x = __uint_as_float(v[j]);
+                        if (x > run) { run = x; arg = (uint32_t)col; }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(tmem_empty_bar(acc));
+        }
+        // Close the documents that are still open (the last one, and empty ones at the end of the run).
+        if (ok && has_work) {
+            while (cur_doc < doc_end) {
+                finish_doc();
+                ++cur_doc;
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// f32 inputs: CUDA cores, f64 dots (include/numkong/maxsim/serial.h:426-459 keeps dot, cosine and
+// angular in f64). One warp per query token; lanes split the depth.
+__global__ void maxsim_f32_kernel(const float *__restrict__ q, const float *__restrict__ d, uint64_t q_stride_elems,
+                                  uint64_t d_stride_elems, const float *__restrict__ q_inv, const float *__restrict__ d_inv,
+                                  uint64_t nq, uint64_t nd, uint64_t depth, double *total) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t warps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+    for (uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < nq; i += warps) {
+        const float *x = q + i * q_stride_elems;
+        double run = -1.7976931348623157e308;
+        uint64_t arg = 0;
+        for (uint64_t j = 0; j < nd; ++j) {
+            const float *y = d + j * d_stride_elems;
+            double s = 0.0;
+            for (uint64_t l = lane; l < depth; l += 32) s = fma((double)x[l], (double)y[l], s);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+            if (s > run) { run = s; arg = j; }
+        }
+        if (lane == 0) {
+            double angular = 1.0 - run * (double)q_inv[i] * (double)d_inv[arg];
+            if (angular < 0.0) angular = 0.0;
+            atomicAdd(total, angular);
+        }
+    }
+}
+
+__global__ void iota_offsets_kernel(uint64_t *out, uint64_t a, uint64_t b) { out[0] = a; out[1] = b; }
+
+cudaError_t launch_maxsim_tc(uint32_t dt, const MaxsimDev &dev_in, cudaStream_t stream) {
+    MaxsimDev dev = dev_in;
+    dev.idesc = make_idesc(1, dt == kBF16 ? 1 : 0, kMsBM, kMsBN);
+    static bool configured[64] = {false};
+    int d = 0;
+    cudaGetDevice(&d);
+    if (d >= 0 && d < 64 && !configured[d]) {
+        cudaError_t e = cudaFuncSetAttribute(maxsim_kernel<kKindF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMsSmemTotal);
+        if (e != cudaSuccess) return e;
+        configured[d] = true;
+    }
+    uint64_t grid = (uint64_t)dev.q_tiles * dev.segments;
+    if (grid == 0 || grid > 0x7fffffffull) return cudaErrorInvalidValue;
+    maxsim_kernel<kKindF16><<<(unsigned)grid, kMsThreads, kMsSmemTotal, stream>>>(dev);
+    return cudaGetLastError();
+}
+
+uint32_t pick_segments(uint64_t d_tokens, uint32_t q_tiles) {
+    // Runs of about 32 document tiles per CTA, but at least two CTAs per SM when the work allows it.
+    uint64_t tiles = (d_tokens + kMsBN - 1) / kMsBN;
+    uint64_t seg = (tiles + 31) / 32;
+    const uint64_t min_ctas = 2 * 148;
+    if ((uint64_t)q_tiles * seg < min_ctas) {
+        uint64_t want = (min_ctas + q_tiles - 1) / q_tiles;
+        seg = want < tiles ? want : tiles;
+    }
+    if (seg < 1) seg = 1;
+    if (seg > 0x7fffffull) seg = 0x7fffffull;
+    return (uint32_t)seg;
+}
+
+uint64_t maxsim_size_impl(uint32_t dt, uint64_t count, uint64_t depth) {
+    if (dt != kBF16 && dt != kF16 && dt != kF32) return 0;
+    return packed_geometry(dt, count, depth).total_bytes;
+}
+
+} // namespace
+
+// Shared with the dots blobs: same header, chunk grid and kernels; the norm slot holds 1/|v| as f32.
+void maxsim_pack_impl(uint32_t dt, const void *vectors, uint64_t count, uint64_t depth, uint64_t stride, void *packed);
+
+namespace {
+
+void maxsim_single_impl(uint32_t dt, const void *q_packed, const void *d_packed, uint64_t nq, uint64_t nd, uint64_t depth,
+                        void *result) {
+    clear_error();
+    const bool wide = dt == kF32;
+    auto fail = [&]() { if (result) std::memset(result, 0xFF, wide ? 8 : 4); };
+    if (!result) { set_error("maxsim_packed: null result%s", ""); return; }
+    const MemKind r_kind = classify(result);
+    auto write_result = [&](double v) {
+        float f = (float)v;
+        if (r_kind == kMemHost) { if (wide) std::memcpy(result, &v, 8); else std::memcpy(result, &f, 4); }
+        else cudaMemcpyAsync(result, wide ? (void *)&v : (void *)&f, wide ? 8 : 4, cudaMemcpyHostToDevice, current_stream());
+    };
+    if (dt != kBF16 && dt != kF16 && dt != kF32) { set_error("maxsim_packed: unsupported element type%s", ""); fail(); return; }
+    if (!q_packed || !d_packed) { set_error("maxsim_packed: null packed operand%s", ""); fail(); return; }
+    if (nq == 0) { write_result(0.0); return; }
+    if (nd == 0) { set_error("maxsim_packed: a document needs at least one vector%s", ""); fail(); return; }
+    cudaStream_t stream = current_stream();
+    PackedHeader qh, dh;
+    const uint8_t *qb = resident_blob(q_packed, classify(q_packed), kMagicMaxsim, dt, nq, depth, &qh);
+    if (!qb) { fail(); return; }
+    const uint8_t *db = resident_blob(d_packed, classify(d_packed), kMagicMaxsim, dt, nd, depth, &dh);
+    if (!db) { fail(); return; }
+    unsigned int *err = device_error_word();
+    double *total = static_cast<double *>(scratch(kSlotAux, 64));
+    if (!err || !total) { set_error("maxsim_packed: could not allocate device scratch%s", ""); fail(); return; }
+    bool ok = cuda_ok(cudaMemsetAsync(total, 0, 8, stream), "clear accumulator");
+    if (ok && dt == kF32) {
+        int blocks = (int)((nq * 32 + 255) / 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        maxsim_f32_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float *>(qb + qh.payload_offset),
+                                                      reinterpret_cast<const float *>(db + dh.payload_offset),
+                                                      qh.depth_padded_bytes / 4, dh.depth_padded_bytes / 4,
+                                                      reinterpret_cast<const float *>(qb + qh.norms_offset),
+                                                      reinterpret_cast<const float *>(db + dh.norms_offset), nq, nd, depth, total);
+        ok = cuda_ok(cudaGetLastError(), "f32 MaxSim kernel");
+        g_launches++;
+    } else if (ok) {
+        uint64_t *offsets = reinterpret_cast<uint64_t *>(total + 1);  // [0,nq] and [0,nd], same scratch slot
+        iota_offsets_kernel<<<1, 1, 0, stream>>>(offsets, 0, nq);
+        iota_offsets_kernel<<<1, 1, 0, stream>>>(offsets + 2, 0, nd);
+        g_launches += 2;
+        MaxsimDev dev{};
+        dev.q_payload = qb + qh.payload_offset; dev.d_payload = db + dh.payload_offset;
+        dev.q_inv = reinterpret_cast<const float *>(qb + qh.norms_offset);
+        dev.d_inv = reinterpret_cast<const float *>(db + dh.norms_offset);
+        dev.q_offsets = offsets; dev.d_offsets = offsets + 2;
+        dev.n_queries = 1; dev.n_docs = 1; dev.q_tokens = nq; dev.d_tokens = nd;
+        dev.kblocks = (uint32_t)(qh.depth_padded_bytes / kChunkRowBytes);
+        dev.q_tiles = (uint32_t)((nq + kMsBM - 1) / kMsBM);
+        dev.segments = 1;  // one document: its tokens cannot be split across CTAs
+        dev.scores_f32 = nullptr; dev.score_stride = 0; dev.total_f64 = total; dev.error_word = err;
+        ok = cuda_ok(launch_maxsim_tc(dt, dev, stream), "MaxSim kernel");
+        g_launches++;
+    }
+    double host_total = 0.0;
+    if (ok) ok = cuda_ok(cudaMemcpyAsync(&host_total, total, 8, cudaMemcpyDeviceToHost, stream), "read accumulator");
+    if (ok) ok = cuda_ok(cudaStreamSynchronize(stream), "maxsim_packed");
+    if (ok) {
+        uint32_t w = read_device_error();
+        if (w) { char buf[64]; std::snprintf(buf, sizeof buf, "0x%08x", w); set_error("a pipeline wait inside the MaxSim kernel gave up (error word %s)", buf); ok = false; }
+    }
+    if (!ok) { fail(); return; }
+    write_result(host_total);
+}
+
+void maxsims_batch_impl(uint32_t dt, const void *q_packed, const void *q_offsets, uint64_t n_queries, const void *d_packed,
+                        const void *d_offsets, uint64_t n_docs, uint64_t depth, void *scores, uint64_t score_stride) {
+    clear_error();
+    if (n_queries == 0 || n_docs == 0) return;
+    const MemKind s_kind = classify(scores);
+    const uint64_t row_bytes = n_docs * 4;
+    auto fail = [&]() { fill_error_output(scores, s_kind, n_queries, row_bytes, score_stride < row_bytes ? row_bytes : score_stride); };
+    if ((dt != kBF16 && dt != kF16) || !q_packed || !d_packed || !q_offsets || !d_offsets || !scores) {
+        set_error("maxsims_packed: unsupported element type or null pointer%s", ""); fail(); return;
+    }
+    if (score_stride % 4 || (n_queries > 1 && score_stride < row_bytes)) { set_error("maxsims_packed: bad score stride%s", ""); fail(); return; }
+    cudaStream_t stream = current_stream();
+    // Offsets: bring to the device when they are host arrays; the totals are needed on the host.
+    uint64_t totals[2] = {0, 0};
+    const uint64_t *q_off_dev = nullptr, *d_off_dev = nullptr;
+    const void *srcs[2] = {q_offsets, d_offsets};
+    const uint64_t counts[2] = {n_queries, n_docs};
+    const int slots[2] = {kSlotAux, kSlotAux2};
+    bool ok = true;
+    for (int s = 0; s < 2 && ok; ++s) {
+        MemKind kind = classify(srcs[s]);
+        const uint64_t *dev_ptr;
+        if (kind == kMemHost) {
+            totals[s] = static_cast<const uint64_t *>(srcs[s])[counts[s]];
+            void *buf = scratch(slots[s], (counts[s] + 1) * 8);
+            ok = buf && cuda_ok(cudaMemcpyAsync(buf, srcs[s], (counts[s] + 1) * 8, cudaMemcpyHostToDevice, stream), "upload offsets");
+            dev_ptr = static_cast<const uint64_t *>(buf);
+        } else {
+            ok = cuda_ok(cudaMemcpyAsync(&totals[s], static_cast<const uint64_t *>(srcs[s]) + counts[s], 8, cudaMemcpyDeviceToHost, stream), "read offsets") &&
+                 cuda_ok(cudaStreamSynchronize(stream), "read offsets");
+            dev_ptr = static_cast<const uint64_t *>(srcs[s]);
+        }
+        if (s == 0) q_off_dev = dev_ptr; else d_off_dev = dev_ptr;
+    }
+    if (!ok) { fail(); return; }
+    const uint64_t q_tokens = totals[0], d_tokens = totals[1];
+    PackedHeader qh, dh;
+    const uint8_t *qb = resident_blob(q_packed, classify(q_packed), kMagicMaxsim, dt, q_tokens, depth, &qh);
+    if (!qb) { fail(); return; }
+    const uint8_t *db = resident_blob(d_packed, classify(d_packed), kMagicMaxsim, dt, d_tokens, depth, &dh);
+    if (!db) { fail(); return; }
+    unsigned int *err = device_error_word();
+    if (!err) { set_error("maxsims_packed: could not allocate the device error word%s", ""); fail(); return; }
+
+    float *s_dev = static_cast<float *>(scores);
+    uint64_t s_pitch = score_stride;
+    if (s_kind == kMemHost) {
+        s_pitch = row_bytes;
+        s_dev = static_cast<float *>(scratch(kSlotC, n_queries * row_bytes));
+        if (!s_dev) { fail(); return; }
+    }
+    ok = cuda_ok(cudaMemset2DAsync(s_dev, s_pitch, 0, row_bytes, n_queries, stream), "clear scores");
+    if (ok && q_tokens && d_tokens) {
+        MaxsimDev dev{};
+        dev.q_payload = qb + qh.payload_offset; dev.d_payload = db + dh.payload_offset;
+        dev.q_inv = reinterpret_cast<const float *>(qb + qh.norms_offset);
+        dev.d_inv = reinterpret_cast<const float *>(db + dh.norms_offset);
+        dev.q_offsets = q_off_dev; dev.d_offsets = d_off_dev;
+        dev.n_queries = n_queries; dev.n_docs = n_docs; dev.q_tokens = q_tokens; dev.d_tokens = d_tokens;
+        dev.kblocks = (uint32_t)(qh.depth_padded_bytes / kChunkRowBytes);
+        dev.q_tiles = (uint32_t)((q_tokens + kMsBM - 1) / kMsBM);
+        dev.segments = pick_segments(d_tokens, dev.q_tiles);
+        dev.scores_f32 = s_dev; dev.score_stride = s_pitch / 4; dev.total_f64 = nullptr; dev.error_word = err;
+        ok = cuda_ok(launch_maxsim_tc(dt, dev, stream), "MaxSim kernel");
+        g_launches++;
+    }
+    if (ok && s_kind == kMemHost)
+        ok = cuda_ok(cudaMemcpy2DAsync(scores, score_stride < row_bytes ? row_bytes : score_stride, s_dev, s_pitch, row_bytes, n_queries,
+                                       cudaMemcpyDeviceToHost, stream), "download scores");
+    const bool must_sync = s_kind == kMemHost || classify(q_packed) == kMemHost || classify(d_packed) == kMemHost ||
+                           classify(q_offsets) == kMemHost || classify(d_offsets) == kMemHost;
+    if (ok && must_sync) {
+        ok = cuda_ok(cudaStreamSynchronize(stream), "maxsims_packed");
+        if (ok) {
+            uint32_t w = read_device_error();
+            if (w) { char buf[64]; std::snprintf(buf, sizeof buf, "0x%08x", w); set_error("a pipeline wait inside the MaxSim kernel gave up (error word %s)", buf); ok = false; }
+        }
+    }
+    if (!ok) fail();
+}
+
+} // namespace
+} // namespace nkb
+
+using namespace nkb;
+
+extern "C" {
+
+#define NKB_DEFINE_MAXSIM_FAMILY(T, DT)                                                                                \
+    NKB_API nk_size_t nk_maxsim_packed_size_##T(nk_size_t count, nk_size_t depth) { return maxsim_size_impl(DT, count, depth); } \
+    NKB_API void nk_maxsim_pack_##T(void const *vectors, nk_size_t count, nk_size_t depth, nk_size_t stride, void *packed) { \
+        maxsim_pack_impl(DT, vectors, count, depth, stride, packed);                                                   \
+    }                                                                                                                  \
+    NKB_API void nk_maxsim_packed_##T(void const *q, void const *d, nk_size_t nq, nk_size_t nd, nk_size_t depth, void *result) { \
+        maxsim_single_impl(DT, q, d, nq, nd, depth, result);                                                           \
+    }
+
+NKB_DEFINE_MAXSIM_FAMILY(bf16, kBF16)
+NKB_DEFINE_MAXSIM_FAMILY(f16, kF16)
+NKB_DEFINE_MAXSIM_FAMILY(f32, kF32)
+
+NKB_API void nkb_maxsims_packed_bf16(void const *q_packed, void const *q_offsets, nk_size_t n_queries, void const *d_packed,
+                                     void const *d_offsets, nk_size_t n_docs, nk_size_t depth, void *scores, nk_size_t score_stride) {
+    maxsims_batch_impl(kBF16, q_packed, q_offsets, n_queries, d_packed, d_offsets, n_docs, depth, scores, score_stride);
+}
+NKB_API void nkb_maxsims_packed_f16(void const *q_packed, void const *q_offsets, nk_size_t n_queries, void const *d_packed,
+                                    void const *d_offsets, nk_size_t n_docs, nk_size_t depth, void *scores, nk_size_t score_stride) {
+    maxsims_batch_impl(kF16, q_packed, q_offsets, n_queries, d_packed, d_offsets, n_docs, depth, scores, score_stride);
+}
+
+} // extern "C"

@@ -16,17 +16,76 @@ namespace {
 
 // 16 bytes from a possibly unaligned, possibly short source. Bytes at and past `valid` read as zero.
 __device__ __forceinline__ uint4 load16_guarded(const uint8_t *src, int64_t valid) {
-    if (valid >= 16 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) return __ldg(reinterpret_cast<const uint4 *>(src));
+    if (valid >= 16 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) return *reinterpret_cast<const uint4 *>(src);
     uint32_t w[4] = {0, 0, 0, 0};
     if (valid > 16) valid = 16;
     for (int i = 0; i < valid; ++i) w[i >> 2] |= (uint32_t)src[i] << ((i & 3) * 8);
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// ---- FP6 operands -------------------------------------------------------------------------------
+// NumKong stores e2m3 / e3m2 one value per byte (0b00SEEMMM / 0b00SEEEMM, include/numkong/types.h:803-814).
+// tcgen05.mma kind::f8f6f4 does not read that layout, so every 16-byte piece (16 values) is rewritten on
+// its way to the tensor cores, in the packer for B and in a copy pass for A. Two rewrites exist:
+//   kPieceFp6ToE4M3  each value becomes the e4m3 code of exactly the same number (both 6-bit formats
+//                    embed in e4m3: at most 3 mantissa bits, exponents within range), MMA runs as e4m3;
+//   kPieceFp6Pack    the 16 six-bit codes are packed back to back into 12 bytes followed by 4 bytes of
+//                    padding (the 16-byte-aligned 6-bit operand layout), MMA runs with the native
+//                    e2m3 / e3m2 operand formats.
+// Zero codes map to zero either way, so zero padding commutes with the rewrite.
+__device__ __forceinline__ uint32_t e2m3_to_e4m3(uint32_t c) {
+    const uint32_t sign = (c & 0x20u) << 2, e = (c >> 3) & 3u, m = c & 7u;
+    if (e == 0) {
+        if (m == 0) return sign;
+        const uint32_t p = 31u - __clz(m);               // m/8 = 2^(p-3) * (m / 2^p)
+        return sign | ((p + 4u) << 3) | ((m << (3u - p)) & 7u);
+    }
+    return sign | ((e + 6u) << 3) | m;                   // (1 + m/8) * 2^(e-1)
+}
+__device__ __forceinline__ uint32_t e3m2_to_e4m3(uint32_t c) {
+    const uint32_t sign = (c & 0x20u) << 2, e = (c >> 2) & 7u, m = c & 3u;
+    if (e == 0) {
+        if (m == 0) return sign;
+        const uint32_t p = 31u - __clz(m);               // m/16 = 2^(p-4) * (m / 2^p)
+        return sign | ((p + 3u) << 3) | ((m << (3u - p)) & 7u);
+    }
+    return sign | ((e + 4u) << 3) | (m << 1);            // (1 + m/4) * 2^(e-3)
+}
+
+__device__ __forceinline__ uint4 transform_piece(uint4 v, int mode) {
+    if (mode == kPieceNone) return v;
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    if (mode == kPieceE2M3ToE4M3 || mode == kPieceE3M2ToE4M3) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t out = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                uint32_t c = (w[i] >> (8 * b)) & 0x3fu;
+                out |= (mode == kPieceE2M3ToE4M3 ? e2m3_to_e4m3(c) : e3m2_to_e4m3(c)) << (8 * b);
+            }
+            w[i] = out;
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    // kPieceFp6Pack: value i occupies bits [6i, 6i+6) of the first 96 bits.
+    unsigned long long lo = 0, hi = 0;  // lo: bits 0..63, hi: bits 64..95
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        unsigned long long c = (w[i >> 2] >> (8 * (i & 3))) & 0x3fu;
+        const int bit = 6 * i;
+        if (bit < 64) {
+            lo |= c << bit;
+            if (bit > 58) hi |= c >> (64 - bit);
+        } else hi |= c << (bit - 64);
+    }
+    return make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, 0u);
+}
+
 // One thread per 16-byte piece of the payload.
 template <bool kSwizzled>
 __global__ void pack_payload_kernel(const uint8_t *__restrict__ b, uint64_t rows, uint64_t row_bytes, uint64_t stride,
-                                    uint4 *__restrict__ payload, uint64_t pieces, uint32_t kblocks) {
+                                    uint4 *__restrict__ payload, uint64_t pieces, uint32_t kblocks, int piece_mode) {
     for (uint64_t o = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; o < pieces; o += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t row, byte_off;
         if constexpr (kSwizzled) {
@@ -46,19 +105,20 @@ __global__ void pack_payload_kernel(const uint8_t *__restrict__ b, uint64_t rows
         }
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < rows && byte_off < row_bytes) v = load16_guarded(b + row * stride + byte_off, (int64_t)(row_bytes - byte_off));
-        payload[o] = v;
+        payload[o] = transform_piece(v, piece_mode);
     }
 }
 
-__global__ void restride_kernel(const uint8_t *__restrict__ src, uint64_t rows, uint64_t row_bytes, uint64_t src_stride,
-                                uint4 *__restrict__ dst, uint64_t dst_pieces_per_row) {
+// `src` and `dst` may be the same buffer (in-place rewrite with equal pitches), hence no __restrict__.
+__global__ void restride_kernel(const uint8_t *src, uint64_t rows, uint64_t row_bytes, uint64_t src_stride,
+                                uint4 *dst, uint64_t dst_pieces_per_row, int piece_mode) {
     uint64_t total = rows * dst_pieces_per_row;
     for (uint64_t o = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; o < total; o += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t row = o / dst_pieces_per_row;
         uint64_t byte_off = (o % dst_pieces_per_row) * 16u;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (byte_off < row_bytes) v = load16_guarded(src + row * src_stride + byte_off, (int64_t)(row_bytes - byte_off));
-        dst[o] = v;
+        dst[o] = transform_piece(v, piece_mode);
     }
 }
 
@@ -125,7 +185,7 @@ __global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, u
                 } else if (out_mode == 1) static_cast<float *>(out)[row] = (float)(uint32_t)acc;
                 else static_cast<uint32_t *>(out)[row] = (uint32_t)acc;
             } else if constexpr (kDtype == kF32) {
-                if (inverse) static_cast<double *>(out)[row] = acc > 0.0 ? 1.0 / sqrt(acc) : 0.0;
+                if (inverse) static_cast<float *>(out)[row] = acc > 0.0 ? (float)(1.0 / sqrt(acc)) : 0.0f;  // MaxSim keeps f32 inverse norms
                 else static_cast<double *>(out)[row] = acc;
             } else {
                 float s = (float)acc;
@@ -163,7 +223,8 @@ cudaError_t launch_row_sumsq(uint32_t dt, const void *x, uint64_t rows, uint64_t
 }
 
 cudaError_t launch_pack_payload(uint32_t dt, const void *b, uint64_t rows, uint64_t depth, uint64_t stride_bytes,
-                                void *payload, uint64_t rows_padded, uint64_t depth_padded_bytes, cudaStream_t stream) {
+                                void *payload, uint64_t rows_padded, uint64_t depth_padded_bytes, int piece_mode,
+                                cudaStream_t stream) {
     const uint64_t pieces = rows_padded * depth_padded_bytes / 16;
     const uint32_t kblocks = (uint32_t)(depth_padded_bytes / kChunkRowBytes);
     const int block = 256;
@@ -171,21 +232,21 @@ cudaError_t launch_pack_payload(uint32_t dt, const void *b, uint64_t rows, uint6
     const uint64_t row_bytes = depth * dtype_bytes(dt);
     if (dt == kF32)
         pack_payload_kernel<false><<<grid, block, 0, stream>>>(static_cast<const uint8_t *>(b), rows, row_bytes, stride_bytes,
-                                                               static_cast<uint4 *>(payload), pieces, kblocks);
+                                                               static_cast<uint4 *>(payload), pieces, kblocks, kPieceNone);
     else
         pack_payload_kernel<true><<<grid, block, 0, stream>>>(static_cast<const uint8_t *>(b), rows, row_bytes, stride_bytes,
-                                                              static_cast<uint4 *>(payload), pieces, kblocks);
+                                                              static_cast<uint4 *>(payload), pieces, kblocks, piece_mode);
     return cudaGetLastError();
 }
 
 cudaError_t launch_restride(const void *src, uint64_t rows, uint64_t row_bytes, uint64_t src_stride, void *dst,
-                            uint64_t dst_stride, cudaStream_t stream) {
+                            uint64_t dst_stride, int piece_mode, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
     const uint64_t per_row = dst_stride / 16;
     const int block = 256;
     const int grid = grid_for(rows * per_row, block, 148 * 32);
     restride_kernel<<<grid, block, 0, stream>>>(static_cast<const uint8_t *>(src), rows, row_bytes, src_stride,
-                                                static_cast<uint4 *>(dst), per_row);
+                                                static_cast<uint4 *>(dst), per_row, piece_mode);
     return cudaGetLastError();
 }
 

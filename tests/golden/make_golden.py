@@ -1,0 +1,57 @@
+"""Generates tests/golden/packed_path.npz from the REFERENCE ITSELF.
+
+Run in a container that has the NumKong source tree (default /root/reference):
+
+    make -C oracle ref            # compiles the reference's own sources into oracle/_ref/
+    python tests/golden/make_golden.py
+
+For every dtype of the packed-contraction path it draws seeded inputs (numkong_b200.synthetic), runs the
+reference's scalar back end (nk_*_serial, bit-reproducible) and its dispatched best back end on this CPU,
+and stores inputs and outputs. tests/test_oracle_pins.py then checks oracle/nk_oracle.c against these
+vectors anywhere, without the reference tree.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import oracle  # noqa: E402
+from numkong_b200 import synthetic as syn  # noqa: E402
+
+SHAPES = [(7, 5, 3), (33, 17, 65), (16, 24, 128), (5, 9, 1031)]
+DTYPES = ["i8", "u8", "bf16", "f16", "e4m3", "e5m2", "e2m3", "e3m2", "f32"]
+
+
+def main():
+    serial, dispatch = oracle.ref_serial(), oracle.ref()
+    if serial is None or dispatch is None:
+        raise SystemExit("compile the reference first: make -C oracle ref")
+    out = {}
+    for dt in DTYPES:
+        for si, (m, n, k) in enumerate(SHAPES):
+            kind_seed = 100 * DTYPES.index(dt) + si
+            if dt in ("e4m3", "e5m2", "e2m3", "e3m2") and si % 2:
+                a, b = syn.finite_codes_matrix(m, k, dt, kind_seed), syn.finite_codes_matrix(n, k, dt, kind_seed + 50)
+            else:
+                a, b = syn.normal_matrix(m, k, dt, kind_seed), syn.normal_matrix(n, k, dt, kind_seed + 50)
+            key = f"{dt}_{m}x{n}x{k}"
+            out[key + "_a"], out[key + "_b"] = a, b
+            for op in ("dots", "angulars", "euclideans"):
+                out[f"{key}_{op}_serial"] = getattr(serial, op)(a, b, dt)
+                out[f"{key}_{op}_dispatch"] = getattr(dispatch, op)(a, b, dt)
+    for dt in ("bf16", "f16", "f32"):
+        for si, (nq, nd, k) in enumerate([(32, 180, 128), (8, 64, 64), (5, 3, 17)]):
+            q, d = syn.normal_matrix(nq, k, dt, 900 + si), syn.normal_matrix(nd, k, dt, 950 + si)
+            key = f"maxsim_{dt}_{nq}x{nd}x{k}"
+            out[key + "_q"], out[key + "_d"] = q, d
+            out[key + "_serial"] = np.float64(serial.maxsim(q, d, dt))
+            out[key + "_dispatch"] = np.float64(dispatch.maxsim(q, d, dt))
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "packed_path.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main()

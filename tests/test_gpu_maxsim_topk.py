@@ -1,0 +1,114 @@
+"""Parity of the fused MaxSim kernel, its all-pairs batch form, and the top-k selection, against the CPU
+oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+import numkong_b200 as nk
+import oracle
+from tests._common import make_matrix
+from numkong_b200 import synthetic as syn
+
+pytestmark = pytest.mark.gpu
+
+# The reference's own back ends disagree with each other by more than this on MaxSim (serial vs fused:
+# ~0.5 %); against the oracle with the SAME semantics the sum of n_q angulars agrees to f32 rounding.
+MAXSIM_RTOL = 2e-5
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("shape", [(32, 180, 128), (8, 64, 64), (5, 3, 17), (1, 1, 1), (130, 257, 96), (256, 128, 1024), (32, 300, 128)])
+def test_maxsim_single_pair(dtype, shape):
+    nq, nd, k = shape
+    q, d = make_matrix(nq, k, dtype, 101), make_matrix(nd, k, dtype, 102)
+    got = nk.maxsim(q, d, dtype)
+    want = oracle.maxsim(q, d, dtype)
+    assert abs(got - want) <= MAXSIM_RTOL * max(1.0, abs(want))
+    assert got >= oracle.maxsim_exhaustive(q, d, dtype) - 1e-3
+
+
+def test_maxsim_of_identical_sides_is_zero():
+    """test/test_maxsim.py:169-175 of the reference."""
+    x = np.ones((8, 64), dtype=np.float32)
+    assert abs(nk.maxsim(x, x)) < 1e-5
+    xb = syn.encode(x, "bf16")
+    assert abs(nk.maxsim(xb, xb, "bf16")) < 1e-5
+
+
+def test_maxsim_ties_go_to_the_first_document_vector():
+    """Strict > on the raw dot: maxsim/serial.h:358-361, maxsim/sapphireamx.h:799-805."""
+    k = 32
+    q = syn.encode(np.ones((1, k), dtype=np.float32), "bf16")
+    d = np.ones((3, k), dtype=np.float32)
+    d[0, : k // 2] = 2.0        # dot 48, norm larger
+    d[1] = 1.5                  # dot 48 as well, but perfectly aligned with q (cosine 1)
+    d[2] = 0.5
+    db = syn.encode(d, "bf16")
+    got = nk.maxsim(q, db, "bf16")
+    want, best = oracle.maxsim(q, db, "bf16", want_best=True)
+    assert best[0] == 0
+    assert abs(got - want) < 1e-6 and got > 1e-3   # the first (worse-aligned) vector was kept
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_all_pairs_batch_matches_pairwise_calls(dtype):
+    rng = np.random.default_rng(7)
+    depth = 128
+    q_counts = [32, 32, 7, 40, 32]
+    d_counts = list(rng.integers(64, 301, size=23)) + [1, 256, 255, 257]
+    q_off = np.concatenate([[0], np.cumsum(q_counts)]).astype(np.int64)
+    d_off = np.concatenate([[0], np.cumsum(d_counts)]).astype(np.int64)
+    q_all = syn.normal_matrix(int(q_off[-1]), depth, dtype, 201, normalize=True)
+    d_all = syn.normal_matrix(int(d_off[-1]), depth, dtype, 202, normalize=True)
+    scores = nk.maxsims_packed(nk.maxsim_pack(q_all, dtype), q_off, nk.maxsim_pack(d_all, dtype), d_off)
+    assert scores.shape == (len(q_counts), len(d_counts))
+    for qi in range(len(q_counts)):
+        for di in range(len(d_counts)):
+            want = oracle.maxsim(q_all[q_off[qi]:q_off[qi + 1]], d_all[d_off[di]:d_off[di + 1]], dtype)
+            assert abs(scores[qi, di] - want) <= MAXSIM_RTOL * max(1.0, want), (qi, di)
+    # device-resident operands give the same matrix
+    import torch
+    store = np.int16
+    tq = nk.maxsim_pack(torch.from_numpy(q_all.view(store)).cuda(), dtype)
+    td = nk.maxsim_pack(torch.from_numpy(d_all.view(store)).cuda(), dtype)
+    dev = nk.maxsims_packed(tq, q_off, td, d_off)
+    assert nk.synchronize() == 0
+    assert np.allclose(dev.cpu().numpy(), scores, rtol=1e-6, atol=1e-6)
+
+
+def test_topk_smallest_matches_a_stable_sort():
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((37, 5000)).astype(np.float32)
+    x[3, :] = 1.0                      # all ties: lowest columns win
+    x[4, 100:200] = x[4, 0]            # ties in the middle
+    x[5, :7] = np.inf
+    for top in (1, 10, 100, 1000):
+        vals, ids = nk.topk_smallest(x, top, id_base=1000)
+        order = np.argsort(x, axis=1, kind="stable")[:, :top]
+        assert np.array_equal(ids - 1000, order)
+        assert np.array_equal(vals, np.take_along_axis(x, order, axis=1))
+    vals, ids = nk.topk_smallest(x[:, :5], 8)
+    assert np.all(ids[:, 5:] == -1) and np.all(np.isinf(vals[:, 5:]))
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("metric", ["angulars", "euclideans"])
+def test_distance_topk_equals_full_matrix_then_select(dtype, metric):
+    m, n, k, top = 70, 3000, 96, 10
+    a = syn.normal_matrix(m, k, dtype, 301, normalize=True)
+    b = syn.normal_matrix(n, k, dtype, 302, normalize=True)
+    p = nk.dots_pack(b, dtype)
+    full = getattr(nk, metric + "_packed")(a, p)
+    dist, ids = getattr(nk, metric + "_packed_topk")(a, p, top, id_base=5)
+    order = np.argsort(full, axis=1, kind="stable")[:, :top]
+    assert np.array_equal(ids - 5, order)
+    assert np.array_equal(dist, np.take_along_axis(full, order, axis=1))
+    # many narrow panels exercise the running merge
+    nk.lib.nkb_set_topk_panel_rows(512)
+    try:
+        dist2, ids2 = getattr(nk, metric + "_packed_topk")(a, p, top, id_base=5)
+    finally:
+        nk.lib.nkb_set_topk_panel_rows(0)
+    assert np.array_equal(ids2, ids) and np.array_equal(dist2, dist)
+    # and the distances themselves agree with the oracle
+    ref = getattr(oracle, metric)(a, b, dtype)
+    assert np.max(np.abs(dist - np.take_along_axis(ref, order, axis=1))) < 2e-6

@@ -1,0 +1,145 @@
+"""Pins the CPU oracle (oracle/nk_oracle.c) to the reference: against golden vectors produced by the
+reference's own kernels (tests/golden/packed_path.npz, generator committed beside it), against the
+known-answer tests of the reference's binding suites, and - when the reference has been compiled into
+oracle/_ref/ - against the reference itself on fresh seeded inputs. No GPU involved."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from numkong_b200 import synthetic as syn
+from tests._common import ALL_DTYPES, MINIFLOATS, make_matrix, ones_matrix
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "packed_path.npz"))
+GOLDEN_SHAPES = [(7, 5, 3), (33, 17, 65), (16, 24, 128), (5, 9, 1031)]
+
+
+def _bits_equal(x, y):
+    return x.shape == y.shape and np.array_equal(np.ascontiguousarray(x).view(np.uint8), np.ascontiguousarray(y).view(np.uint8))
+
+
+@pytest.mark.parametrize("dtype", ALL_DTYPES)
+@pytest.mark.parametrize("shape", GOLDEN_SHAPES)
+def test_oracle_matches_reference_serial_golden_bit_for_bit(dtype, shape):
+    m, n, k = shape
+    key = f"{dtype}_{m}x{n}x{k}"
+    a, b = GOLDEN[key + "_a"], GOLDEN[key + "_b"]
+    assert _bits_equal(oracle.dots(a, b, dtype), GOLDEN[key + "_dots_serial"])
+    assert _bits_equal(oracle.angulars(a, b, dtype), GOLDEN[key + "_angulars_serial"])
+    assert _bits_equal(oracle.euclideans(a, b, dtype), GOLDEN[key + "_euclideans_serial"])
+
+
+@pytest.mark.parametrize("dtype", ALL_DTYPES)
+def test_oracle_within_envelope_of_reference_dispatched_backend(dtype):
+    """The reference's SIMD/AMX back ends differ from its scalar one only by summation order."""
+    for (m, n, k) in GOLDEN_SHAPES:
+        key = f"{dtype}_{m}x{n}x{k}"
+        a, b = GOLDEN[key + "_a"], GOLDEN[key + "_b"]
+        got, ref = oracle.dots(a, b, dtype).astype(np.float64), GOLDEN[key + "_dots_dispatch"].astype(np.float64)
+        if dtype in ("i8", "u8"):
+            assert np.array_equal(got, ref)
+        else:
+            scale = np.abs(oracle.decode(a, dtype)).astype(np.float64) @ np.abs(oracle.decode(b, dtype)).astype(np.float64).T
+            assert np.max(np.abs(got - ref) / np.maximum(scale, 1e-30)) < 5e-7  # the spread between the reference's own back ends
+        assert np.nanmax(np.abs(oracle.angulars(a, b, dtype) - GOLDEN[key + "_angulars_dispatch"])) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+def test_maxsim_oracles_against_golden(dtype):
+    for (nq, nd, k) in [(32, 180, 128), (8, 64, 64), (5, 3, 17)]:
+        key = f"maxsim_{dtype}_{nq}x{nd}x{k}"
+        q, d = GOLDEN[key + "_q"], GOLDEN[key + "_d"]
+        serial, dispatch = float(GOLDEN[key + "_serial"]), float(GOLDEN[key + "_dispatch"])
+        # The scalar back end (i8 screening): winners are reproduced exactly, the sum to f32 rounding noise
+        # (the reference refines with a run-time dispatched dot).
+        assert abs(oracle.maxsim_coarse_i8(q, d, dtype) - serial) <= 2e-6 * max(1.0, abs(serial))
+        # Fused semantics (first argmax of the raw dot): never better than the exhaustive minimum beyond rounding.
+        fused, exhaustive = oracle.maxsim(q, d, dtype), oracle.maxsim_exhaustive(q, d, dtype)
+        assert fused >= exhaustive - 1e-4
+        if dtype == "bf16":
+            # The fixture was generated on a CPU whose dispatched bf16 MaxSim is the reference's fused
+            # tensor-engine back end (maxsim/sapphireamx.h:716-861): same winners, sum within f32 rounding.
+            assert abs(fused - dispatch) <= 2e-5 * max(1.0, abs(dispatch))
+
+
+@pytest.mark.parametrize("dtype", ALL_DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1, 1), (1, 8, 3), (3, 1, 7), (7, 5, 3), (33, 17, 65)])
+def test_all_ones_known_answers(dtype, shape):
+    """rust/matrix.rs:4610-4773 of the reference: all-ones inputs give dots == depth, distances == 0."""
+    h, w, k = shape
+    a, b = ones_matrix(h, k, dtype), ones_matrix(w, k, dtype)
+    assert np.all(oracle.dots(a, b, dtype) == k)
+    assert np.all(oracle.angulars(a, b, dtype) <= 2e-7)
+    assert np.all(oracle.euclideans(a, b, dtype) <= 1e-3 * np.sqrt(k) * 1e-3 + 1e-6)
+
+
+def test_tiny_integer_and_identity_known_answers():
+    """golang/unit_test.go:558-652 (2x3 integer matrices) and test/test.mjs:167-200 (identity-row B)."""
+    a = np.array([[1, 2, 3], [4, 5, 6]], dtype=np.int8)
+    b = np.array([[7, 8, 9], [10, 11, 12]], dtype=np.int8)
+    assert np.array_equal(oracle.dots(a, b, "i8"), np.array([[50, 68], [122, 167]], dtype=np.int32))
+    a = np.array([[1, 2, 3], [4, 5, 6], [7, 8, 9], [10, 11, 12]], dtype=np.float32)
+    b = np.array([[1, 0, 0], [0, 1, 0], [0, 0, 1], [1, 1, 0], [1, 1, 1]], dtype=np.float32)
+    expect = np.array([[1, 2, 3, 3, 6], [4, 5, 6, 9, 15], [7, 8, 9, 15, 24], [10, 11, 12, 21, 33]], dtype=np.float64)
+    assert np.array_equal(oracle.dots(a, b, "f32"), expect)
+
+
+def test_maxsim_of_identical_sides_is_zero():
+    """test/test_maxsim.py:169-175 of the reference."""
+    x = np.ones((8, 64), dtype=np.float32)
+    assert abs(oracle.maxsim(x, x, "f32")) < 1e-6
+    assert abs(oracle.maxsim_coarse_i8(x, x, "f32")) < 1e-6
+
+
+def test_zero_norm_rule_and_clamps():
+    """include/numkong/spatial/serial.h:261-267: zero norm product -> 0 if the dot is 0 else 1; results >= 0."""
+    a = np.zeros((2, 8), dtype=np.float32)
+    b = np.zeros((3, 8), dtype=np.float32)
+    b[1, 0] = 2.0
+    assert np.array_equal(oracle.angulars(a, b, "f32"), np.zeros((2, 3)))
+    assert np.array_equal(oracle.euclideans(a, b, "f32")[:, 1], np.array([2.0, 2.0]))
+    x = syn.normal_matrix(9, 33, "bf16", 3)
+    assert np.all(oracle.angulars(x, x, "bf16") >= 0)
+    assert np.all(np.diag(oracle.euclideans(x, x, "bf16")) < 1e-2)
+
+
+needs_ref = pytest.mark.skipif(oracle.ref_serial() is None or oracle.ref() is None,
+                               reason="reference not compiled (make -C oracle ref)")
+
+
+@needs_ref
+@pytest.mark.parametrize("dtype", ALL_DTYPES)
+def test_oracle_against_live_reference_on_fresh_inputs(dtype):
+    serial = oracle.ref_serial()
+    for seed, (m, n, k) in enumerate([(9, 11, 40), (4, 6, 515), (31, 8, 96)]):
+        kind = "codes" if dtype in MINIFLOATS and seed % 2 else "normal"
+        a, b = make_matrix(m, k, dtype, 7000 + seed, kind), make_matrix(n, k, dtype, 7100 + seed, kind)
+        assert _bits_equal(oracle.dots(a, b, dtype), serial.dots(a, b, dtype))
+        assert _bits_equal(oracle.angulars(a, b, dtype), serial.angulars(a, b, dtype))
+        assert _bits_equal(oracle.euclideans(a, b, dtype), serial.euclideans(a, b, dtype))
+
+
+@needs_ref
+def test_decoders_and_encoders_against_reference_cast():
+    import ctypes
+    ref = oracle.ref()
+    ref.lib.nk_cast.restype = None
+    ref.lib.nk_cast.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_int]
+    x = (np.random.default_rng(0).standard_normal(20000) * 4).astype(np.float32)
+    for dt in MINIFLOATS:
+        codes = np.arange(64 if dt in ("e2m3", "e3m2") else 256, dtype=np.uint8)
+        out = np.zeros(len(codes), dtype=np.float32)
+        ref.lib.nk_cast(codes.ctypes.data, oracle.CODES[dt], len(codes), out.ctypes.data, oracle.CODES["f32"])
+        mine = oracle.decode(codes.reshape(1, -1), dt).ravel()
+        assert np.array_equal(np.isnan(out), np.isnan(mine))
+        assert np.array_equal(out[~np.isnan(out)], mine[~np.isnan(mine)])
+        table = syn.minifloat_values(dt)[:len(codes)].astype(np.float32)
+        assert np.array_equal(np.nan_to_num(table, nan=-1.0), np.nan_to_num(out, nan=-1.0))
+        enc = np.zeros(len(x), dtype=np.uint8)
+        ref.lib.nk_cast(x.ctypes.data, oracle.CODES["f32"], len(x), enc.ctypes.data, oracle.CODES[dt])
+        assert np.array_equal(enc, syn.encode(x, dt))
+    for dt in ("bf16", "f16"):
+        enc = np.zeros(len(x), dtype=np.uint16)
+        ref.lib.nk_cast(x.ctypes.data, oracle.CODES["f32"], len(x), enc.ctypes.data, oracle.CODES[dt])
+        assert np.array_equal(enc, syn.encode(x, dt))
