@@ -211,8 +211,12 @@ def main():
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the per-dtype table and the CPU baseline")
+    ap.add_argument("--rows", type=int, default=8192,
+                    help="rows of A per GPU; anything but 8192 is a reduced case for profiler captures, not the benchmark")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
+    global M
+    M = args.rows
+    args.warmup = max(args.warmup, 3) if M == 8192 else args.warmup
     if args.impl == "reference":
         reference_arm(args)
         return

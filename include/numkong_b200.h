@@ -156,8 +156,8 @@ NKB_API uint32_t nkb_synchronize(void);
 NKB_API uint64_t nkb_launch_count(void);
 /** Forces a GEMM tile configuration for testing/tuning: 0 = choose by shape. */
 NKB_API void nkb_set_gemm_variant(int variant);
-/** How e2m3 / e3m2 operands reach the tensor cores: 0 (default) = recoded to the e4m3 code of the same value,
- *  1 = packed 6-bit operands with the native e2m3 / e3m2 MMA formats. Applies to later pack AND multiply calls;
+/** How e2m3 / e3m2 operands reach the tensor cores: 1 (default) = packed 6-bit operands with the native
+ *  e2m3 / e3m2 MMA formats, 0 = recoded to the e4m3 code of the same value (exact as well). Applies to later pack AND multiply calls;
  *  a blob packed under one setting must be multiplied under the same one. */
 NKB_API void nkb_set_fp6_native(int native);
 /** Packed rows handled per panel by the distance top-k (rounded up to 256); 0 = sized from the scratch budget. */

@@ -21,7 +21,7 @@ std::atomic<uint64_t> g_launches{0};
 namespace {
 
 std::atomic<int> g_variant{0};
-std::atomic<int> g_fp6_native{0};
+std::atomic<int> g_fp6_native{1};
 std::atomic<uint64_t> g_nonce_counter{0};
 
 // ---------------------------------------------------------------- per-thread context
@@ -35,6 +35,14 @@ struct ThreadCtx {
     cudaStream_t stream = nullptr;
     std::string error;
     Scratch slots[kScratchSlots];
+    // Row-pipelined host calls alternate between two private streams, each with its own set of staging buffers.
+    cudaStream_t pipe[2] = {nullptr, nullptr};
+    cudaEvent_t pipe_done[2] = {nullptr, nullptr};
+    cudaEvent_t fork = nullptr;
+    int pipe_device = -1;
+    int slot_set = 0;
+    cudaStream_t override_stream = nullptr;
+    bool use_override = false;
     ~ThreadCtx() {}  // device memory is reclaimed with the context at process exit
 };
 thread_local ThreadCtx t_ctx;
@@ -75,7 +83,7 @@ void set_error(const char *fmt, const char *detail) {
     t_ctx.error = buf;
 }
 void clear_error() { t_ctx.error.clear(); }
-cudaStream_t current_stream() { return t_ctx.stream; }
+cudaStream_t current_stream() { return t_ctx.use_override ? t_ctx.override_stream : t_ctx.stream; }
 int current_variant() { return g_variant.load(); }
 int fp6_native() { return g_fp6_native.load(); }
 
@@ -98,12 +106,12 @@ MemKind classify(const void *p) {
 }
 
 void *scratch(int slot, size_t bytes) {
-    Scratch &s = t_ctx.slots[slot];
+    Scratch &s = t_ctx.slots[slot + t_ctx.slot_set * kSlotsPerSet];
     int dev = 0;
     cudaGetDevice(&dev);
     if (s.ptr && s.device == dev && s.bytes >= bytes) return s.ptr;
     if (s.ptr) {
-        cudaStreamSynchronize(t_ctx.stream);
+        cudaDeviceSynchronize();  // earlier calls on any stream may still be using the old buffer
         cudaFree(s.ptr);
         s.ptr = nullptr; s.bytes = 0;
     }
@@ -221,15 +229,15 @@ const void *resident_matrix(const void *src, MemKind kind, uint64_t rows, uint64
     if (!dst) return nullptr;
     if (kind == kMemHost) {
         if (pitch != row_bytes) {
-            if (!cuda_ok(cudaMemsetAsync(dst, 0, rows * pitch, t_ctx.stream), "clear staging")) return nullptr;
+            if (!cuda_ok(cudaMemsetAsync(dst, 0, rows * pitch, current_stream()), "clear staging")) return nullptr;
         }
-        if (!cuda_ok(cudaMemcpy2DAsync(dst, pitch, src, stride, row_bytes, rows, cudaMemcpyHostToDevice, t_ctx.stream), "upload of input matrix")) return nullptr;
+        if (!cuda_ok(cudaMemcpy2DAsync(dst, pitch, src, stride, row_bytes, rows, cudaMemcpyHostToDevice, current_stream()), "upload of input matrix")) return nullptr;
         if (piece_mode != kPieceNone) {  // in place: every piece is read and written by the same thread
-            if (!cuda_ok(launch_restride(dst, rows, pitch, pitch, dst, pitch, piece_mode, t_ctx.stream), "operand rewrite kernel")) return nullptr;
+            if (!cuda_ok(launch_restride(dst, rows, pitch, pitch, dst, pitch, piece_mode, current_stream()), "operand rewrite kernel")) return nullptr;
             g_launches++;
         }
     } else {
-        if (!cuda_ok(launch_restride(src, rows, row_bytes, stride, dst, pitch, piece_mode, t_ctx.stream), "restride kernel")) return nullptr;
+        if (!cuda_ok(launch_restride(src, rows, row_bytes, stride, dst, pitch, piece_mode, current_stream()), "restride kernel")) return nullptr;
         g_launches++;
     }
     *pitch_out = pitch;
@@ -313,26 +321,27 @@ void pack_impl(uint32_t magic, uint32_t dt, const void *b, uint64_t rows, uint64
     }
 }
 
-void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed, void *c, uint64_t m, uint64_t n,
-                 uint64_t k, uint64_t a_stride, uint64_t c_stride) {
-    clear_error();
-    const uint32_t out_bytes = dot_out_bytes(dt);  // distances share the cell width of the dots
+bool ensure_pipe_streams() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (t_ctx.pipe[0] && t_ctx.pipe_device == dev) return true;
+    for (int s = 0; s < 2; ++s) {
+        if (cudaStreamCreateWithFlags(&t_ctx.pipe[s], cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); t_ctx.pipe[0] = nullptr; return false; }
+        if (cudaEventCreateWithFlags(&t_ctx.pipe_done[s], cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); t_ctx.pipe[0] = nullptr; return false; }
+    }
+    if (cudaEventCreateWithFlags(&t_ctx.fork, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); t_ctx.pipe[0] = nullptr; return false; }
+    t_ctx.pipe_device = dev;
+    return true;
+}
+
+// One packed call on `stream` without the final synchronisation: stages A and C as needed, launches the
+// kernels, copies C back. Returns false (error text set) on failure.
+bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const uint8_t *blob, const PackedHeader &h,
+                 unsigned int *err, void *c, MemKind c_kind, uint64_t m, uint64_t n, uint64_t k, uint64_t a_stride,
+                 uint64_t c_stride, cudaStream_t stream) {
+    const uint32_t out_bytes = dot_out_bytes(dt);
     const uint64_t c_row_bytes = n * out_bytes;
-    if (m == 0 || n == 0) return;
-    const MemKind c_kind = classify(c);
-    auto fail = [&]() { fill_error_output(c, c_kind, m, c_row_bytes, c_stride < c_row_bytes ? c_row_bytes : c_stride); };
-    if (!dtype_supported(dt) || !a || !b_packed || !c) { set_error("packed: unsupported element type or null pointer%s", ""); fail(); return; }
-    if (m > 1 && c_stride < c_row_bytes) { set_error("packed: c_stride is smaller than a row of the result%s", ""); fail(); return; }
-    if (c_stride % out_bytes) { set_error("packed: c_stride must be a multiple of the output cell size%s", ""); fail(); return; }
-    cudaStream_t stream = t_ctx.stream;
-    const MemKind a_kind = classify(a), b_kind = classify(b_packed);
-
-    PackedHeader h;
-    const uint8_t *blob = resident_blob(b_packed, b_kind, kMagicDots, dt, n, k, &h);
-    if (!blob) { fail(); return; }
-    unsigned int *err = device_error_word();
-    if (!err) { set_error("could not allocate the device error word%s", ""); fail(); return; }
-
+    auto fail = [&]() {};
     // Output: in place when it is device memory with 4-byte aligned rows, else a dense device copy.
     uint8_t *c_dev = static_cast<uint8_t *>(c);
     uint64_t c_pitch = c_stride;
@@ -340,7 +349,7 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
     if (!c_direct) {
         c_pitch = round_up(c_row_bytes, 16);
         c_dev = static_cast<uint8_t *>(scratch(kSlotC, m * c_pitch));
-        if (!c_dev) { fail(); return; }
+        if (!c_dev) return false;
     }
     bool ok = true;
     if (k == 0) {
@@ -350,7 +359,7 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
         uint64_t a_pitch = a_stride;
         if (a_kind == kMemHost || (reinterpret_cast<uintptr_t>(a) & 3u) || (a_stride & 3u)) {
             a_dev = resident_matrix(a, a_kind, m, k * 4, a_stride, kSlotA, kPieceNone, &a_pitch);
-            if (!a_dev) { fail(); return; }
+            if (!a_dev) return false;
         }
         double *a_norms = nullptr;
         if (epilogue != kEpiDot) {
@@ -374,11 +383,11 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
         float *a_norms = nullptr;
         if (epilogue != kEpiDot) {
             a_norms = static_cast<float *>(scratch(kSlotNorms, m * 4));
-            if (!a_norms) { fail(); return; }
+            if (!a_norms) return false;
         }
         if (piece_mode == kPieceNone) {
             a_dev = resident_matrix(a, a_kind, m, k * dtype_bytes(dt), a_stride, kSlotA, kPieceNone, &a_pitch);
-            if (!a_dev) { fail(); return; }
+            if (!a_dev) return false;
             if (a_norms) {
                 ok = cuda_ok(launch_row_sumsq(dt, a_dev, m, k, a_pitch, a_norms, true, false, stream), "row norm kernel");
                 g_launches++;
@@ -389,10 +398,10 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
                 g_launches++;
             }
             a_dev = resident_matrix(a, a_kind, m, k, a_stride, kSlotA, piece_mode, &a_pitch);
-            if (!a_dev) { fail(); return; }
+            if (!a_dev) return false;
         } else {
             a_dev = resident_matrix(a, a_kind, m, k, a_stride, kSlotA, kPieceNone, &a_pitch);
-            if (!a_dev) { fail(); return; }
+            if (!a_dev) return false;
             if (a_norms) {
                 ok = cuda_ok(launch_row_sumsq(dt, a_dev, m, k, a_pitch, a_norms, true, false, stream), "row norm kernel");
                 g_launches++;
@@ -414,6 +423,56 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
     if (ok && !c_direct) {
         cudaMemcpyKind kind = c_kind == kMemHost ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
         ok = cuda_ok(cudaMemcpy2DAsync(c, c_stride < c_row_bytes ? c_row_bytes : c_stride, c_dev, c_pitch, c_row_bytes, m, kind, stream), "download of result");
+    }
+    return ok;
+}
+
+void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed, void *c, uint64_t m, uint64_t n,
+                 uint64_t k, uint64_t a_stride, uint64_t c_stride) {
+    clear_error();
+    const uint32_t out_bytes = dot_out_bytes(dt);  // distances share the cell width of the dots
+    const uint64_t c_row_bytes = n * out_bytes;
+    if (m == 0 || n == 0) return;
+    const MemKind c_kind = classify(c);
+    auto fail = [&]() { fill_error_output(c, c_kind, m, c_row_bytes, c_stride < c_row_bytes ? c_row_bytes : c_stride); };
+    if (!dtype_supported(dt) || !a || !b_packed || !c) { set_error("packed: unsupported element type or null pointer%s", ""); fail(); return; }
+    if (m > 1 && c_stride < c_row_bytes) { set_error("packed: c_stride is smaller than a row of the result%s", ""); fail(); return; }
+    if (c_stride % out_bytes) { set_error("packed: c_stride must be a multiple of the output cell size%s", ""); fail(); return; }
+    cudaStream_t stream = t_ctx.stream;
+    const MemKind a_kind = classify(a), b_kind = classify(b_packed);
+
+    PackedHeader h;
+    const uint8_t *blob = resident_blob(b_packed, b_kind, kMagicDots, dt, n, k, &h);
+    if (!blob) { fail(); return; }
+    unsigned int *err = device_error_word();
+    if (!err) { set_error("could not allocate the device error word%s", ""); fail(); return; }
+
+    bool ok = true;
+    // Large host-to-host calls are cut into row blocks that alternate between two private streams, so the
+    // upload of one block, the kernels of another and the download of a third overlap.
+    constexpr uint64_t kPipeRows = 1024;
+    const bool pipelined = a_kind == kMemHost && c_kind == kMemHost && k > 0 && m >= 2 * kPipeRows && ensure_pipe_streams();
+    if (pipelined) {
+        ok = cuda_ok(cudaEventRecord(t_ctx.fork, stream), "pipeline fork");
+        for (int s = 0; s < 2 && ok; ++s) ok = cuda_ok(cudaStreamWaitEvent(t_ctx.pipe[s], t_ctx.fork, 0), "pipeline fork");
+        int block = 0;
+        for (uint64_t r0 = 0; r0 < m && ok; r0 += kPipeRows, ++block) {
+            const uint64_t rows = m - r0 < kPipeRows ? m - r0 : kPipeRows;
+            t_ctx.slot_set = block & 1;
+            t_ctx.use_override = true;
+            t_ctx.override_stream = t_ctx.pipe[block & 1];
+            ok = packed_core(dt, epilogue, static_cast<const uint8_t *>(a) + r0 * a_stride, a_kind, blob, h, err,
+                             static_cast<uint8_t *>(c) + r0 * c_stride, c_kind, rows, n, k, a_stride, c_stride, t_ctx.pipe[block & 1]);
+        }
+        t_ctx.slot_set = 0;
+        t_ctx.use_override = false;
+        for (int s = 0; s < 2; ++s) {
+            bool joined = cuda_ok(cudaEventRecord(t_ctx.pipe_done[s], t_ctx.pipe[s]), "pipeline join") &&
+                          cuda_ok(cudaStreamWaitEvent(stream, t_ctx.pipe_done[s], 0), "pipeline join");
+            ok = ok && joined;
+        }
+    } else {
+        ok = packed_core(dt, epilogue, a, a_kind, blob, h, err, c, c_kind, m, n, k, a_stride, c_stride, stream);
     }
     const bool must_sync = a_kind == kMemHost || b_kind == kMemHost || c_kind == kMemHost;
     if (ok && must_sync) {

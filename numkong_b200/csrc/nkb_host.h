@@ -8,7 +8,7 @@ namespace nkb {
 enum MemKind : int { kMemHost = 0, kMemDevice = 1 };
 
 // Per-thread staging buffers (grow-only device allocations).
-enum ScratchSlot : int { kSlotA = 0, kSlotC = 1, kSlotNorms = 2, kSlotAux = 3, kSlotAux2 = 4, kScratchSlots = 5 };
+enum ScratchSlot : int { kSlotA = 0, kSlotC = 1, kSlotNorms = 2, kSlotAux = 3, kSlotAux2 = 4, kSlotsPerSet = 5, kScratchSlots = 10 };
 
 extern std::atomic<uint64_t> g_launches;
 

@@ -213,18 +213,24 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                         if (x > run) { run = x; arg = (uint32_t)(col0 + j); }
                     }
                 } else {
-#pragma unroll 1
-                    for (int j = 0; j < 32; ++j) {
-                        const uint64_t col = col0 + j;
-                        if (col < tok_begin) continue;
-                        if (col >= tok_end) break;
-                        while (col >= cur_end) {  // document boundaries are the same for every thread
+                    // A document boundary (or an end of this CTA's run) falls inside the chunk. Walk it one
+                    // document piece at a time; every piece is a predicated pass over all 32 registers, so the
+                    // values never leave the register file. Boundaries are the same for every thread.
+                    uint32_t j0 = col0 < tok_begin ? (uint32_t)(tok_begin - col0) : 0u;
+                    const uint32_t j_stop = tok_end - col0 < 32 ? (uint32_t)(tok_end - col0) : 32u;
+                    while (j0 < j_stop) {
+                        while (col0 + j0 >= cur_end) {
                             finish_doc();
                             ++cur_doc;
                             cur_end = p.d_offsets[cur_doc + 1];
                         }
-                        float x = __uint_as_float(v[j]);
-                        if (x > run) { run = x; arg = (uint32_t)col; }
+                        const uint32_t j1 = cur_end - col0 < j_stop ? (uint32_t)(cur_end - col0) : j_stop;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float x = __uint_as_float(v[j]);
+                            if ((uint32_t)j >= j0 && (uint32_t)j < j1 && x > run) { run = x; arg = (uint32_t)(col0 + j); }
+                        }
+                        j0 = j1;
                     }
                 }
             }

@@ -35,7 +35,7 @@ def test_dots_packed_host_buffers(dtype, shape):
     assert c.dtype == oracle.out_dtype(dtype)
     _check_dots(c, a, b, dtype)
     # out= path equals the allocating path (test/test_cross.py:306-310 of the reference)
-    out = np.full_like(c, -7)
+    out = np.full_like(c, 7)
     assert nk.dots_packed(a, packed, out=out) is out
     assert np.array_equal(out.view(np.uint8), c.view(np.uint8))
 
