@@ -145,6 +145,29 @@ NKB_DECLARE_MAXSIMS_FAMILY(f16)
 NKB_API void nkb_topk_smallest_f32(void const *scores, nk_size_t rows, nk_size_t cols, nk_size_t stride, nk_size_t top,
                                    nk_size_t id_base, void *out_values, void *out_ids);
 
+/* ---- batched angular distances without any device allocation -----------------------------------
+ * No counterpart in the reference (which never allocates because it runs on the caller's CPU buffers).
+ *
+ * Same result as nk_angulars_packed_<t>, for callers that must not trigger cudaMalloc: code inside a stream
+ * capture, latency-critical serving loops, hosts whose pool allocator owns the whole device heap. The scratch the
+ * regular path allocates (one f32 squared norm per row of A, plus the error word of the pipeline waits) lives in
+ * fixed device arrays inside this library instead: 256 KiB + 256 B per GPU, held from library load to process exit.
+ *
+ *  - `dtype` is one of NKB_DTYPE_{BF16,F16,E4M3,E5M2,I8,U8}; c receives height x width f32.
+ *  - height <= NKB_NOALLOC_MAX_ROWS; larger calls are refused (split them by rows of A).
+ *  - a, b_packed and c must be device or managed memory; a and b_packed 16-byte aligned, a_stride a multiple of 16
+ *    (nothing can be staged or re-strided without allocating).
+ *  - Returns 0 when the work was enqueued on the calling thread's stream, a non-zero code (and nkb_last_error())
+ *    when the call was refused; nothing is written to c in that case.
+ *  - The first call on each GPU looks up the device addresses of the fixed arrays and clears the error word with a
+ *    synchronous memset; make that first call (any small problem) before starting a stream capture.
+ *  - All calls on one GPU share the fixed arrays: the norms are rewritten by every call, so two calls that overlap
+ *    on the GPU (different streams or threads) race; run them in stream order.
+ */
+#define NKB_NOALLOC_MAX_ROWS 65536
+NKB_API int nkb_angulars_packed_noalloc(uint32_t dtype, void const *a, void const *b_packed, void *c, nk_size_t height,
+                                        nk_size_t width, nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride);
+
 /* ---- additions (no counterpart in the reference) -------------------------------------------- */
 /** Last error of the calling thread, "" when the last call succeeded. The string stays valid until the next call. */
 NKB_API char const *nkb_last_error(void);
