@@ -5,13 +5,14 @@
 // AMX form include/numkong/dots/sapphireamx.h:981-) and the second pass of
 // nk_angulars_packed_<t> / nk_euclideans_packed_<t> (include/numkong/dots/serial.h:2756-2800).
 //
-// One persistent CTA per SM, six warps:
+// One persistent CTA per SM, ten warps:
 //   warp 0      producer: TMA tiled loads of A (128-byte swizzle) and untiled bulk copies of the
 //               pre-swizzled B chunks into a multi-stage shared-memory ring (mbarrier full/empty pairs)
 //   warp 1      allocates TMEM and issues tcgen05.mma from one thread; accumulators live in TMEM,
 //               two of them, so reading one out overlaps the MMAs that fill the other
 //   warps 2..9  epilogue: tcgen05.ld of their 32-lane quarter and column half, f32/i32 summation of the
 //               accumulation spans in registers, finalisation, global stores
+#include <cmath>
 #include "nkb_internal.h"
 #include "nkb_ptx.cuh"
 
@@ -42,6 +43,9 @@ struct GemmDev {
     unsigned int *error_word;
 };
 
+// Epilogue scratch after the barriers: column factors (2 x 256 f32) + eight 32 x 20-word staging blocks.
+constexpr int kEpiSmemBytesDecl = 2 * 256 * 4 + 8 * 32 * 20 * 4;
+
 template <int kBN, int kStages>
 struct SmemPlan {
     static constexpr int kABytes = kBM * kBKBytes;
@@ -49,7 +53,7 @@ struct SmemPlan {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarrierOffset = kStages * kStageBytes;
     static constexpr int kBarrierBytes = 256;
-    static constexpr int kTotal = kBarrierOffset + kBarrierBytes + 1024;  // + slack for manual 1024-byte alignment
+    static constexpr int kTotal = kBarrierOffset + kBarrierBytes + kEpiSmemBytesDecl + 1024;  // + slack for manual 1024-byte alignment
 };
 
 __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t &mt, uint32_t &nt) {
@@ -79,6 +83,100 @@ __device__ __forceinline__ float finalize(float dot, float a_norm, float b_norm)
         // include/numkong/spatial/serial.h:272-278
         float d2 = a_norm + b_norm - 2.0f * dot;
         return d2 > 0.0f ? sqrtf(d2) : 0.0f;
+    }
+}
+
+// ---- epilogue helpers shared by the single-CTA and the CTA-pair kernels ---------------------------------
+// Shared memory after the barriers: per-tile column factors (two tiles deep) and one 32 x 16 staging block per
+// epilogue warp (row pitch 20 words keeps 16-byte vector accesses aligned and nearly conflict-free).
+constexpr int kEpiColfBytes = 2 * 256 * 4;
+constexpr int kEpiStagePitch = 20;
+constexpr int kEpiStageWords = 32 * kEpiStagePitch;
+constexpr int kEpiSmemBytes = kEpiColfBytes + kEpilogueWarps * kEpiStageWords * 4;
+static_assert(kEpiSmemBytes == kEpiSmemBytesDecl, "epilogue scratch size");
+
+__device__ __forceinline__ float rsqrt_refined(float x) {
+    float r = rsqrtf(x);
+    return r * (1.5f - 0.5f * x * r * r);
+}
+__device__ __forceinline__ float sqrt_approx(float x) {
+    float r;
+    asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueWarps * 32) : "memory"); }
+
+// Column factor of one packed row for the distance epilogues: 1/|b| (0 for a zero row) for angular, |b|^2 for euclidean.
+template <int kEpi>
+__device__ __forceinline__ float column_factor(const GemmDev &p, uint32_t col) {
+    if (col >= p.n) return 0.0f;
+    float bn = p.int_mode == 0 ? __ldg(reinterpret_cast<const float *>(p.b_norms) + col)
+                               : (float)__ldg(reinterpret_cast<const uint32_t *>(p.b_norms) + col);
+    if constexpr (kEpi == kEpiAngular) return bn > 0.0f ? rsqrt_refined(bn) : 0.0f;
+    return bn;
+}
+
+// Finalises and stores this thread's row x kCols accumulators. Values go through the warp's staging block 16 columns at a
+// time so that each store instruction writes 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
+//   row_base  first of the 32 rows this warp owns;  col_base  first of this thread's kCols columns
+//   colf      this tile's column factors in shared memory, indexed by column inside the tile;  colf_off  col_base inside the tile
+// Angular: max(0, 1 - dot/(|a||b|)), and for a zero norm 0 when the dot is 0 else 1 (include/numkong/spatial/serial.h:257-269).
+// Euclidean: sqrt(max(0, |a|^2 + |b|^2 - 2 dot)) (include/numkong/spatial/serial.h:272-278).
+template <int kEpi, int kCols>
+__device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev &p, uint32_t row_base, uint32_t col_base,
+                                           uint32_t *stage, const float *colf, uint32_t colf_off, int lane) {
+    const uint32_t my_row = row_base + lane;
+    float row_factor = 0.0f;
+    if constexpr (kEpi != kEpiDot) {
+        float an = my_row < p.m ? p.a_norms[my_row] : 0.0f;
+        row_factor = kEpi == kEpiAngular ? (an > 0.0f ? rsqrt_refined(an) : 0.0f) : an;
+    }
+#pragma unroll
+    for (int c = 0; c < kCols / 16; ++c) {
+        const uint32_t col0 = col_base + c * 16;
+        if (col0 >= p.n) break;  // same for the whole warp
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t out[4];
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if constexpr (kEpi != kEpiDot) f = *reinterpret_cast<const float4 *>(colf + colf_off + c * 16 + q * 4);
+            const float cf[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t raw = acc[c * 16 + q * 4 + j];
+                if constexpr (kEpi == kEpiDot) out[j] = raw;
+                else {
+                    const float dot = p.int_mode == 0 ? __uint_as_float(raw) : p.int_mode == 1 ? (float)(int32_t)raw : (float)raw;
+                    float r;
+                    if constexpr (kEpi == kEpiAngular) {
+                        r = fmaxf(fmaf(-(dot * row_factor), cf[j], 1.0f), 0.0f);
+                        if (row_factor == 0.0f || cf[j] == 0.0f) r = dot == 0.0f ? 0.0f : 1.0f;
+                    } else {
+                        r = sqrt_approx(fmaxf(fmaf(-2.0f, dot, row_factor + cf[j]), 0.0f));
+                    }
+                    out[j] = __float_as_uint(r);
+                }
+            }
+            *reinterpret_cast<uint4 *>(stage + lane * kEpiStagePitch + q * 4) = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const uint32_t r = it * 8 + (lane >> 2), q = lane & 3u;
+            const uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kEpiStagePitch + q * 4);
+            const uint32_t row = row_base + r, col = col0 + q * 4;
+            if (row < p.m && col < p.n) {
+                uint32_t *dst = reinterpret_cast<uint32_t *>(p.c + (uint64_t)row * p.c_stride) + col;
+                if (col + 4 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) *reinterpret_cast<uint4 *>(dst) = v;
+                else {
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (col + j < p.n) dst[j] = w[j];
+                }
+            }
+        }
+        __syncwarp();
     }
 }
 
@@ -197,11 +295,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
         // ------------------------------------------------------------ epilogue (warps 2..9)
         const uint32_t quarter = warp & 3u;               // TMEM lanes this warp may read: 32*quarter .. +31
         const uint32_t half = (uint32_t)(warp - 2) >> 2;  // which half of the tile's columns
-        uint32_t seq = 0;
+        float *colf = reinterpret_cast<float *>(smem_gen + Plan::kBarrierOffset + Plan::kBarrierBytes);
+        uint32_t *epi_stage = reinterpret_cast<uint32_t *>(smem_gen + Plan::kBarrierOffset + Plan::kBarrierBytes + kEpiColfBytes) +
+                              (warp - 2) * kEpiStageWords;
+        uint32_t seq = 0, local_tile = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
             uint32_t mt, nt;
             tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+            if constexpr (kEpi != kEpiDot) {
+                // One column factor per epilogue thread, shared by all rows of the tile (double-buffered by tile parity).
+                const uint32_t e = threadIdx.x - 64u;
+                colf[(local_tile & 1u) * 256 + e] = e < (uint32_t)kBN ? column_factor<kEpi>(p, nt * kBN + e) : 0.0f;
+                epilogue_barrier();
+            }
             uint32_t acc[kColsPerThread];
 #pragma unroll
             for (int j = 0; j < kColsPerThread; ++j) acc[j] = 0u;
@@ -225,38 +332,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                 mbar_arrive(tmem_empty_bar(buf));
             }
             if (!ok) break;
-            const uint32_t row = mt * kBM + quarter * 32u + lane;
-            if (row >= p.m) continue;
-            uint8_t *c_row = p.c + (uint64_t)row * p.c_stride;
-            float a_norm = 0.0f;
-            if constexpr (kEpi != kEpiDot) a_norm = p.a_norms[row];
-#pragma unroll
-            for (int c = 0; c < kColsPerThread / 32; ++c) {
-                const uint32_t col0 = nt * kBN + half * kColsPerThread + c * 32;
-                if (col0 >= p.n) break;
-                if constexpr (kEpi != kEpiDot) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const uint32_t raw = acc[c * 32 + j];
-                        float dot = p.int_mode == 0 ? __uint_as_float(raw) : p.int_mode == 1 ? (float)(int32_t)raw : (float)raw;
-                        float b_norm = 0.0f;
-                        if (col0 + j < p.n)
-                            b_norm = p.int_mode == 0 ? __ldg(reinterpret_cast<const float *>(p.b_norms) + col0 + j)
-                                                     : (float)__ldg(reinterpret_cast<const uint32_t *>(p.b_norms) + col0 + j);
-                        acc[c * 32 + j] = __float_as_uint(finalize<kEpi>(dot, a_norm, b_norm));
-                    }
-                }
-                uint32_t *dst = reinterpret_cast<uint32_t *>(c_row) + col0;
-                if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<uint4 *>(dst + j) = make_uint4(acc[c * 32 + j], acc[c * 32 + j + 1], acc[c * 32 + j + 2], acc[c * 32 + j + 3]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.n) dst[j] = acc[c * 32 + j];
-                }
-            }
+            store_tile<kEpi, kColsPerThread>(acc, p, mt * kBM + quarter * 32u, nt * kBN + half * kColsPerThread, epi_stage,
+                                             colf + (local_tile & 1u) * 256, half * kColsPerThread, lane);
         }
     }
 
@@ -265,6 +342,175 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// CTA-pair variant (tcgen05 cta_group::2): two CTAs on neighbouring SMs share one 256 x 256 output tile. Each
+// CTA loads its own 128 rows of A and HALF of the B tile (128 packed rows); the MMA issued by the leader CTA
+// reads B from both CTAs' shared memory, so every SM fetches 32 KiB per stage instead of 48 KiB, and each CTA
+// accumulates its 128 x 256 half in its own TMEM. No multicast: every CTA issues its own loads.
+//   - loads of both CTAs complete on the LEADER's `full` barrier (pair-form TMA);
+//   - the leader's tcgen05.commit releases a stage / publishes an accumulator in BOTH CTAs;
+//   - epilogue warps of both CTAs report a drained accumulator to the leader's `tmem_empty` barrier.
+constexpr int kPairStages = 6;
+constexpr int kPairBN = 256;
+constexpr int kPairStageBytes = kBM * kBKBytes + (kPairBN / 2) * kBKBytes;  // 16 KiB of A + 16 KiB of B per CTA
+constexpr int kPairBarrierOffset = kPairStages * kPairStageBytes;
+constexpr int kPairSmemTotal = kPairBarrierOffset + 256 + kEpiSmemBytesDecl + 1024;
+
+template <int kKind, int kEpi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map, const GemmDev p) {
+    constexpr int kBN = kPairBN;
+    constexpr int kStages = kPairStages;
+    constexpr int kTmemCols = 2 * kBN;
+    constexpr int kColsPerThread = kBN / 2;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + kPairBarrierOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+    auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kPairBarrierOffset + 8 * (2 * kStages + 4));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();           // 0 = leader
+    const uint32_t pair = blockIdx.x >> 1;
+    const uint32_t num_pairs = gridDim.x >> 1;
+    const uint32_t num_tiles = p.tiles_m * p.tiles_n;  // 256 x 256 tiles
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&a_map);
+        prefetch_tensormap(&b_map);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tmem_full_bar(a), 1);
+            mbar_init(tmem_empty_bar(a), 2 * kEpilogueWarps);  // one arrival per epilogue warp of both CTAs
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc<2>(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+        tmem_relinquish<2>();
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_sync_all();  // the peer's barriers must exist before anything is signalled across the pair
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                uint32_t mt, nt;
+                tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+                const uint32_t a_row = mt * 256u + rank * 128u;
+                const uint64_t b_chunk0 = ((uint64_t)nt * 2u + rank) * p.kblocks;  // this CTA's half of the B tile
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
+                    const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+                    const uint32_t b_dst = a_dst + kBM * kBKBytes;
+                    const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kPairStageBytes);
+                    tma_load_2d_pair(a_dst, &a_map, (int)(kb * p.elems_per_kblock), (int)a_row, leader_full);
+                    tma_load_2d_pair(b_dst, &b_map, 0, (int)((b_chunk0 + kb) * kChunkRows), leader_full);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            int stage = 0;
+            uint32_t phase = 0, seq = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
+                    const uint32_t buf = seq & 1u, buf_phase = (seq >> 1) & 1u;
+                    if (!mbar_wait<true>(tmem_empty_bar(buf), buf_phase ^ 1u, 2, p.error_word)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + buf * kBN;
+                    const uint32_t kb1 = min(kb0 + p.flush_kblocks, p.kblocks);
+                    for (uint32_t kb = kb0; kb < kb1; ++kb) {
+                        if (!mbar_wait<true>(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        const uint32_t a_src = smem_base + stage * kPairStageBytes;
+                        const uint64_t a_desc = make_smem_desc_sw128(a_src);
+                        const uint64_t b_desc = make_smem_desc_sw128(a_src + kBM * kBKBytes);
+#pragma unroll
+                        for (int k = 0; k < kBKBytes / kUmmaKBytes; ++k)
+                            umma<kKind, 2>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, ((kb - kb0) | (uint32_t)k) != 0u);
+                        umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
+                    if (ok) umma_commit_pair(tmem_full_bar(buf), 3);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs): rows of this CTA's half
+        const uint32_t quarter = warp & 3u;
+        const uint32_t half = (uint32_t)(warp - 2) >> 2;
+        float *colf = reinterpret_cast<float *>(smem_gen + kPairBarrierOffset + 256);
+        uint32_t *epi_stage = reinterpret_cast<uint32_t *>(smem_gen + kPairBarrierOffset + 256 + kEpiColfBytes) + (warp - 2) * kEpiStageWords;
+        uint32_t seq = 0, local_tile = 0;
+        bool ok = true;
+        for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+            uint32_t mt, nt;
+            tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+            if constexpr (kEpi != kEpiDot) {
+                const uint32_t e = threadIdx.x - 64u;
+                colf[(local_tile & 1u) * 256 + e] = column_factor<kEpi>(p, nt * kBN + e);
+                epilogue_barrier();
+            }
+            uint32_t acc[kColsPerThread];
+#pragma unroll
+            for (int j = 0; j < kColsPerThread; ++j) acc[j] = 0u;
+            for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
+                const uint32_t buf = seq & 1u, buf_phase = (seq >> 1) & 1u;
+                if (!mbar_wait<true>(tmem_full_bar(buf), buf_phase, 4, p.error_word)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < kColsPerThread / 16; ++c) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 16, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if constexpr (kKind == kKindI8) acc[c * 16 + j] += v[j];
+                        else acc[c * 16 + j] = __float_as_uint(__uint_as_float(acc[c * 16 + j]) + __uint_as_float(v[j]));
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(tmem_empty_bar(buf), 0));
+            }
+            if (!ok) break;
+            store_tile<kEpi, kColsPerThread>(acc, p, mt * 256u + rank * 128u + quarter * 32u, nt * kBN + half * kColsPerThread,
+                                             epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane);
+        }
+    }
+
+    // Neither CTA may retire while its partner can still read its shared memory or signal its barriers.
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<2>(tmem_base, kTmemCols);
     }
 }
 
@@ -337,6 +583,46 @@ cudaError_t launch_by_epilogue(int epi, int bn, const CUtensorMap &map, const Ge
     }
 }
 
+template <int kKind, int kEpi>
+cudaError_t launch_pair(const CUtensorMap &a_map, const CUtensorMap &b_map, const GemmDev &dev, cudaStream_t stream) {
+    auto kernel = gemm_tc_pair_kernel<kKind, kEpi>;
+    static int max_pairs[64] = {0};
+    int d = 0;
+    cudaGetDevice(&d);
+    if (d < 0 || d >= 64) d = 0;
+    if (max_pairs[d] == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemTotal);
+        if (e != cudaSuccess) return e;
+        // How many CTA pairs can be resident at once (pairs must sit on SMs that can form a cluster).
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * device_sm_count());
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kPairSmemTotal;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = device_sm_count() / 2; }
+        max_pairs[d] = n;
+    }
+    uint32_t tiles = dev.tiles_m * dev.tiles_n;
+    uint32_t pairs = tiles < (uint32_t)max_pairs[d] ? tiles : (uint32_t)max_pairs[d];
+    kernel<<<2 * pairs, kThreads, kPairSmemTotal, stream>>>(a_map, b_map, dev);
+    return cudaGetLastError();
+}
+
+template <int kKind>
+cudaError_t launch_pair_by_epilogue(int epi, const CUtensorMap &a_map, const CUtensorMap &b_map, const GemmDev &dev, cudaStream_t stream) {
+    switch (epi) {
+    case kEpiDot: return launch_pair<kKind, kEpiDot>(a_map, b_map, dev, stream);
+    case kEpiAngular: return launch_pair<kKind, kEpiAngular>(a_map, b_map, dev, stream);
+    case kEpiEuclidean: return launch_pair<kKind, kEpiEuclidean>(a_map, b_map, dev, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
 } // namespace
 
 EncodeTiledFn get_encode_tiled() {
@@ -361,6 +647,15 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     if ((reinterpret_cast<uintptr_t>(args.a) & 15u) || (args.a_stride & 15u)) return cudaErrorMisalignedAddress;
 
     const uint32_t eb = dtype_bytes(args.dtype);
+    // Tile configuration: 3 = CTA pairs sharing 256 x 256 tiles, 1 = 128 x 256 per CTA, 2 = 128 x 128 per CTA.
+    const uint64_t chunk_rows_total = round_up(args.n, kRowPad) * (args.depth_padded_bytes / kBKBytes);
+    // Measured on B200 at 8192^3 the pair kernel is 5-10 % faster (bf16 1440 vs 1368, i8 3090 vs 2802 Tops); with a
+    // short depth (768) and a distance epilogue the single-CTA kernel wins (834 vs 719 Tops), so pairs are used for
+    // deep problems (>= 32 stages) that have at least one 256 x 256 tile per CTA pair.
+    const uint64_t pair_tiles = ((args.m + 255) / 256) * ((args.n + 255) / 256);
+    const bool pair_by_shape = (args.variant & 0xff) == 0 && args.depth_padded_bytes / kBKBytes >= 32 &&
+                               pair_tiles >= (uint64_t)device_sm_count() / 2;
+    const bool use_pair = ((args.variant & 0xff) == 3 || pair_by_shape) && chunk_rows_total < 0x7fffffffull;
     int bn = 256;
     if ((args.variant & 0xff) == 1) bn = 256;
     else if ((args.variant & 0xff) == 2) bn = 128;
@@ -395,14 +690,44 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     dev.tiles_n = (uint32_t)((args.n + bn - 1) / bn);
     dev.idesc = make_idesc(ki.c_fmt, ki.ab_fmt, kBM, bn);
     dev.int_mode = ki.int_mode;
-    // Float kinds: spans of 16 stages (1024 16-bit or 2048 8-bit values): measured on B200, the normalised error
-    // at depth 8192 is 8.6e-8 (bf16) / 1.0e-8 (e4m3), against 3.7e-7 / 3.7e-8 for one long chain, for ~3 % of the
-    // run time (reading a 128 KiB accumulator out of TMEM stalls the MMAs for ~256 cycles). Integers are exact: one span.
+    // Span length for float kinds. Measured on B200: one long accumulation chain has a normalised error of
+    // ~7.6e-9 * span / sqrt(depth) for 16-bit floats (truncating accumulate), e.g. 3.7e-7 at depth 8192, 3e-7 at
+    // depth 1000; the 8/6-bit kinds sit ten times lower and level off at 1e-8. Reading a 128 KiB accumulator out of
+    // TMEM stalls the MMAs for ~256 cycles, so spans are made as long as the error target (1e-7, NumKong's own f32
+    // kernels measure 3e-8..7e-8) allows: span = 12 * sqrt(depth) values for 16-bit floats, capped at 16 stages;
+    // 16 stages for the 8/6-bit kinds. Integers are exact: one span.
     const uint32_t forced_flush = (uint32_t)args.variant >> 8;
-    dev.flush_kblocks = ki.kind == kKindI8 ? dev.kblocks : (forced_flush ? forced_flush : 16u);
+    uint32_t auto_flush = 16u;
+    if (ki.kind == kKindF16) {
+        uint32_t span_values = (uint32_t)(12.0 * sqrt((double)args.k));
+        auto_flush = span_values / dev.elems_per_kblock;
+        if (auto_flush < 1u) auto_flush = 1u;
+        if (auto_flush > 16u) auto_flush = 16u;
+    }
+    dev.flush_kblocks = ki.kind == kKindI8 ? dev.kblocks : (forced_flush ? forced_flush : auto_flush);
     if (dev.flush_kblocks == 0) dev.flush_kblocks = 1;
     dev.error_word = args.error_word;
 
+    if (use_pair) {
+        // The packed payload seen as rows of 128 bytes: one 16 KiB chunk = 128 consecutive rows, copied verbatim
+        // (the swizzle is already in the data).
+        CUtensorMap b_map;
+        cuuint64_t b_dims[2] = {kBKBytes, chunk_rows_total};
+        cuuint64_t b_strides[1] = {kBKBytes};
+        cuuint32_t b_box[2] = {kBKBytes, kChunkRows};
+        r = encode(&b_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(args.b_payload), b_dims, b_strides, b_box,
+                   elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+        dev.tiles_m = (uint32_t)((args.m + 255) / 256);
+        dev.tiles_n = (uint32_t)((args.n + 255) / 256);
+        dev.idesc = make_idesc(ki.c_fmt, ki.ab_fmt, 256, 256);
+        switch (ki.kind) {
+        case kKindF16: return launch_pair_by_epilogue<kKindF16>(args.epilogue, map, b_map, dev, stream);
+        case kKindF8F6F4: return launch_pair_by_epilogue<kKindF8F6F4>(args.epilogue, map, b_map, dev, stream);
+        default: return launch_pair_by_epilogue<kKindI8>(args.epilogue, map, b_map, dev, stream);
+        }
+    }
     switch (ki.kind) {
     case kKindF16: return launch_by_epilogue<kKindF16>(args.epilogue, bn, map, dev, stream);
     case kKindF8F6F4: return launch_by_epilogue<kKindF8F6F4>(args.epilogue, bn, map, dev, stream);

@@ -26,18 +26,26 @@ namespace {
 
 constexpr int kMsBM = 128;
 constexpr int kMsBN = 256;
-constexpr int kMsStages = 4;
+constexpr int kMsStages = 3;
 constexpr int kMsThreads = 192;
 constexpr int kMsABytes = kMsBM * 128;
 constexpr int kMsBBytes = kMsBN * 128;
 constexpr int kMsStageBytes = kMsABytes + kMsBBytes;
 constexpr int kMsBarrierOffset = kMsStages * kMsStageBytes;
-constexpr int kMsSmemTotal = kMsBarrierOffset + 256 + 1024;
+// The epilogue warps run alone on their SM sub-partitions, so every global load they wait for is dead time. The
+// inverse norms of the document tokens a CTA walks and the ends of its documents are therefore copied into shared
+// memory once per CTA (lookups beyond these windows fall back to global memory).
+constexpr int kMsInvCache = 36 * kMsBN;   // tokens (a run is about 32 tiles plus one document)
+constexpr int kMsEndCache = 256;          // documents
+constexpr int kMsCacheOffset = kMsBarrierOffset + 256;
+constexpr int kMsSmemTotal = kMsCacheOffset + kMsInvCache * 4 + kMsEndCache * 8 + 1024;
 
 struct MaxsimDev {
     const uint8_t *q_payload, *d_payload;
     const float *q_inv, *d_inv;          // inverse norms per token
     const uint64_t *q_offsets, *d_offsets;  // token offsets per query / document (device), length count+1
+    const uint32_t *q_token_query;       // query index of every query token (filled by maxsim_prepare_kernel)
+    const uint64_t *segment_bounds;      // first document of every segment, length segments+1 (same kernel)
     uint64_t n_queries, n_docs;
     uint64_t q_tokens, d_tokens;
     uint32_t kblocks;
@@ -59,6 +67,48 @@ __device__ __forceinline__ uint64_t lower_bound_offsets(const uint64_t *offsets,
     return lo;
 }
 
+// Runs once before maxsim_kernel: the query each query token belongs to, and the first document of every segment
+// (a segment = the documents whose first token falls into its equal share of all document tokens).
+__global__ void maxsim_prepare_kernel(const uint64_t *q_offsets, uint64_t n_queries, uint64_t q_tokens, uint32_t *q_token_query,
+                                      const uint64_t *d_offsets, uint64_t n_docs, uint64_t d_tokens, uint32_t segments,
+                                      uint64_t *segment_bounds) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < q_tokens) q_token_query[i] = (uint32_t)(lower_bound_offsets(q_offsets, n_queries, i + 1) - 1);
+    if (i <= segments) {
+        const uint64_t per_seg = (d_tokens + segments - 1) / segments;
+        segment_bounds[i] = i == segments ? n_docs : lower_bound_offsets(d_offsets, n_docs, i * per_seg);
+    }
+}
+
+// Largest value and its FIRST position among columns [j0, j1) of a 32-column chunk held in registers (all 32 when
+// kFull). Eight independent running maxima (columns j, j+8, ...) keep the comparison chains short; they are merged
+// pairwise with ties going to the lower position, which is exactly the winner of a left-to-right scan with `>`.
+template <bool kFull>
+__device__ __forceinline__ void chunk_argmax(const uint32_t (&v)[32], uint32_t j0, uint32_t j1, float &best, uint32_t &best_j) {
+    constexpr float kLowest = -3.402823466e+38f;
+    float bv[8];
+    uint32_t bi[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        bv[c] = (kFull || ((uint32_t)c >= j0 && (uint32_t)c < j1)) ? __uint_as_float(v[c]) : kLowest;
+        bi[c] = c;
+    }
+#pragma unroll
+    for (int j = 8; j < 32; ++j) {
+        const float x = __uint_as_float(v[j]);
+        const bool inside = kFull || ((uint32_t)j >= j0 && (uint32_t)j < j1);
+        if (inside && x > bv[j & 7]) { bv[j & 7] = x; bi[j & 7] = j; }
+    }
+#pragma unroll
+    for (int s = 1; s < 8; s <<= 1) {
+#pragma unroll
+        for (int c = 0; c < 8; c += 2 * s)
+            if (bv[c + s] > bv[c] || (bv[c + s] == bv[c] && bi[c + s] < bi[c])) { bv[c] = bv[c + s]; bi[c] = bi[c + s]; }
+    }
+    best = bv[0];
+    best_j = bi[0];
+}
+
 template <int kKind>
 __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p) {
     constexpr int kTmemCols = 2 * kMsBN;
@@ -71,7 +121,6 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
     auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kMsStages + a); };
     auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMsStages + 2 + a); };
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kMsBarrierOffset + 8 * (2 * kMsStages + 4));
-    volatile uint64_t *seg_slot = reinterpret_cast<volatile uint64_t *>(smem_gen + kMsBarrierOffset + 8 * (2 * kMsStages + 6));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -82,28 +131,40 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
         for (int s = 0; s < kMsStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), 128); }
         fence_mbar_init();
-        // This CTA's run of whole documents: documents whose first token falls in its share of the tokens.
-        uint64_t per_seg = (p.d_tokens + p.segments - 1) / p.segments;
-        uint64_t t0 = (uint64_t)segment * per_seg, t1 = t0 + per_seg;
-        uint64_t d0 = lower_bound_offsets(p.d_offsets, p.n_docs, t0);
-        uint64_t d1 = (segment + 1 == p.segments) ? p.n_docs : lower_bound_offsets(p.d_offsets, p.n_docs, t1);
-        seg_slot[0] = d0;
-        seg_slot[1] = d1;
     }
     if (warp == 1) {
         tmem_alloc<1>(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
         tmem_relinquish<1>();
     }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint64_t doc_begin = seg_slot[0], doc_end = seg_slot[1];
+    // This CTA's run of whole documents (bounds computed by maxsim_prepare_kernel).
+    const uint64_t doc_begin = p.segment_bounds[segment], doc_end = p.segment_bounds[segment + 1];
     const bool has_work = doc_begin < doc_end;
     const uint64_t tok_begin = has_work ? p.d_offsets[doc_begin] : 0;
     const uint64_t tok_end = has_work ? p.d_offsets[doc_end] : 0;
     const uint64_t tile_begin = tok_begin / kMsBN;
     const uint64_t tile_end = has_work ? (tok_end + kMsBN - 1) / kMsBN : tile_begin;  // empty documents only -> no tiles
+    // Shared-memory copies of what the epilogue looks up per document.
+    float *inv_cache = reinterpret_cast<float *>(smem_gen + kMsCacheOffset);
+    uint64_t *end_cache = reinterpret_cast<uint64_t *>(smem_gen + kMsCacheOffset + kMsInvCache * 4);
+    const uint64_t cache_base = tile_begin * kMsBN;  // first token held in inv_cache
+    if (has_work) {
+        for (uint32_t i = threadIdx.x; i < (uint32_t)kMsInvCache; i += blockDim.x)
+            inv_cache[i] = cache_base + i < p.d_tokens ? __ldg(p.d_inv + cache_base + i) : 0.0f;
+        for (uint32_t i = threadIdx.x; i < (uint32_t)kMsEndCache; i += blockDim.x)
+            end_cache[i] = doc_begin + i < p.n_docs ? p.d_offsets[doc_begin + i + 1] : p.d_tokens;
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    auto inverse_norm_of = [&](uint32_t token) {
+        const uint64_t rel = (uint64_t)token - cache_base;
+        return rel < (uint64_t)kMsInvCache ? inv_cache[rel] : __ldg(p.d_inv + token);
+    };
+    auto end_of_doc = [&](uint64_t doc) {
+        const uint64_t rel = doc - doc_begin;
+        return rel < (uint64_t)kMsEndCache ? end_cache[rel] : p.d_offsets[doc + 1];
+    };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -160,12 +221,12 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
         const float q_inv = row_ok ? p.q_inv[row] : 0.0f;
         // Query this token belongs to (-1 for padding rows).
         long long qid = -1;
-        if (row_ok) qid = (long long)lower_bound_offsets(p.q_offsets, p.n_queries, row + 1) - 1;
+        if (row_ok) qid = (long long)p.q_token_query[row];
         const long long qid_above = __shfl_up_sync(0xffffffffu, qid, 1);
         const bool segment_head = qid >= 0 && (lane == 0 || qid_above != qid);
 
         uint64_t cur_doc = doc_begin;
-        uint64_t cur_end = has_work ? p.d_offsets[cur_doc + 1] : 0;
+        uint64_t cur_end = has_work ? end_of_doc(cur_doc) : 0;
         float run = -3.402823466e+38f;
         uint32_t arg = 0;
 
@@ -173,7 +234,7 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
         auto finish_doc = [&]() {
             float angular = 0.0f;
             if (row_ok) {
-                float cosine = run * q_inv * __ldg(p.d_inv + arg);
+                float cosine = run * q_inv * inverse_norm_of(arg);
                 angular = 1.0f - cosine;
                 if (!(angular > 0.0f)) angular = angular < 0.0f ? 0.0f : angular;  // clamp, keep NaN
             }
@@ -198,20 +259,16 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
             if (!mbar_wait(tmem_full_bar(acc), acc_phase, 4, p.error_word)) { ok = false; break; }
             tc_fence_after_sync();
-#pragma unroll 1
-            for (int chunk = 0; chunk < kMsBN / 32; ++chunk) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + acc * kMsBN + chunk * 32, v);
-                tmem_ld_wait();
+            // Scans one 32-column chunk held in registers.
+            auto scan_chunk = [&](const uint32_t (&v)[32], int chunk) {
                 const uint64_t col0 = t * kMsBN + (uint64_t)chunk * 32;
-                if (col0 + 32 <= tok_begin || col0 >= tok_end) continue;
+                if (col0 + 32 <= tok_begin || col0 >= tok_end) return;
                 if (col0 >= tok_begin && col0 + 32 <= cur_end) {
                     // The whole chunk lies inside the current document.
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float x = __uint_as_float(v[j]);
-                        if (x > run) { run = x; arg = (uint32_t)(col0 + j); }
-                    }
+                    float best;
+                    uint32_t best_j;
+                    chunk_argmax<true>(v, 0, 32, best, best_j);
+                    if (best > run) { run = best; arg = (uint32_t)(col0 + best_j); }
                 } else {
                     // A document boundary (or an end of this CTA's run) falls inside the chunk. Walk it one
                     // document piece at a time; every piece is a predicated pass over all 32 registers, so the
@@ -222,17 +279,29 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                         while (col0 + j0 >= cur_end) {
                             finish_doc();
                             ++cur_doc;
-                            cur_end = p.d_offsets[cur_doc + 1];
+                            cur_end = end_of_doc(cur_doc);
                         }
                         const uint32_t j1 = cur_end - col0 < j_stop ? (uint32_t)(cur_end - col0) : j_stop;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            float x = __uint_as_float(v[j]);
-                            if ((uint32_t)j >= j0 && (uint32_t)j < j1 && x > run) { run = x; arg = (uint32_t)(col0 + j); }
-                        }
+                        float best;
+                        uint32_t best_j;
+                        chunk_argmax<false>(v, j0, j1, best, best_j);
+                        if (best > run) { run = best; arg = (uint32_t)(col0 + best_j); }
                         j0 = j1;
                     }
                 }
+            };
+            // Two register buffers: the next chunk's TMEM load is in flight while the current chunk is scanned.
+            const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + acc * kMsBN;
+            uint32_t va[32], vb[32];
+            tmem_ld_32x32(t_addr, va);
+#pragma unroll
+            for (int chunk = 0; chunk < kMsBN / 32; chunk += 2) {
+                tmem_ld_wait_for(va);
+                tmem_ld_32x32(t_addr + (chunk + 1) * 32, vb);
+                scan_chunk(va, chunk);
+                tmem_ld_wait_for(vb);
+                if (chunk + 2 < kMsBN / 32) tmem_ld_32x32(t_addr + (chunk + 2) * 32, va);
+                scan_chunk(vb, chunk + 1);
             }
             tc_fence_before_sync();
             mbar_arrive(tmem_empty_bar(acc));
@@ -295,7 +364,21 @@ cudaError_t launch_maxsim_tc(uint32_t dt, const MaxsimDev &dev_in, cudaStream_t 
         configured[d] = true;
     }
     uint64_t grid = (uint64_t)dev.q_tiles * dev.segments;
-    if (grid == 0 || grid > 0x7fffffffull) return cudaErrorInvalidValue;
+    if (grid == 0 || grid > 0x7fffffffull || dev.q_tokens > 0xffffffffull) return cudaErrorInvalidValue;
+    // Look-up tables for the main kernel: token -> query, segment -> first document.
+    const uint64_t map_bytes = round_up(dev.q_tokens * 4, 16);
+    uint8_t *tables = static_cast<uint8_t *>(scratch(kSlotNorms, map_bytes + ((uint64_t)dev.segments + 1) * 8));
+    if (!tables) return cudaErrorMemoryAllocation;
+    uint32_t *token_query = reinterpret_cast<uint32_t *>(tables);
+    uint64_t *bounds = reinterpret_cast<uint64_t *>(tables + map_bytes);
+    const uint64_t items = dev.q_tokens > (uint64_t)dev.segments + 1 ? dev.q_tokens : (uint64_t)dev.segments + 1;
+    maxsim_prepare_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(dev.q_offsets, dev.n_queries, dev.q_tokens, token_query,
+                                                                             dev.d_offsets, dev.n_docs, dev.d_tokens, dev.segments, bounds);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    g_launches++;
+    dev.q_token_query = token_query;
+    dev.segment_bounds = bounds;
     maxsim_kernel<kKindF16><<<(unsigned)grid, kMsThreads, kMsSmemTotal, stream>>>(dev);
     return cudaGetLastError();
 }

@@ -52,6 +52,8 @@ def merge_topk(values: torch.Tensor, ids: torch.Tensor, top: int, group=None, ds
     if world == 1:
         return values, ids
     packed = torch.cat([values.to(torch.float64), ids.to(torch.float64)], dim=1).contiguous()  # ids < 2^53 stay exact
+    if packed.is_cuda and dist.get_backend(group) == "gloo":
+        packed = packed.cpu()  # gloo moves host memory only; the merged lists then stay on the host
     gathered = [torch.empty_like(packed) for _ in range(world)] if rank == dst else None
     dist.gather(packed, gathered, dst=dst, group=group)
     if rank != dst:
