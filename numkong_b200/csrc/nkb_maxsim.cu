@@ -27,7 +27,8 @@ namespace {
 constexpr int kMsBM = 128;
 constexpr int kMsBN = 256;
 constexpr int kMsStages = 3;
-constexpr int kMsThreads = 192;
+constexpr int kMsEpilogueWarps = 16;
+constexpr int kMsThreads = 64 + 32 * kMsEpilogueWarps;
 constexpr int kMsABytes = kMsBM * 128;
 constexpr int kMsBBytes = kMsBN * 128;
 constexpr int kMsStageBytes = kMsABytes + kMsBBytes;
@@ -38,7 +39,9 @@ constexpr int kMsBarrierOffset = kMsStages * kMsStageBytes;
 constexpr int kMsInvCache = 36 * kMsBN;   // tokens (a run is about 32 tiles plus one document)
 constexpr int kMsEndCache = 256;          // documents
 constexpr int kMsCacheOffset = kMsBarrierOffset + 256;
-constexpr int kMsSmemTotal = kMsCacheOffset + kMsInvCache * 4 + kMsEndCache * 8 + 1024;
+constexpr int kMsPartialOffset = kMsCacheOffset + kMsInvCache * 4 + kMsEndCache * 8;
+constexpr int kMsPartialBytes = 2 * 4 * 4 * 32 * 8;  // (max, argmax) of 3 partner warps x 4 quarters, two documents deep
+constexpr int kMsSmemTotal = kMsPartialOffset + kMsPartialBytes + 1024;
 
 struct MaxsimDev {
     const uint8_t *q_payload, *d_payload;
@@ -50,6 +53,7 @@ struct MaxsimDev {
     uint64_t q_tokens, d_tokens;
     uint32_t kblocks;
     uint32_t q_tiles, segments;
+    uint32_t q_group;                    // query tiles that walk the same document segment side by side
     uint32_t idesc;
     float *scores_f32;                   // batch: n_queries x n_docs
     uint64_t score_stride;               // in floats
@@ -124,12 +128,17 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const uint32_t q_tile = blockIdx.x % p.q_tiles;
-    const uint32_t segment = blockIdx.x / p.q_tiles;
+    // Block order: `q_group` query tiles share a document segment (so a segment is fetched from HBM once per group and
+    // from L2 by the others), then the next segment, and so on; then the next group of query tiles. Keeping the group
+    // small keeps the number of SMs that ask L2 for the same lines at the same moment small.
+    const uint32_t per_group = p.q_group * p.segments;
+    const uint32_t q_tile = (blockIdx.x / per_group) * p.q_group + (blockIdx.x % per_group) % p.q_group;
+    const uint32_t segment = (blockIdx.x % per_group) / p.q_group;
+    if (q_tile >= p.q_tiles) return;  // padding blocks of the last group (nothing allocated yet)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMsStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), 128); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), kMsEpilogueWarps * 32); }
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -214,41 +223,61 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue: one query token per thread
+        // ------------------------------------------------------------ epilogue (warps 2..17)
+        // Sixteen warps: four per TMEM lane quarter (= 32 query tokens), each scanning its own 64 of the tile's 256
+        // columns. One warp per scheduler could not hide the latency of its dependent compare/select chains (measured:
+        // 32 % issue utilisation); four do. The four warps of a quarter keep partial (max, argmax) pairs per document
+        // and combine them when a document ends: partners park their pair in shared memory, meet at a named barrier,
+        // and the first warp merges (larger dot wins, equal dots go to the lower token), normalises and accumulates.
         const uint32_t quarter = warp & 3u;
+        const uint32_t sub = (uint32_t)(warp - 2) >> 2;  // which 64-column slice of every tile
         const uint64_t row = (uint64_t)q_tile * kMsBM + quarter * 32u + lane;
         const bool row_ok = row < p.q_tokens;
         const float q_inv = row_ok ? p.q_inv[row] : 0.0f;
-        // Query this token belongs to (-1 for padding rows).
-        long long qid = -1;
+        long long qid = -1;  // query this token belongs to (-1 for padding rows)
         if (row_ok) qid = (long long)p.q_token_query[row];
         const long long qid_above = __shfl_up_sync(0xffffffffu, qid, 1);
         const bool segment_head = qid >= 0 && (lane == 0 || qid_above != qid);
+        float *part_val = reinterpret_cast<float *>(smem_gen + kMsPartialOffset);
+        uint32_t *part_arg = reinterpret_cast<uint32_t *>(smem_gen + kMsPartialOffset + kMsPartialBytes / 2);
 
         uint64_t cur_doc = doc_begin;
         uint64_t cur_end = has_work ? end_of_doc(cur_doc) : 0;
+        uint32_t docs_done = 0;
         float run = -3.402823466e+38f;
         uint32_t arg = 0;
 
-        // Closes the current document: normalise the winner, add up the angulars of each query's tokens.
+        // Closes the current document for this quarter. Called by all four warps of the quarter, in the same order.
         auto finish_doc = [&]() {
-            float angular = 0.0f;
-            if (row_ok) {
-                float cosine = run * q_inv * inverse_norm_of(arg);
-                angular = 1.0f - cosine;
-                if (!(angular > 0.0f)) angular = angular < 0.0f ? 0.0f : angular;  // clamp, keep NaN
-            }
-            double sum = (double)angular;
+            const uint32_t slot = (((docs_done & 1u) * 4u + quarter) * 4u + sub) * 32u + lane;
+            if (sub != 0) { part_val[slot] = run; part_arg[slot] = arg; }
+            asm volatile("bar.sync %0, 128;" ::"r"(1u + quarter) : "memory");
+            if (sub == 0) {
 #pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                double other = __shfl_down_sync(0xffffffffu, sum, off);
-                long long other_q = __shfl_down_sync(0xffffffffu, qid, off);
-                if (lane + off < 32 && other_q == qid) sum += other;
+                for (uint32_t s = 1; s < 4; ++s) {
+                    const float v = part_val[slot + s * 32u];
+                    const uint32_t a = part_arg[slot + s * 32u];
+                    if (v > run || (v == run && a < arg)) { run = v; arg = a; }
+                }
+                float angular = 0.0f;
+                if (row_ok) {
+                    const float cosine = run * q_inv * inverse_norm_of(arg);
+                    angular = 1.0f - cosine;
+                    if (!(angular > 0.0f)) angular = angular < 0.0f ? 0.0f : angular;  // clamp, keep NaN
+                }
+                double sum = (double)angular;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const double other = __shfl_down_sync(0xffffffffu, sum, off);
+                    const long long other_q = __shfl_down_sync(0xffffffffu, qid, off);
+                    if (lane + off < 32 && other_q == qid) sum += other;
+                }
+                if (segment_head) {
+                    if (p.total_f64) atomicAdd(p.total_f64, sum);
+                    else atomicAdd(p.scores_f32 + (uint64_t)qid * p.score_stride + cur_doc, (float)sum);
+                }
             }
-            if (segment_head) {
-                if (p.total_f64) atomicAdd(p.total_f64, sum);
-                else atomicAdd(p.scores_f32 + (uint64_t)qid * p.score_stride + cur_doc, (float)sum);
-            }
+            ++docs_done;
             run = -3.402823466e+38f;
             arg = 0;
         };
@@ -259,54 +288,52 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
             if (!mbar_wait(tmem_full_bar(acc), acc_phase, 4, p.error_word)) { ok = false; break; }
             tc_fence_after_sync();
-            // Scans one 32-column chunk held in registers.
-            auto scan_chunk = [&](const uint32_t (&v)[32], int chunk) {
-                const uint64_t col0 = t * kMsBN + (uint64_t)chunk * 32;
-                if (col0 + 32 <= tok_begin || col0 >= tok_end) return;
-                if (col0 >= tok_begin && col0 + 32 <= cur_end) {
+            const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + acc * kMsBN + sub * 64u;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_addr + half * 32, v);
+                tmem_ld_wait_for(v);
+                const uint64_t c0 = t * kMsBN + sub * 64u + (uint64_t)half * 32;
+                const uint64_t lo = c0 > tok_begin ? c0 : tok_begin;
+                const uint64_t hi = c0 + 32 < tok_end ? c0 + 32 : tok_end;
+                if (lo >= hi) continue;  // nothing of this CTA's run in the chunk
+                if (lo == c0 && hi == c0 + 32 && hi <= cur_end) {
                     // The whole chunk lies inside the current document.
                     float best;
                     uint32_t best_j;
                     chunk_argmax<true>(v, 0, 32, best, best_j);
-                    if (best > run) { run = best; arg = (uint32_t)(col0 + best_j); }
+                    if (best > run) { run = best; arg = (uint32_t)(c0 + best_j); }
                 } else {
-                    // A document boundary (or an end of this CTA's run) falls inside the chunk. Walk it one
-                    // document piece at a time; every piece is a predicated pass over all 32 registers, so the
-                    // values never leave the register file. Boundaries are the same for every thread.
-                    uint32_t j0 = col0 < tok_begin ? (uint32_t)(tok_begin - col0) : 0u;
-                    const uint32_t j_stop = tok_end - col0 < 32 ? (uint32_t)(tok_end - col0) : 32u;
-                    while (j0 < j_stop) {
-                        while (col0 + j0 >= cur_end) {
+                    // Document boundaries (or an end of the run) fall inside or before the chunk: walk it piece by piece
+                    // with predicated passes over the 32 registers. Boundaries are the same for every thread.
+                    uint64_t pos = lo;
+                    while (pos < hi) {
+                        while (pos >= cur_end) {
                             finish_doc();
                             ++cur_doc;
                             cur_end = end_of_doc(cur_doc);
                         }
-                        const uint32_t j1 = cur_end - col0 < j_stop ? (uint32_t)(cur_end - col0) : j_stop;
+                        const uint64_t piece_end = cur_end < hi ? cur_end : hi;
                         float best;
                         uint32_t best_j;
-                        chunk_argmax<false>(v, j0, j1, best, best_j);
-                        if (best > run) { run = best; arg = (uint32_t)(col0 + best_j); }
-                        j0 = j1;
+                        chunk_argmax<false>(v, (uint32_t)(pos - c0), (uint32_t)(piece_end - c0), best, best_j);
+                        if (best > run) { run = best; arg = (uint32_t)(c0 + best_j); }
+                        pos = piece_end;
                     }
                 }
-            };
-            // Two register buffers: the next chunk's TMEM load is in flight while the current chunk is scanned.
-            const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + acc * kMsBN;
-            uint32_t va[32], vb[32];
-            tmem_ld_32x32(t_addr, va);
-#pragma unroll
-            for (int chunk = 0; chunk < kMsBN / 32; chunk += 2) {
-                tmem_ld_wait_for(va);
-                tmem_ld_32x32(t_addr + (chunk + 1) * 32, vb);
-                scan_chunk(va, chunk);
-                tmem_ld_wait_for(vb);
-                if (chunk + 2 < kMsBN / 32) tmem_ld_32x32(t_addr + (chunk + 2) * 32, va);
-                scan_chunk(vb, chunk + 1);
             }
             tc_fence_before_sync();
             mbar_arrive(tmem_empty_bar(acc));
+            // Documents that end inside this tile are complete for every warp of the quarter once it gets here.
+            const uint64_t tile_hi = (t + 1) * kMsBN < tok_end ? (t + 1) * kMsBN : tok_end;
+            while (cur_doc < doc_end && cur_end <= tile_hi) {
+                finish_doc();
+                ++cur_doc;
+                cur_end = cur_doc < doc_end ? end_of_doc(cur_doc) : ~0ull;
+            }
         }
-        // Close the documents that are still open (the last one, and empty ones at the end of the run).
+        // Normally nothing is left here: every document of the run ends inside one of its tiles.
         if (ok && has_work) {
             while (cur_doc < doc_end) {
                 finish_doc();
@@ -363,7 +390,12 @@ cudaError_t launch_maxsim_tc(uint32_t dt, const MaxsimDev &dev_in, cudaStream_t 
         if (e != cudaSuccess) return e;
         configured[d] = true;
     }
-    uint64_t grid = (uint64_t)dev.q_tiles * dev.segments;
+    // Group size: 8 query tiles per segment unless overridden for tuning (bits 16..23 of the variant word).
+    uint32_t group = ((uint32_t)current_variant() >> 16) & 0xffu;
+    if (group == 0) group = 8;
+    if (group > dev.q_tiles) group = dev.q_tiles;
+    dev.q_group = group;
+    uint64_t grid = (uint64_t)((dev.q_tiles + group - 1) / group) * group * dev.segments;
     if (grid == 0 || grid > 0x7fffffffull || dev.q_tokens > 0xffffffffull) return cudaErrorInvalidValue;
     // Look-up tables for the main kernel: token -> query, segment -> first document.
     const uint64_t map_bytes = round_up(dev.q_tokens * 4, 16);
