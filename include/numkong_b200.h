@@ -185,6 +185,14 @@ NKB_API void nkb_set_gemm_variant(int variant);
 NKB_API void nkb_set_fp6_native(int native);
 /** Packed rows handled per panel by the distance top-k (rounded up to 256); 0 = sized from the scratch budget. */
 NKB_API void nkb_set_topk_panel_rows(nk_size_t rows);
+/** How the distance top-k selects. 1 (default): for k <= 128 and at least 8,192 packed rows only the first 2,048 packed
+ *  rows are materialised; the rest go through a GEMM whose epilogue stores nothing but values below each row's current
+ *  k-th smallest (at most 512 per row and panel, a row that overflows sends the whole call to the materialising path;
+ *  the filtered path synchronises with its stream before returning). 0: always materialise panels. >= 256: filter with
+ *  that many bootstrap rows whenever the packed matrix is larger (testing). Results are identical in every mode. */
+NKB_API void nkb_set_topk_filter(int mode);
+/** Number of top-k calls redone on the materialising path after a candidate list overflowed (process-wide). */
+NKB_API nk_size_t nkb_topk_filter_fallbacks(void);
 /** Drops the cached device copies of host-resident packed blobs and the staging buffers of the calling thread. */
 NKB_API void nkb_release_caches(void);
 

@@ -57,6 +57,8 @@ def _load() -> ctypes.CDLL:
     lib.nkb_release_caches.restype, lib.nkb_release_caches.argtypes = None, []
     lib.nkb_set_fp6_native.restype, lib.nkb_set_fp6_native.argtypes = None, [ctypes.c_int]
     lib.nkb_set_topk_panel_rows.restype, lib.nkb_set_topk_panel_rows.argtypes = None, [sz]
+    lib.nkb_set_topk_filter.restype, lib.nkb_set_topk_filter.argtypes = None, [ctypes.c_int]
+    lib.nkb_topk_filter_fallbacks.restype, lib.nkb_topk_filter_fallbacks.argtypes = sz, []
     for t in ("f16", "bf16"):
         for op in ("angulars", "euclideans"):
             f = getattr(lib, f"nkb_{op}_packed_topk_{t}")

@@ -41,6 +41,12 @@ struct GemmDev {
     uint32_t int_mode;            // 0 float accumulators, 1 signed i32, 2 unsigned u32
     uint32_t flush_kblocks;       // stages per accumulation span (see the MMA issuer)
     unsigned int *error_word;
+    // Candidate filter of the distance epilogues (see GemmArgs); `candidates == nullptr` means "store the tile".
+    const uint32_t *threshold_keys;
+    uint32_t *candidate_counts;
+    uint2 *candidates;
+    uint32_t candidate_capacity;
+    uint32_t column_id_base;
 };
 
 // Epilogue scratch after the barriers: column factors (2 x 256 f32) + eight 32 x 20-word staging blocks.
@@ -64,26 +70,6 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
     uint32_t in_group = tile % per_group;
     mt = first_m + in_group % group_rows;
     nt = in_group / group_rows;
-}
-
-template <int kEpi>
-__device__ __forceinline__ float finalize(float dot, float a_norm, float b_norm) {
-    if constexpr (kEpi == kEpiAngular) {
-        // NumKong batched rule (include/numkong/spatial/serial.h:257-269): zero norm product gives
-        // 0 when the dot is 0 and 1 otherwise; the result is clamped at 0.
-        float product = a_norm * b_norm;
-        if (product > 0.0f) {
-            float r = rsqrtf(product);
-            r = r * (1.5f - 0.5f * product * r * r);
-            float v = 1.0f - dot * r;
-            return v > 0.0f ? v : 0.0f;
-        }
-        return dot == 0.0f ? 0.0f : 1.0f;
-    } else {
-        // include/numkong/spatial/serial.h:272-278
-        float d2 = a_norm + b_norm - 2.0f * dot;
-        return d2 > 0.0f ? sqrtf(d2) : 0.0f;
-    }
 }
 
 // ---- epilogue helpers shared by the single-CTA and the CTA-pair kernels ---------------------------------
@@ -130,6 +116,39 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
     if constexpr (kEpi != kEpiDot) {
         float an = my_row < p.m ? p.a_norms[my_row] : 0.0f;
         row_factor = kEpi == kEpiAngular ? (an > 0.0f ? rsqrt_refined(an) : 0.0f) : an;
+    }
+    if constexpr (kEpi != kEpiDot) {
+        if (p.candidates != nullptr) {
+            // Filter mode: nothing is stored; a value below its row's threshold is appended to the row's candidate list.
+            // Lists fill in no particular order; a count beyond the capacity tells the consumer that values were dropped.
+            // Values are compared as order-preserving integer keys (selection_key), NaN last, like the selection kernels do.
+            const uint32_t threshold = my_row < p.m ? __ldg(p.threshold_keys + my_row) : 0u;
+#pragma unroll
+            for (int c = 0; c < kCols / 4; ++c) {
+                const float4 f = *reinterpret_cast<const float4 *>(colf + colf_off + c * 4);
+                const float cf[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t raw = acc[c * 4 + j];
+                    const float dot = p.int_mode == 0 ? __uint_as_float(raw) : p.int_mode == 1 ? (float)(int32_t)raw : (float)raw;
+                    float r;
+                    if constexpr (kEpi == kEpiAngular) {
+                        r = fmaxf(fmaf(-(dot * row_factor), cf[j], 1.0f), 0.0f);
+                        if (row_factor == 0.0f || cf[j] == 0.0f) r = dot == 0.0f ? 0.0f : 1.0f;
+                    } else {
+                        r = sqrt_approx(fmaxf(fmaf(-2.0f, dot, row_factor + cf[j]), 0.0f));
+                    }
+                    const uint32_t col = col_base + c * 4 + j;
+                    const uint32_t key = selection_key(r);
+                    if (key < threshold && col < p.n) {
+                        const uint32_t slot = atomicAdd(p.candidate_counts + my_row, 1u);
+                        if (slot < p.candidate_capacity)
+                            p.candidates[(uint64_t)my_row * p.candidate_capacity + slot] = make_uint2(key, col + p.column_id_base);
+                    }
+                }
+            }
+            return;
+        }
     }
 #pragma unroll
     for (int c = 0; c < kCols / 16; ++c) {
@@ -707,6 +726,12 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     dev.flush_kblocks = ki.kind == kKindI8 ? dev.kblocks : (forced_flush ? forced_flush : auto_flush);
     if (dev.flush_kblocks == 0) dev.flush_kblocks = 1;
     dev.error_word = args.error_word;
+    const bool filtering = args.candidates != nullptr && args.epilogue != kEpiDot;
+    dev.threshold_keys = filtering ? args.threshold_keys : nullptr;
+    dev.candidate_counts = filtering ? args.candidate_counts : nullptr;
+    dev.candidates = filtering ? args.candidates : nullptr;
+    dev.candidate_capacity = args.candidate_capacity;
+    dev.column_id_base = args.column_id_base;
 
     if (use_pair) {
         // The packed payload seen as rows of 128 bytes: one 16 KiB chunk = 128 consecutive rows, copied verbatim

@@ -79,6 +79,19 @@ inline bool dtype_supported(uint32_t dt) {
 
 inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 
+#ifdef __CUDACC__
+// Order-preserving integer key of an f32 for selection: a < b  <=>  key(a) < key(b); every NaN shares the last key
+// but one (0xffffffff stays free as "no value").
+__device__ __forceinline__ uint32_t selection_key(float f) {
+    const uint32_t u = __float_as_uint(f);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return 0xfffffffeu;
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float selection_value(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+#endif
+
 struct PackedGeometry {
     uint64_t rows_padded, depth_padded_bytes, payload_offset, norms_offset, total_bytes;
 };
@@ -134,6 +147,14 @@ struct GemmArgs {
     uint64_t depth_padded_bytes;
     unsigned int *error_word;     // device
     int variant;                  // 0 = default for the shape; otherwise forces a tile configuration (testing/tuning)
+    // Candidate filter (distance epilogues only). When `candidates` is set nothing is written to `c`: every value whose
+    // selection key is below its row's threshold key is appended to that row's candidate list as
+    // (selection key, column + column_id_base).
+    const uint32_t *threshold_keys = nullptr;  // one per row of A
+    uint32_t *candidate_counts = nullptr;  // one per row of A; may run past `candidate_capacity` (overflow marker)
+    uint2 *candidates = nullptr;           // rows x candidate_capacity
+    uint32_t candidate_capacity = 0;
+    uint32_t column_id_base = 0;
 };
 cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream);
 // Number of kernels launch_gemm_tc enqueues for these arguments (for launch accounting).

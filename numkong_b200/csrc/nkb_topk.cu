@@ -23,19 +23,14 @@ namespace nkb {
 namespace {
 
 std::atomic<uint64_t> g_panel_rows{0};  // 0 = choose by scratch size
+std::atomic<int> g_filter_mode{1};      // 0 = always materialise; 1 = filter when the shape allows; >= 256 = bootstrap width
+std::atomic<uint64_t> g_filter_fallbacks{0};  // calls redone without the filter after a candidate list overflowed
 
 constexpr int kTopThreads = 256;
 constexpr int kTopMax = 1024;  // largest k supported
 
-__device__ __forceinline__ uint32_t order_key(float f) {
-    uint32_t u = __float_as_uint(f);
-    if ((u & 0x7fffffffu) > 0x7f800000u) return 0xfffffffeu;  // every NaN sorts last
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-__device__ __forceinline__ float key_value(uint32_t k) {
-    uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
-    return __uint_as_float(u);
-}
+__device__ __forceinline__ uint32_t order_key(float f) { return selection_key(f); }
+__device__ __forceinline__ float key_value(uint32_t k) { return selection_value(k); }
 
 // Sorts `n` (a power of two) 64-bit words ascending in shared memory.
 __device__ void bitonic_sort_u64(unsigned long long *data, int n) {
@@ -173,6 +168,82 @@ merge_topk_kernel(float *__restrict__ run_vals, long long *__restrict__ run_ids,
     }
 }
 
+// ---- fused selection: the GEMM epilogue filters, these kernels keep the running lists -------------------
+constexpr uint32_t kFilterTopMax = 128;       // largest k the filtered path serves
+constexpr uint32_t kFilterCapacity = 512;     // candidates kept per row and panel
+constexpr uint32_t kFilterBootstrap = 2048;   // packed rows selected from a materialised panel to get first thresholds
+
+// Sets every row's threshold key from its running list (k-th entry, or "everything passes" while the list is short)
+// and clears the candidate counts and the overflow word.
+__global__ void filter_init_kernel(const float *__restrict__ run_vals, const long long *__restrict__ run_ids, uint32_t top,
+                                   uint64_t rows, uint32_t *__restrict__ threshold_keys, uint32_t *__restrict__ counts,
+                                   uint32_t *__restrict__ overflow) {
+    const uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row == 0) *overflow = 0;
+    if (row >= rows) return;
+    const uint64_t last = row * top + top - 1;
+    threshold_keys[row] = run_ids[last] < 0 ? 0xffffffffu : order_key(run_vals[last]);
+    counts[row] = 0;
+}
+
+// run <- k smallest of (run ++ this row's candidates), ordered by (value, id); then the row's threshold key is renewed
+// and its candidate count cleared. Candidates come from packed rows after everything the running list has seen, so
+// their ids are larger: positions in the combined list break value ties exactly like ids do. One CTA per row.
+__global__ void __launch_bounds__(kTopThreads)
+filter_refine_kernel(float *__restrict__ run_vals, long long *__restrict__ run_ids, const uint2 *__restrict__ candidates,
+                     uint32_t *__restrict__ counts, uint32_t *__restrict__ threshold_keys, uint32_t capacity, uint32_t top,
+                     uint64_t id_origin, uint32_t *__restrict__ overflow) {
+    __shared__ unsigned long long keys[1024];
+    __shared__ long long old_ids[kFilterTopMax];
+    const uint64_t row = blockIdx.x;
+    uint32_t count = counts[row];
+    if (count == 0) return;  // uniform for the CTA: nothing beat the threshold
+    if (count > capacity) {
+        if (threadIdx.x == 0) atomicOr(overflow, 1u);
+        count = capacity;
+    }
+    uint32_t padded = 2;
+    while (padded < top + count) padded <<= 1;
+    const uint64_t base = row * top;
+    for (uint32_t i = threadIdx.x; i < padded; i += blockDim.x) {
+        unsigned long long key = ~0ull;
+        if (i < top) {
+            const long long id = run_ids[base + i];
+            old_ids[i] = id;
+            if (id >= 0) key = ((unsigned long long)order_key(run_vals[base + i]) << 32) | i;
+        } else if (i < top + count) {
+            const uint2 c = candidates[row * capacity + (i - top)];
+            key = ((unsigned long long)c.x << 32) | (unsigned long long)(top + c.y);
+        }
+        keys[i] = key;
+    }
+    bitonic_sort_u64(keys, (int)padded);  // starts and ends with a block-wide barrier
+    for (uint32_t i = threadIdx.x; i < top; i += blockDim.x) {
+        const unsigned long long e = keys[i];
+        const uint32_t low = (uint32_t)e;
+        if (e != ~0ull) {
+            run_vals[base + i] = key_value((uint32_t)(e >> 32));
+            run_ids[base + i] = low < top ? old_ids[low] : (long long)(id_origin + (low - top));
+        } else {
+            run_vals[base + i] = __uint_as_float(0x7f800000u);
+            run_ids[base + i] = -1;
+        }
+        if (i == top - 1) threshold_keys[row] = e != ~0ull ? (uint32_t)(e >> 32) : 0xffffffffu;
+    }
+    if (threadIdx.x == 0) counts[row] = 0;
+}
+
+// Widest panel the filter may scan after `seen` packed rows: the number of later values below the k-th smallest of
+// `seen` grows like (panel / seen) * Gamma(k), so the ratio is chosen to keep k + 8 sqrt(k) + 8 "expected" candidates,
+// scaled by the ratio, inside the capacity (an overflow is still detected and the call redone without the filter).
+uint64_t filter_growth(uint32_t top) {
+    uint32_t root = 1;
+    while (root * root < top) ++root;
+    const uint32_t budget = top + 8 * root + 8;
+    uint32_t ratio = kFilterCapacity / budget;
+    return ratio > 8 ? 8 : ratio;
+}
+
 bool topk_on_device(const float *scores, uint64_t rows, uint64_t cols, uint64_t stride_bytes, uint32_t top,
                     uint64_t id_base, float *vals, long long *ids, cudaStream_t stream) {
     if (rows == 0) return true;
@@ -216,7 +287,8 @@ void topk_smallest_impl(const void *scores, uint64_t rows, uint64_t cols, uint64
 
 // Nearest-k rows of the packed matrix for every row of A, without materialising the distance matrix.
 void spatial_topk_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed, uint64_t m, uint64_t n, uint64_t k,
-                       uint64_t a_stride, uint64_t top, void *out_vals, void *out_ids, uint64_t id_base) {
+                       uint64_t a_stride, uint64_t top, void *out_vals, void *out_ids, uint64_t id_base,
+                       bool allow_filter = true) {
     clear_error();
     if (m == 0 || top == 0) return;
     const MemKind v_kind = classify(out_vals), i_kind = classify(out_ids);
@@ -237,12 +309,22 @@ void spatial_topk_impl(uint32_t dt, int epilogue, const void *a, const void *b_p
     const void *a_dev = resident_matrix(a, a_kind, m, k * dtype_bytes(dt), a_stride, kSlotA, kPieceNone, &a_pitch);
     if (!err || !a_dev) { fail(); return; }
 
+    // Filtered path: only a first narrow panel is materialised and selected from; it gives every row a threshold
+    // (its k-th smallest so far). Wider and wider panels then go through the GEMM with the filter epilogue, which
+    // stores nothing but the few values below the threshold, and a refine kernel folds those into the running lists.
+    const int filter_mode = g_filter_mode.load();
+    const uint64_t bootstrap = filter_mode >= 256 ? round_up((uint64_t)filter_mode, 256) : kFilterBootstrap;
+    const uint64_t growth = filter_growth((uint32_t)top);
+    const bool filtered = allow_filter && filter_mode != 0 && top <= kFilterTopMax && growth >= 2 && bootstrap >= 2 * top &&
+                          (filter_mode >= 256 ? n > bootstrap : n >= 4 * bootstrap) && m <= 131072;
+
     // Panel width: a multiple of 256 packed rows whose m x width f32 scratch stays near 1 GiB.
     uint64_t width = ((1ull << 30) / (m * 4)) / 256 * 256;
     if (g_panel_rows.load()) width = round_up(g_panel_rows.load(), 256);
+    if (filtered) width = bootstrap;
     if (width < 256) width = 256;
     if (width > h.rows_padded) width = h.rows_padded;
-    const uint64_t panels = (n + width - 1) / width;
+    const uint64_t panels = filtered ? 1 : (n + width - 1) / width;
 
     float *a_norms = static_cast<float *>(scratch(kSlotNorms, m * 4));
     float *panel = static_cast<float *>(scratch(kSlotC, m * width * 4));
@@ -281,6 +363,53 @@ void spatial_topk_impl(uint32_t dt, int epilogue, const void *a, const void *b_p
             ok = cuda_ok(cudaGetLastError(), "merge kernel");
         }
     }
+    if (ok && filtered) {
+        // [candidates: m x capacity x 8 B | threshold keys: m x 4 B | counts: m x 4 B | overflow word]
+        const uint64_t cand_bytes = m * kFilterCapacity * 8;
+        uint8_t *filter_mem = static_cast<uint8_t *>(scratch(kSlotAux2, cand_bytes + m * 8 + 64));
+        if (!filter_mem) { fail(); return; }
+        uint2 *candidates = reinterpret_cast<uint2 *>(filter_mem);
+        uint32_t *threshold_keys = reinterpret_cast<uint32_t *>(filter_mem + cand_bytes);
+        uint32_t *counts = threshold_keys + m;
+        uint32_t *overflow = counts + m;
+        filter_init_kernel<<<(unsigned)((m + 255) / 256), 256, 0, stream>>>(run_vals, run_ids, (uint32_t)top, m, threshold_keys,
+                                                                           counts, overflow);
+        g_launches++;
+        ok = cuda_ok(cudaGetLastError(), "filter init kernel");
+        uint64_t seen = width;
+        while (ok && seen < n) {
+            uint64_t cols = growth * seen / 256 * 256;
+            if (cols > n - seen) cols = n - seen;
+            GemmArgs g;
+            g.dtype = dt; g.epilogue = epilogue; g.a = a_dev; g.a_stride = a_pitch;
+            g.b_payload = blob + h.payload_offset + (seen / kChunkRows) * (uint64_t)kblocks * kChunkBytes;
+            g.b_norms = blob + h.norms_offset + seen * 4;
+            g.a_norms = a_norms;
+            g.c = nullptr; g.c_stride = 0; g.m = m; g.n = cols; g.k = k;
+            g.depth_padded_bytes = h.depth_padded_bytes; g.error_word = err; g.variant = current_variant();
+            g.threshold_keys = threshold_keys; g.candidate_counts = counts; g.candidates = candidates;
+            g.candidate_capacity = kFilterCapacity; g.column_id_base = 0;
+            ok = cuda_ok(launch_gemm_tc(g, stream), "tensor-core GEMM kernel (filter)");
+            g_launches += gemm_tc_launch_count(g);
+            if (!ok) break;
+            filter_refine_kernel<<<(unsigned)m, kTopThreads, 0, stream>>>(run_vals, run_ids, candidates, counts, threshold_keys,
+                                                                         kFilterCapacity, (uint32_t)top, id_base + seen, overflow);
+            g_launches++;
+            ok = cuda_ok(cudaGetLastError(), "filter refine kernel");
+            seen += cols;
+        }
+        // A row whose candidates did not fit lost values: redo the whole call on the materialising path. Reading the
+        // word back makes the filtered path synchronise with its stream before it returns.
+        uint32_t overflowed = 0;
+        if (ok) ok = cuda_ok(cudaMemcpyAsync(&overflowed, overflow, 4, cudaMemcpyDeviceToHost, stream), "read overflow word") &&
+                     cuda_ok(cudaStreamSynchronize(stream), "packed_topk");
+        if (ok && read_device_error()) { set_error("a pipeline wait inside the GEMM kernel gave up%s", ""); ok = false; }
+        if (ok && overflowed) {
+            g_filter_fallbacks++;
+            spatial_topk_impl(dt, epilogue, a, b_packed, m, n, k, a_stride, top, out_vals, out_ids, id_base, false);
+            return;
+        }
+    }
     if (ok && v_kind == kMemHost) ok = cuda_ok(cudaMemcpyAsync(out_vals, run_vals, m * top * 4, cudaMemcpyDeviceToHost, stream), "download top-k values");
     if (ok && i_kind == kMemHost) ok = cuda_ok(cudaMemcpyAsync(out_ids, run_ids, m * top * 8, cudaMemcpyDeviceToHost, stream), "download top-k ids");
     if (ok && (v_kind == kMemHost || i_kind == kMemHost || a_kind == kMemHost || b_kind == kMemHost)) {
@@ -298,6 +427,8 @@ using namespace nkb;
 extern "C" {
 
 NKB_API void nkb_set_topk_panel_rows(nk_size_t rows) { g_panel_rows.store(rows); }
+NKB_API void nkb_set_topk_filter(int mode) { g_filter_mode.store(mode < 0 ? 0 : mode); }
+NKB_API nk_size_t nkb_topk_filter_fallbacks(void) { return g_filter_fallbacks.load(); }
 
 NKB_API void nkb_topk_smallest_f32(void const *scores, nk_size_t rows, nk_size_t cols, nk_size_t stride, nk_size_t top,
                                    nk_size_t id_base, void *out_values, void *out_ids) {

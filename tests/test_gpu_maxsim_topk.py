@@ -112,3 +112,64 @@ def test_distance_topk_equals_full_matrix_then_select(dtype, metric):
     # and the distances themselves agree with the oracle
     ref = getattr(oracle, metric)(a, b, dtype)
     assert np.max(np.abs(dist - np.take_along_axis(ref, order, axis=1))) < 2e-6
+
+
+def _select_reference(full, top):
+    order = np.argsort(full, axis=1, kind="stable")[:, :top]
+    return np.take_along_axis(full, order, axis=1), order
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("metric", ["angulars", "euclideans"])
+def test_distance_topk_filtered_equals_materialised(dtype, metric):
+    """The filter epilogue + refine kernels return exactly what selecting from the stored matrix returns,
+    for ragged shapes, duplicated packed rows (ties go to the lower id) and every k the filter serves."""
+    m, n, k = 200, 9001, 64
+    a = syn.normal_matrix(m, k, dtype, 311, normalize=True)
+    b = syn.normal_matrix(n, k, dtype, 312, normalize=True)
+    b[5000:8000] = b[:3000]  # exact duplicates in later panels
+    p = nk.dots_pack(b, dtype)
+    full = getattr(nk, metric + "_packed")(a, p)
+    before = nk.lib.nkb_topk_filter_fallbacks()
+    try:
+        for top in (1, 10, 100, 128):
+            want_d, want_i = _select_reference(full, top)
+            nk.lib.nkb_set_topk_filter(256)
+            dist, ids = getattr(nk, metric + "_packed_topk")(a, p, top, id_base=7)
+            assert np.array_equal(ids - 7, want_i), top
+            assert np.array_equal(dist, want_d), top
+            nk.lib.nkb_set_topk_filter(0)
+            dist0, ids0 = getattr(nk, metric + "_packed_topk")(a, p, top, id_base=7)
+            assert np.array_equal(ids0, ids) and np.array_equal(dist0, dist)
+    finally:
+        nk.lib.nkb_set_topk_filter(1)
+    assert nk.lib.nkb_topk_filter_fallbacks() == before  # random order never overflows a candidate list
+    # default mode picks the filter by itself at this size (>= 8192 packed rows)
+    launches = nk.launch_count()
+    dist, ids = getattr(nk, metric + "_packed_topk")(a, p, 10)
+    want_d, want_i = _select_reference(full, 10)
+    assert np.array_equal(ids, want_i) and np.array_equal(dist, want_d)
+    # norms, bootstrap GEMM + select, threshold init, one filtered panel (GEMM + refine), possibly a staging kernel
+    assert 6 <= nk.launch_count() - launches <= 7
+
+
+def test_distance_topk_filter_overflow_falls_back():
+    """Packed rows ordered from far to near make every later value beat the threshold: the candidate lists
+    overflow, the call is redone on the materialising path, and the answer is still exact."""
+    dtype, m, n, k, top = "f16", 40, 6000, 64, 10
+    rng = np.random.default_rng(5)
+    direction = rng.standard_normal(k)
+    a = syn.encode((direction + 0.05 * rng.standard_normal((m, k))), dtype)
+    mix = np.linspace(-1.0, 1.0, n)[:, None]
+    b = syn.encode(mix * direction + 0.3 * rng.standard_normal((n, k)), dtype)
+    p = nk.dots_pack(b, dtype)
+    full = nk.angulars_packed(a, p)
+    want_d, want_i = _select_reference(full, top)
+    before = nk.lib.nkb_topk_filter_fallbacks()
+    nk.lib.nkb_set_topk_filter(256)
+    try:
+        dist, ids = nk.angulars_packed_topk(a, p, top)
+    finally:
+        nk.lib.nkb_set_topk_filter(1)
+    assert nk.lib.nkb_topk_filter_fallbacks() == before + 1
+    assert np.array_equal(ids, want_i) and np.array_equal(dist, want_d)
