@@ -42,7 +42,7 @@ struct GemmDev {
     uint32_t flush_kblocks;       // stages per accumulation span (see the MMA issuer)
     unsigned int *error_word;
     // Candidate filter of the distance epilogues (see GemmArgs); `candidates == nullptr` means "store the tile".
-    const uint32_t *threshold_keys;
+    const uint32_t *threshold_bits;
     uint32_t *candidate_counts;
     uint2 *candidates;
     uint32_t candidate_capacity;
@@ -102,6 +102,77 @@ __device__ __forceinline__ float column_factor(const GemmDev &p, uint32_t col) {
     return bn;
 }
 
+// One finalised distance. Never NaN and never below -0: a NaN dot or factor falls out of fmaxf as 0.
+template <int kEpi>
+__device__ __forceinline__ float distance_value(uint32_t raw, uint32_t int_mode, float row_factor, float col_factor) {
+    const float dot = int_mode == 0 ? __uint_as_float(raw) : int_mode == 1 ? (float)(int32_t)raw : (float)raw;
+    if constexpr (kEpi == kEpiAngular) {
+        float r = fmaxf(fmaf(-(dot * row_factor), col_factor, 1.0f), 0.0f);
+        if (row_factor == 0.0f || col_factor == 0.0f) r = dot == 0.0f ? 0.0f : 1.0f;
+        return r;
+    } else {
+        return sqrt_approx(fmaxf(fmaf(-2.0f, dot, row_factor + col_factor), 0.0f));
+    }
+}
+
+// Filter mode of the distance epilogues: nothing is stored; the values of this thread's row that lie below the row's
+// threshold are appended to the row's candidate list (in no particular order; a count beyond the capacity tells the
+// consumer that values were dropped). Distances are >= -0 and never NaN, so the signed integer order of their bit
+// patterns is their numeric order (with -0 before +0, as the selection kernels order them) and one integer compare per
+// value decides. Pass 1 only builds a bit mask; a row then reserves all its slots with ONE atomic (a per-value atomic
+// would put its round trip on the critical path of every hit), and pass 2 recomputes and writes the few hits.
+template <int kEpi, int kCols>
+__device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDev &p, uint32_t my_row, uint32_t col_base,
+                                            float row_factor, const float *colf, uint32_t *stage, int lane) {
+    static_assert(kCols % 32 == 0, "whole mask words");
+    const int threshold = my_row < p.m ? (int)__ldg(p.threshold_bits + my_row) : (int)0x80000000;
+    uint32_t mask[kCols / 32];
+#pragma unroll
+    for (int w = 0; w < kCols / 32; ++w) {
+        uint32_t bits = 0;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float4 f = *reinterpret_cast<const float4 *>(colf + w * 32 + c * 4);
+            const float cf[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float r = distance_value<kEpi>(acc[w * 32 + c * 4 + j], p.int_mode, row_factor, cf[j]);
+                bits |= (uint32_t)((int)__float_as_uint(r) < threshold) << (c * 4 + j);
+            }
+        }
+        // Columns past the end of the packed matrix are padding.
+        const uint32_t first = col_base + w * 32;
+        const uint32_t valid = first >= p.n ? 0u : (p.n - first >= 32u ? 0xffffffffu : (1u << (p.n - first)) - 1u);
+        mask[w] = bits & valid;
+    }
+    uint32_t hits = 0;
+#pragma unroll
+    for (int w = 0; w < kCols / 32; ++w) hits += __popc(mask[w]);
+    if (!__any_sync(0xffffffffu, hits != 0)) return;
+    uint32_t slot = 0;
+    if (hits) slot = atomicAdd(p.candidate_counts + my_row, hits);
+    uint2 *list = p.candidates + (uint64_t)my_row * p.candidate_capacity;
+    // Pass 2, 16 columns at a time: a thread with hits parks the 16 accumulators in its own row of the warp's staging
+    // block (shared memory can be indexed by a run-time value, registers cannot) and walks the set bits.
+    uint32_t *mine = stage + lane * kEpiStagePitch;
+#pragma unroll
+    for (int c = 0; c < kCols / 16; ++c) {
+        uint32_t m16 = (mask[c / 2] >> ((c & 1) * 16)) & 0xffffu;
+        if (m16 == 0) continue;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4 *>(mine + q * 4) =
+                make_uint4(acc[c * 16 + q * 4], acc[c * 16 + q * 4 + 1], acc[c * 16 + q * 4 + 2], acc[c * 16 + q * 4 + 3]);
+        while (m16) {
+            const int j = __ffs((int)m16) - 1;
+            m16 &= m16 - 1;
+            const float r = distance_value<kEpi>(mine[j], p.int_mode, row_factor, colf[c * 16 + j]);
+            if (slot < p.candidate_capacity) list[slot] = make_uint2(__float_as_uint(r), col_base + c * 16 + j + p.column_id_base);
+            ++slot;
+        }
+    }
+}
+
 // Finalises and stores this thread's row x kCols accumulators. Values go through the warp's staging block 16 columns at a
 // time so that each store instruction writes 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
 //   row_base  first of the 32 rows this warp owns;  col_base  first of this thread's kCols columns
@@ -119,34 +190,7 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
     }
     if constexpr (kEpi != kEpiDot) {
         if (p.candidates != nullptr) {
-            // Filter mode: nothing is stored; a value below its row's threshold is appended to the row's candidate list.
-            // Lists fill in no particular order; a count beyond the capacity tells the consumer that values were dropped.
-            // Values are compared as order-preserving integer keys (selection_key), NaN last, like the selection kernels do.
-            const uint32_t threshold = my_row < p.m ? __ldg(p.threshold_keys + my_row) : 0u;
-#pragma unroll
-            for (int c = 0; c < kCols / 4; ++c) {
-                const float4 f = *reinterpret_cast<const float4 *>(colf + colf_off + c * 4);
-                const float cf[4] = {f.x, f.y, f.z, f.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t raw = acc[c * 4 + j];
-                    const float dot = p.int_mode == 0 ? __uint_as_float(raw) : p.int_mode == 1 ? (float)(int32_t)raw : (float)raw;
-                    float r;
-                    if constexpr (kEpi == kEpiAngular) {
-                        r = fmaxf(fmaf(-(dot * row_factor), cf[j], 1.0f), 0.0f);
-                        if (row_factor == 0.0f || cf[j] == 0.0f) r = dot == 0.0f ? 0.0f : 1.0f;
-                    } else {
-                        r = sqrt_approx(fmaxf(fmaf(-2.0f, dot, row_factor + cf[j]), 0.0f));
-                    }
-                    const uint32_t col = col_base + c * 4 + j;
-                    const uint32_t key = selection_key(r);
-                    if (key < threshold && col < p.n) {
-                        const uint32_t slot = atomicAdd(p.candidate_counts + my_row, 1u);
-                        if (slot < p.candidate_capacity)
-                            p.candidates[(uint64_t)my_row * p.candidate_capacity + slot] = make_uint2(key, col + p.column_id_base);
-                    }
-                }
-            }
+            filter_tile<kEpi, kCols>(acc, p, my_row, col_base, row_factor, colf + colf_off, stage, lane);
             return;
         }
     }
@@ -165,15 +209,7 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
                 const uint32_t raw = acc[c * 16 + q * 4 + j];
                 if constexpr (kEpi == kEpiDot) out[j] = raw;
                 else {
-                    const float dot = p.int_mode == 0 ? __uint_as_float(raw) : p.int_mode == 1 ? (float)(int32_t)raw : (float)raw;
-                    float r;
-                    if constexpr (kEpi == kEpiAngular) {
-                        r = fmaxf(fmaf(-(dot * row_factor), cf[j], 1.0f), 0.0f);
-                        if (row_factor == 0.0f || cf[j] == 0.0f) r = dot == 0.0f ? 0.0f : 1.0f;
-                    } else {
-                        r = sqrt_approx(fmaxf(fmaf(-2.0f, dot, row_factor + cf[j]), 0.0f));
-                    }
-                    out[j] = __float_as_uint(r);
+                    out[j] = __float_as_uint(distance_value<kEpi>(raw, p.int_mode, row_factor, cf[j]));
                 }
             }
             *reinterpret_cast<uint4 *>(stage + lane * kEpiStagePitch + q * 4) = make_uint4(out[0], out[1], out[2], out[3]);
@@ -727,7 +763,7 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     if (dev.flush_kblocks == 0) dev.flush_kblocks = 1;
     dev.error_word = args.error_word;
     const bool filtering = args.candidates != nullptr && args.epilogue != kEpiDot;
-    dev.threshold_keys = filtering ? args.threshold_keys : nullptr;
+    dev.threshold_bits = filtering ? args.threshold_bits : nullptr;
     dev.candidate_counts = filtering ? args.candidate_counts : nullptr;
     dev.candidates = filtering ? args.candidates : nullptr;
     dev.candidate_capacity = args.candidate_capacity;

@@ -147,10 +147,11 @@ struct GemmArgs {
     uint64_t depth_padded_bytes;
     unsigned int *error_word;     // device
     int variant;                  // 0 = default for the shape; otherwise forces a tile configuration (testing/tuning)
-    // Candidate filter (distance epilogues only). When `candidates` is set nothing is written to `c`: every value whose
-    // selection key is below its row's threshold key is appended to that row's candidate list as
-    // (selection key, column + column_id_base).
-    const uint32_t *threshold_keys = nullptr;  // one per row of A
+    // Candidate filter (distance epilogues only). When `candidates` is set nothing is written to `c`: every value below
+    // its row's threshold is appended to that row's candidate list as (f32 bits of the distance, column + column_id_base).
+    // Thresholds are f32 bit patterns compared as signed integers (distances are >= -0 and never NaN); 0x7fffffff
+    // lets everything pass.
+    const uint32_t *threshold_bits = nullptr;  // one per row of A
     uint32_t *candidate_counts = nullptr;  // one per row of A; may run past `candidate_capacity` (overflow marker)
     uint2 *candidates = nullptr;           // rows x candidate_capacity
     uint32_t candidate_capacity = 0;

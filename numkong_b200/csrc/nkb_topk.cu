@@ -172,17 +172,20 @@ merge_topk_kernel(float *__restrict__ run_vals, long long *__restrict__ run_ids,
 constexpr uint32_t kFilterTopMax = 128;       // largest k the filtered path serves
 constexpr uint32_t kFilterCapacity = 512;     // candidates kept per row and panel
 constexpr uint32_t kFilterBootstrap = 2048;   // packed rows selected from a materialised panel to get first thresholds
+// Thresholds travel as f32 bit patterns that the epilogue compares as signed integers (distances are >= -0, never NaN);
+// the largest positive pattern lets every value pass.
+constexpr uint32_t kPassAll = 0x7fffffffu;
 
-// Sets every row's threshold key from its running list (k-th entry, or "everything passes" while the list is short)
+// Sets every row's threshold from its running list (k-th entry, or "everything passes" while the list is short)
 // and clears the candidate counts and the overflow word.
 __global__ void filter_init_kernel(const float *__restrict__ run_vals, const long long *__restrict__ run_ids, uint32_t top,
-                                   uint64_t rows, uint32_t *__restrict__ threshold_keys, uint32_t *__restrict__ counts,
+                                   uint64_t rows, uint32_t *__restrict__ threshold_bits, uint32_t *__restrict__ counts,
                                    uint32_t *__restrict__ overflow) {
     const uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (row == 0) *overflow = 0;
     if (row >= rows) return;
     const uint64_t last = row * top + top - 1;
-    threshold_keys[row] = run_ids[last] < 0 ? 0xffffffffu : order_key(run_vals[last]);
+    threshold_bits[row] = run_ids[last] < 0 ? kPassAll : __float_as_uint(run_vals[last]);
     counts[row] = 0;
 }
 
@@ -191,7 +194,7 @@ __global__ void filter_init_kernel(const float *__restrict__ run_vals, const lon
 // their ids are larger: positions in the combined list break value ties exactly like ids do. One CTA per row.
 __global__ void __launch_bounds__(kTopThreads)
 filter_refine_kernel(float *__restrict__ run_vals, long long *__restrict__ run_ids, const uint2 *__restrict__ candidates,
-                     uint32_t *__restrict__ counts, uint32_t *__restrict__ threshold_keys, uint32_t capacity, uint32_t top,
+                     uint32_t *__restrict__ counts, uint32_t *__restrict__ threshold_bits, uint32_t capacity, uint32_t top,
                      uint64_t id_origin, uint32_t *__restrict__ overflow) {
     __shared__ unsigned long long keys[1024];
     __shared__ long long old_ids[kFilterTopMax];
@@ -213,7 +216,7 @@ filter_refine_kernel(float *__restrict__ run_vals, long long *__restrict__ run_i
             if (id >= 0) key = ((unsigned long long)order_key(run_vals[base + i]) << 32) | i;
         } else if (i < top + count) {
             const uint2 c = candidates[row * capacity + (i - top)];
-            key = ((unsigned long long)c.x << 32) | (unsigned long long)(top + c.y);
+            key = ((unsigned long long)order_key(__uint_as_float(c.x)) << 32) | (unsigned long long)(top + c.y);
         }
         keys[i] = key;
     }
@@ -228,7 +231,7 @@ filter_refine_kernel(float *__restrict__ run_vals, long long *__restrict__ run_i
             run_vals[base + i] = __uint_as_float(0x7f800000u);
             run_ids[base + i] = -1;
         }
-        if (i == top - 1) threshold_keys[row] = e != ~0ull ? (uint32_t)(e >> 32) : 0xffffffffu;
+        if (i == top - 1) threshold_bits[row] = e != ~0ull ? __float_as_uint(key_value((uint32_t)(e >> 32))) : kPassAll;
     }
     if (threadIdx.x == 0) counts[row] = 0;
 }
@@ -369,10 +372,10 @@ void spatial_topk_impl(uint32_t dt, int epilogue, const void *a, const void *b_p
         uint8_t *filter_mem = static_cast<uint8_t *>(scratch(kSlotAux2, cand_bytes + m * 8 + 64));
         if (!filter_mem) { fail(); return; }
         uint2 *candidates = reinterpret_cast<uint2 *>(filter_mem);
-        uint32_t *threshold_keys = reinterpret_cast<uint32_t *>(filter_mem + cand_bytes);
-        uint32_t *counts = threshold_keys + m;
+        uint32_t *threshold_bits = reinterpret_cast<uint32_t *>(filter_mem + cand_bytes);
+        uint32_t *counts = threshold_bits + m;
         uint32_t *overflow = counts + m;
-        filter_init_kernel<<<(unsigned)((m + 255) / 256), 256, 0, stream>>>(run_vals, run_ids, (uint32_t)top, m, threshold_keys,
+        filter_init_kernel<<<(unsigned)((m + 255) / 256), 256, 0, stream>>>(run_vals, run_ids, (uint32_t)top, m, threshold_bits,
                                                                            counts, overflow);
         g_launches++;
         ok = cuda_ok(cudaGetLastError(), "filter init kernel");
@@ -387,12 +390,12 @@ void spatial_topk_impl(uint32_t dt, int epilogue, const void *a, const void *b_p
             g.a_norms = a_norms;
             g.c = nullptr; g.c_stride = 0; g.m = m; g.n = cols; g.k = k;
             g.depth_padded_bytes = h.depth_padded_bytes; g.error_word = err; g.variant = current_variant();
-            g.threshold_keys = threshold_keys; g.candidate_counts = counts; g.candidates = candidates;
+            g.threshold_bits = threshold_bits; g.candidate_counts = counts; g.candidates = candidates;
             g.candidate_capacity = kFilterCapacity; g.column_id_base = 0;
             ok = cuda_ok(launch_gemm_tc(g, stream), "tensor-core GEMM kernel (filter)");
             g_launches += gemm_tc_launch_count(g);
             if (!ok) break;
-            filter_refine_kernel<<<(unsigned)m, kTopThreads, 0, stream>>>(run_vals, run_ids, candidates, counts, threshold_keys,
+            filter_refine_kernel<<<(unsigned)m, kTopThreads, 0, stream>>>(run_vals, run_ids, candidates, counts, threshold_bits,
                                                                          kFilterCapacity, (uint32_t)top, id_base + seen, overflow);
             g_launches++;
             ok = cuda_ok(cudaGetLastError(), "filter refine kernel");
