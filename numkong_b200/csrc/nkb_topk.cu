@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(kTopThreads)
 topk_smallest_kernel(const float *__restrict__ scores, uint64_t cols, uint64_t stride_elems, uint32_t top,
                      uint64_t id_base, float *__restrict__ out_vals, long long *__restrict__ out_ids) {
     __shared__ uint32_t hist[256];
-    __shared__ uint32_t s_prefix, s_remaining, s_count, s_eq_seen;
+    __shared__ uint32_t s_prefix, s_remaining, s_equal, s_count, s_eq_seen;
     __shared__ uint32_t warp_tot[kTopThreads / 32];
     __shared__ unsigned long long cand[kTopMax];
     const float *row = scores + (uint64_t)blockIdx.x * stride_elems;
@@ -72,15 +72,26 @@ topk_smallest_kernel(const float *__restrict__ scores, uint64_t cols, uint64_t s
                 if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
             }
             __syncthreads();
-            if (threadIdx.x == 0) {
-                uint32_t cum = 0, bin = 0;
-                for (; bin < 256; ++bin) {
-                    if (cum + hist[bin] >= remaining) break;
-                    cum += hist[bin];
+            {
+                // One bin per thread (the block has exactly 256): inclusive prefix sum over the bins, then the one
+                // thread whose bin holds the remaining-th smallest key publishes it.
+                const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+                const uint32_t mine = hist[threadIdx.x];
+                uint32_t incl = mine;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const uint32_t o = __shfl_up_sync(0xffffffffu, incl, off);
+                    if (lane >= off) incl += o;
                 }
-                if (bin > 255) bin = 255;
-                s_prefix = prefix | (bin << shift);
-                s_remaining = remaining - cum;
+                if (lane == 31) warp_tot[w] = incl;
+                __syncthreads();
+                for (int i = 0; i < w; ++i) incl += warp_tot[i];
+                const uint32_t excl = incl - mine;
+                if (excl < remaining && incl >= remaining) {
+                    s_prefix = prefix | ((uint32_t)threadIdx.x << shift);
+                    s_remaining = remaining - excl;
+                    s_equal = mine;
+                }
             }
             __syncthreads();
             prefix = s_prefix;
@@ -94,7 +105,16 @@ topk_smallest_kernel(const float *__restrict__ scores, uint64_t cols, uint64_t s
     if (threadIdx.x == 0) { s_count = 0; s_eq_seen = 0; }
     for (int i = threadIdx.x; i < (int)padded; i += blockDim.x) cand[i] = ~0ull;
     __syncthreads();
-    if (want > 0) {
+    if (want > 0 && s_equal == remaining) {
+        // Every element equal to the k-th smallest is kept: no order to respect while collecting (the sort restores it).
+        for (uint64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+            const uint32_t key = order_key(row[c]);
+            if (key <= prefix) {
+                const uint32_t slot = atomicAdd(&s_count, 1u);
+                if (slot < kTopMax) cand[slot] = ((unsigned long long)key << 32) | (unsigned long long)(uint32_t)c;
+            }
+        }
+    } else if (want > 0) {
         const uint64_t rounds = (cols + blockDim.x - 1) / blockDim.x;
         for (uint64_t r = 0; r < rounds; ++r) {
             const uint64_t c = r * blockDim.x + threadIdx.x;
