@@ -39,6 +39,12 @@ STORE = {1: np.uint8, 2: np.int16}
 SEEDS = {"bf16": 1, "f16": 1, "e4m3": 2, "e5m2": 2, "e2m3": 2, "e3m2": 2, "i8": 0, "u8": 0}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu capture summarised in
+# profiles/gemm_tc_pair_bf16_8192_dram_traffic.md (1.116e9 read + 2.52e8 written; algorithmic bytes A + packed B + C
+# are 5.37e8). Keyed by (dtype, rows of A); other configurations report null.
+NCU_DRAM_BYTES_PER_LAUNCH = {("bf16", 8192): 1_367_000_000}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -343,7 +349,7 @@ def main():
             "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": dtype_arith(dtype), "data": "synthetic", "config": workload_config(dtype, world),
             "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peak, "unit": "TFLOP/s", "frac": achieved_tflops / peak,
-                         "traffic": None,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((dtype, args.rows)),
                          "note": f"peak = {peaks['source']} cuBLAS bf16 burst {peaks['bf16_tflops']} TF/s"
                                  + ("" if dtype in ("bf16", "f16") else " x 2 for 8-bit operands (no measured 8-bit figure on this pool)")},
             "cpu_baseline": cpu_baseline,

@@ -84,33 +84,46 @@ __global__ void maxsim_prepare_kernel(const uint64_t *q_offsets, uint64_t n_quer
     }
 }
 
-// Largest value and its FIRST position among columns [j0, j1) of a 32-column chunk held in registers (all 32 when
-// kFull). Eight independent running maxima (columns j, j+8, ...) keep the comparison chains short; they are merged
-// pairwise with ties going to the lower position, which is exactly the winner of a left-to-right scan with `>`.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// Largest value of a 32-column chunk held in registers and, on request, its FIRST position. Column j counts when bit j
+// of `inside` is set (kFull: every column counts); the others read as the lowest float.
+//   chunk_maximum()   four group maxima (8 columns each, three-input max) and their maximum: 18 instructions per chunk
+//   chunk_position()  first column equal to the maximum: the first group whose maximum matches is selected into eight
+//                     values and scanned from the back. Only needed when the chunk beats the running maximum of some row.
+// Equal dots resolve to the lower column, like a left-to-right scan with `>` does.
 template <bool kFull>
-__device__ __forceinline__ void chunk_argmax(const uint32_t (&v)[32], uint32_t j0, uint32_t j1, float &best, uint32_t &best_j) {
-    constexpr float kLowest = -3.402823466e+38f;
-    float bv[8];
-    uint32_t bi[8];
+__device__ __forceinline__ float chunk_value(const uint32_t (&v)[32], uint32_t inside, int j) {
+    return (kFull || ((inside >> j) & 1u)) ? __uint_as_float(v[j]) : -3.402823466e+38f;
+}
+template <bool kFull>
+__device__ __forceinline__ float chunk_maximum(const uint32_t (&v)[32], uint32_t inside, float (&group)[4]) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        bv[c] = (kFull || ((uint32_t)c >= j0 && (uint32_t)c < j1)) ? __uint_as_float(v[c]) : kLowest;
-        bi[c] = c;
+    for (int g = 0; g < 4; ++g) {
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = chunk_value<kFull>(v, inside, 8 * g + i);
+        group[g] = max3(max3(x[0], x[1], x[2]), max3(x[3], x[4], x[5]), fmaxf(x[6], x[7]));
     }
+    return fmaxf(max3(group[0], group[1], group[2]), group[3]);
+}
+template <bool kFull>
+__device__ __forceinline__ uint32_t chunk_position(const uint32_t (&v)[32], uint32_t inside, const float (&group)[4], float top) {
+    const bool in0 = group[0] == top, in1 = group[1] == top, in2 = group[2] == top;
+    const uint32_t first = in0 ? 0u : in1 ? 8u : in2 ? 16u : 24u;
+    const uint32_t group_inside = inside >> first;
+    uint32_t at = 7;
 #pragma unroll
-    for (int j = 8; j < 32; ++j) {
-        const float x = __uint_as_float(v[j]);
-        const bool inside = kFull || ((uint32_t)j >= j0 && (uint32_t)j < j1);
-        if (inside && x > bv[j & 7]) { bv[j & 7] = x; bi[j & 7] = j; }
+    for (int i = 6; i >= 0; --i) {
+        const uint32_t raw = in0 ? v[i] : in1 ? v[8 + i] : in2 ? v[16 + i] : v[24 + i];
+        const float w = (kFull || ((group_inside >> i) & 1u)) ? __uint_as_float(raw) : -3.402823466e+38f;
+        at = w == top ? (uint32_t)i : at;
     }
-#pragma unroll
-    for (int s = 1; s < 8; s <<= 1) {
-#pragma unroll
-        for (int c = 0; c < 8; c += 2 * s)
-            if (bv[c + s] > bv[c] || (bv[c + s] == bv[c] && bi[c + s] < bi[c])) { bv[c] = bv[c + s]; bi[c] = bi[c + s]; }
-    }
-    best = bv[0];
-    best_j = bi[0];
+    return first + at;
 }
 
 template <int kKind>
@@ -234,10 +247,17 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
         const uint64_t row = (uint64_t)q_tile * kMsBM + quarter * 32u + lane;
         const bool row_ok = row < p.q_tokens;
         const float q_inv = row_ok ? p.q_inv[row] : 0.0f;
-        long long qid = -1;  // query this token belongs to (-1 for padding rows)
-        if (row_ok) qid = (long long)p.q_token_query[row];
-        const long long qid_above = __shfl_up_sync(0xffffffffu, qid, 1);
-        const bool segment_head = qid >= 0 && (lane == 0 || qid_above != qid);
+        constexpr uint32_t kNoQuery = 0xffffffffu;  // padding rows
+        const uint32_t qid = row_ok ? p.q_token_query[row] : kNoQuery;
+        const uint32_t qid_above = __shfl_up_sync(0xffffffffu, qid, 1);
+        const bool segment_head = qid != kNoQuery && (lane == 0 || qid_above != qid);
+        // Bit b: the lane 2^b further down belongs to the same query (the per-document sums are segmented by query).
+        uint32_t joins = 0;
+#pragma unroll
+        for (int b = 0; b < 5; ++b) {
+            const uint32_t other_q = __shfl_down_sync(0xffffffffu, qid, 1u << b);
+            if (lane + (1 << b) < 32 && other_q == qid) joins |= 1u << b;
+        }
         float *part_val = reinterpret_cast<float *>(smem_gen + kMsPartialOffset);
         uint32_t *part_arg = reinterpret_cast<uint32_t *>(smem_gen + kMsPartialOffset + kMsPartialBytes / 2);
 
@@ -267,10 +287,9 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                 }
                 double sum = (double)angular;
 #pragma unroll
-                for (int off = 1; off < 32; off <<= 1) {
-                    const double other = __shfl_down_sync(0xffffffffu, sum, off);
-                    const long long other_q = __shfl_down_sync(0xffffffffu, qid, off);
-                    if (lane + off < 32 && other_q == qid) sum += other;
+                for (int b = 0; b < 5; ++b) {
+                    const double other = __shfl_down_sync(0xffffffffu, sum, 1u << b);
+                    if ((joins >> b) & 1u) sum += other;
                 }
                 if (segment_head) {
                     if (p.total_f64) atomicAdd(p.total_f64, sum);
@@ -298,15 +317,14 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                 const uint64_t lo = c0 > tok_begin ? c0 : tok_begin;
                 const uint64_t hi = c0 + 32 < tok_end ? c0 + 32 : tok_end;
                 if (lo >= hi) continue;  // nothing of this CTA's run in the chunk
+                float group[4];
                 if (lo == c0 && hi == c0 + 32 && hi <= cur_end) {
                     // The whole chunk lies inside the current document.
-                    float best;
-                    uint32_t best_j;
-                    chunk_argmax<true>(v, 0, 32, best, best_j);
-                    if (best > run) { run = best; arg = (uint32_t)(c0 + best_j); }
+                    const float best = chunk_maximum<true>(v, 0xffffffffu, group);
+                    if (best > run) { run = best; arg = (uint32_t)c0 + chunk_position<true>(v, 0xffffffffu, group, best); }
                 } else {
-                    // Document boundaries (or an end of the run) fall inside or before the chunk: walk it piece by piece
-                    // with predicated passes over the 32 registers. Boundaries are the same for every thread.
+                    // Document boundaries (or an end of the run) fall inside or before the chunk: walk it piece by piece,
+                    // masking the columns outside the piece. Boundaries are the same for every thread.
                     uint64_t pos = lo;
                     while (pos < hi) {
                         while (pos >= cur_end) {
@@ -315,10 +333,10 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                             cur_end = end_of_doc(cur_doc);
                         }
                         const uint64_t piece_end = cur_end < hi ? cur_end : hi;
-                        float best;
-                        uint32_t best_j;
-                        chunk_argmax<false>(v, (uint32_t)(pos - c0), (uint32_t)(piece_end - c0), best, best_j);
-                        if (best > run) { run = best; arg = (uint32_t)(c0 + best_j); }
+                        const uint32_t j0 = (uint32_t)(pos - c0), j1 = (uint32_t)(piece_end - c0);  // 0 <= j0 < j1 <= 32
+                        const uint32_t inside = (0xffffffffu >> (32u - j1)) & (0xffffffffu << j0);
+                        const float best = chunk_maximum<false>(v, inside, group);
+                        if (best > run) { run = best; arg = (uint32_t)c0 + chunk_position<false>(v, inside, group, best); }
                         pos = piece_end;
                     }
                 }
