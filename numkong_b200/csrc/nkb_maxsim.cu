@@ -39,7 +39,7 @@ constexpr int kMsBarrierOffset = kMsStages * kMsStageBytes;
 constexpr int kMsInvCache = 36 * kMsBN;   // tokens (a run is about 32 tiles plus one document)
 constexpr int kMsEndCache = 256;          // documents
 constexpr int kMsCacheOffset = kMsBarrierOffset + 256;
-constexpr int kMsPartialOffset = kMsCacheOffset + kMsInvCache * 4 + kMsEndCache * 8;
+constexpr int kMsPartialOffset = kMsCacheOffset + kMsInvCache * 4 + kMsEndCache * 4;
 constexpr int kMsPartialBytes = 2 * 4 * 4 * 32 * 8;  // (max, argmax) of 3 partner warps x 4 quarters, two documents deep
 constexpr int kMsSmemTotal = kMsPartialOffset + kMsPartialBytes + 1024;
 
@@ -167,25 +167,28 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
     const uint64_t tile_end = has_work ? (tok_end + kMsBN - 1) / kMsBN : tile_begin;  // empty documents only -> no tiles
     // Shared-memory copies of what the epilogue looks up per document.
     float *inv_cache = reinterpret_cast<float *>(smem_gen + kMsCacheOffset);
-    uint64_t *end_cache = reinterpret_cast<uint64_t *>(smem_gen + kMsCacheOffset + kMsInvCache * 4);
-    const uint64_t cache_base = tile_begin * kMsBN;  // first token held in inv_cache
+    // Everything the epilogue indexes with is kept relative to the CTA's first tile / first document, in 32 bits (a run
+    // of 2^32 tokens or documents would take hours): 64-bit compares cost the epilogue's busiest pipe twice as much.
+    uint32_t *end_cache = reinterpret_cast<uint32_t *>(smem_gen + kMsCacheOffset + kMsInvCache * 4);
+    const uint64_t cache_base = tile_begin * kMsBN;  // first token held in inv_cache = origin of relative token positions
+    const uint32_t run_lo = (uint32_t)(tok_begin - cache_base), run_hi = (uint32_t)(tok_end - cache_base);
+    const uint32_t run_docs = (uint32_t)(doc_end - doc_begin), run_tiles = (uint32_t)(tile_end - tile_begin);
     if (has_work) {
         for (uint32_t i = threadIdx.x; i < (uint32_t)kMsInvCache; i += blockDim.x)
             inv_cache[i] = cache_base + i < p.d_tokens ? __ldg(p.d_inv + cache_base + i) : 0.0f;
         for (uint32_t i = threadIdx.x; i < (uint32_t)kMsEndCache; i += blockDim.x)
-            end_cache[i] = doc_begin + i < p.n_docs ? p.d_offsets[doc_begin + i + 1] : p.d_tokens;
+            end_cache[i] = i < run_docs ? (uint32_t)(p.d_offsets[doc_begin + i + 1] - cache_base) : run_hi;
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    auto inverse_norm_of = [&](uint32_t token) {
-        const uint64_t rel = (uint64_t)token - cache_base;
-        return rel < (uint64_t)kMsInvCache ? inv_cache[rel] : __ldg(p.d_inv + token);
+    // Inverse norm of the document token at relative position `rel`; end (relative) of the run's document number `doc`.
+    auto inverse_norm_of = [&](uint32_t rel) {
+        return rel < (uint32_t)kMsInvCache ? inv_cache[rel] : __ldg(p.d_inv + cache_base + rel);
     };
-    auto end_of_doc = [&](uint64_t doc) {
-        const uint64_t rel = doc - doc_begin;
-        return rel < (uint64_t)kMsEndCache ? end_cache[rel] : p.d_offsets[doc + 1];
+    auto end_of_doc = [&](uint32_t doc) {
+        return doc < (uint32_t)kMsEndCache ? end_cache[doc] : (uint32_t)(p.d_offsets[doc_begin + doc + 1] - cache_base);
     };
 
     if (warp == 0) {
@@ -258,14 +261,16 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             const uint32_t other_q = __shfl_down_sync(0xffffffffu, qid, 1u << b);
             if (lane + (1 << b) < 32 && other_q == qid) joins |= 1u << b;
         }
+        // Where this query's scores of the run's documents go (segment heads of the all-pairs call only).
+        float *score_row = segment_head && p.scores_f32 ? p.scores_f32 + (uint64_t)qid * p.score_stride + doc_begin : nullptr;
         float *part_val = reinterpret_cast<float *>(smem_gen + kMsPartialOffset);
         uint32_t *part_arg = reinterpret_cast<uint32_t *>(smem_gen + kMsPartialOffset + kMsPartialBytes / 2);
 
-        uint64_t cur_doc = doc_begin;
-        uint64_t cur_end = has_work ? end_of_doc(cur_doc) : 0;
+        uint32_t cur_doc = 0;                                    // number of the current document within the run
+        uint32_t cur_end = has_work ? end_of_doc(0) : 0;         // its end, relative
         uint32_t docs_done = 0;
         float run = -3.402823466e+38f;
-        uint32_t arg = 0;
+        uint32_t arg = 0;                                        // relative position of the running winner
 
         // Closes the current document for this quarter. Called by all four warps of the quarter, in the same order.
         auto finish_doc = [&]() {
@@ -293,7 +298,7 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                 }
                 if (segment_head) {
                     if (p.total_f64) atomicAdd(p.total_f64, sum);
-                    else atomicAdd(p.scores_f32 + (uint64_t)qid * p.score_stride + cur_doc, (float)sum);
+                    else atomicAdd(score_row + cur_doc, (float)sum);
                 }
             }
             ++docs_done;
@@ -301,9 +306,8 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             arg = 0;
         };
 
-        uint32_t local = 0;
         bool ok = true;
-        for (uint64_t t = tile_begin; t < tile_end && ok; ++t, ++local) {
+        for (uint32_t local = 0; local < run_tiles && ok; ++local) {
             const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
             if (!mbar_wait(tmem_full_bar(acc), acc_phase, 4, p.error_word)) { ok = false; break; }
             tc_fence_after_sync();
@@ -313,30 +317,28 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                 uint32_t v[32];
                 tmem_ld_32x32(t_addr + half * 32, v);
                 tmem_ld_wait_for(v);
-                const uint64_t c0 = t * kMsBN + sub * 64u + (uint64_t)half * 32;
-                const uint64_t lo = c0 > tok_begin ? c0 : tok_begin;
-                const uint64_t hi = c0 + 32 < tok_end ? c0 + 32 : tok_end;
-                if (lo >= hi) continue;  // nothing of this CTA's run in the chunk
+                const uint32_t c0 = local * kMsBN + sub * 64u + (uint32_t)half * 32u;  // relative position of column 0
                 float group[4];
-                if (lo == c0 && hi == c0 + 32 && hi <= cur_end) {
-                    // The whole chunk lies inside the current document.
+                if (c0 >= run_lo && c0 + 32u <= cur_end) {
+                    // The whole chunk lies inside the current document (documents end inside the run).
                     const float best = chunk_maximum<true>(v, 0xffffffffu, group);
-                    if (best > run) { run = best; arg = (uint32_t)c0 + chunk_position<true>(v, 0xffffffffu, group, best); }
+                    if (best > run) { run = best; arg = c0 + chunk_position<true>(v, 0xffffffffu, group, best); }
                 } else {
                     // Document boundaries (or an end of the run) fall inside or before the chunk: walk it piece by piece,
                     // masking the columns outside the piece. Boundaries are the same for every thread.
-                    uint64_t pos = lo;
+                    const uint32_t hi = c0 + 32u < run_hi ? c0 + 32u : run_hi;
+                    uint32_t pos = c0 > run_lo ? c0 : run_lo;
                     while (pos < hi) {
                         while (pos >= cur_end) {
                             finish_doc();
                             ++cur_doc;
                             cur_end = end_of_doc(cur_doc);
                         }
-                        const uint64_t piece_end = cur_end < hi ? cur_end : hi;
-                        const uint32_t j0 = (uint32_t)(pos - c0), j1 = (uint32_t)(piece_end - c0);  // 0 <= j0 < j1 <= 32
+                        const uint32_t piece_end = cur_end < hi ? cur_end : hi;
+                        const uint32_t j0 = pos - c0, j1 = piece_end - c0;  // 0 <= j0 < j1 <= 32
                         const uint32_t inside = (0xffffffffu >> (32u - j1)) & (0xffffffffu << j0);
                         const float best = chunk_maximum<false>(v, inside, group);
-                        if (best > run) { run = best; arg = (uint32_t)c0 + chunk_position<false>(v, inside, group, best); }
+                        if (best > run) { run = best; arg = c0 + chunk_position<false>(v, inside, group, best); }
                         pos = piece_end;
                     }
                 }
@@ -344,16 +346,16 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             tc_fence_before_sync();
             mbar_arrive(tmem_empty_bar(acc));
             // Documents that end inside this tile are complete for every warp of the quarter once it gets here.
-            const uint64_t tile_hi = (t + 1) * kMsBN < tok_end ? (t + 1) * kMsBN : tok_end;
-            while (cur_doc < doc_end && cur_end <= tile_hi) {
+            const uint32_t tile_hi = (local + 1u) * kMsBN < run_hi ? (local + 1u) * kMsBN : run_hi;
+            while (cur_doc < run_docs && cur_end <= tile_hi) {
                 finish_doc();
                 ++cur_doc;
-                cur_end = cur_doc < doc_end ? end_of_doc(cur_doc) : ~0ull;
+                cur_end = cur_doc < run_docs ? end_of_doc(cur_doc) : 0u;  // 0: no chunk is "inside" once the run is done
             }
         }
         // Normally nothing is left here: every document of the run ends inside one of its tiles.
         if (ok && has_work) {
-            while (cur_doc < doc_end) {
+            while (cur_doc < run_docs) {
                 finish_doc();
                 ++cur_doc;
             }
