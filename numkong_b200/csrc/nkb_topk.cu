@@ -9,8 +9,13 @@
 //   topk_smallest_kernel   one CTA per row: exact radix select (4 x 8-bit passes over order-preserving
 //                          integer keys), ordered tie handling, bitonic sort of the survivors
 //   merge_topk_kernel      merges a panel's k best into the running k best
-// The batched-distance top-k walks the packed B matrix in column panels: tensor-core GEMM with the
-// distance epilogue into a scratch panel, select, merge.
+//   filter_init_kernel / filter_refine_kernel   thresholds and running lists of the filtered path
+// The batched-distance top-k walks the packed B matrix in column panels. Materialising path: tensor-core GEMM
+// with the distance epilogue into a scratch panel, select, merge. Filtered path (k <= 128, large packed
+// matrices): only a first narrow panel is materialised; it gives every row a threshold (its k-th smallest so
+// far), and the remaining, ever wider panels run the GEMM with a filter epilogue that writes nothing but the few
+// values below the threshold, which a refine kernel folds into the running lists. Both paths return the same
+// bits; a candidate list that overflows sends the call back to the materialising path.
 #include <atomic>
 #include <cstdio>
 #include <cstring>

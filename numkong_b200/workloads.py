@@ -30,25 +30,46 @@ def _timed(torch, fn, steps: int, warmup: int = 2) -> float:
     return start.elapsed_time(stop) / steps / 1e3
 
 
-def run_nearest(queries: int, corpus: int, depth: int, top: int, dtype: str = "f16", steps: int = 5, seed: int = 3):
+def _device_rows(torch, rows: int, depth: int, dtype: str, seed: int):
+    """L2-normalised N(0,1) rows made on the device (large corpora: the host generator would dominate the run)."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    out = torch.empty((rows, depth), dtype=torch.float16 if dtype == "f16" else torch.bfloat16, device="cuda")
+    for r in range(0, rows, 1 << 18):
+        n = min(1 << 18, rows - r)
+        x = torch.randn((n, depth), generator=gen, device="cuda", dtype=torch.float32)
+        out[r:r + n] = (x / x.norm(dim=1, keepdim=True)).to(out.dtype)
+    return out
+
+
+def run_nearest(queries: int, corpus: int, depth: int, top: int, dtype: str = "f16", steps: int = 5, seed: int = 3,
+                warmup: int = 2):
     import torch
     import numkong_b200 as nk
     from numkong_b200 import synthetic as syn
-    q = syn.normal_matrix(queries, depth, dtype, seed, normalize=True)
-    c = np.concatenate([syn.normal_matrix(min(65536, corpus - r), depth, dtype, seed + 1 + r, normalize=True)
-                        for r in range(0, corpus, 65536)])
-    tq, tc = torch.from_numpy(q.view(np.int16)).cuda(), torch.from_numpy(c.view(np.int16)).cuda()
+    if corpus * depth > (1 << 27):
+        tq, tc = _device_rows(torch, queries, depth, dtype, seed), _device_rows(torch, corpus, depth, dtype, seed + 1)
+        data = "device generator"
+    else:
+        q = syn.normal_matrix(queries, depth, dtype, seed, normalize=True)
+        c = np.concatenate([syn.normal_matrix(min(65536, corpus - r), depth, dtype, seed + 1 + r, normalize=True)
+                            for r in range(0, corpus, 65536)])
+        tq, tc = torch.from_numpy(q.view(np.int16)).cuda(), torch.from_numpy(c.view(np.int16)).cuda()
+        data = "host generator"
     packed = nk.dots_pack(tc, dtype)
+    del tc
     launches0 = nk.launch_count()
-    seconds = _timed(torch, lambda: nk.angulars_packed_topk(tq, packed, top, dtype=dtype), steps)
-    launches = (nk.launch_count() - launches0) // (steps + 2)
+    seconds = _timed(torch, lambda: nk.angulars_packed_topk(tq, packed, top, dtype=dtype), steps, warmup)
+    launches = (nk.launch_count() - launches0) // (steps + warmup)
     assert nk.synchronize() == 0
     ops = 2.0 * queries * corpus * depth
     return {"workload": f"angular top-{top}: {queries} {dtype} queries x {corpus} corpus rows, depth {depth}", "ms": seconds * 1e3,
-            "gso_per_s": ops / seconds / 1e9, "kernels_per_call": int(launches)}
+            "gso_per_s": ops / seconds / 1e9, "kernels_per_call": int(launches), "steps": steps, "warmup": warmup, "data": data,
+            "filter_fallbacks": int(nk.lib.nkb_topk_filter_fallbacks())}
 
 
-def run_maxsim(queries: int, docs: int, depth: int = 128, top: int = 100, q_tokens: int = 32, steps: int = 3, seed: int = 5):
+def run_maxsim(queries: int, docs: int, depth: int = 128, top: int = 100, q_tokens: int = 32, steps: int = 3, seed: int = 5,
+               warmup: int = 2):
     import torch
     import numkong_b200 as nk
     from numkong_b200 import synthetic as syn
@@ -57,11 +78,16 @@ def run_maxsim(queries: int, docs: int, depth: int = 128, top: int = 100, q_toke
     d_off = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
     q_off = (np.arange(queries + 1) * q_tokens).astype(np.int64)
     total = int(d_off[-1])
-    q = syn.normal_matrix(queries * q_tokens, depth, "bf16", seed + 1, normalize=True)
-    d = np.concatenate([syn.normal_matrix(min(1 << 20, total - r), depth, "bf16", seed + 2 + r, normalize=True)
-                        for r in range(0, total, 1 << 20)])
-    tq = nk.maxsim_pack(torch.from_numpy(q.view(np.int16)).cuda(), "bf16")
-    td = nk.maxsim_pack(torch.from_numpy(d.view(np.int16)).cuda(), "bf16")
+    if total * depth > (1 << 27):
+        q, d = _device_rows(torch, queries * q_tokens, depth, "bf16", seed + 1), _device_rows(torch, total, depth, "bf16", seed + 2)
+    else:
+        qh = syn.normal_matrix(queries * q_tokens, depth, "bf16", seed + 1, normalize=True)
+        dh = np.concatenate([syn.normal_matrix(min(1 << 20, total - r), depth, "bf16", seed + 2 + r, normalize=True)
+                             for r in range(0, total, 1 << 20)])
+        q, d = torch.from_numpy(qh.view(np.int16)).cuda(), torch.from_numpy(dh.view(np.int16)).cuda()
+    tq = nk.maxsim_pack(q, "bf16")
+    td = nk.maxsim_pack(d, "bf16")
+    del q, d
     tqo, tdo = torch.from_numpy(q_off).cuda(), torch.from_numpy(d_off).cuda()
     state = {}
 
@@ -69,13 +95,11 @@ def run_maxsim(queries: int, docs: int, depth: int = 128, top: int = 100, q_toke
         state["scores"] = nk.maxsims_packed(tq, tqo, td, tdo)
         state["best"] = nk.topk_smallest(state["scores"], min(top, docs))
 
-    seconds = _timed(torch, step, steps)
-    score_seconds = _timed(torch, lambda: nk.maxsims_packed(tq, tqo, td, tdo), steps, warmup=1)
+    seconds = _timed(torch, step, steps, warmup)
     assert nk.synchronize() == 0
     ops = 2.0 * queries * q_tokens * total * depth
     return {"workload": f"MaxSim top-{top}: {queries} queries x {q_tokens} tokens vs {docs} documents ({total} tokens), depth {depth}, bf16",
-            "ms": seconds * 1e3, "score_ms": score_seconds * 1e3, "gso_per_s": ops / seconds / 1e9,
-            "score_gso_per_s": ops / score_seconds / 1e9}
+            "ms": seconds * 1e3, "gso_per_s": ops / seconds / 1e9, "steps": steps, "warmup": warmup}
 
 
 def main():
@@ -88,11 +112,12 @@ def main():
     ap.add_argument("--top", type=int, default=None)
     ap.add_argument("--dtype", default="f16")
     ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=2)
     a = ap.parse_args()
     if a.workload == "nearest":
-        out = run_nearest(a.queries or 8192, a.corpus, a.depth or 768, a.top or 10, a.dtype, a.steps)
+        out = run_nearest(a.queries or 8192, a.corpus, a.depth or 768, a.top or 10, a.dtype, a.steps, warmup=a.warmup)
     else:
-        out = run_maxsim(a.queries or 256, a.docs, a.depth or 128, a.top or 100, steps=a.steps)
+        out = run_maxsim(a.queries or 256, a.docs, a.depth or 128, a.top or 100, steps=a.steps, warmup=a.warmup)
     print(json.dumps(out))
 
 
