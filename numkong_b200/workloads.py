@@ -2,6 +2,13 @@
 
     python -m numkong_b200.workloads nearest --queries 8192 --corpus 65536 --depth 768 --top 10 --dtype f16
     python -m numkong_b200.workloads maxsim  --queries 256 --docs 20000 --depth 128 --top 100
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 4 --master-addr 127.0.0.1 --master-port 29500 \
+        -m numkong_b200.workloads nearest --queries 65536 --corpus 10000000 --sharded
+
+With --sharded (one process per GPU under torchrun) the corpus rows / the documents are split across the ranks, every rank
+searches its own shard and the k best per query are merged on rank 0 with one gather; the time is the slowest rank's, from
+"shards packed and resident" to "merged lists on rank 0". Shards are generated per rank, so their content depends on the
+number of ranks; sizes and distributions do not.
 
 `nearest`: L2-normalised N(0,1) queries against an L2-normalised corpus, angular top-k per query (the batched
 distance kernels + selection). `maxsim`: ColBERT-style late interaction, queries of 32 tokens against documents of
@@ -102,6 +109,87 @@ def run_maxsim(queries: int, docs: int, depth: int = 128, top: int = 100, q_toke
             "ms": seconds * 1e3, "gso_per_s": ops / seconds / 1e9, "steps": steps, "warmup": warmup}
 
 
+def _distributed(torch):
+    import os
+    import torch.distributed as dist
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return dist, rank, world
+
+
+def _timed_all_ranks(torch, dist, fn, steps: int, warmup: int) -> float:
+    """Seconds per step of the slowest rank: barrier + synchronize on both sides, CUDA events in between."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    seconds = torch.tensor([start.elapsed_time(stop) / steps / 1e3], device="cuda")
+    dist.all_reduce(seconds, op=dist.ReduceOp.MAX)
+    return float(seconds.item())
+
+
+def run_nearest_sharded(queries: int, corpus: int, depth: int, top: int, dtype: str = "f16", steps: int = 2, seed: int = 3,
+                        warmup: int = 1):
+    import torch
+    import numkong_b200 as nk
+    from numkong_b200 import search, sharding
+    dist, rank, world = _distributed(torch)
+    lo, hi = sharding.row_shard(corpus, world, rank)
+    tq = _device_rows(torch, queries, depth, dtype, seed)          # same seed everywhere = replicated queries
+    packed = nk.dots_pack(_device_rows(torch, hi - lo, depth, dtype, seed + 1 + rank), dtype)
+
+    def step():
+        d, i = search.nearest_in_shard(tq, packed, top, id_base=lo, dtype=dtype)
+        sharding.merge_topk(d, i, top)
+
+    seconds = _timed_all_ranks(torch, dist, step, steps, warmup)
+    assert nk.synchronize() == 0
+    ops = 2.0 * queries * corpus * depth
+    out = {"workload": f"angular top-{top}: {queries} {dtype} queries x {corpus} corpus rows over {world} GPUs, depth {depth}",
+           "ms": seconds * 1e3, "gso_per_s": ops / seconds / 1e9, "n_gpus": world, "steps": steps, "warmup": warmup,
+           "filter_fallbacks": int(nk.lib.nkb_topk_filter_fallbacks())}
+    dist.barrier()
+    return out if rank == 0 else None
+
+
+def run_maxsim_sharded(queries: int, docs: int, depth: int = 128, top: int = 100, q_tokens: int = 32, steps: int = 2, seed: int = 5,
+                       warmup: int = 1):
+    import torch
+    import numkong_b200 as nk
+    from numkong_b200 import sharding
+    dist, rank, world = _distributed(torch)
+    counts = np.random.default_rng(seed).integers(64, 301, size=docs)
+    d_off = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+    q_off = torch.from_numpy((np.arange(queries + 1) * q_tokens).astype(np.int64)).cuda()
+    d0, d1 = sharding.token_balanced_shards(torch.from_numpy(d_off), world)[rank]
+    local_off = torch.from_numpy(d_off[d0:d1 + 1] - d_off[d0]).cuda()
+    tq = nk.maxsim_pack(_device_rows(torch, queries * q_tokens, depth, "bf16", seed + 1), "bf16")
+    td = nk.maxsim_pack(_device_rows(torch, int(d_off[d1] - d_off[d0]), depth, "bf16", seed + 2 + rank), "bf16")
+
+    def step():
+        scores = nk.maxsims_packed(tq, q_off, td, local_off)
+        vals, ids = nk.topk_smallest(scores, min(top, d1 - d0), id_base=d0)
+        sharding.merge_topk(vals, ids, min(top, d1 - d0))
+
+    seconds = _timed_all_ranks(torch, dist, step, steps, warmup)
+    assert nk.synchronize() == 0
+    total = int(d_off[-1])
+    ops = 2.0 * queries * q_tokens * total * depth
+    out = {"workload": f"MaxSim top-{top}: {queries} queries x {q_tokens} tokens vs {docs} documents ({total} tokens) over {world} GPUs, depth {depth}, bf16",
+           "ms": seconds * 1e3, "gso_per_s": ops / seconds / 1e9, "n_gpus": world, "steps": steps, "warmup": warmup}
+    dist.barrier()
+    return out if rank == 0 else None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("workload", choices=["nearest", "maxsim"])
@@ -113,12 +201,19 @@ def main():
     ap.add_argument("--dtype", default="f16")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--sharded", action="store_true", help="split the corpus / documents over the ranks of a torchrun launch")
     a = ap.parse_args()
     if a.workload == "nearest":
-        out = run_nearest(a.queries or 8192, a.corpus, a.depth or 768, a.top or 10, a.dtype, a.steps, warmup=a.warmup)
+        fn = run_nearest_sharded if a.sharded else run_nearest
+        out = fn(a.queries or 8192, a.corpus, a.depth or 768, a.top or 10, a.dtype, a.steps, warmup=a.warmup)
     else:
-        out = run_maxsim(a.queries or 256, a.docs, a.depth or 128, a.top or 100, steps=a.steps, warmup=a.warmup)
-    print(json.dumps(out))
+        fn = run_maxsim_sharded if a.sharded else run_maxsim
+        out = fn(a.queries or 256, a.docs, a.depth or 128, a.top or 100, steps=a.steps, warmup=a.warmup)
+    if out is not None:
+        print(json.dumps(out))
+    if a.sharded:
+        import torch.distributed as dist
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
