@@ -166,6 +166,78 @@ def time_reference(dtype: str, steps: int, warmup: int, rows_per_step: int | Non
             "ms_per_step": total / steps * 1e3, "rows_per_step": rows_per_step}
 
 
+def time_reference_search():
+    """CPU legs for the two search workloads, on bounded twins: the reference's dispatched nk_angulars_packed_f16 (full
+    distance matrix; it has no top-k) and nk_maxsim_packed_bf16 (one call per query/document pair), work split over all
+    host threads. Throughput is work-normalised (2 x rows x columns x depth), so it compares with the GPU figures."""
+    ref = _ref_library()
+    if ref is None:
+        return None
+    from numkong_b200 import synthetic as syn
+    threads = max(1, len(os.sched_getaffinity(0)))
+    u64, vp = ctypes.c_uint64, ctypes.c_void_p
+
+    def run_threads(work):
+        barrier = threading.Barrier(threads + 1)
+
+        def body(t):
+            ref.configure_thread()
+            barrier.wait()
+            work(t)
+            barrier.wait()
+
+        pool = [threading.Thread(target=body, args=(t,)) for t in range(threads)]
+        for th in pool:
+            th.start()
+        barrier.wait()
+        t0 = time.perf_counter()
+        barrier.wait()
+        dt = time.perf_counter() - t0
+        for th in pool:
+            th.join()
+        return dt
+
+    out = {}
+    # nearest: 1024 queries x 20,000 corpus rows x 768, f16
+    q_rows, c_rows, depth = 1024, 20000, 768
+    q = syn.normal_matrix(q_rows, depth, "f16", 3, normalize=True)
+    c = syn.normal_matrix(c_rows, depth, "f16", 4, normalize=True)
+    blob = ref.pack(c, "f16")
+    fn = getattr(ref.lib, "nk_angulars_packed_f16")
+    fn.restype, fn.argtypes = None, [vp, vp, vp, u64, u64, u64, u64, u64]
+    dist_m = np.zeros((q_rows, c_rows), dtype=np.float32)
+    per = (q_rows + threads - 1) // threads
+
+    def nearest_work(t):
+        lo, hi = t * per, min(q_rows, (t + 1) * per)
+        if hi > lo:
+            fn(q[lo:hi].ctypes.data, blob.ctypes.data, dist_m[lo:hi].ctypes.data, hi - lo, c_rows, depth, depth * 2, c_rows * 4)
+
+    run_threads(nearest_work)
+    dt = min(run_threads(nearest_work) for _ in range(2))
+    out["nearest"] = {"gso_per_s": 2.0 * q_rows * c_rows * depth / dt / 1e9, "cores": threads, "kind": "reference",
+                      "sample": f"nk_angulars_packed_f16, {q_rows} queries x {c_rows} corpus rows x {depth}, distance matrix only (no selection)"}
+    # MaxSim: 8 queries x 32 tokens against 256 documents of 64..300 tokens, bf16, depth 128
+    rng = np.random.default_rng(5)
+    counts = rng.integers(64, 301, size=256)
+    queries = [ref.pack(syn.normal_matrix(32, 128, "bf16", 100 + i, normalize=True), "bf16", "maxsim") for i in range(8)]
+    docs = [ref.pack(syn.normal_matrix(int(n), 128, "bf16", 200 + i, normalize=True), "bf16", "maxsim") for i, n in enumerate(counts)]
+    ms = getattr(ref.lib, "nk_maxsim_packed_bf16")
+    ms.restype, ms.argtypes = None, [vp, vp, u64, u64, u64, vp]
+    scores = np.zeros((8, 256), dtype=np.float32)
+
+    def maxsim_work(t):
+        for j in range(t, 256, threads):
+            for i in range(8):
+                ms(queries[i].ctypes.data, docs[j].ctypes.data, 32, int(counts[j]), 128, scores[i, j:j + 1].ctypes.data)
+
+    run_threads(maxsim_work)
+    dt = min(run_threads(maxsim_work) for _ in range(2))
+    out["maxsim"] = {"gso_per_s": 2.0 * 8 * 32 * float(counts.sum()) * 128 / dt / 1e9, "cores": threads, "kind": "reference",
+                     "sample": f"nk_maxsim_packed_bf16, 8 queries x 32 tokens vs 256 documents ({int(counts.sum())} tokens), one call per pair"}
+    return out
+
+
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -321,6 +393,7 @@ def main():
     peak = peaks["bf16_tflops"] * (1.0 if dtype in ("bf16", "f16") else 2.0)
 
     extras = {}
+    search = {}
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_extras:
         del a_pin, c_pin
@@ -342,6 +415,13 @@ def main():
         res = time_reference(dtype, steps=3, warmup=1)
         if res is not None:
             cpu_baseline = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        # The two search workloads on their small twins (BASELINE configs 4 and 5 scaled down), GPU and reference CPU.
+        from numkong_b200 import workloads
+        near = workloads.run_nearest(1024, 200000, 768, 10, "f16", steps=5)
+        late = workloads.run_maxsim(64, 20000, steps=3)
+        cpu_search = time_reference_search() or {}
+        search = {"nearest_top10_1024x200000x768_f16": {"gso_per_s": near["gso_per_s"], "ms": near["ms"], "cpu": cpu_search.get("nearest")},
+                  "maxsim_top100_64x20000_bf16": {"gso_per_s": late["gso_per_s"], "ms": late["ms"], "cpu": cpu_search.get("maxsim")}}
 
     if rank == 0:
         line = {
@@ -356,7 +436,7 @@ def main():
             "e2e": {"value": ops_per_step * world * e2e_steps / e2e_seconds / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": M * K * eb, "d2h_bytes_per_step": M * N * 4, "steps": e2e_steps,
                     "ms_per_step": e2e_seconds / e2e_steps * 1e3},
-            "gpu_launches": int(launches), "clocks": clocks, "per_dtype": extras,
+            "gpu_launches": int(launches), "clocks": clocks, "per_dtype": extras, "search_workloads": search,
         }
         print(json.dumps(line))
     if world > 1:
