@@ -84,6 +84,33 @@ NKB_DECLARE_PACKED_FAMILY(e2m3)
 NKB_DECLARE_PACKED_FAMILY(e3m2)
 NKB_DECLARE_PACKED_FAMILY(f32)
 
+/* ---- symmetric products A x A^T and the distance matrices built on them ----------------------------
+ * nk_dots_symmetric_<t>        replaces include/numkong/dots.h:309-359      (wrappers c/numkong.c:673-686)
+ * nk_angulars_symmetric_<t> / nk_euclideans_symmetric_<t> replace include/numkong/spatials.h:77-
+ * (generator include/numkong/dots/serial.h:2802-2872). Only rows [row_start, row_start + row_count) are touched and of
+ * those only the cells with column >= row; the rest of `result` is left as it was. Dots put the squared norm on the
+ * diagonal, the distances put 0 there. Cell types as for the packed family.
+ */
+#define NKB_DECLARE_SYMMETRIC_FAMILY(T)                                                                                \
+    NKB_API void nk_dots_symmetric_##T(void const *vectors, nk_size_t vectors_count, nk_size_t depth, nk_size_t stride, \
+                                       void *result, nk_size_t result_stride, nk_size_t row_start, nk_size_t row_count); \
+    NKB_API void nk_angulars_symmetric_##T(void const *vectors, nk_size_t vectors_count, nk_size_t depth,              \
+                                           nk_size_t stride, void *result, nk_size_t result_stride,                    \
+                                           nk_size_t row_start, nk_size_t row_count);                                  \
+    NKB_API void nk_euclideans_symmetric_##T(void const *vectors, nk_size_t vectors_count, nk_size_t depth,            \
+                                             nk_size_t stride, void *result, nk_size_t result_stride,                  \
+                                             nk_size_t row_start, nk_size_t row_count);
+
+NKB_DECLARE_SYMMETRIC_FAMILY(i8)
+NKB_DECLARE_SYMMETRIC_FAMILY(u8)
+NKB_DECLARE_SYMMETRIC_FAMILY(bf16)
+NKB_DECLARE_SYMMETRIC_FAMILY(f16)
+NKB_DECLARE_SYMMETRIC_FAMILY(e4m3)
+NKB_DECLARE_SYMMETRIC_FAMILY(e5m2)
+NKB_DECLARE_SYMMETRIC_FAMILY(e2m3)
+NKB_DECLARE_SYMMETRIC_FAMILY(e3m2)
+NKB_DECLARE_SYMMETRIC_FAMILY(f32)
+
 /* ---- MaxSim late interaction -------------------------------------------------------------------
  * replaces include/numkong/maxsim.h:72-114 (wrappers c/numkong.c:738-765). Both sides are packed
  * with the same function. result: f32 for bf16/f16, f64 for f32 (maxsim.h:350-357):

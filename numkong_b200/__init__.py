@@ -26,6 +26,7 @@ from ._lib import DTYPE_BYTES, DTYPE_CODES, MAXSIM_DTYPES, PACKED_DTYPES, check,
 
 __all__ = [
     "PackedMatrix", "MaxSimPackedMatrix", "dots_pack", "dots_packed", "angulars_packed", "euclideans_packed",
+    "dots_symmetric", "angulars_symmetric", "euclideans_symmetric",
     "maxsim_pack", "maxsim_packed", "maxsim", "maxsims_packed", "angulars_packed_topk", "euclideans_packed_topk",
     "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error",
 ]
@@ -209,6 +210,56 @@ def angulars_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Opt
 def euclideans_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Optional[str] = None):
     """Batched Euclidean distances. Mirrors nk.euclideans_packed."""
     return _packed_call("euclideans", a, packed, out, dtype)
+
+
+def _symmetric_call(op: str, vectors: Any, out: Any, dtype: Optional[str], start_row: Optional[int], end_row: Optional[int]):
+    v = _View(vectors, dtype)
+    t = v.dtype
+    if t not in PACKED_DTYPES:
+        raise LookupError(f"no symmetric kernels for dtype {t!r}")
+    n = v.rows
+    cell = 8 if t == "f32" else 4
+    if out is None:
+        # Cells below the diagonal are not written by the call; a fresh result starts as zeros (as the reference's does).
+        if v.is_cuda:
+            import torch
+            tdt = torch.float64 if t == "f32" else (torch.int32 if (t in ("i8", "u8") and op == "dots") else torch.float32)
+            out = torch.zeros((n, n), dtype=tdt, device=v.obj.device)
+        else:
+            ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if op == "dots" else np.float32)
+            out = np.zeros((n, n), dtype=ndt)
+    if _is_torch(out):
+        if tuple(out.shape) != (n, n) or out.element_size() != cell:
+            raise ValueError("out has the wrong shape or cell size")
+        ptr, stride = out.data_ptr(), (int(out.stride(0)) * cell if n > 1 else n * cell)
+    else:
+        if out.shape != (n, n) or out.itemsize != cell:
+            raise ValueError("out has the wrong shape or cell size")
+        ptr, stride = out.ctypes.data, (int(out.strides[0]) if n > 1 else n * cell)
+    first = 0 if start_row is None else int(start_row)
+    last = n if end_row is None else min(int(end_row), n)
+    if last > first:
+        getattr(lib, f"nk_{op}_symmetric_{t}")(v.ptr, n, v.cols, v.stride, ptr, stride, first, last - first)
+        check(f"{op}_symmetric")
+    return out
+
+
+def dots_symmetric(vectors: Any, *, dtype: Optional[str] = None, out: Any = None, start_row: Optional[int] = None,
+                   end_row: Optional[int] = None):
+    """Upper triangle (diagonal included) of A . A^T for rows [start_row, end_row). Mirrors nk.dots_symmetric."""
+    return _symmetric_call("dots", vectors, out, dtype, start_row, end_row)
+
+
+def angulars_symmetric(vectors: Any, *, dtype: Optional[str] = None, out: Any = None, start_row: Optional[int] = None,
+                       end_row: Optional[int] = None):
+    """Upper triangle of the pairwise angular distances (diagonal 0). Mirrors nk.angulars_symmetric."""
+    return _symmetric_call("angulars", vectors, out, dtype, start_row, end_row)
+
+
+def euclideans_symmetric(vectors: Any, *, dtype: Optional[str] = None, out: Any = None, start_row: Optional[int] = None,
+                         end_row: Optional[int] = None):
+    """Upper triangle of the pairwise Euclidean distances (diagonal 0). Mirrors nk.euclideans_symmetric."""
+    return _symmetric_call("euclideans", vectors, out, dtype, start_row, end_row)
 
 
 def maxsim_pack(vectors: Any, dtype: Optional[str] = None) -> MaxSimPackedMatrix:

@@ -37,6 +37,8 @@ def _load() -> ctypes.CDLL:
         for op in ("dots", "angulars", "euclideans"):
             f = getattr(lib, f"nk_{op}_packed_{t}")
             f.restype, f.argtypes = None, [vp, vp, vp, sz, sz, sz, sz, sz]
+            f = getattr(lib, f"nk_{op}_symmetric_{t}")
+            f.restype, f.argtypes = None, [vp, sz, sz, sz, vp, sz, sz, sz]
     for t in MAXSIM_DTYPES:
         f = getattr(lib, f"nk_maxsim_packed_size_{t}")
         f.restype, f.argtypes = sz, [sz, sz]

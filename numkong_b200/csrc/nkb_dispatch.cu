@@ -15,7 +15,8 @@ struct Entry {
 #define NKB_PACKED_ENTRIES(T, DT)                                                                  \
     {'P', DT, (void *)&nk_dots_packed_size_##T}, {'Q', DT, (void *)&nk_dots_pack_##T},            \
     {'G', DT, (void *)&nk_dots_packed_##T}, {'N', DT, (void *)&nk_angulars_packed_##T},           \
-    {'E', DT, (void *)&nk_euclideans_packed_##T}
+    {'E', DT, (void *)&nk_euclideans_packed_##T}, {'y', DT, (void *)&nk_dots_symmetric_##T},      \
+    {'n', DT, (void *)&nk_angulars_symmetric_##T}, {'D', DT, (void *)&nk_euclideans_symmetric_##T}
 #define NKB_MAXSIM_ENTRIES(T, DT)                                                                  \
     {'L', DT, (void *)&nk_maxsim_packed_size_##T}, {'l', DT, (void *)&nk_maxsim_pack_##T},        \
     {'T', DT, (void *)&nk_maxsim_packed_##T}

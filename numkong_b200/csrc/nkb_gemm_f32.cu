@@ -16,7 +16,9 @@ template <int kEpi>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const uint8_t *__restrict__ a, uint64_t a_stride, const float *__restrict__ b, uint64_t b_stride_elems,
                 const double *__restrict__ b_norms, const double *__restrict__ a_norms, uint8_t *__restrict__ c,
-                uint64_t c_stride, uint32_t m, uint32_t n, uint32_t k) {
+                uint64_t c_stride, uint32_t m, uint32_t n, uint32_t k, int32_t tri_diag) {
+    // Triangular mode (A x A^T): only cells with column >= row + tri_diag are wanted; blocks wholly below that line leave.
+    if (tri_diag >= 0 && (blockIdx.x + 1) * kTile <= blockIdx.y * kTile + (uint32_t)tri_diag) return;
     __shared__ float a_s[kDepth][kTile + 1];
     __shared__ float b_s[kDepth][kTile + 1];
     const uint32_t m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
@@ -66,7 +68,7 @@ gemm_f32_kernel(const uint8_t *__restrict__ a, uint64_t a_stride, const float *_
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             uint32_t col = n0 + tx * 4 + j;
-            if (col >= n) continue;
+            if (col >= n || (tri_diag >= 0 && col < row + (uint32_t)tri_diag)) continue;
             double v = acc[i][j];
             if constexpr (kEpi == kEpiAngular) {
                 double product = an * b_norms[col];
@@ -78,6 +80,7 @@ gemm_f32_kernel(const uint8_t *__restrict__ a, uint64_t a_stride, const float *_
                 double d2 = an + b_norms[col] - 2.0 * v;
                 v = d2 > 0.0 ? sqrt(d2) : 0.0;
             }
+            if (kEpi != kEpiDot && tri_diag >= 0 && col == row + (uint32_t)tri_diag) v = 0.0;  // distance to itself
             c_row[col] = v;
         }
     }
@@ -87,7 +90,7 @@ gemm_f32_kernel(const uint8_t *__restrict__ a, uint64_t a_stride, const float *_
 
 cudaError_t launch_gemm_f32(int epilogue, const float *a, uint64_t a_stride, const float *b, uint64_t b_stride,
                             const double *b_norms, const double *a_norms, double *c, uint64_t c_stride, uint64_t m,
-                            uint64_t n, uint64_t k, cudaStream_t stream) {
+                            uint64_t n, uint64_t k, cudaStream_t stream, int32_t tri_diag) {
     if (m == 0 || n == 0) return cudaSuccess;
     if (m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull) return cudaErrorInvalidValue;
     dim3 grid((unsigned)((n + kTile - 1) / kTile), (unsigned)((m + kTile - 1) / kTile));
@@ -97,13 +100,13 @@ cudaError_t launch_gemm_f32(int epilogue, const float *a, uint64_t a_stride, con
     const uint64_t bse = b_stride / 4;
     switch (epilogue) {
     case kEpiDot:
-        gemm_f32_kernel<kEpiDot><<<grid, 256, 0, stream>>>(ab, a_stride, b, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k);
+        gemm_f32_kernel<kEpiDot><<<grid, 256, 0, stream>>>(ab, a_stride, b, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k, tri_diag);
         break;
     case kEpiAngular:
-        gemm_f32_kernel<kEpiAngular><<<grid, 256, 0, stream>>>(ab, a_stride, b, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k);
+        gemm_f32_kernel<kEpiAngular><<<grid, 256, 0, stream>>>(ab, a_stride, b, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k, tri_diag);
         break;
     case kEpiEuclidean:
-        gemm_f32_kernel<kEpiEuclidean><<<grid, 256, 0, stream>>>(ab, a_stride, b, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k);
+        gemm_f32_kernel<kEpiEuclidean><<<grid, 256, 0, stream>>>(ab, a_stride, b, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k, tri_diag);
         break;
     default: return cudaErrorInvalidValue;
     }

@@ -41,6 +41,9 @@ struct GemmDev {
     uint32_t int_mode;            // 0 float accumulators, 1 signed i32, 2 unsigned u32
     uint32_t flush_kblocks;       // stages per accumulation span (see the MMA issuer)
     unsigned int *error_word;
+    // Triangular mode (A x A^T): >= 0 keeps only cells with column >= row + tri_diag (the diagonal itself reads 0 under a
+    // distance epilogue), tiles wholly below that line are never computed; -1 = plain rectangular product.
+    int32_t tri_diag;
     // Candidate filter of the distance epilogues (see GemmArgs); `candidates == nullptr` means "store the tile".
     const uint32_t *threshold_bits;
     uint32_t *candidate_counts;
@@ -70,6 +73,12 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
     uint32_t in_group = tile % per_group;
     mt = first_m + in_group % group_rows;
     nt = in_group / group_rows;
+}
+
+// True when no cell of a tile (first row, one past its last column) survives the triangular mask. Every warp role asks
+// the same question for the same tile, so skipped tiles move no barrier.
+__device__ __forceinline__ bool tile_skipped(int32_t tri_diag, uint32_t first_row, uint32_t end_col) {
+    return tri_diag >= 0 && end_col <= first_row + (uint32_t)tri_diag;
 }
 
 // ---- epilogue helpers shared by the single-CTA and the CTA-pair kernels ---------------------------------
@@ -220,14 +229,18 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
             const uint32_t r = it * 8 + (lane >> 2), q = lane & 3u;
             const uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kEpiStagePitch + q * 4);
             const uint32_t row = row_base + r, col = col0 + q * 4;
-            if (row < p.m && col < p.n) {
+            // Triangular mode: the first column this row keeps (0 when the product is rectangular).
+            const uint32_t keep_from = p.tri_diag >= 0 ? row + (uint32_t)p.tri_diag : 0u;
+            if (row < p.m && col < p.n && col + 4 > keep_from) {
                 uint32_t *dst = reinterpret_cast<uint32_t *>(p.c + (uint64_t)row * p.c_stride) + col;
-                if (col + 4 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) *reinterpret_cast<uint4 *>(dst) = v;
+                if (col + 4 <= p.n && col >= keep_from + (kEpi != kEpiDot ? 1u : 0u) && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0)
+                    *reinterpret_cast<uint4 *>(dst) = v;
                 else {
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        if (col + j < p.n) dst[j] = w[j];
+                        if (col + j < p.n && col + j >= keep_from)
+                            dst[j] = (kEpi != kEpiDot && p.tri_diag >= 0 && col + j == keep_from) ? 0u : w[j];  // distance to itself
                 }
             }
         }
@@ -290,6 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 uint32_t mt, nt;
                 tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+                if (tile_skipped(p.tri_diag, mt * kBM, (nt + 1) * kBN)) continue;
                 const uint8_t *b_tile = p.b_payload + (uint64_t)nt * (kBN / kChunkRows) * p.kblocks * kChunkBytes;
                 for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
@@ -321,6 +335,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
             uint32_t seq = 0;  // spans issued so far, across tiles
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                uint32_t mt, nt;
+                tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+                if (tile_skipped(p.tri_diag, mt * kBM, (nt + 1) * kBN)) continue;
                 for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
                     const uint32_t buf = seq & 1u;
                     const uint32_t buf_phase = (seq >> 1) & 1u;
@@ -355,9 +372,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                               (warp - 2) * kEpiStageWords;
         uint32_t seq = 0, local_tile = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             uint32_t mt, nt;
             tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+            if (tile_skipped(p.tri_diag, mt * kBM, (nt + 1) * kBN)) continue;
             if constexpr (kEpi != kEpiDot) {
                 // One column factor per epilogue thread, shared by all rows of the tile (double-buffered by tile parity).
                 const uint32_t e = threadIdx.x - 64u;
@@ -389,6 +407,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
             if (!ok) break;
             store_tile<kEpi, kColsPerThread>(acc, p, mt * kBM + quarter * 32u, nt * kBN + half * kColsPerThread, epi_stage,
                                              colf + (local_tile & 1u) * 256, half * kColsPerThread, lane);
+            ++local_tile;
         }
     }
 
@@ -471,6 +490,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
             for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
                 uint32_t mt, nt;
                 tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+                if (tile_skipped(p.tri_diag, mt * 256u, (nt + 1) * kBN)) continue;
                 const uint32_t a_row = mt * 256u + rank * 128u;
                 const uint64_t b_chunk0 = ((uint64_t)nt * 2u + rank) * p.kblocks;  // this CTA's half of the B tile
                 for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
@@ -493,6 +513,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
             uint32_t phase = 0, seq = 0;
             bool ok = true;
             for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                uint32_t mt, nt;
+                tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+                if (tile_skipped(p.tri_diag, mt * 256u, (nt + 1) * kBN)) continue;
                 for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
                     const uint32_t buf = seq & 1u, buf_phase = (seq >> 1) & 1u;
                     if (!mbar_wait<true>(tmem_empty_bar(buf), buf_phase ^ 1u, 2, p.error_word)) { ok = false; break; }
@@ -523,9 +546,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
         uint32_t *epi_stage = reinterpret_cast<uint32_t *>(smem_gen + kPairBarrierOffset + 256 + kEpiColfBytes) + (warp - 2) * kEpiStageWords;
         uint32_t seq = 0, local_tile = 0;
         bool ok = true;
-        for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
+        for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
             uint32_t mt, nt;
             tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+            if (tile_skipped(p.tri_diag, mt * 256u, (nt + 1) * kBN)) continue;
             if constexpr (kEpi != kEpiDot) {
                 const uint32_t e = threadIdx.x - 64u;
                 colf[(local_tile & 1u) * 256 + e] = column_factor<kEpi>(p, nt * kBN + e);
@@ -556,6 +580,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
             if (!ok) break;
             store_tile<kEpi, kColsPerThread>(acc, p, mt * 256u + rank * 128u + quarter * 32u, nt * kBN + half * kColsPerThread,
                                              epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane);
+            ++local_tile;
         }
     }
 
@@ -762,6 +787,7 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     dev.flush_kblocks = ki.kind == kKindI8 ? dev.kblocks : (forced_flush ? forced_flush : auto_flush);
     if (dev.flush_kblocks == 0) dev.flush_kblocks = 1;
     dev.error_word = args.error_word;
+    dev.tri_diag = args.tri_diag;
     const bool filtering = args.candidates != nullptr && args.epilogue != kEpiDot;
     dev.threshold_bits = filtering ? args.threshold_bits : nullptr;
     dev.candidate_counts = filtering ? args.candidate_counts : nullptr;

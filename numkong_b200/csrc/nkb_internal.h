@@ -147,6 +147,10 @@ struct GemmArgs {
     uint64_t depth_padded_bytes;
     unsigned int *error_word;     // device
     int variant;                  // 0 = default for the shape; otherwise forces a tile configuration (testing/tuning)
+    // Triangular mode for A x A^T: >= 0 stores only the cells with column >= row + tri_diag (rows and columns counted from
+    // the first row of `a` / first packed row), writes 0 on that diagonal under a distance epilogue, and skips the tiles
+    // that lie wholly below it. -1 = rectangular.
+    int32_t tri_diag = -1;
     // Candidate filter (distance epilogues only). When `candidates` is set nothing is written to `c`: every value below
     // its row's threshold is appended to that row's candidate list as (f32 bits of the distance, column + column_id_base).
     // Thresholds are f32 bit patterns compared as signed integers (distances are >= -0 and never NaN); 0x7fffffff
@@ -164,7 +168,7 @@ int gemm_tc_launch_count(const GemmArgs &args);
 // f32 x f32 -> f64 on CUDA cores. `b` is the padded row-major f32 payload.
 cudaError_t launch_gemm_f32(int epilogue, const float *a, uint64_t a_stride, const float *b, uint64_t b_stride,
                             const double *b_norms, const double *a_norms, double *c, uint64_t c_stride,
-                            uint64_t m, uint64_t n, uint64_t k, cudaStream_t stream);
+                            uint64_t m, uint64_t n, uint64_t k, cudaStream_t stream, int32_t tri_diag = -1);
 
 // Resolves cuTensorMapEncodeTiled through the runtime (no link-time dependency on libcuda).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
