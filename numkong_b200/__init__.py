@@ -46,12 +46,64 @@ def _is_torch(x: Any) -> bool:
     return type(x).__module__.startswith("torch")
 
 
+_CAI_TYPES = {"<f2": "f16", "<f4": "f32", "|i1": "i8", "|u1": "u8"}  # other element types need dtype=...
+
+
+def _adopt_device_array(x: Any) -> Any:
+    """Zero-copy handle on a foreign CUDA array: a torch tensor sharing the memory when the object speaks DLPack for a
+    CUDA device, a pointer/shape/stride record when it only has __cuda_array_interface__. Anything else is returned
+    unchanged and handled as a host array."""
+    dl_device = getattr(x, "__dlpack_device__", None)
+    if dl_device is not None and hasattr(x, "__dlpack__"):
+        kind = int(dl_device()[0])
+        if kind in (2, 13):  # kDLCUDA, kDLCUDAManaged
+            import torch
+            return torch.from_dlpack(x)
+        return x
+    cai = getattr(x, "__cuda_array_interface__", None)
+    return _ForeignCuda(x, cai) if cai is not None else x
+
+
+class _ForeignCuda:
+    """A 2-D CUDA array described by __cuda_array_interface__ (pointer, shape, byte strides); used in place."""
+
+    def __init__(self, owner: Any, cai: dict):
+        if len(cai["shape"]) != 2:
+            raise ValueError("expected a 2-D matrix")
+        self.owner = owner  # keeps the exporter's memory alive
+        self.rows, self.cols = (int(s) for s in cai["shape"])
+        self.itemsize = int(cai["typestr"][2:])
+        strides = cai.get("strides") or (self.cols * self.itemsize, self.itemsize)
+        if self.cols > 1 and int(strides[1]) != self.itemsize:
+            raise ValueError("rows must be contiguous (column-major inputs are not supported)")
+        self.stride = int(strides[0])
+        self.ptr = int(cai["data"][0])
+        self.name = _CAI_TYPES.get(cai["typestr"])
+
+    @property
+    def device(self):
+        import torch
+        return torch.device("cuda", torch.cuda.current_device())
+
+
 class _View:
     """Pointer, shape and byte strides of a 2-D matrix, plus where it lives."""
 
     def __init__(self, x: Any, dtype: Optional[str]):
+        # Device arrays of other libraries (CuPy, Numba, ...) come in without a copy: through DLPack when the object
+        # offers it for a CUDA device, else through __cuda_array_interface__. The reference's binding rejects CUDA
+        # capsules (python/dlpack_interop.c:97-99); here they are the fast path.
+        if not _is_torch(x) and not isinstance(x, np.ndarray):
+            x = _adopt_device_array(x)
         self.obj = x
-        if _is_torch(x):
+        if isinstance(x, _ForeignCuda):
+            name = dtype or x.name
+            if name is None:
+                raise TypeError("pass dtype='bf16' etc. for storage words that have no element type of their own")
+            self.is_cuda, self.ptr, self.rows, self.cols = True, x.ptr, x.rows, x.cols
+            self.stride = x.stride if x.rows > 1 else x.cols * x.itemsize
+            item = x.itemsize
+        elif _is_torch(x):
             if x.dim() != 2:
                 raise ValueError("expected a 2-D matrix")
             if x.stride(1) != 1 and x.shape[1] > 1:
