@@ -341,7 +341,6 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
                  uint64_t c_stride, cudaStream_t stream) {
     const uint32_t out_bytes = dot_out_bytes(dt);
     const uint64_t c_row_bytes = n * out_bytes;
-    auto fail = [&]() {};
     // Output: in place when it is device memory with 4-byte aligned rows, else a dense device copy.
     uint8_t *c_dev = static_cast<uint8_t *>(c);
     uint64_t c_pitch = c_stride;
