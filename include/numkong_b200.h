@@ -52,6 +52,8 @@ typedef uint64_t nk_size_t; /* types.h:854-856 */
 #define NKB_DTYPE_BF16 (1u << 13)
 #define NKB_DTYPE_E4M3 (1u << 14)
 #define NKB_DTYPE_E5M2 (1u << 15)
+#define NKB_DTYPE_I4 (1u << 16) /* two values per byte, low nibble first; `depth` counts values */
+#define NKB_DTYPE_U4 (1u << 17)
 #define NKB_DTYPE_E2M3 (1u << 18)
 #define NKB_DTYPE_E3M2 (1u << 19)
 
@@ -83,6 +85,8 @@ NKB_DECLARE_PACKED_FAMILY(e5m2)
 NKB_DECLARE_PACKED_FAMILY(e2m3)
 NKB_DECLARE_PACKED_FAMILY(e3m2)
 NKB_DECLARE_PACKED_FAMILY(f32)
+NKB_DECLARE_PACKED_FAMILY(i4) /* include/numkong/dots.h:197,239,289; both nibbles of the last byte count (dot/serial.h:185-215) */
+NKB_DECLARE_PACKED_FAMILY(u4)
 
 /* ---- symmetric products A x A^T and the distance matrices built on them ----------------------------
  * nk_dots_symmetric_<t>        replaces include/numkong/dots.h:309-359      (wrappers c/numkong.c:673-686)
@@ -110,6 +114,8 @@ NKB_DECLARE_SYMMETRIC_FAMILY(e5m2)
 NKB_DECLARE_SYMMETRIC_FAMILY(e2m3)
 NKB_DECLARE_SYMMETRIC_FAMILY(e3m2)
 NKB_DECLARE_SYMMETRIC_FAMILY(f32)
+NKB_DECLARE_SYMMETRIC_FAMILY(i4)
+NKB_DECLARE_SYMMETRIC_FAMILY(u4)
 
 /* ---- MaxSim late interaction -------------------------------------------------------------------
  * replaces include/numkong/maxsim.h:72-114 (wrappers c/numkong.c:738-765). Both sides are packed

@@ -22,7 +22,7 @@ from typing import Any, Optional, Tuple
 import numpy as np
 
 from . import _lib
-from ._lib import DTYPE_BYTES, DTYPE_CODES, MAXSIM_DTYPES, PACKED_DTYPES, check, last_error, lib
+from ._lib import DIMENSIONS_PER_VALUE, DTYPE_BYTES, DTYPE_CODES, MAXSIM_DTYPES, PACKED_DTYPES, check, last_error, lib
 
 __all__ = [
     "PackedMatrix", "MaxSimPackedMatrix", "dots_pack", "dots_packed", "angulars_packed", "euclideans_packed",
@@ -39,7 +39,7 @@ _TORCH_NAMES = {
     "torch.int8": "i8", "torch.uint8": "u8", "torch.float32": "f32", "torch.float16": "f16",
     "torch.bfloat16": "bf16", "torch.float8_e4m3fn": "e4m3", "torch.float8_e5m2": "e5m2",
 }
-_OUT_NUMPY = {"i8": np.int32, "u8": np.uint32, "f32": np.float64}
+_OUT_NUMPY = {"i8": np.int32, "u8": np.uint32, "i4": np.int32, "u4": np.uint32, "f32": np.float64}
 
 
 def _is_torch(x: Any) -> bool:
@@ -136,6 +136,7 @@ class _View:
         if item != DTYPE_BYTES[name]:
             raise TypeError(f"dtype {name!r} needs {DTYPE_BYTES[name]}-byte elements, got {item}-byte storage")
         self.dtype = name
+        self.depth = self.cols * DIMENSIONS_PER_VALUE.get(name, 1)  # logical dimensions of a row
 
 
 def _view_like(x: Any, dtype: Optional[str], packed_dtype: str) -> _View:
@@ -143,7 +144,8 @@ def _view_like(x: Any, dtype: Optional[str], packed_dtype: str) -> _View:
     uint16 / int16) stand for the 8/6-bit and 16-bit float types NumPy and torch cannot name."""
     if dtype is None:
         name = (_TORCH_NAMES.get(str(x.dtype)) if _is_torch(x) else _NUMPY_NAMES.get(np.asarray(x).dtype.name))
-        container = name in (None, "u8") and packed_dtype not in ("i8", "u8", "f32")
+        container = (name in (None, "u8") and packed_dtype not in ("i8", "u8", "f32")) or \
+                    (name == "i8" and packed_dtype in ("i4", "u4"))
         dtype = packed_dtype if container else name
     v = _View(x, dtype)
     if v.dtype != packed_dtype:
@@ -206,11 +208,11 @@ def dots_pack(b: Any, dtype: Optional[str] = None) -> PackedMatrix:
     v = _View(b, dtype)
     if v.dtype not in PACKED_DTYPES:
         raise LookupError(f"no packed kernels for dtype {v.dtype!r}")
-    size = PackedMatrix.packed_size(v.rows, v.cols, v.dtype)
+    size = PackedMatrix.packed_size(v.rows, v.depth, v.dtype)
     buf = _alloc_bytes(size, v.is_cuda)
-    getattr(lib, f"nk_dots_pack_{v.dtype}")(v.ptr, v.rows, v.cols, v.stride, _ptr(buf))
+    getattr(lib, f"nk_dots_pack_{v.dtype}")(v.ptr, v.rows, v.depth, v.stride, _ptr(buf))
     check("dots_pack")
-    return PackedMatrix(buf, v.dtype, v.rows, v.cols)
+    return PackedMatrix(buf, v.dtype, v.rows, v.depth)
 
 
 def _out_matrix(v: _View, width: int, out: Any, dtype_name: str):
@@ -230,21 +232,21 @@ def _packed_call(op: str, a: Any, packed: PackedMatrix, out: Any, dtype: Optiona
     if not isinstance(packed, PackedMatrix) or packed.kind != "dots":
         raise TypeError("second argument must be a PackedMatrix produced by dots_pack")
     v = _view_like(a, dtype, packed.dtype)
-    if v.cols != packed.depth:
-        raise ValueError(f"depth mismatch: a has {v.cols} columns, packed matrix has depth {packed.depth}")
+    if v.depth != packed.depth:
+        raise ValueError(f"depth mismatch: a has {v.depth} dimensions, packed matrix has depth {packed.depth}")
     t = v.dtype
     obj, ptr, stride = _out_matrix(v, packed.width, out, t)
     if obj is None:
         if v.is_cuda:
             import torch
-            tdt = torch.float64 if t == "f32" else (torch.int32 if (t in ("i8", "u8") and op == "dots") else torch.float32)
+            tdt = torch.float64 if t == "f32" else (torch.int32 if (t in ("i8", "u8", "i4", "u4") and op == "dots") else torch.float32)
             obj = torch.empty((v.rows, packed.width), dtype=tdt, device=v.obj.device)
             ptr, stride = obj.data_ptr(), packed.width * obj.element_size()
         else:
             ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if op == "dots" else np.float32)
             obj = np.empty((v.rows, packed.width), dtype=ndt)
             ptr, stride = obj.ctypes.data, packed.width * obj.itemsize
-    getattr(lib, f"nk_{op}_packed_{t}")(v.ptr, _ptr(packed.buffer), ptr, v.rows, packed.width, v.cols, v.stride, stride)
+    getattr(lib, f"nk_{op}_packed_{t}")(v.ptr, _ptr(packed.buffer), ptr, v.rows, packed.width, v.depth, v.stride, stride)
     check(f"{op}_packed")
     return obj
 
@@ -275,7 +277,7 @@ def _symmetric_call(op: str, vectors: Any, out: Any, dtype: Optional[str], start
         # Cells below the diagonal are not written by the call; a fresh result starts as zeros (as the reference's does).
         if v.is_cuda:
             import torch
-            tdt = torch.float64 if t == "f32" else (torch.int32 if (t in ("i8", "u8") and op == "dots") else torch.float32)
+            tdt = torch.float64 if t == "f32" else (torch.int32 if (t in ("i8", "u8", "i4", "u4") and op == "dots") else torch.float32)
             out = torch.zeros((n, n), dtype=tdt, device=v.obj.device)
         else:
             ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if op == "dots" else np.float32)
@@ -291,7 +293,7 @@ def _symmetric_call(op: str, vectors: Any, out: Any, dtype: Optional[str], start
     first = 0 if start_row is None else int(start_row)
     last = n if end_row is None else min(int(end_row), n)
     if last > first:
-        getattr(lib, f"nk_{op}_symmetric_{t}")(v.ptr, n, v.cols, v.stride, ptr, stride, first, last - first)
+        getattr(lib, f"nk_{op}_symmetric_{t}")(v.ptr, n, v.depth, v.stride, ptr, stride, first, last - first)
         check(f"{op}_symmetric")
     return out
 

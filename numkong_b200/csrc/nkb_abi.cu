@@ -224,10 +224,17 @@ const void *resident_matrix(const void *src, MemKind kind, uint64_t rows, uint64
     if (rows <= 1 && stride < row_bytes) stride = row_bytes;
     const bool aligned = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) && ((stride & 15u) == 0);
     if (kind == kMemDevice && aligned && piece_mode == kPieceNone) { *pitch_out = stride; return src; }
-    uint64_t pitch = round_up(row_bytes, 16);
-    void *dst = scratch(slot, rows * pitch + 16);
+    const bool expands = piece_mode_expands(piece_mode);  // 4-bit rows come out twice as long
+    uint64_t pitch = round_up(expands ? row_bytes * 2 : row_bytes, 16);
+    void *dst = scratch(slot, rows * pitch + 16 + (expands && kind == kMemHost ? rows * row_bytes + 16 : 0));
     if (!dst) return nullptr;
-    if (kind == kMemHost) {
+    if (kind == kMemHost && expands) {
+        // Raw rows are uploaded behind the destination, then expanded into it.
+        uint8_t *raw = static_cast<uint8_t *>(dst) + round_up(rows * pitch, 16);
+        if (!cuda_ok(cudaMemcpy2DAsync(raw, row_bytes, src, stride, row_bytes, rows, cudaMemcpyHostToDevice, current_stream()), "upload of input matrix")) return nullptr;
+        if (!cuda_ok(launch_restride(raw, rows, row_bytes, row_bytes, dst, pitch, piece_mode, current_stream()), "operand expansion kernel")) return nullptr;
+        g_launches++;
+    } else if (kind == kMemHost) {
         if (pitch != row_bytes) {
             if (!cuda_ok(cudaMemsetAsync(dst, 0, rows * pitch, current_stream()), "clear staging")) return nullptr;
         }
@@ -285,7 +292,7 @@ void pack_impl(uint32_t magic, uint32_t dt, const void *b, uint64_t rows, uint64
     if (rows && depth) {
         if (in_kind == kMemHost) {
             // Dense upload; the pack kernel reads any alignment, so no re-pitching is needed.
-            uint64_t row_bytes = depth * dtype_bytes(dt);
+            uint64_t row_bytes = source_row_bytes(dt, depth);
             void *stage = scratch(kSlotA, rows * row_bytes + 16);
             ok = stage && cuda_ok(cudaMemcpy2DAsync(stage, row_bytes, b, stride < row_bytes ? row_bytes : stride, row_bytes, rows,
                                                     cudaMemcpyHostToDevice, stream), "upload of matrix to pack");
@@ -384,7 +391,15 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
             a_norms = static_cast<float *>(scratch(kSlotNorms, m * 4));
             if (!a_norms) return false;
         }
-        if (piece_mode == kPieceNone) {
+        if (is_nibble(dt)) {
+            // 4-bit rows are expanded to one byte per value on their way into the staging buffer; norms come from that copy.
+            a_dev = resident_matrix(a, a_kind, m, source_row_bytes(dt, k), a_stride, kSlotA, piece_mode, &a_pitch);
+            if (!a_dev) return false;
+            if (a_norms) {
+                ok = cuda_ok(launch_row_sumsq(operand_dtype(dt), a_dev, m, operand_depth(dt, k), a_pitch, a_norms, true, false, stream), "row norm kernel");
+                g_launches++;
+            }
+        } else if (piece_mode == kPieceNone) {
             a_dev = resident_matrix(a, a_kind, m, k * dtype_bytes(dt), a_stride, kSlotA, kPieceNone, &a_pitch);
             if (!a_dev) return false;
             if (a_norms) {
@@ -411,9 +426,9 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
         }
         if (ok) {
             GemmArgs g;
-            g.dtype = dt; g.epilogue = epilogue; g.a = a_dev; g.a_stride = a_pitch;
+            g.dtype = operand_dtype(dt); g.epilogue = epilogue; g.a = a_dev; g.a_stride = a_pitch;
             g.b_payload = blob + h.payload_offset; g.b_norms = blob + h.norms_offset; g.a_norms = a_norms;
-            g.c = c_dev; g.c_stride = c_pitch; g.m = m; g.n = n; g.k = k;
+            g.c = c_dev; g.c_stride = c_pitch; g.m = m; g.n = n; g.k = operand_depth(dt, k);
             g.depth_padded_bytes = h.depth_padded_bytes; g.error_word = err; g.variant = g_variant.load();
             ok = cuda_ok(launch_gemm_tc(g, stream), "tensor-core GEMM kernel");
             g_launches += gemm_tc_launch_count(g);
@@ -524,6 +539,8 @@ NKB_DEFINE_PACKED_FAMILY(e5m2, kE5M2)
 NKB_DEFINE_PACKED_FAMILY(e2m3, kE2M3)
 NKB_DEFINE_PACKED_FAMILY(e3m2, kE3M2)
 NKB_DEFINE_PACKED_FAMILY(f32, kF32)
+NKB_DEFINE_PACKED_FAMILY(i4, kI4)
+NKB_DEFINE_PACKED_FAMILY(u4, kU4)
 
 NKB_API char const *nkb_last_error(void) { return t_ctx.error.c_str(); }
 NKB_API void nkb_set_stream(void *cuda_stream) { t_ctx.stream = static_cast<cudaStream_t>(cuda_stream); }

@@ -26,7 +26,8 @@ const Entry kTable[] = {
     NKB_PACKED_ENTRIES(bf16, NKB_DTYPE_BF16), NKB_PACKED_ENTRIES(f16, NKB_DTYPE_F16),
     NKB_PACKED_ENTRIES(e4m3, NKB_DTYPE_E4M3), NKB_PACKED_ENTRIES(e5m2, NKB_DTYPE_E5M2),
     NKB_PACKED_ENTRIES(e2m3, NKB_DTYPE_E2M3), NKB_PACKED_ENTRIES(e3m2, NKB_DTYPE_E3M2),
-    NKB_PACKED_ENTRIES(f32, NKB_DTYPE_F32),
+    NKB_PACKED_ENTRIES(f32, NKB_DTYPE_F32),   NKB_PACKED_ENTRIES(i4, NKB_DTYPE_I4),
+    NKB_PACKED_ENTRIES(u4, NKB_DTYPE_U4),
     NKB_MAXSIM_ENTRIES(bf16, NKB_DTYPE_BF16), NKB_MAXSIM_ENTRIES(f16, NKB_DTYPE_F16),
     NKB_MAXSIM_ENTRIES(f32, NKB_DTYPE_F32),
 };

@@ -17,6 +17,8 @@ enum Dtype : uint32_t {
     kBF16 = 1u << 13,
     kE4M3 = 1u << 14,
     kE5M2 = 1u << 15,
+    kI4 = 1u << 16,   // two signed 4-bit values per byte, low nibble first (include/numkong/types.h:1551-1558)
+    kU4 = 1u << 17,   // two unsigned 4-bit values per byte
     kE2M3 = 1u << 18,
     kE3M2 = 1u << 19,
 };
@@ -72,12 +74,20 @@ inline uint32_t norm_bytes(uint32_t dt) { return dt == kF32 ? 8 : 4; }
 inline uint32_t dot_out_bytes(uint32_t dt) { return dt == kF32 ? 8 : 4; }
 inline bool dtype_supported(uint32_t dt) {
     switch (dt) {
-    case kI8: case kU8: case kF32: case kF16: case kBF16: case kE4M3: case kE5M2: case kE2M3: case kE3M2: return true;
+    case kI8: case kU8: case kF32: case kF16: case kBF16: case kE4M3: case kE5M2: case kE2M3: case kE3M2: case kI4: case kU4: return true;
     default: return false;
     }
 }
 
 inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
+
+// 4-bit types: `depth` counts nibbles, a row occupies ceil(depth / 2) bytes, and - like the reference's kernels
+// (include/numkong/dot/serial.h:185-215) - BOTH nibbles of the last byte take part when depth is odd. On the device a
+// nibble row is expanded to one i8 / u8 per value, so everything after the packer and the operand staging sees i8 / u8.
+inline bool is_nibble(uint32_t dt) { return dt == kI4 || dt == kU4; }
+inline uint64_t source_row_bytes(uint32_t dt, uint64_t depth) { return is_nibble(dt) ? (depth + 1) / 2 : depth * dtype_bytes(dt); }
+inline uint32_t operand_dtype(uint32_t dt) { return dt == kI4 ? kI8 : dt == kU4 ? kU8 : dt; }
+inline uint64_t operand_depth(uint32_t dt, uint64_t depth) { return is_nibble(dt) ? (depth + 1) / 2 * 2 : depth; }
 
 #ifdef __CUDACC__
 // Order-preserving integer key of an f32 for selection: a < b  <=>  key(a) < key(b); every NaN shares the last key
@@ -98,7 +108,7 @@ struct PackedGeometry {
 inline PackedGeometry packed_geometry(uint32_t dt, uint64_t rows, uint64_t depth) {
     PackedGeometry g;
     g.rows_padded = round_up(rows ? rows : 1, kRowPad);
-    g.depth_padded_bytes = round_up((depth ? depth : 1) * dtype_bytes(dt), kChunkRowBytes);
+    g.depth_padded_bytes = round_up((depth ? operand_depth(dt, depth) : 1) * dtype_bytes(dt), kChunkRowBytes);
     g.payload_offset = kHeaderBytes;
     g.norms_offset = g.payload_offset + g.rows_padded * g.depth_padded_bytes;
     g.total_bytes = g.norms_offset + round_up(rows * norm_bytes(dt), 128);
@@ -114,10 +124,17 @@ cudaError_t launch_row_sumsq(uint32_t dt, const void *x, uint64_t rows, uint64_t
                              void *out, bool as_f32, bool inverse, cudaStream_t stream);
 
 // Rewrites applied to each 16-byte piece of an FP6 operand on its way to the tensor cores.
-enum PieceMode : int { kPieceNone = 0, kPieceE2M3ToE4M3 = 1, kPieceE3M2ToE4M3 = 2, kPieceFp6Pack = 3 };
+enum PieceMode : int { kPieceNone = 0, kPieceE2M3ToE4M3 = 1, kPieceE3M2ToE4M3 = 2, kPieceFp6Pack = 3,
+                       kPieceI4ToI8 = 4, kPieceU4ToU8 = 5 };  // the last two read 8 source bytes per 16-byte piece
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+inline bool piece_mode_expands(int mode) { return mode == kPieceI4ToI8 || mode == kPieceU4ToU8; }
 // How FP6 operands are fed to tcgen05.mma: 0 = recoded to e4m3 (exact), 1 = native 6-bit operand formats.
 int fp6_native();
 inline int piece_mode_for(uint32_t dt) {
+    if (dt == kI4) return kPieceI4ToI8;
+    if (dt == kU4) return kPieceU4ToU8;
     if (dt != kE2M3 && dt != kE3M2) return kPieceNone;
     if (fp6_native()) return kPieceFp6Pack;
     return dt == kE2M3 ? kPieceE2M3ToE4M3 : kPieceE3M2ToE4M3;
@@ -129,7 +146,8 @@ cudaError_t launch_pack_payload(uint32_t dt, const void *b, uint64_t rows, uint6
                                 cudaStream_t stream);
 
 // Copies a strided matrix into a 16-byte-aligned, 16-byte-pitched scratch copy (for TMA),
-// applying `piece_mode` to every 16-byte piece.
+// applying `piece_mode` to every 16-byte piece. `row_bytes` counts SOURCE bytes (half the written bytes for the
+// nibble-expanding modes).
 cudaError_t launch_restride(const void *src, uint64_t rows, uint64_t row_bytes, uint64_t src_stride,
                             void *dst, uint64_t dst_stride, int piece_mode, cudaStream_t stream);
 

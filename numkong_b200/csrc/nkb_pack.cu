@@ -52,8 +52,25 @@ __device__ __forceinline__ uint32_t e3m2_to_e4m3(uint32_t c) {
     return sign | ((e + 4u) << 3) | (m << 1);            // (1 + m/4) * 2^(e-3)
 }
 
+// 4-bit operands: the low 8 bytes of `v` hold 16 nibbles, low nibble first; each becomes one i8 (sign extended through
+// (x ^ 8) - 8, include/numkong/types.h:1556-1558) or u8.
+__device__ __forceinline__ uint4 expand_nibbles(uint4 v, bool is_signed) {
+    const uint32_t src[2] = {v.x, v.y};
+    uint32_t out[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const uint32_t two_bytes = (src[w >> 1] >> ((w & 1) * 16)) & 0xffffu;
+        // nibbles n0..n3 of these two bytes -> bytes 0..3 of the output word
+        uint32_t spread = (two_bytes & 0xfu) | ((two_bytes & 0xf0u) << 4) | ((two_bytes & 0xf00u) << 8) | ((two_bytes & 0xf000u) << 12);
+        if (is_signed) spread |= ((spread >> 3) & 0x01010101u) * 0xF0u;  // nibbles 8..15 are -8..-1: fill the byte's upper half
+        out[w] = spread;
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
 __device__ __forceinline__ uint4 transform_piece(uint4 v, int mode) {
     if (mode == kPieceNone) return v;
+    if (mode == kPieceI4ToI8 || mode == kPieceU4ToU8) return expand_nibbles(v, mode == kPieceI4ToI8);
     uint32_t w[4] = {v.x, v.y, v.z, v.w};
     if (mode == kPieceE2M3ToE4M3 || mode == kPieceE3M2ToE4M3) {
 #pragma unroll
@@ -103,8 +120,15 @@ __global__ void pack_payload_kernel(const uint8_t *__restrict__ b, uint64_t rows
             row = o / pieces_per_row;
             byte_off = (o % pieces_per_row) * 16u;
         }
+        // Nibble-expanding modes produce a 16-byte piece from 8 source bytes.
+        const bool expands = piece_mode_expands(piece_mode);
+        const uint64_t src_off = expands ? byte_off >> 1 : byte_off;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < rows && byte_off < row_bytes) v = load16_guarded(b + row * stride + byte_off, (int64_t)(row_bytes - byte_off));
+        if (row < rows && src_off < row_bytes) {
+            int64_t valid = (int64_t)(row_bytes - src_off);
+            if (expands && valid > 8) valid = 8;
+            v = load16_guarded(b + row * stride + src_off, valid);
+        }
         payload[o] = transform_piece(v, piece_mode);
     }
 }
@@ -116,8 +140,14 @@ __global__ void restride_kernel(const uint8_t *src, uint64_t rows, uint64_t row_
     for (uint64_t o = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; o < total; o += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t row = o / dst_pieces_per_row;
         uint64_t byte_off = (o % dst_pieces_per_row) * 16u;
+        const bool expands = piece_mode_expands(piece_mode);
+        const uint64_t src_off = expands ? byte_off >> 1 : byte_off;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (byte_off < row_bytes) v = load16_guarded(src + row * src_stride + byte_off, (int64_t)(row_bytes - byte_off));
+        if (src_off < row_bytes) {
+            int64_t valid = (int64_t)(row_bytes - src_off);
+            if (expands && valid > 8) valid = 8;
+            v = load16_guarded(src + row * src_stride + src_off, valid);
+        }
         dst[o] = transform_piece(v, piece_mode);
     }
 }
@@ -144,6 +174,24 @@ struct SumSq<kU8> {
     static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) {
         unsigned v = *p;
         acc += (unsigned long long)(v * v);
+    }
+};
+
+// 4-bit rows: one "element" of the loop below is a byte holding two values.
+template <>
+struct SumSq<kI4> {
+    using Acc = unsigned long long;
+    static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) {
+        const int lo = (int)((*p & 0xfu) ^ 8u) - 8, hi = (int)((*p >> 4) ^ 8u) - 8;
+        acc += (unsigned long long)(lo * lo + hi * hi);
+    }
+};
+template <>
+struct SumSq<kU4> {
+    using Acc = unsigned long long;
+    static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) {
+        const unsigned lo = *p & 0xfu, hi = *p >> 4;
+        acc += (unsigned long long)(lo * lo + hi * hi);
     }
 };
 
@@ -178,7 +226,7 @@ __global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, u
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
         if (lane == 0) {
-            if constexpr (kDtype == kI8 || kDtype == kU8) {
+            if constexpr (kDtype == kI8 || kDtype == kU8 || kDtype == kI4 || kDtype == kU4) {
                 if (inverse) {
                     float s = (float)acc;
                     static_cast<float *>(out)[row] = s > 0.0f ? (float)(1.0 / sqrt((double)s)) : 0.0f;
@@ -212,10 +260,11 @@ cudaError_t launch_row_sumsq(uint32_t dt, const void *x, uint64_t rows, uint64_t
     const int grid = grid_for(rows * 32, block);
     const uint8_t *p = static_cast<const uint8_t *>(x);
     const int mode = as_f32 ? 1 : 0, inv = inverse ? 1 : 0;
+    if (is_nibble(dt)) depth = source_row_bytes(dt, depth);  // the kernel walks bytes, two values each
 #define NKB_CASE(DT) case DT: row_sumsq_kernel<DT><<<grid, block, 0, stream>>>(p, rows, depth, stride_bytes, out, mode, inv); break
     switch (dt) {
         NKB_CASE(kI8); NKB_CASE(kU8); NKB_CASE(kF32); NKB_CASE(kF16); NKB_CASE(kBF16);
-        NKB_CASE(kE4M3); NKB_CASE(kE5M2); NKB_CASE(kE2M3); NKB_CASE(kE3M2);
+        NKB_CASE(kE4M3); NKB_CASE(kE5M2); NKB_CASE(kE2M3); NKB_CASE(kE3M2); NKB_CASE(kI4); NKB_CASE(kU4);
     default: return cudaErrorInvalidValue;
     }
 #undef NKB_CASE
@@ -229,7 +278,7 @@ cudaError_t launch_pack_payload(uint32_t dt, const void *b, uint64_t rows, uint6
     const uint32_t kblocks = (uint32_t)(depth_padded_bytes / kChunkRowBytes);
     const int block = 256;
     const int grid = grid_for(pieces, block, 148 * 32);
-    const uint64_t row_bytes = depth * dtype_bytes(dt);
+    const uint64_t row_bytes = source_row_bytes(dt, depth);
     if (dt == kF32)
         pack_payload_kernel<false><<<grid, block, 0, stream>>>(static_cast<const uint8_t *>(b), rows, row_bytes, stride_bytes,
                                                                static_cast<uint4 *>(payload), pieces, kblocks, kPieceNone);

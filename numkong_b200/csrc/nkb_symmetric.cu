@@ -27,7 +27,7 @@ void symmetric_impl(uint32_t dt, int epilogue, const void *vectors, uint64_t cou
     if (count == 0 || row_count == 0 || row_start >= count) return;
     const uint64_t row_end = row_start + row_count < count ? row_start + row_count : count;
     const uint64_t m = row_end - row_start;
-    const uint32_t out_bytes = dot_out_bytes(dt), eb = dtype_bytes(dt);
+    const uint32_t out_bytes = dot_out_bytes(dt);
     const MemKind v_kind = classify(vectors), r_kind = classify(result);
     // First packed column: the 256-row block that holds row_start (nothing to its left is wanted).
     const uint64_t col0 = row_start / kRowPad * kRowPad;
@@ -44,12 +44,15 @@ void symmetric_impl(uint32_t dt, int epilogue, const void *vectors, uint64_t cou
     if (!dtype_supported(dt) || !vectors || !result) { set_error("symmetric: unsupported element type or null pointer%s", ""); fail(); return; }
     if (depth == 0) { set_error("symmetric: depth must be positive%s", ""); fail(); return; }
     if (result_stride < count * out_bytes || result_stride % out_bytes) { set_error("symmetric: bad result stride%s", ""); fail(); return; }
-    if (stride < depth * eb && count > 1) { set_error("symmetric: stride is smaller than a vector%s", ""); fail(); return; }
+    if (stride < source_row_bytes(dt, depth) && count > 1) { set_error("symmetric: stride is smaller than a vector%s", ""); fail(); return; }
     cudaStream_t stream = current_stream();
     unsigned int *err = device_error_word();
     if (!err) { set_error("could not allocate the device error word%s", ""); fail(); return; }
 
-    const uint64_t row_bytes = depth * eb;
+    const uint64_t row_bytes = source_row_bytes(dt, depth);
+    const uint32_t op_dt = operand_dtype(dt);          // 4-bit rows are expanded to i8 / u8 on the device
+    const uint64_t op_depth = operand_depth(dt, depth);
+    const int piece_mode = piece_mode_for(dt);
     bool ok = true;
     // ---- column operand: rows [col0, count) packed into a scratch blob
     const PackedGeometry g = packed_geometry(dt, cols, depth);
@@ -76,17 +79,16 @@ void symmetric_impl(uint32_t dt, int epilogue, const void *vectors, uint64_t cou
     // ---- row operand: rows [row_start, row_end). They already sit in the staged / caller's device copy.
     const uint8_t *a_src = col_src + (row_start - col0) * col_pitch;
     uint64_t a_pitch = 0;
-    const void *a_raw = ok ? resident_matrix(a_src, kMemDevice, m, row_bytes, col_pitch, kSlotA, kPieceNone, &a_pitch) : nullptr;
+    const void *a_raw = ok ? resident_matrix(a_src, kMemDevice, m, row_bytes, col_pitch, kSlotA, is_nibble(dt) ? piece_mode : kPieceNone, &a_pitch) : nullptr;
     if (!a_raw) { fail(); return; }
     void *a_norms = nullptr;
     if (epilogue != kEpiDot) {
         a_norms = scratch(kSlotNorms, m * 8);
-        ok = a_norms && cuda_ok(launch_row_sumsq(dt, a_raw, m, depth, a_pitch, a_norms, dt != kF32, false, stream), "row norm kernel");
+        ok = a_norms && cuda_ok(launch_row_sumsq(op_dt, a_raw, m, op_depth, a_pitch, a_norms, dt != kF32, false, stream), "row norm kernel");
         g_launches++;
     }
     const void *a_dev = a_raw;
-    const int piece_mode = piece_mode_for(dt);
-    if (ok && piece_mode != kPieceNone) {
+    if (ok && piece_mode != kPieceNone && !is_nibble(dt)) {
         // FP6 rows are rewritten for the tensor cores: in place when they already live in this thread's staging buffer.
         void *dst = const_cast<void *>(a_raw);
         uint64_t dst_pitch = a_pitch;
@@ -122,9 +124,9 @@ void symmetric_impl(uint32_t dt, int epilogue, const void *vectors, uint64_t cou
         g_launches++;
     } else if (ok) {
         GemmArgs args;
-        args.dtype = dt; args.epilogue = epilogue; args.a = a_dev; args.a_stride = a_pitch;
+        args.dtype = op_dt; args.epilogue = epilogue; args.a = a_dev; args.a_stride = a_pitch;
         args.b_payload = blob + g.payload_offset; args.b_norms = blob + g.norms_offset; args.a_norms = static_cast<const float *>(a_norms);
-        args.c = c_dev; args.c_stride = c_pitch; args.m = m; args.n = cols; args.k = depth;
+        args.c = c_dev; args.c_stride = c_pitch; args.m = m; args.n = cols; args.k = op_depth;
         args.depth_padded_bytes = g.depth_padded_bytes; args.error_word = err; args.variant = current_variant();
         args.tri_diag = tri_diag;
         ok = cuda_ok(launch_gemm_tc(args, stream), "tensor-core GEMM kernel");
@@ -174,5 +176,7 @@ NKB_DEFINE_SYMMETRIC(e4m3, kE4M3)
 NKB_DEFINE_SYMMETRIC(e5m2, kE5M2)
 NKB_DEFINE_SYMMETRIC(e2m3, kE2M3)
 NKB_DEFINE_SYMMETRIC(e3m2, kE3M2)
+NKB_DEFINE_SYMMETRIC(i4, kI4)
+NKB_DEFINE_SYMMETRIC(u4, kU4)
 
 } // extern "C"

@@ -20,10 +20,15 @@ REF_SO = _HERE / "_ref" / "libnumkong.so"
 REF_SERIAL_SO = _HERE / "_ref" / "libnkref_serial.so"
 
 CODES = {"i8": 1 << 2, "u8": 1 << 6, "f32": 1 << 11, "f16": 1 << 12, "bf16": 1 << 13,
-         "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19}
-BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1}
+         "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17}
+BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i4": 1, "u4": 1}
 STORAGE = {"i8": np.int8, "u8": np.uint8, "f32": np.float32, "f16": np.uint16, "bf16": np.uint16,
-           "e4m3": np.uint8, "e5m2": np.uint8, "e2m3": np.uint8, "e3m2": np.uint8}
+           "e4m3": np.uint8, "e5m2": np.uint8, "e2m3": np.uint8, "e3m2": np.uint8, "i4": np.uint8, "u4": np.uint8}
+
+
+def _depth(x: np.ndarray, dtype: str, depth: Optional[int]) -> int:
+    """Logical dimensions of a row: 4-bit types hold two per byte (an explicit `depth` may be odd)."""
+    return int(depth) if depth is not None else x.shape[1] * (2 if dtype in ("i4", "u4") else 1)
 
 
 def build(force: bool = False) -> Path:
@@ -87,40 +92,40 @@ def decode(x: np.ndarray, dtype: str) -> np.ndarray:
 def out_dtype(dtype: str, op: str = "dots"):
     if dtype == "f32":
         return np.float64
-    if op == "dots" and dtype == "i8":
+    if op == "dots" and dtype in ("i8", "i4"):
         return np.int32
-    if op == "dots" and dtype == "u8":
+    if op == "dots" and dtype in ("u8", "u4"):
         return np.uint32
     return np.float32
 
 
-def dots(a: np.ndarray, b: np.ndarray, dtype: str) -> np.ndarray:
+def dots(a: np.ndarray, b: np.ndarray, dtype: str, depth: Optional[int] = None) -> np.ndarray:
     a, b = _as_storage(a, dtype), _as_storage(b, dtype)
     c = np.empty((a.shape[0], b.shape[0]), dtype=out_dtype(dtype))
     _lib.orc_dots(CODES[dtype], a.ctypes.data, _stride(a), b.ctypes.data, _stride(b), c.ctypes.data,
-                  c.shape[1] * c.itemsize, a.shape[0], b.shape[0], a.shape[1])
+                  c.shape[1] * c.itemsize, a.shape[0], b.shape[0], _depth(a, dtype, depth))
     return c
 
 
-def _spatials(kind: int, a, b, dtype):
+def _spatials(kind: int, a, b, dtype, depth=None):
     a, b = _as_storage(a, dtype), _as_storage(b, dtype)
     c = np.empty((a.shape[0], b.shape[0]), dtype=out_dtype(dtype, "spatial"))
     _lib.orc_spatials(kind, CODES[dtype], a.ctypes.data, _stride(a), b.ctypes.data, _stride(b), c.ctypes.data,
-                      c.shape[1] * c.itemsize, a.shape[0], b.shape[0], a.shape[1])
+                      c.shape[1] * c.itemsize, a.shape[0], b.shape[0], _depth(a, dtype, depth))
     return c
 
 
-def angulars(a, b, dtype):
-    return _spatials(0, a, b, dtype)
+def angulars(a, b, dtype, depth: Optional[int] = None):
+    return _spatials(0, a, b, dtype, depth)
 
 
-def euclideans(a, b, dtype):
-    return _spatials(1, a, b, dtype)
+def euclideans(a, b, dtype, depth: Optional[int] = None):
+    return _spatials(1, a, b, dtype, depth)
 
 
-def sumsq(x: np.ndarray, dtype: str) -> np.ndarray:
+def sumsq(x: np.ndarray, dtype: str, depth: Optional[int] = None) -> np.ndarray:
     x = _as_storage(x, dtype)
-    return np.array([_lib.orc_sumsq(CODES[dtype], x[i:i + 1].ctypes.data, x.shape[1]) for i in range(x.shape[0])])
+    return np.array([_lib.orc_sumsq(CODES[dtype], x[i:i + 1].ctypes.data, _depth(x, dtype, depth)) for i in range(x.shape[0])])
 
 
 def _maxsim(fn, q, d, dtype, want_best):
@@ -174,32 +179,33 @@ class _Ref:
         f.restype, f.argtypes = restype, argtypes
         return f
 
-    def pack(self, b: np.ndarray, dtype: str, family: str = "dots") -> np.ndarray:
+    def pack(self, b: np.ndarray, dtype: str, family: str = "dots", depth: Optional[int] = None) -> np.ndarray:
         b = _as_storage(b, dtype)
         u64, vp = ctypes.c_uint64, ctypes.c_void_p
-        size = self._fn(f"{family}_packed_size_{dtype}", u64, [u64, u64])(b.shape[0], b.shape[1])
+        k = _depth(b, dtype, depth)
+        size = self._fn(f"{family}_packed_size_{dtype}", u64, [u64, u64])(b.shape[0], k)
         blob = np.zeros(size + 64, dtype=np.uint8)
-        self._fn(f"{family}_pack_{dtype}", None, [vp, u64, u64, u64, vp])(b.ctypes.data, b.shape[0], b.shape[1], _stride(b), blob.ctypes.data)
+        self._fn(f"{family}_pack_{dtype}", None, [vp, u64, u64, u64, vp])(b.ctypes.data, b.shape[0], k, _stride(b), blob.ctypes.data)
         return blob
 
     def packed(self, op: str, a: np.ndarray, blob: np.ndarray, n: int, dtype: str, out: Optional[np.ndarray] = None,
-               rows: Optional[slice] = None) -> np.ndarray:
+               rows: Optional[slice] = None, depth: Optional[int] = None) -> np.ndarray:
         a = _as_storage(a, dtype)
         u64, vp = ctypes.c_uint64, ctypes.c_void_p
         c = out if out is not None else np.empty((a.shape[0], n), dtype=out_dtype(dtype, op))
         f = self._fn(f"{op}_packed_{dtype}", None, [vp, vp, vp, u64, u64, u64, u64, u64])
         lo, hi = (0, a.shape[0]) if rows is None else (rows.start, rows.stop)
-        f(a[lo:hi].ctypes.data, blob.ctypes.data, c[lo:hi].ctypes.data, hi - lo, n, a.shape[1], _stride(a), c.strides[0])
+        f(a[lo:hi].ctypes.data, blob.ctypes.data, c[lo:hi].ctypes.data, hi - lo, n, _depth(a, dtype, depth), _stride(a), c.strides[0])
         return c
 
-    def dots(self, a, b, dtype):
-        return self.packed("dots", a, self.pack(b, dtype), np.asarray(b).shape[0], dtype)
+    def dots(self, a, b, dtype, depth=None):
+        return self.packed("dots", a, self.pack(b, dtype, depth=depth), np.asarray(b).shape[0], dtype, depth=depth)
 
-    def angulars(self, a, b, dtype):
-        return self.packed("angulars", a, self.pack(b, dtype), np.asarray(b).shape[0], dtype)
+    def angulars(self, a, b, dtype, depth=None):
+        return self.packed("angulars", a, self.pack(b, dtype, depth=depth), np.asarray(b).shape[0], dtype, depth=depth)
 
-    def euclideans(self, a, b, dtype):
-        return self.packed("euclideans", a, self.pack(b, dtype), np.asarray(b).shape[0], dtype)
+    def euclideans(self, a, b, dtype, depth=None):
+        return self.packed("euclideans", a, self.pack(b, dtype, depth=depth), np.asarray(b).shape[0], dtype, depth=depth)
 
     def maxsim(self, q, d, dtype) -> float:
         q, d = _as_storage(q, dtype), _as_storage(d, dtype)

@@ -24,7 +24,10 @@
 enum {
     ORC_I8 = 1 << 2, ORC_U8 = 1 << 6, ORC_F32 = 1 << 11, ORC_F16 = 1 << 12, ORC_BF16 = 1 << 13,
     ORC_E4M3 = 1 << 14, ORC_E5M2 = 1 << 15, ORC_E2M3 = 1 << 18, ORC_E3M2 = 1 << 19,
+    ORC_I4 = 1 << 16, ORC_U4 = 1 << 17, /* two values per byte, low nibble first; depth counts values */
 };
+#define ORC_IS_INT(dt) ((dt) == ORC_I8 || (dt) == ORC_U8 || (dt) == ORC_I4 || (dt) == ORC_U4)
+#define ORC_IS_SIGNED_INT(dt) ((dt) == ORC_I8 || (dt) == ORC_I4)
 
 static float bits_to_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
 static uint32_t f32_to_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
@@ -143,8 +146,19 @@ static double dot_f64lanes(const uint8_t *a, const uint8_t *b, uint64_t k) {
     }
     return s[0] + s[1] + s[2] + s[3];
 }
+/* 4-bit values: low nibble first, signed ones through (x ^ 8) - 8 (include/numkong/types.h:1551-1558). The depth is
+ * rounded up to a whole byte, so both nibbles of the last byte always count (include/numkong/dot/serial.h:185-215). */
+static int nibble(int dt, uint8_t byte, int high) {
+    int x = high ? (byte >> 4) & 0xf : byte & 0xf;
+    return dt == ORC_I4 ? (x ^ 8) - 8 : x;
+}
 static int64_t dot_int(int dt, const uint8_t *a, const uint8_t *b, uint64_t k) {
     int64_t s = 0;
+    if (dt == ORC_I4 || dt == ORC_U4) {
+        for (uint64_t l = 0; l < (k + 1) / 2; ++l)
+            s += (int64_t)nibble(dt, a[l], 0) * nibble(dt, b[l], 0) + (int64_t)nibble(dt, a[l], 1) * nibble(dt, b[l], 1);
+        return s;
+    }
     if (dt == ORC_I8) for (uint64_t l = 0; l < k; ++l) s += (int64_t)(int8_t)a[l] * (int8_t)b[l];
     else for (uint64_t l = 0; l < k; ++l) s += (int64_t)a[l] * b[l];
     return s;
@@ -158,7 +172,7 @@ ORC_API void orc_dots(int dt, const void *a, uint64_t a_stride, const void *b, u
         uint8_t *row = (uint8_t *)c + i * c_stride;
         for (uint64_t j = 0; j < n; ++j) {
             const uint8_t *x = ap + i * a_stride, *y = bp + j * b_stride;
-            if (dt == ORC_I8 || dt == ORC_U8) ((int32_t *)row)[j] = (int32_t)dot_int(dt, x, y, k);
+            if (ORC_IS_INT(dt)) ((int32_t *)row)[j] = (int32_t)dot_int(dt, x, y, k);
             else if (dt == ORC_F32) ((double *)row)[j] = dot_f64lanes(x, y, k);
             else ((float *)row)[j] = dot_f32lanes(dt, x, y, k);
         }
@@ -183,7 +197,7 @@ static float sumsq_f32_neumaier(int dt, const uint8_t *x, uint64_t k) {
 }
 ORC_API double orc_sumsq(int dt, const void *x, uint64_t k) {
     const uint8_t *p = (const uint8_t *)x;
-    if (dt == ORC_I8 || dt == ORC_U8) return (double)(uint32_t)(uint64_t)dot_int(dt, p, p, k);
+    if (ORC_IS_INT(dt)) return (double)(uint32_t)(uint64_t)dot_int(dt, p, p, k);
     if (dt == ORC_F32) {
         /* the same compensated sum carried in f64 (reduce/serial.h:50-70) */
         double run = 0, comp = 0;
@@ -238,8 +252,8 @@ ORC_API void orc_spatials(int kind, int dt, const void *a, uint64_t a_stride, co
                 ((double *)row)[j] = r;
             } else {
                 float dot, fa, fb;
-                if (dt == ORC_I8) { dot = (float)(int32_t)dot_int(dt, x, y, k); fa = (float)(int32_t)(uint32_t)an; fb = (float)(int32_t)(uint32_t)bn[j]; }
-                else if (dt == ORC_U8) { dot = (float)(uint32_t)dot_int(dt, x, y, k); fa = (float)(uint32_t)an; fb = (float)(uint32_t)bn[j]; }
+                if (ORC_IS_SIGNED_INT(dt)) { dot = (float)(int32_t)dot_int(dt, x, y, k); fa = (float)(int32_t)(uint32_t)an; fb = (float)(int32_t)(uint32_t)bn[j]; }
+                else if (dt == ORC_U8 || dt == ORC_U4) { dot = (float)(uint32_t)dot_int(dt, x, y, k); fa = (float)(uint32_t)an; fb = (float)(uint32_t)bn[j]; }
                 else { dot = dot_f32lanes(dt, x, y, k); fa = (float)an; fb = (float)bn[j]; }
                 ((float *)row)[j] = kind == 0 ? angular_from_dot_f32(dot, fa, fb) : euclidean_from_dot_f32(dot, fa, fb);
             }

@@ -35,6 +35,8 @@ REF_PACKED_FAMILY(e5m2, nk_e5m2_t, nk_f32_t, nk_f32_t)
 REF_PACKED_FAMILY(e2m3, nk_e2m3_t, nk_f32_t, nk_f32_t)
 REF_PACKED_FAMILY(e3m2, nk_e3m2_t, nk_f32_t, nk_f32_t)
 REF_PACKED_FAMILY(f32, nk_f32_t, nk_f64_t, nk_f64_t)
+REF_PACKED_FAMILY(i4, nk_i4x2_t, nk_i32_t, nk_f32_t)
+REF_PACKED_FAMILY(u4, nk_u4x2_t, nk_u32_t, nk_f32_t)
 
 #define REF_MAXSIM_FAMILY(T, IN, OUT)                                                                                \
     REF_API nk_size_t ref_maxsim_packed_size_##T(nk_size_t n, nk_size_t k) { return nk_maxsim_packed_size_##T##_serial(n, k); } \
