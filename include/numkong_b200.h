@@ -45,6 +45,7 @@ extern "C" {
 typedef uint64_t nk_size_t; /* types.h:854-856 */
 
 /* dtype codes, numerically nk_dtype_t (types.h:923-953) */
+#define NKB_DTYPE_U1 (1u << 1) /* eight values per byte; `depth` counts bits */
 #define NKB_DTYPE_I8 (1u << 2)
 #define NKB_DTYPE_U8 (1u << 6)
 #define NKB_DTYPE_F32 (1u << 11)
@@ -116,6 +117,27 @@ NKB_DECLARE_SYMMETRIC_FAMILY(e3m2)
 NKB_DECLARE_SYMMETRIC_FAMILY(f32)
 NKB_DECLARE_SYMMETRIC_FAMILY(i4)
 NKB_DECLARE_SYMMETRIC_FAMILY(u4)
+
+/* ---- one-bit vectors: AND-popcount products and the set distances built on them -----------------------
+ * nk_dots_packed_size_u1 / nk_dots_pack_u1 / nk_dots_packed_u1 / nk_dots_symmetric_u1 replace
+ * include/numkong/dots.h:201,245,295,357 (u32 cells); nk_hammings_* and nk_jaccards_* replace include/numkong/sets.h:69-117:
+ * Hamming = |a| + |b| - 2 |a & b| (u32 cells), Jaccard = 1 - |a & b| / |a | b| (f32 cells, 0 for two empty sets). The
+ * blob packed by nk_dots_pack_u1 serves all three; every bit of the last byte counts when `depth` stops inside it.
+ */
+NKB_API nk_size_t nk_dots_packed_size_u1(nk_size_t width, nk_size_t depth);
+NKB_API void nk_dots_pack_u1(void const *b, nk_size_t width, nk_size_t depth, nk_size_t b_stride, void *b_packed);
+NKB_API void nk_dots_packed_u1(void const *a, void const *b_packed, void *c, nk_size_t height, nk_size_t width,
+                               nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride);
+NKB_API void nk_dots_symmetric_u1(void const *vectors, nk_size_t vectors_count, nk_size_t depth, nk_size_t stride,
+                                  void *result, nk_size_t result_stride, nk_size_t row_start, nk_size_t row_count);
+NKB_API void nk_hammings_packed_u1(void const *v, void const *q_packed, void *result, nk_size_t rows, nk_size_t cols,
+                                   nk_size_t d, nk_size_t v_stride_in_bytes, nk_size_t r_stride_in_bytes);
+NKB_API void nk_hammings_symmetric_u1(void const *vectors, nk_size_t vectors_count, nk_size_t d, nk_size_t stride,
+                                      void *result, nk_size_t result_stride, nk_size_t row_start, nk_size_t row_count);
+NKB_API void nk_jaccards_packed_u1(void const *v, void const *q_packed, void *result, nk_size_t rows, nk_size_t cols,
+                                   nk_size_t d, nk_size_t v_stride_in_bytes, nk_size_t r_stride_in_bytes);
+NKB_API void nk_jaccards_symmetric_u1(void const *vectors, nk_size_t vectors_count, nk_size_t d, nk_size_t stride,
+                                      void *result, nk_size_t result_stride, nk_size_t row_start, nk_size_t row_count);
 
 /* ---- MaxSim late interaction -------------------------------------------------------------------
  * replaces include/numkong/maxsim.h:72-114 (wrappers c/numkong.c:738-765). Both sides are packed

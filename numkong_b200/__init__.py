@@ -27,6 +27,7 @@ from ._lib import DIMENSIONS_PER_VALUE, DTYPE_BYTES, DTYPE_CODES, MAXSIM_DTYPES,
 __all__ = [
     "PackedMatrix", "MaxSimPackedMatrix", "dots_pack", "dots_packed", "angulars_packed", "euclideans_packed",
     "dots_symmetric", "angulars_symmetric", "euclideans_symmetric",
+    "hammings_packed", "jaccards_packed", "hammings_symmetric", "jaccards_symmetric",
     "maxsim_pack", "maxsim_packed", "maxsim", "maxsims_packed", "angulars_packed_topk", "euclideans_packed_topk",
     "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error",
 ]
@@ -39,7 +40,12 @@ _TORCH_NAMES = {
     "torch.int8": "i8", "torch.uint8": "u8", "torch.float32": "f32", "torch.float16": "f16",
     "torch.bfloat16": "bf16", "torch.float8_e4m3fn": "e4m3", "torch.float8_e5m2": "e5m2",
 }
-_OUT_NUMPY = {"i8": np.int32, "u8": np.uint32, "i4": np.int32, "u4": np.uint32, "f32": np.float64}
+_OUT_NUMPY = {"i8": np.int32, "u8": np.uint32, "i4": np.int32, "u4": np.uint32, "u1": np.uint32, "f32": np.float64}
+
+
+def _integer_cells(dtype: str, op: str) -> bool:
+    """Integer result cells: dots of the integer types, and Hamming distances."""
+    return (op == "dots" and dtype in ("i8", "u8", "i4", "u4", "u1")) or op == "hammings"
 
 
 def _is_torch(x: Any) -> bool:
@@ -145,7 +151,7 @@ def _view_like(x: Any, dtype: Optional[str], packed_dtype: str) -> _View:
     if dtype is None:
         name = (_TORCH_NAMES.get(str(x.dtype)) if _is_torch(x) else _NUMPY_NAMES.get(np.asarray(x).dtype.name))
         container = (name in (None, "u8") and packed_dtype not in ("i8", "u8", "f32")) or \
-                    (name == "i8" and packed_dtype in ("i4", "u4"))
+                    (name == "i8" and packed_dtype in ("i4", "u4")) or (name == "u8" and packed_dtype == "u1")
         dtype = packed_dtype if container else name
     v = _View(x, dtype)
     if v.dtype != packed_dtype:
@@ -239,11 +245,11 @@ def _packed_call(op: str, a: Any, packed: PackedMatrix, out: Any, dtype: Optiona
     if obj is None:
         if v.is_cuda:
             import torch
-            tdt = torch.float64 if t == "f32" else (torch.int32 if (t in ("i8", "u8", "i4", "u4") and op == "dots") else torch.float32)
+            tdt = torch.float64 if t == "f32" else (torch.int32 if _integer_cells(t, op) else torch.float32)
             obj = torch.empty((v.rows, packed.width), dtype=tdt, device=v.obj.device)
             ptr, stride = obj.data_ptr(), packed.width * obj.element_size()
         else:
-            ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if op == "dots" else np.float32)
+            ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if _integer_cells(t, op) else np.float32)
             obj = np.empty((v.rows, packed.width), dtype=ndt)
             ptr, stride = obj.ctypes.data, packed.width * obj.itemsize
     getattr(lib, f"nk_{op}_packed_{t}")(v.ptr, _ptr(packed.buffer), ptr, v.rows, packed.width, v.depth, v.stride, stride)
@@ -277,10 +283,10 @@ def _symmetric_call(op: str, vectors: Any, out: Any, dtype: Optional[str], start
         # Cells below the diagonal are not written by the call; a fresh result starts as zeros (as the reference's does).
         if v.is_cuda:
             import torch
-            tdt = torch.float64 if t == "f32" else (torch.int32 if (t in ("i8", "u8", "i4", "u4") and op == "dots") else torch.float32)
+            tdt = torch.float64 if t == "f32" else (torch.int32 if _integer_cells(t, op) else torch.float32)
             out = torch.zeros((n, n), dtype=tdt, device=v.obj.device)
         else:
-            ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if op == "dots" else np.float32)
+            ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if _integer_cells(t, op) else np.float32)
             out = np.zeros((n, n), dtype=ndt)
     if _is_torch(out):
         if tuple(out.shape) != (n, n) or out.element_size() != cell:
@@ -314,6 +320,28 @@ def euclideans_symmetric(vectors: Any, *, dtype: Optional[str] = None, out: Any 
                          end_row: Optional[int] = None):
     """Upper triangle of the pairwise Euclidean distances (diagonal 0). Mirrors nk.euclideans_symmetric."""
     return _symmetric_call("euclideans", vectors, out, dtype, start_row, end_row)
+
+
+def hammings_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Optional[str] = "u1"):
+    """Hamming distances between bit vectors (u32 cells). Mirrors nk.hammings_packed."""
+    return _packed_call("hammings", a, packed, out, dtype)
+
+
+def jaccards_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Optional[str] = "u1"):
+    """Jaccard distances between bit vectors (f32 cells). Mirrors nk.jaccards_packed."""
+    return _packed_call("jaccards", a, packed, out, dtype)
+
+
+def hammings_symmetric(vectors: Any, *, dtype: Optional[str] = "u1", out: Any = None, start_row: Optional[int] = None,
+                       end_row: Optional[int] = None):
+    """Upper triangle of the pairwise Hamming distances (diagonal 0). Mirrors nk.hammings_symmetric."""
+    return _symmetric_call("hammings", vectors, out, dtype, start_row, end_row)
+
+
+def jaccards_symmetric(vectors: Any, *, dtype: Optional[str] = "u1", out: Any = None, start_row: Optional[int] = None,
+                       end_row: Optional[int] = None):
+    """Upper triangle of the pairwise Jaccard distances (diagonal 0). Mirrors nk.jaccards_symmetric."""
+    return _symmetric_call("jaccards", vectors, out, dtype, start_row, end_row)
 
 
 def maxsim_pack(vectors: Any, dtype: Optional[str] = None) -> MaxSimPackedMatrix:

@@ -14,12 +14,13 @@ LIB_PATH = _HERE / "libnumkong_b200.so"
 # name -> numerically nk_dtype_t (include/numkong/types.h:923-953 of the reference)
 DTYPE_CODES = {
     "i8": 1 << 2, "u8": 1 << 6, "f32": 1 << 11, "f16": 1 << 12, "bf16": 1 << 13,
-    "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17,
+    "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17, "u1": 1 << 1,
 }
-DTYPE_BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i4": 1, "u4": 1}
+DTYPE_BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i4": 1, "u4": 1, "u1": 1}
 # Logical dimensions per storage element: 4-bit types hold two values per byte and `depth` counts values, as in the
 # reference's binding (python/matrix.c:400-401 multiplies the byte width by nk_dimensions_per_value).
-DIMENSIONS_PER_VALUE = {"i4": 2, "u4": 2}
+DIMENSIONS_PER_VALUE = {"i4": 2, "u4": 2, "u1": 8}
+SET_DTYPES = ("u1",)  # dots (AND-popcount), Hamming and Jaccard instead of angular / Euclidean
 PACKED_DTYPES = tuple(DTYPE_CODES)
 MAXSIM_DTYPES = ("bf16", "f16", "f32")
 
@@ -37,7 +38,7 @@ def _load() -> ctypes.CDLL:
         f.restype, f.argtypes = sz, [sz, sz]
         f = getattr(lib, f"nk_dots_pack_{t}")
         f.restype, f.argtypes = None, [vp, sz, sz, sz, vp]
-        for op in ("dots", "angulars", "euclideans"):
+        for op in (("dots", "hammings", "jaccards") if t in SET_DTYPES else ("dots", "angulars", "euclideans")):
             f = getattr(lib, f"nk_{op}_packed_{t}")
             f.restype, f.argtypes = None, [vp, vp, vp, sz, sz, sz, sz, sz]
             f = getattr(lib, f"nk_{op}_symmetric_{t}")

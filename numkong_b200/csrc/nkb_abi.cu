@@ -224,8 +224,9 @@ const void *resident_matrix(const void *src, MemKind kind, uint64_t rows, uint64
     if (rows <= 1 && stride < row_bytes) stride = row_bytes;
     const bool aligned = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) && ((stride & 15u) == 0);
     if (kind == kMemDevice && aligned && piece_mode == kPieceNone) { *pitch_out = stride; return src; }
-    const bool expands = piece_mode_expands(piece_mode);  // 4-bit rows come out twice as long
-    uint64_t pitch = round_up(expands ? row_bytes * 2 : row_bytes, 16);
+    const int shift = piece_mode_shift(piece_mode);  // sub-byte rows come out 2 or 8 times as long
+    const bool expands = shift != 0;
+    uint64_t pitch = round_up(row_bytes << shift, 16);
     void *dst = scratch(slot, rows * pitch + 16 + (expands && kind == kMemHost ? rows * row_bytes + 16 : 0));
     if (!dst) return nullptr;
     if (kind == kMemHost && expands) {
@@ -391,8 +392,8 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
             a_norms = static_cast<float *>(scratch(kSlotNorms, m * 4));
             if (!a_norms) return false;
         }
-        if (is_nibble(dt)) {
-            // 4-bit rows are expanded to one byte per value on their way into the staging buffer; norms come from that copy.
+        if (is_subbyte(dt)) {
+            // Sub-byte rows are expanded to one byte per value on their way into the staging buffer; norms come from that copy.
             a_dev = resident_matrix(a, a_kind, m, source_row_bytes(dt, k), a_stride, kSlotA, piece_mode, &a_pitch);
             if (!a_dev) return false;
             if (a_norms) {
@@ -541,6 +542,25 @@ NKB_DEFINE_PACKED_FAMILY(e3m2, kE3M2)
 NKB_DEFINE_PACKED_FAMILY(f32, kF32)
 NKB_DEFINE_PACKED_FAMILY(i4, kI4)
 NKB_DEFINE_PACKED_FAMILY(u4, kU4)
+
+// One-bit vectors: the "dot" is the AND-popcount, the packed norms are population counts, and the two set distances are
+// epilogues of the same product (include/numkong/sets.h:69-117, generators include/numkong/sets/serial.h:19-39).
+NKB_API nk_size_t nk_dots_packed_size_u1(nk_size_t width, nk_size_t depth) { return packed_size_impl(kU1, width, depth); }
+NKB_API void nk_dots_pack_u1(void const *b, nk_size_t width, nk_size_t depth, nk_size_t b_stride, void *b_packed) {
+    pack_impl(kMagicDots, kU1, b, width, depth, b_stride, b_packed, false);
+}
+NKB_API void nk_dots_packed_u1(void const *a, void const *b_packed, void *c, nk_size_t height, nk_size_t width, nk_size_t depth,
+                               nk_size_t a_stride, nk_size_t c_stride) {
+    packed_impl(kU1, kEpiDot, a, b_packed, c, height, width, depth, a_stride, c_stride);
+}
+NKB_API void nk_hammings_packed_u1(void const *v, void const *q_packed, void *result, nk_size_t rows, nk_size_t cols, nk_size_t d,
+                                   nk_size_t v_stride, nk_size_t r_stride) {
+    packed_impl(kU1, kEpiHamming, v, q_packed, result, rows, cols, d, v_stride, r_stride);
+}
+NKB_API void nk_jaccards_packed_u1(void const *v, void const *q_packed, void *result, nk_size_t rows, nk_size_t cols, nk_size_t d,
+                                   nk_size_t v_stride, nk_size_t r_stride) {
+    packed_impl(kU1, kEpiJaccard, v, q_packed, result, rows, cols, d, v_stride, r_stride);
+}
 
 NKB_API char const *nkb_last_error(void) { return t_ctx.error.c_str(); }
 NKB_API void nkb_set_stream(void *cuda_stream) { t_ctx.stream = static_cast<cudaStream_t>(cuda_stream); }

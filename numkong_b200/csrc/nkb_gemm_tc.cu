@@ -131,6 +131,23 @@ __device__ __forceinline__ float distance_value(uint32_t raw, uint32_t int_mode,
     }
 }
 
+// Bits of one finalised output cell for every epilogue but the raw dot. The set distances (one-bit inputs: `raw` is the
+// AND-popcount, the factors are the two population counts, exact in f32 below 2^24) follow
+// include/numkong/set/serial.h:150-168: Hamming = |a| + |b| - 2 |a & b| in u32, Jaccard = 1 - |a & b| / (|a| + |b| - |a & b|)
+// in f32 with the reference's operation order (0 for two empty sets).
+template <int kEpi>
+__device__ __forceinline__ uint32_t cell_bits(uint32_t raw, uint32_t int_mode, float row_factor, float col_factor) {
+    if constexpr (kEpi == kEpiHamming) {
+        return __float2uint_rn(row_factor) + __float2uint_rn(col_factor) - 2u * raw;
+    } else if constexpr (kEpi == kEpiJaccard) {
+        const float dot = (float)raw;
+        const float union_size = row_factor + col_factor - dot;
+        return __float_as_uint(union_size != 0.0f ? 1.0f - __fdiv_rn(dot, union_size) : 0.0f);
+    } else {
+        return __float_as_uint(distance_value<kEpi>(raw, int_mode, row_factor, col_factor));
+    }
+}
+
 // Filter mode of the distance epilogues: nothing is stored; the values of this thread's row that lie below the row's
 // threshold are appended to the row's candidate list (in no particular order; a count beyond the capacity tells the
 // consumer that values were dropped). Distances are >= -0 and never NaN, so the signed integer order of their bit
@@ -208,7 +225,7 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
         float an = my_row < p.m ? p.a_norms[my_row] : 0.0f;
         row_factor = kEpi == kEpiAngular ? (an > 0.0f ? rsqrt_refined(an) : 0.0f) : an;
     }
-    if constexpr (kEpi != kEpiDot) {
+    if constexpr (kEpi == kEpiAngular || kEpi == kEpiEuclidean) {
         if (p.candidates != nullptr) {
             filter_tile<kEpi, kCols>(acc, p, my_row, col_base, row_factor, colf + colf_off, stage, lane);
             return;
@@ -228,9 +245,7 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
             for (int j = 0; j < 4; ++j) {
                 const uint32_t raw = acc[c * kW + q * 4 + j];
                 if constexpr (kEpi == kEpiDot) out[j] = raw;
-                else {
-                    out[j] = __float_as_uint(distance_value<kEpi>(raw, p.int_mode, row_factor, cf[j]));
-                }
+                else out[j] = cell_bits<kEpi>(raw, p.int_mode, row_factor, cf[j]);
             }
             *reinterpret_cast<uint4 *>(stage + lane * kPitch + q * 4) = make_uint4(out[0], out[1], out[2], out[3]);
         }
@@ -671,6 +686,12 @@ cudaError_t launch_by_epilogue(int epi, int bn, bool wide_store, const CUtensorM
     case kEpiDot: return launch_by_tile<kKind, kEpiDot>(bn, wide_store, map, dev, stream);
     case kEpiAngular: return launch_by_tile<kKind, kEpiAngular>(bn, wide_store, map, dev, stream);
     case kEpiEuclidean: return launch_by_tile<kKind, kEpiEuclidean>(bn, wide_store, map, dev, stream);
+    case kEpiHamming:  // the set distances exist for one-bit inputs only, which run on the integer kind
+        if constexpr (kKind == kKindI8) return launch_by_tile<kKind, kEpiHamming>(bn, wide_store, map, dev, stream);
+        else return cudaErrorInvalidValue;
+    case kEpiJaccard:
+        if constexpr (kKind == kKindI8) return launch_by_tile<kKind, kEpiJaccard>(bn, wide_store, map, dev, stream);
+        else return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
     }
 }
@@ -711,6 +732,12 @@ cudaError_t launch_pair_by_epilogue(int epi, const CUtensorMap &a_map, const CUt
     case kEpiDot: return launch_pair<kKind, kEpiDot>(a_map, b_map, dev, stream);
     case kEpiAngular: return launch_pair<kKind, kEpiAngular>(a_map, b_map, dev, stream);
     case kEpiEuclidean: return launch_pair<kKind, kEpiEuclidean>(a_map, b_map, dev, stream);
+    case kEpiHamming:
+        if constexpr (kKind == kKindI8) return launch_pair<kKind, kEpiHamming>(a_map, b_map, dev, stream);
+        else return cudaErrorInvalidValue;
+    case kEpiJaccard:
+        if constexpr (kKind == kKindI8) return launch_pair<kKind, kEpiJaccard>(a_map, b_map, dev, stream);
+        else return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
     }
 }

@@ -10,6 +10,7 @@
 namespace nkb {
 
 enum Dtype : uint32_t {
+    kU1 = 1u << 1,    // eight one-bit values per byte (include/numkong/types.h:925)
     kI8 = 1u << 2,
     kU8 = 1u << 6,
     kF32 = 1u << 11,
@@ -24,7 +25,9 @@ enum Dtype : uint32_t {
 };
 
 // What the accumulators are turned into before they are stored.
-enum Epilogue : int { kEpiDot = 0, kEpiAngular = 1, kEpiEuclidean = 2 };
+// Hamming / Jaccard (u1 only) turn the AND-popcount "dot" and the two population counts into a set distance
+// (include/numkong/set/serial.h:150-168).
+enum Epilogue : int { kEpiDot = 0, kEpiAngular = 1, kEpiEuclidean = 2, kEpiHamming = 3, kEpiJaccard = 4 };
 
 constexpr uint32_t kMagicDots = 0x32424B4Eu;    // "NKB2"
 constexpr uint32_t kMagicMaxsim = 0x4D424B4Eu;  // "NKBM"
@@ -74,20 +77,28 @@ inline uint32_t norm_bytes(uint32_t dt) { return dt == kF32 ? 8 : 4; }
 inline uint32_t dot_out_bytes(uint32_t dt) { return dt == kF32 ? 8 : 4; }
 inline bool dtype_supported(uint32_t dt) {
     switch (dt) {
-    case kI8: case kU8: case kF32: case kF16: case kBF16: case kE4M3: case kE5M2: case kE2M3: case kE3M2: case kI4: case kU4: return true;
+    case kI8: case kU8: case kF32: case kF16: case kBF16: case kE4M3: case kE5M2: case kE2M3: case kE3M2: case kI4: case kU4: case kU1: return true;
     default: return false;
     }
 }
 
 inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 
-// 4-bit types: `depth` counts nibbles, a row occupies ceil(depth / 2) bytes, and - like the reference's kernels
-// (include/numkong/dot/serial.h:185-215) - BOTH nibbles of the last byte take part when depth is odd. On the device a
-// nibble row is expanded to one i8 / u8 per value, so everything after the packer and the operand staging sees i8 / u8.
-inline bool is_nibble(uint32_t dt) { return dt == kI4 || dt == kU4; }
-inline uint64_t source_row_bytes(uint32_t dt, uint64_t depth) { return is_nibble(dt) ? (depth + 1) / 2 : depth * dtype_bytes(dt); }
-inline uint32_t operand_dtype(uint32_t dt) { return dt == kI4 ? kI8 : dt == kU4 ? kU8 : dt; }
-inline uint64_t operand_depth(uint32_t dt, uint64_t depth) { return is_nibble(dt) ? (depth + 1) / 2 * 2 : depth; }
+// Sub-byte types: `depth` counts values (nibbles for i4 / u4, bits for u1), a row occupies ceil(depth / per_byte) bytes,
+// and - like the reference's kernels (include/numkong/dot/serial.h:185-215) - every value of the last byte takes part
+// even when `depth` stops inside it. On the device such a row is expanded to one i8 / u8 per value, so everything after
+// the packer and the operand staging sees i8 / u8.
+inline uint32_t values_per_byte(uint32_t dt) { return dt == kU1 ? 8u : (dt == kI4 || dt == kU4) ? 2u : 0u; }  // 0: not sub-byte
+inline bool is_subbyte(uint32_t dt) { return values_per_byte(dt) != 0; }
+inline uint64_t source_row_bytes(uint32_t dt, uint64_t depth) {
+    const uint32_t per = values_per_byte(dt);
+    return per ? (depth + per - 1) / per : depth * dtype_bytes(dt);
+}
+inline uint32_t operand_dtype(uint32_t dt) { return dt == kI4 ? kI8 : (dt == kU4 || dt == kU1) ? kU8 : dt; }
+inline uint64_t operand_depth(uint32_t dt, uint64_t depth) {
+    const uint32_t per = values_per_byte(dt);
+    return per ? (depth + per - 1) / per * per : depth;
+}
 
 #ifdef __CUDACC__
 // Order-preserving integer key of an f32 for selection: a < b  <=>  key(a) < key(b); every NaN shares the last key
@@ -125,16 +136,18 @@ cudaError_t launch_row_sumsq(uint32_t dt, const void *x, uint64_t rows, uint64_t
 
 // Rewrites applied to each 16-byte piece of an FP6 operand on its way to the tensor cores.
 enum PieceMode : int { kPieceNone = 0, kPieceE2M3ToE4M3 = 1, kPieceE3M2ToE4M3 = 2, kPieceFp6Pack = 3,
-                       kPieceI4ToI8 = 4, kPieceU4ToU8 = 5 };  // the last two read 8 source bytes per 16-byte piece
+                       kPieceI4ToI8 = 4, kPieceU4ToU8 = 5, kPieceU1ToU8 = 6 };
+// The expanding modes write a 16-byte piece from 16 >> shift source bytes (8 for nibbles, 2 for bits).
 #ifdef __CUDACC__
 __host__ __device__
 #endif
-inline bool piece_mode_expands(int mode) { return mode == kPieceI4ToI8 || mode == kPieceU4ToU8; }
+inline int piece_mode_shift(int mode) { return mode == kPieceU1ToU8 ? 3 : (mode == kPieceI4ToI8 || mode == kPieceU4ToU8) ? 1 : 0; }
 // How FP6 operands are fed to tcgen05.mma: 0 = recoded to e4m3 (exact), 1 = native 6-bit operand formats.
 int fp6_native();
 inline int piece_mode_for(uint32_t dt) {
     if (dt == kI4) return kPieceI4ToI8;
     if (dt == kU4) return kPieceU4ToU8;
+    if (dt == kU1) return kPieceU1ToU8;
     if (dt != kE2M3 && dt != kE3M2) return kPieceNone;
     if (fp6_native()) return kPieceFp6Pack;
     return dt == kE2M3 ? kPieceE2M3ToE4M3 : kPieceE3M2ToE4M3;
@@ -146,8 +159,8 @@ cudaError_t launch_pack_payload(uint32_t dt, const void *b, uint64_t rows, uint6
                                 cudaStream_t stream);
 
 // Copies a strided matrix into a 16-byte-aligned, 16-byte-pitched scratch copy (for TMA),
-// applying `piece_mode` to every 16-byte piece. `row_bytes` counts SOURCE bytes (half the written bytes for the
-// nibble-expanding modes).
+// applying `piece_mode` to every 16-byte piece. `row_bytes` counts SOURCE bytes (a half / an eighth of the written bytes for
+// the expanding modes).
 cudaError_t launch_restride(const void *src, uint64_t rows, uint64_t row_bytes, uint64_t src_stride,
                             void *dst, uint64_t dst_stride, int piece_mode, cudaStream_t stream);
 

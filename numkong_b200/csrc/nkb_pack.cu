@@ -68,9 +68,22 @@ __device__ __forceinline__ uint4 expand_nibbles(uint4 v, bool is_signed) {
     return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
+// One-bit operands: the low 2 bytes of `v` hold 16 bits, least significant first; each becomes a byte 0 / 1. (Any fixed
+// bit order gives the same AND-popcount as long as both operands use it.)
+__device__ __forceinline__ uint4 expand_bits(uint4 v) {
+    uint32_t out[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const uint32_t four = (v.x >> (4 * w)) & 0xfu;
+        out[w] = (four & 1u) | ((four & 2u) << 7) | ((four & 4u) << 14) | ((four & 8u) << 21);
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
 __device__ __forceinline__ uint4 transform_piece(uint4 v, int mode) {
     if (mode == kPieceNone) return v;
     if (mode == kPieceI4ToI8 || mode == kPieceU4ToU8) return expand_nibbles(v, mode == kPieceI4ToI8);
+    if (mode == kPieceU1ToU8) return expand_bits(v);
     uint32_t w[4] = {v.x, v.y, v.z, v.w};
     if (mode == kPieceE2M3ToE4M3 || mode == kPieceE3M2ToE4M3) {
 #pragma unroll
@@ -120,13 +133,13 @@ __global__ void pack_payload_kernel(const uint8_t *__restrict__ b, uint64_t rows
             row = o / pieces_per_row;
             byte_off = (o % pieces_per_row) * 16u;
         }
-        // Nibble-expanding modes produce a 16-byte piece from 8 source bytes.
-        const bool expands = piece_mode_expands(piece_mode);
-        const uint64_t src_off = expands ? byte_off >> 1 : byte_off;
+        // Expanding modes produce a 16-byte piece from 8 (nibbles) or 2 (bits) source bytes.
+        const int shift = piece_mode_shift(piece_mode);
+        const uint64_t src_off = byte_off >> shift;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < rows && src_off < row_bytes) {
             int64_t valid = (int64_t)(row_bytes - src_off);
-            if (expands && valid > 8) valid = 8;
+            if (valid > (16 >> shift)) valid = 16 >> shift;
             v = load16_guarded(b + row * stride + src_off, valid);
         }
         payload[o] = transform_piece(v, piece_mode);
@@ -140,12 +153,12 @@ __global__ void restride_kernel(const uint8_t *src, uint64_t rows, uint64_t row_
     for (uint64_t o = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; o < total; o += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t row = o / dst_pieces_per_row;
         uint64_t byte_off = (o % dst_pieces_per_row) * 16u;
-        const bool expands = piece_mode_expands(piece_mode);
-        const uint64_t src_off = expands ? byte_off >> 1 : byte_off;
+        const int shift = piece_mode_shift(piece_mode);
+        const uint64_t src_off = byte_off >> shift;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (src_off < row_bytes) {
             int64_t valid = (int64_t)(row_bytes - src_off);
-            if (expands && valid > 8) valid = 8;
+            if (valid > (16 >> shift)) valid = 16 >> shift;
             v = load16_guarded(src + row * src_stride + src_off, valid);
         }
         dst[o] = transform_piece(v, piece_mode);
@@ -195,6 +208,12 @@ struct SumSq<kU4> {
     }
 };
 
+template <>
+struct SumSq<kU1> {  // a bit squared is the bit: the "norm" of a bit row is its population count
+    using Acc = unsigned long long;
+    static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) { acc += (unsigned long long)__popc((unsigned)*p); }
+};
+
 // One warp per row; 16-byte vector loads when the row start allows it.
 template <uint32_t kDtype>
 __global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, uint64_t depth, uint64_t stride,
@@ -226,7 +245,7 @@ __global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, u
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
         if (lane == 0) {
-            if constexpr (kDtype == kI8 || kDtype == kU8 || kDtype == kI4 || kDtype == kU4) {
+            if constexpr (kDtype == kI8 || kDtype == kU8 || kDtype == kI4 || kDtype == kU4 || kDtype == kU1) {
                 if (inverse) {
                     float s = (float)acc;
                     static_cast<float *>(out)[row] = s > 0.0f ? (float)(1.0 / sqrt((double)s)) : 0.0f;
@@ -260,11 +279,11 @@ cudaError_t launch_row_sumsq(uint32_t dt, const void *x, uint64_t rows, uint64_t
     const int grid = grid_for(rows * 32, block);
     const uint8_t *p = static_cast<const uint8_t *>(x);
     const int mode = as_f32 ? 1 : 0, inv = inverse ? 1 : 0;
-    if (is_nibble(dt)) depth = source_row_bytes(dt, depth);  // the kernel walks bytes, two values each
+    if (is_subbyte(dt)) depth = source_row_bytes(dt, depth);  // the kernel walks bytes, several values each
 #define NKB_CASE(DT) case DT: row_sumsq_kernel<DT><<<grid, block, 0, stream>>>(p, rows, depth, stride_bytes, out, mode, inv); break
     switch (dt) {
         NKB_CASE(kI8); NKB_CASE(kU8); NKB_CASE(kF32); NKB_CASE(kF16); NKB_CASE(kBF16);
-        NKB_CASE(kE4M3); NKB_CASE(kE5M2); NKB_CASE(kE2M3); NKB_CASE(kE3M2); NKB_CASE(kI4); NKB_CASE(kU4);
+        NKB_CASE(kE4M3); NKB_CASE(kE5M2); NKB_CASE(kE2M3); NKB_CASE(kE3M2); NKB_CASE(kI4); NKB_CASE(kU4); NKB_CASE(kU1);
     default: return cudaErrorInvalidValue;
     }
 #undef NKB_CASE

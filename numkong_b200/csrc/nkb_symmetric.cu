@@ -79,7 +79,7 @@ void symmetric_impl(uint32_t dt, int epilogue, const void *vectors, uint64_t cou
     // ---- row operand: rows [row_start, row_end). They already sit in the staged / caller's device copy.
     const uint8_t *a_src = col_src + (row_start - col0) * col_pitch;
     uint64_t a_pitch = 0;
-    const void *a_raw = ok ? resident_matrix(a_src, kMemDevice, m, row_bytes, col_pitch, kSlotA, is_nibble(dt) ? piece_mode : kPieceNone, &a_pitch) : nullptr;
+    const void *a_raw = ok ? resident_matrix(a_src, kMemDevice, m, row_bytes, col_pitch, kSlotA, is_subbyte(dt) ? piece_mode : kPieceNone, &a_pitch) : nullptr;
     if (!a_raw) { fail(); return; }
     void *a_norms = nullptr;
     if (epilogue != kEpiDot) {
@@ -88,7 +88,7 @@ void symmetric_impl(uint32_t dt, int epilogue, const void *vectors, uint64_t cou
         g_launches++;
     }
     const void *a_dev = a_raw;
-    if (ok && piece_mode != kPieceNone && !is_nibble(dt)) {
+    if (ok && piece_mode != kPieceNone && !is_subbyte(dt)) {
         // FP6 rows are rewritten for the tensor cores: in place when they already live in this thread's staging buffer.
         void *dst = const_cast<void *>(a_raw);
         uint64_t dst_pitch = a_pitch;
@@ -178,5 +178,19 @@ NKB_DEFINE_SYMMETRIC(e2m3, kE2M3)
 NKB_DEFINE_SYMMETRIC(e3m2, kE3M2)
 NKB_DEFINE_SYMMETRIC(i4, kI4)
 NKB_DEFINE_SYMMETRIC(u4, kU4)
+
+// One-bit vectors (include/numkong/dots.h:357, include/numkong/sets.h:84-117).
+NKB_API void nk_dots_symmetric_u1(void const *vectors, nk_size_t count, nk_size_t depth, nk_size_t stride, void *result,
+                                  nk_size_t result_stride, nk_size_t row_start, nk_size_t row_count) {
+    symmetric_impl(kU1, kEpiDot, vectors, count, depth, stride, result, result_stride, row_start, row_count);
+}
+NKB_API void nk_hammings_symmetric_u1(void const *vectors, nk_size_t count, nk_size_t depth, nk_size_t stride, void *result,
+                                      nk_size_t result_stride, nk_size_t row_start, nk_size_t row_count) {
+    symmetric_impl(kU1, kEpiHamming, vectors, count, depth, stride, result, result_stride, row_start, row_count);
+}
+NKB_API void nk_jaccards_symmetric_u1(void const *vectors, nk_size_t count, nk_size_t depth, nk_size_t stride, void *result,
+                                      nk_size_t result_stride, nk_size_t row_start, nk_size_t row_count) {
+    symmetric_impl(kU1, kEpiJaccard, vectors, count, depth, stride, result, result_stride, row_start, row_count);
+}
 
 } // extern "C"

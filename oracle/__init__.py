@@ -20,15 +20,15 @@ REF_SO = _HERE / "_ref" / "libnumkong.so"
 REF_SERIAL_SO = _HERE / "_ref" / "libnkref_serial.so"
 
 CODES = {"i8": 1 << 2, "u8": 1 << 6, "f32": 1 << 11, "f16": 1 << 12, "bf16": 1 << 13,
-         "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17}
-BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i4": 1, "u4": 1}
+         "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17, "u1": 1 << 1}
+BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i4": 1, "u4": 1, "u1": 1}
 STORAGE = {"i8": np.int8, "u8": np.uint8, "f32": np.float32, "f16": np.uint16, "bf16": np.uint16,
-           "e4m3": np.uint8, "e5m2": np.uint8, "e2m3": np.uint8, "e3m2": np.uint8, "i4": np.uint8, "u4": np.uint8}
+           "e4m3": np.uint8, "e5m2": np.uint8, "e2m3": np.uint8, "e3m2": np.uint8, "i4": np.uint8, "u4": np.uint8, "u1": np.uint8}
 
 
 def _depth(x: np.ndarray, dtype: str, depth: Optional[int]) -> int:
     """Logical dimensions of a row: 4-bit types hold two per byte (an explicit `depth` may be odd)."""
-    return int(depth) if depth is not None else x.shape[1] * (2 if dtype in ("i4", "u4") else 1)
+    return int(depth) if depth is not None else x.shape[1] * {"i4": 2, "u4": 2, "u1": 8}.get(dtype, 1)
 
 
 def build(force: bool = False) -> Path:
@@ -54,6 +54,7 @@ def _load() -> ctypes.CDLL:
     lib.orc_dots.restype, lib.orc_dots.argtypes = None, [i32, vp, u64, vp, u64, vp, u64, u64, u64, u64]
     lib.orc_spatials.restype, lib.orc_spatials.argtypes = None, [i32, i32, vp, u64, vp, u64, vp, u64, u64, u64, u64]
     lib.orc_sumsq.restype, lib.orc_sumsq.argtypes = ctypes.c_double, [i32, vp, u64]
+    lib.orc_sets.restype, lib.orc_sets.argtypes = None, [i32, vp, u64, vp, u64, vp, u64, u64, u64, u64]
     lib.orc_rsqrt_f32.restype, lib.orc_rsqrt_f32.argtypes = ctypes.c_float, [ctypes.c_float]
     for name in ("orc_maxsim_argmax_dot", "orc_maxsim_coarse_i8"):
         f = getattr(lib, name)
@@ -94,7 +95,7 @@ def out_dtype(dtype: str, op: str = "dots"):
         return np.float64
     if op == "dots" and dtype in ("i8", "i4"):
         return np.int32
-    if op == "dots" and dtype in ("u8", "u4"):
+    if (op == "dots" and dtype in ("u8", "u4", "u1")) or op == "hammings":
         return np.uint32
     return np.float32
 
@@ -121,6 +122,24 @@ def angulars(a, b, dtype, depth: Optional[int] = None):
 
 def euclideans(a, b, dtype, depth: Optional[int] = None):
     return _spatials(1, a, b, dtype, depth)
+
+
+def _sets(kind: int, a, b, depth=None):
+    a, b = _as_storage(a, "u1"), _as_storage(b, "u1")
+    c = np.empty((a.shape[0], b.shape[0]), dtype=np.uint32 if kind == 0 else np.float32)
+    _lib.orc_sets(kind, a.ctypes.data, _stride(a), b.ctypes.data, _stride(b), c.ctypes.data, c.shape[1] * c.itemsize,
+                  a.shape[0], b.shape[0], _depth(a, "u1", depth))
+    return c
+
+
+def hammings(a, b, dtype: str = "u1", depth: Optional[int] = None):
+    """Hamming distances between bit vectors (u32)."""
+    return _sets(0, a, b, depth)
+
+
+def jaccards(a, b, dtype: str = "u1", depth: Optional[int] = None):
+    """Jaccard distances between bit vectors (f32)."""
+    return _sets(1, a, b, depth)
 
 
 def sumsq(x: np.ndarray, dtype: str, depth: Optional[int] = None) -> np.ndarray:
@@ -206,6 +225,12 @@ class _Ref:
 
     def euclideans(self, a, b, dtype, depth=None):
         return self.packed("euclideans", a, self.pack(b, dtype, depth=depth), np.asarray(b).shape[0], dtype, depth=depth)
+
+    def hammings(self, a, b, dtype="u1", depth=None):
+        return self.packed("hammings", a, self.pack(b, "u1", depth=depth), np.asarray(b).shape[0], "u1", depth=depth)
+
+    def jaccards(self, a, b, dtype="u1", depth=None):
+        return self.packed("jaccards", a, self.pack(b, "u1", depth=depth), np.asarray(b).shape[0], "u1", depth=depth)
 
     def maxsim(self, q, d, dtype) -> float:
         q, d = _as_storage(q, dtype), _as_storage(d, dtype)

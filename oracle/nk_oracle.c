@@ -25,8 +25,9 @@ enum {
     ORC_I8 = 1 << 2, ORC_U8 = 1 << 6, ORC_F32 = 1 << 11, ORC_F16 = 1 << 12, ORC_BF16 = 1 << 13,
     ORC_E4M3 = 1 << 14, ORC_E5M2 = 1 << 15, ORC_E2M3 = 1 << 18, ORC_E3M2 = 1 << 19,
     ORC_I4 = 1 << 16, ORC_U4 = 1 << 17, /* two values per byte, low nibble first; depth counts values */
+    ORC_U1 = 1 << 1,                    /* eight values per byte; depth counts bits */
 };
-#define ORC_IS_INT(dt) ((dt) == ORC_I8 || (dt) == ORC_U8 || (dt) == ORC_I4 || (dt) == ORC_U4)
+#define ORC_IS_INT(dt) ((dt) == ORC_I8 || (dt) == ORC_U8 || (dt) == ORC_I4 || (dt) == ORC_U4 || (dt) == ORC_U1)
 #define ORC_IS_SIGNED_INT(dt) ((dt) == ORC_I8 || (dt) == ORC_I4)
 
 static float bits_to_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
@@ -154,6 +155,10 @@ static int nibble(int dt, uint8_t byte, int high) {
 }
 static int64_t dot_int(int dt, const uint8_t *a, const uint8_t *b, uint64_t k) {
     int64_t s = 0;
+    if (dt == ORC_U1) { /* AND-popcount over whole bytes (include/numkong/dots/serial.h u1 instantiation, set/serial.h) */
+        for (uint64_t l = 0; l < (k + 7) / 8; ++l) s += __builtin_popcount((unsigned)(a[l] & b[l]));
+        return s;
+    }
     if (dt == ORC_I4 || dt == ORC_U4) {
         for (uint64_t l = 0; l < (k + 1) / 2; ++l)
             s += (int64_t)nibble(dt, a[l], 0) * nibble(dt, b[l], 0) + (int64_t)nibble(dt, a[l], 1) * nibble(dt, b[l], 1);
@@ -260,6 +265,29 @@ ORC_API void orc_spatials(int kind, int dt, const void *a, uint64_t a_stride, co
         }
     }
     free(bn);
+}
+
+/* ---- set distances of one-bit vectors --------------------------------------------------------------
+ * include/numkong/sets/serial.h:19-39 drives (AND-popcount product, population counts as norms); formulas
+ * include/numkong/set/serial.h:150-168. kind 0 = Hamming (u32 cells), 1 = Jaccard (f32 cells).
+ */
+ORC_API void orc_sets(int kind, const void *a, uint64_t a_stride, const void *b, uint64_t b_stride, void *c, uint64_t c_stride,
+                      uint64_t m, uint64_t n, uint64_t k) {
+    const uint8_t *ap = (const uint8_t *)a, *bp = (const uint8_t *)b;
+    for (uint64_t i = 0; i < m; ++i) {
+        const uint8_t *x = ap + i * a_stride;
+        uint32_t pa = (uint32_t)dot_int(ORC_U1, x, x, k);
+        uint8_t *row = (uint8_t *)c + i * c_stride;
+        for (uint64_t j = 0; j < n; ++j) {
+            const uint8_t *y = bp + j * b_stride;
+            uint32_t pb = (uint32_t)dot_int(ORC_U1, y, y, k), dot = (uint32_t)dot_int(ORC_U1, x, y, k);
+            if (kind == 0) ((uint32_t *)row)[j] = pa + pb - 2 * dot;
+            else {
+                float fdot = (float)dot, union_size = (float)pa + (float)pb - fdot;
+                ((float *)row)[j] = union_size != 0 ? 1.0f - fdot / union_size : 0.0f;
+            }
+        }
+    }
 }
 
 /* ---- MaxSim ------------------------------------------------------------------------------------

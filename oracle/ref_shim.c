@@ -38,6 +38,19 @@ REF_PACKED_FAMILY(f32, nk_f32_t, nk_f64_t, nk_f64_t)
 REF_PACKED_FAMILY(i4, nk_i4x2_t, nk_i32_t, nk_f32_t)
 REF_PACKED_FAMILY(u4, nk_u4x2_t, nk_u32_t, nk_f32_t)
 
+/* one-bit vectors: AND-popcount product and the two set distances */
+REF_API nk_size_t ref_dots_packed_size_u1(nk_size_t n, nk_size_t k) { return nk_dots_packed_size_u1_serial(n, k); }
+REF_API void ref_dots_pack_u1(nk_u1x8_t const *b, nk_size_t n, nk_size_t k, nk_size_t s, void *p) { nk_dots_pack_u1_serial(b, n, k, s, p); }
+REF_API void ref_dots_packed_u1(nk_u1x8_t const *a, void const *p, nk_u32_t *c, nk_size_t m, nk_size_t n, nk_size_t k, nk_size_t as, nk_size_t cs) {
+    nk_dots_packed_u1_serial(a, p, c, m, n, k, as, cs);
+}
+REF_API void ref_hammings_packed_u1(nk_u1x8_t const *a, void const *p, nk_u32_t *c, nk_size_t m, nk_size_t n, nk_size_t k, nk_size_t as, nk_size_t cs) {
+    nk_hammings_packed_u1_serial(a, p, c, m, n, k, as, cs);
+}
+REF_API void ref_jaccards_packed_u1(nk_u1x8_t const *a, void const *p, nk_f32_t *c, nk_size_t m, nk_size_t n, nk_size_t k, nk_size_t as, nk_size_t cs) {
+    nk_jaccards_packed_u1_serial(a, p, c, m, n, k, as, cs);
+}
+
 #define REF_MAXSIM_FAMILY(T, IN, OUT)                                                                                \
     REF_API nk_size_t ref_maxsim_packed_size_##T(nk_size_t n, nk_size_t k) { return nk_maxsim_packed_size_##T##_serial(n, k); } \
     REF_API void ref_maxsim_pack_##T(IN const *v, nk_size_t n, nk_size_t k, nk_size_t s, void *p) {                   \

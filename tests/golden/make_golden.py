@@ -51,7 +51,7 @@ def main():
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "packed_path.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
-    # 4-bit types: uniformly random bytes (every nibble value), depths counted in values - odd ones included, where the
+    # Sub-byte types (file nibble_path.npz). 4-bit types: uniformly random bytes (every nibble value), depths counted in values - odd ones included, where the
     # reference lets the second nibble of the last byte take part.
     out = {}
     for dt in ("i4", "u4"):
@@ -64,6 +64,16 @@ def main():
             for op in ("dots", "angulars", "euclideans"):
                 out[f"{key}_{op}_serial"] = getattr(serial, op)(a, b, dt, depth=k)
                 out[f"{key}_{op}_dispatch"] = getattr(dispatch, op)(a, b, dt, depth=k)
+    # One-bit vectors: depth counted in bits (every bit of the last byte takes part), AND-popcount dots and set distances.
+    for si, (m, n, k) in enumerate(SHAPES):
+        rng = np.random.default_rng(3000 + si)
+        a = rng.integers(0, 256, (m, (k + 7) // 8), dtype=np.uint8)
+        b = rng.integers(0, 256, (n, (k + 7) // 8), dtype=np.uint8)
+        key = f"u1_{m}x{n}x{k}"
+        out[key + "_a"], out[key + "_b"] = a, b
+        for op in ("dots", "hammings", "jaccards"):
+            out[f"{key}_{op}_serial"] = getattr(serial, op)(a, b, "u1", depth=k)
+            out[f"{key}_{op}_dispatch"] = getattr(dispatch, op)(a, b, "u1", depth=k)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "nibble_path.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")

@@ -20,6 +20,7 @@ def declared_symbols():
     names = set(re.findall(r"NKB_API[^;(]*?\b(nkb?_[a-z0-9_]+)\s*\(", text))
     for macro, pattern in (("NKB_DECLARE_PACKED_FAMILY", ["nk_dots_packed_size_{}", "nk_dots_pack_{}", "nk_dots_packed_{}",
                                                           "nk_angulars_packed_{}", "nk_euclideans_packed_{}"]),
+                           ("NKB_DECLARE_SYMMETRIC_FAMILY", ["nk_dots_symmetric_{}", "nk_angulars_symmetric_{}", "nk_euclideans_symmetric_{}"]),
                            ("NKB_DECLARE_MAXSIM_FAMILY", ["nk_maxsim_packed_size_{}", "nk_maxsim_pack_{}", "nk_maxsim_packed_{}"]),
                            ("NKB_DECLARE_TOPK_FAMILY", ["nkb_angulars_packed_topk_{}", "nkb_euclideans_packed_topk_{}"]),
                            ("NKB_DECLARE_MAXSIMS_FAMILY", ["nkb_maxsims_packed_{}"])):
@@ -32,7 +33,7 @@ def declared_symbols():
 def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(str(_lib.LIB_PATH))
     names = declared_symbols()
-    assert len(names) >= 9 * 5 + 3 * 3 + 8
+    assert len(names) >= 11 * 8 + 8 + 3 * 3 + 8
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
 
@@ -56,10 +57,13 @@ def test_find_kernel_punned_contract():
     """c/numkong.c:848-913: known (kind, dtype) -> entry point + non-zero capability; unknown -> NULL + 0."""
     fn, cap = ctypes.c_void_p(), ctypes.c_uint64()
     lib = _lib.lib
-    for kind in "PQGNE":
-        for dt in nk.PACKED_DTYPES:
+    for dt in nk.PACKED_DTYPES:
+        # bit vectors have set distances (Hamming 'M'/'Y', Jaccard 'p'/'Z') where the others have angular / Euclidean
+        for kind in ("PQGyMYpZ" if dt == "u1" else "PQGNEynD"):
             lib.nk_find_kernel_punned(ord(kind), nk.DTYPE_CODES[dt], (1 << 64) - 1, ctypes.byref(fn), ctypes.byref(cap))
-            assert fn.value and cap.value == 1 << 40
+            assert fn.value and cap.value == 1 << 40, (kind, dt)
+    lib.nk_find_kernel_punned(ord("N"), nk.DTYPE_CODES["u1"], (1 << 64) - 1, ctypes.byref(fn), ctypes.byref(cap))
+    assert not fn.value and cap.value == 0  # no angular distance between bit vectors
     lib.nk_find_kernel_punned(ord("G"), nk.DTYPE_CODES["i8"], (1 << 64) - 1, ctypes.byref(fn), ctypes.byref(cap))
     direct = ctypes.cast(lib.nk_dots_packed_i8, ctypes.c_void_p).value
     assert fn.value == direct

@@ -182,3 +182,26 @@ def test_four_bit_oracle_against_live_reference(dtype):
     # an all-sevens row against itself: the dot is depth * 49 (both nibbles of the last byte count, so odd depths round up)
     ones = np.full((1, 4), 0x77, dtype=np.uint8)
     assert oracle.dots(ones, ones, dtype, depth=7)[0, 0] == 8 * 49
+
+
+@pytest.mark.parametrize("shape", GOLDEN_SHAPES)
+def test_one_bit_oracle_matches_reference_golden(shape):
+    """Bit vectors: AND-popcount dots, Hamming and Jaccard distances, bit for bit against the reference's scalar kernels;
+    its dispatched back end agrees exactly on the integer results and to rounding on the Jaccard division."""
+    m, n, k = shape
+    key = f"u1_{m}x{n}x{k}"
+    a, b = NIBBLE_GOLDEN[key + "_a"], NIBBLE_GOLDEN[key + "_b"]
+    for op in ("dots", "hammings", "jaccards"):
+        assert _bits_equal(getattr(oracle, op)(a, b, "u1", depth=k), NIBBLE_GOLDEN[f"{key}_{op}_serial"])
+    assert _bits_equal(oracle.dots(a, b, "u1", depth=k), NIBBLE_GOLDEN[key + "_dots_dispatch"])
+    assert _bits_equal(oracle.hammings(a, b, depth=k), NIBBLE_GOLDEN[key + "_hammings_dispatch"])
+    assert np.max(np.abs(oracle.jaccards(a, b, depth=k) - NIBBLE_GOLDEN[key + "_jaccards_dispatch"])) < 1e-6
+
+
+def test_one_bit_known_answers():
+    a = np.array([[0b10110000, 0b00000001]], dtype=np.uint8)   # 4 bits set
+    b = np.array([[0b10010000, 0b00000001], [0, 0]], dtype=np.uint8)  # 3 bits set, all shared; the empty set
+    assert oracle.dots(a, b, "u1").tolist() == [[3, 0]]
+    assert oracle.hammings(a, b).tolist() == [[1, 4]]
+    assert np.allclose(oracle.jaccards(a, b), [[1 - 3 / 4, 1.0]])
+    assert oracle.jaccards(b[1:], b[1:])[0, 0] == 0.0  # two empty sets
