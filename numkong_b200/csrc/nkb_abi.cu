@@ -470,9 +470,13 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
     if (pipelined) {
         ok = cuda_ok(cudaEventRecord(t_ctx.fork, stream), "pipeline fork");
         for (int s = 0; s < 2 && ok; ++s) ok = cuda_ok(cudaStreamWaitEvent(t_ctx.pipe[s], t_ctx.fork, 0), "pipeline fork");
+        // The first blocks are short so that the download of results (the longest leg of a host-to-host call) starts
+        // almost at once; after that, blocks of kPipeRows rows keep the copies long enough to run at full PCIe speed.
         int block = 0;
-        for (uint64_t r0 = 0; r0 < m && ok; r0 += kPipeRows, ++block) {
-            const uint64_t rows = m - r0 < kPipeRows ? m - r0 : kPipeRows;
+        uint64_t rows = 0;
+        for (uint64_t r0 = 0; r0 < m && ok; r0 += rows, ++block) {
+            const uint64_t ramp = block < 2 ? kPipeRows / 4 : block == 2 ? kPipeRows / 2 : kPipeRows;
+            rows = m - r0 < ramp ? m - r0 : ramp;
             t_ctx.slot_set = block & 1;
             t_ctx.use_override = true;
             t_ctx.override_stream = t_ctx.pipe[block & 1];
