@@ -398,7 +398,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                               (warp - 2) * 32 * (Plan::kStageCols + 4);
         uint32_t seq = 0, local_tile = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        // After a wait has given up (`ok` false) the epilogue warps stop waiting and stop touching TMEM but still walk every
+        // tile: they share a named barrier per tile, and a warp that left early would strand the others inside it.
+        for (uint32_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             uint32_t mt, nt;
             tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
             if (tile_skipped(p.tri_diag, mt * kBM, (nt + 1) * kBN)) continue;
@@ -430,7 +432,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                 tc_fence_before_sync();
                 mbar_arrive(tmem_empty_bar(buf));
             }
-            if (!ok) break;
+            if (!ok) continue;  // nothing valid to store; the next tile's barrier is still met
             store_tile<kEpi, kColsPerThread, Plan::kStageCols>(acc, p, mt * kBM + quarter * 32u, nt * kBN + half * kColsPerThread,
                                                                epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane);
             ++local_tile;
@@ -572,7 +574,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
         uint32_t *epi_stage = reinterpret_cast<uint32_t *>(smem_gen + kPairBarrierOffset + 256 + kEpiColfBytes) + (warp - 2) * kEpiStageWords;
         uint32_t seq = 0, local_tile = 0;
         bool ok = true;
-        for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs) {  // keeps walking after a failed wait, see above
             uint32_t mt, nt;
             tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
             if (tile_skipped(p.tri_diag, mt * 256u, (nt + 1) * kBN)) continue;
@@ -603,7 +605,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(tmem_empty_bar(buf), 0));
             }
-            if (!ok) break;
+            if (!ok) continue;
             store_tile<kEpi, kColsPerThread>(acc, p, mt * 256u + rank * 128u + quarter * 32u, nt * kBN + half * kColsPerThread,
                                              epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane);
             ++local_tile;

@@ -307,9 +307,11 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
         };
 
         bool ok = true;
-        for (uint32_t local = 0; local < run_tiles && ok; ++local) {
+        // After a wait has given up (`ok` false) a warp stops waiting but keeps walking tiles and documents: the four
+        // warps of a quarter meet at a named barrier per document, and one that left early would strand its partners.
+        for (uint32_t local = 0; local < run_tiles; ++local) {
             const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
-            if (!mbar_wait(tmem_full_bar(acc), acc_phase, 4, p.error_word)) { ok = false; break; }
+            if (ok && !mbar_wait(tmem_full_bar(acc), acc_phase, 4, p.error_word)) ok = false;
             tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + acc * kMsBN + sub * 64u;
 #pragma unroll
@@ -354,7 +356,7 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             }
         }
         // Normally nothing is left here: every document of the run ends inside one of its tiles.
-        if (ok && has_work) {
+        if (has_work) {
             while (cur_doc < run_docs) {
                 finish_doc();
                 ++cur_doc;
