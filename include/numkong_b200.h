@@ -48,6 +48,7 @@ typedef uint64_t nk_size_t; /* types.h:854-856 */
 #define NKB_DTYPE_U1 (1u << 1) /* eight values per byte; `depth` counts bits */
 #define NKB_DTYPE_I8 (1u << 2)
 #define NKB_DTYPE_U8 (1u << 6)
+#define NKB_DTYPE_F64 (1u << 10)
 #define NKB_DTYPE_F32 (1u << 11)
 #define NKB_DTYPE_F16 (1u << 12)
 #define NKB_DTYPE_BF16 (1u << 13)
@@ -88,6 +89,7 @@ NKB_DECLARE_PACKED_FAMILY(e3m2)
 NKB_DECLARE_PACKED_FAMILY(f32)
 NKB_DECLARE_PACKED_FAMILY(i4) /* include/numkong/dots.h:197,239,289; both nibbles of the last byte count (dot/serial.h:185-215) */
 NKB_DECLARE_PACKED_FAMILY(u4)
+NKB_DECLARE_PACKED_FAMILY(f64) /* f64 cells; dots accumulate with the reference's two-lane Dot2 (dot/serial.h:274-303): bit-identical */
 
 /* ---- symmetric products A x A^T and the distance matrices built on them ----------------------------
  * nk_dots_symmetric_<t>        replaces include/numkong/dots.h:309-359      (wrappers c/numkong.c:673-686)
@@ -117,6 +119,7 @@ NKB_DECLARE_SYMMETRIC_FAMILY(e3m2)
 NKB_DECLARE_SYMMETRIC_FAMILY(f32)
 NKB_DECLARE_SYMMETRIC_FAMILY(i4)
 NKB_DECLARE_SYMMETRIC_FAMILY(u4)
+NKB_DECLARE_SYMMETRIC_FAMILY(f64)
 
 /* ---- one-bit vectors: AND-popcount products and the set distances built on them -----------------------
  * nk_dots_packed_size_u1 / nk_dots_pack_u1 / nk_dots_packed_u1 / nk_dots_symmetric_u1 replace

@@ -33,14 +33,14 @@ __all__ = [
 ]
 
 _NUMPY_NAMES = {
-    "int8": "i8", "uint8": "u8", "float32": "f32", "float16": "f16", "bfloat16": "bf16",
+    "int8": "i8", "uint8": "u8", "float32": "f32", "float64": "f64", "float16": "f16", "bfloat16": "bf16",
     "float8_e4m3fn": "e4m3", "float8_e5m2": "e5m2", "float6_e2m3fn": "e2m3", "float6_e3m2fn": "e3m2",
 }
 _TORCH_NAMES = {
-    "torch.int8": "i8", "torch.uint8": "u8", "torch.float32": "f32", "torch.float16": "f16",
+    "torch.int8": "i8", "torch.uint8": "u8", "torch.float32": "f32", "torch.float64": "f64", "torch.float16": "f16",
     "torch.bfloat16": "bf16", "torch.float8_e4m3fn": "e4m3", "torch.float8_e5m2": "e5m2",
 }
-_OUT_NUMPY = {"i8": np.int32, "u8": np.uint32, "i4": np.int32, "u4": np.uint32, "u1": np.uint32, "f32": np.float64}
+_OUT_NUMPY = {"i8": np.int32, "u8": np.uint32, "i4": np.int32, "u4": np.uint32, "u1": np.uint32, "f32": np.float64, "f64": np.float64}
 
 
 def _integer_cells(dtype: str, op: str) -> bool:
@@ -52,7 +52,7 @@ def _is_torch(x: Any) -> bool:
     return type(x).__module__.startswith("torch")
 
 
-_CAI_TYPES = {"<f2": "f16", "<f4": "f32", "|i1": "i8", "|u1": "u8"}  # other element types need dtype=...
+_CAI_TYPES = {"<f2": "f16", "<f4": "f32", "<f8": "f64", "|i1": "i8", "|u1": "u8"}  # other element types need dtype=...
 
 
 def _adopt_device_array(x: Any) -> Any:
@@ -150,7 +150,7 @@ def _view_like(x: Any, dtype: Optional[str], packed_dtype: str) -> _View:
     uint16 / int16) stand for the 8/6-bit and 16-bit float types NumPy and torch cannot name."""
     if dtype is None:
         name = (_TORCH_NAMES.get(str(x.dtype)) if _is_torch(x) else _NUMPY_NAMES.get(np.asarray(x).dtype.name))
-        container = (name in (None, "u8") and packed_dtype not in ("i8", "u8", "f32")) or \
+        container = (name in (None, "u8") and packed_dtype not in ("i8", "u8", "f32", "f64")) or \
                     (name == "i8" and packed_dtype in ("i4", "u4")) or (name == "u8" and packed_dtype == "u1")
         dtype = packed_dtype if container else name
     v = _View(x, dtype)
@@ -225,10 +225,10 @@ def _out_matrix(v: _View, width: int, out: Any, dtype_name: str):
     """Allocates (or validates) the result matrix; returns (object, ptr, stride)."""
     if out is not None:
         if _is_torch(out):
-            if tuple(out.shape) != (v.rows, width) or out.element_size() != (8 if dtype_name == "f32" else 4):
+            if tuple(out.shape) != (v.rows, width) or out.element_size() != (8 if dtype_name in ("f32", "f64") else 4):
                 raise ValueError("out has the wrong shape or cell size")
             return out, out.data_ptr(), (int(out.stride(0)) * out.element_size() if v.rows > 1 else width * out.element_size())
-        if out.shape != (v.rows, width) or out.itemsize != (8 if dtype_name == "f32" else 4):
+        if out.shape != (v.rows, width) or out.itemsize != (8 if dtype_name in ("f32", "f64") else 4):
             raise ValueError("out has the wrong shape or cell size")
         return out, out.ctypes.data, (int(out.strides[0]) if v.rows > 1 else width * out.itemsize)
     return None, 0, 0
@@ -245,11 +245,11 @@ def _packed_call(op: str, a: Any, packed: PackedMatrix, out: Any, dtype: Optiona
     if obj is None:
         if v.is_cuda:
             import torch
-            tdt = torch.float64 if t == "f32" else (torch.int32 if _integer_cells(t, op) else torch.float32)
+            tdt = torch.float64 if t in ("f32", "f64") else (torch.int32 if _integer_cells(t, op) else torch.float32)
             obj = torch.empty((v.rows, packed.width), dtype=tdt, device=v.obj.device)
             ptr, stride = obj.data_ptr(), packed.width * obj.element_size()
         else:
-            ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if _integer_cells(t, op) else np.float32)
+            ndt = np.float64 if t in ("f32", "f64") else (_OUT_NUMPY.get(t, np.float32) if _integer_cells(t, op) else np.float32)
             obj = np.empty((v.rows, packed.width), dtype=ndt)
             ptr, stride = obj.ctypes.data, packed.width * obj.itemsize
     getattr(lib, f"nk_{op}_packed_{t}")(v.ptr, _ptr(packed.buffer), ptr, v.rows, packed.width, v.depth, v.stride, stride)
@@ -278,15 +278,15 @@ def _symmetric_call(op: str, vectors: Any, out: Any, dtype: Optional[str], start
     if t not in PACKED_DTYPES:
         raise LookupError(f"no symmetric kernels for dtype {t!r}")
     n = v.rows
-    cell = 8 if t == "f32" else 4
+    cell = 8 if t in ("f32", "f64") else 4
     if out is None:
         # Cells below the diagonal are not written by the call; a fresh result starts as zeros (as the reference's does).
         if v.is_cuda:
             import torch
-            tdt = torch.float64 if t == "f32" else (torch.int32 if _integer_cells(t, op) else torch.float32)
+            tdt = torch.float64 if t in ("f32", "f64") else (torch.int32 if _integer_cells(t, op) else torch.float32)
             out = torch.zeros((n, n), dtype=tdt, device=v.obj.device)
         else:
-            ndt = np.float64 if t == "f32" else (_OUT_NUMPY.get(t, np.float32) if _integer_cells(t, op) else np.float32)
+            ndt = np.float64 if t in ("f32", "f64") else (_OUT_NUMPY.get(t, np.float32) if _integer_cells(t, op) else np.float32)
             out = np.zeros((n, n), dtype=ndt)
     if _is_torch(out):
         if tuple(out.shape) != (n, n) or out.element_size() != cell:

@@ -14,9 +14,9 @@ LIB_PATH = _HERE / "libnumkong_b200.so"
 # name -> numerically nk_dtype_t (include/numkong/types.h:923-953 of the reference)
 DTYPE_CODES = {
     "i8": 1 << 2, "u8": 1 << 6, "f32": 1 << 11, "f16": 1 << 12, "bf16": 1 << 13,
-    "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17, "u1": 1 << 1,
+    "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17, "u1": 1 << 1, "f64": 1 << 10,
 }
-DTYPE_BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i4": 1, "u4": 1, "u1": 1}
+DTYPE_BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i4": 1, "u4": 1, "u1": 1, "f64": 8}
 # Logical dimensions per storage element: 4-bit types hold two values per byte and `depth` counts values, as in the
 # reference's binding (python/matrix.c:400-401 multiplies the byte width by nk_dimensions_per_value).
 DIMENSIONS_PER_VALUE = {"i4": 2, "u4": 2, "u1": 8}

@@ -361,11 +361,12 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
     bool ok = true;
     if (k == 0) {
         ok = cuda_ok(cudaMemset2DAsync(c_dev, c_pitch, 0, c_row_bytes, m, stream), "clear result");
-    } else if (dt == kF32) {
+    } else if (is_cuda_core_dtype(dt)) {
+        const uint32_t eb = dtype_bytes(dt);
         const void *a_dev = a;
         uint64_t a_pitch = a_stride;
-        if (a_kind == kMemHost || (reinterpret_cast<uintptr_t>(a) & 3u) || (a_stride & 3u)) {
-            a_dev = resident_matrix(a, a_kind, m, k * 4, a_stride, kSlotA, kPieceNone, &a_pitch);
+        if (a_kind == kMemHost || (reinterpret_cast<uintptr_t>(a) & (eb - 1)) || (a_stride & (eb - 1))) {
+            a_dev = resident_matrix(a, a_kind, m, k * eb, a_stride, kSlotA, kPieceNone, &a_pitch);
             if (!a_dev) return false;
         }
         double *a_norms = nullptr;
@@ -374,11 +375,17 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
             ok = a_norms && cuda_ok(launch_row_sumsq(dt, a_dev, m, k, a_pitch, a_norms, false, false, stream), "row norm kernel");
             g_launches++;
         }
-        if (ok) {
+        if (ok && dt == kF32) {
             ok = cuda_ok(launch_gemm_f32(epilogue, static_cast<const float *>(a_dev), a_pitch,
                                          reinterpret_cast<const float *>(blob + h.payload_offset), h.depth_padded_bytes,
                                          reinterpret_cast<const double *>(blob + h.norms_offset), a_norms,
                                          reinterpret_cast<double *>(c_dev), c_pitch, m, n, k, stream), "f32 GEMM kernel");
+            g_launches++;
+        } else if (ok) {
+            ok = cuda_ok(launch_gemm_f64(epilogue, static_cast<const double *>(a_dev), a_pitch,
+                                         reinterpret_cast<const double *>(blob + h.payload_offset), h.depth_padded_bytes,
+                                         reinterpret_cast<const double *>(blob + h.norms_offset), a_norms,
+                                         reinterpret_cast<double *>(c_dev), c_pitch, m, n, k, stream), "f64 GEMM kernel");
             g_launches++;
         }
     } else {
@@ -546,6 +553,7 @@ NKB_DEFINE_PACKED_FAMILY(e3m2, kE3M2)
 NKB_DEFINE_PACKED_FAMILY(f32, kF32)
 NKB_DEFINE_PACKED_FAMILY(i4, kI4)
 NKB_DEFINE_PACKED_FAMILY(u4, kU4)
+NKB_DEFINE_PACKED_FAMILY(f64, kF64)
 
 // One-bit vectors: the "dot" is the AND-popcount, the packed norms are population counts, and the two set distances are
 // epilogues of the same product (include/numkong/sets.h:69-117, generators include/numkong/sets/serial.h:19-39).

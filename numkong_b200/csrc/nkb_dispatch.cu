@@ -27,7 +27,7 @@ const Entry kTable[] = {
     NKB_PACKED_ENTRIES(e4m3, NKB_DTYPE_E4M3), NKB_PACKED_ENTRIES(e5m2, NKB_DTYPE_E5M2),
     NKB_PACKED_ENTRIES(e2m3, NKB_DTYPE_E2M3), NKB_PACKED_ENTRIES(e3m2, NKB_DTYPE_E3M2),
     NKB_PACKED_ENTRIES(f32, NKB_DTYPE_F32),   NKB_PACKED_ENTRIES(i4, NKB_DTYPE_I4),
-    NKB_PACKED_ENTRIES(u4, NKB_DTYPE_U4),
+    NKB_PACKED_ENTRIES(u4, NKB_DTYPE_U4),     NKB_PACKED_ENTRIES(f64, NKB_DTYPE_F64),
     {'P', NKB_DTYPE_U1, (void *)&nk_dots_packed_size_u1}, {'Q', NKB_DTYPE_U1, (void *)&nk_dots_pack_u1},
     {'G', NKB_DTYPE_U1, (void *)&nk_dots_packed_u1}, {'y', NKB_DTYPE_U1, (void *)&nk_dots_symmetric_u1},
     {'M', NKB_DTYPE_U1, (void *)&nk_hammings_packed_u1}, {'Y', NKB_DTYPE_U1, (void *)&nk_hammings_symmetric_u1},

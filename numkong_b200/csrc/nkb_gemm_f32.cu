@@ -1,7 +1,15 @@
-// f32 x f32 -> f64 packed GEMM on CUDA cores: inputs stay f32 in memory, every product and
-// the whole accumulation run in f64, the result is stored as f64. This is NumKong's contract for
-// nk_dots_packed_f32 (f64 lane sums, include/numkong/dot/serial.h:305-335; f64 output,
+// f32 x f32 -> f64 and f64 x f64 -> f64 packed GEMMs on CUDA cores.
+//
+// f32: inputs stay f32 in memory, every product and the whole accumulation run in f64, the result is stored as f64.
+// This is NumKong's contract for nk_dots_packed_f32 (f64 lane sums, include/numkong/dot/serial.h:305-335; f64 output,
 // include/numkong/dots.h:276-277), which no tensor-core kind can meet, so it uses DFMA.
+//
+// f64: NumKong accumulates with Dot2 (error-free product through FMA, error-free sum through TwoSum, errors gathered
+// in a compensation term; include/numkong/scalar/serial.h:128-136) in two lanes - even and odd depth indices
+// (include/numkong/dot/serial.h:274-303) - and folds the lanes with include/numkong/reduce/serial.h:33-48. The kernel
+// below performs exactly those IEEE operations in exactly that order (explicit round-to-nearest intrinsics keep the
+// compiler from contracting or re-associating them), so its dots equal the reference's scalar kernel bit for bit.
+//
 // The angular / euclidean epilogues follow include/numkong/spatial/serial.h:281-302 in f64.
 #include "nkb_internal.h"
 
@@ -10,57 +18,96 @@ namespace nkb {
 namespace {
 
 constexpr int kTile = 64;   // output tile edge
-constexpr int kDepth = 16;  // depth slice per shared-memory stage
+constexpr int kDepth = 16;  // depth slice per shared-memory stage (even, so lane parity = parity inside the slice)
 
-template <int kEpi>
+// Accumulator of one output cell.
+template <typename In>
+struct Cell;
+template <>
+struct Cell<float> {  // one f64 running sum (the reference's four f32 lanes summed in f64 differ only in rounding order)
+    double sum = 0.0;
+    __device__ __forceinline__ void add(double a, double b, int) { sum = fma(a, b, sum); }
+    __device__ __forceinline__ double total() const { return sum; }
+};
+template <>
+struct Cell<double> {  // two Dot2 lanes
+    double sums[2] = {0.0, 0.0}, compensations[2] = {0.0, 0.0};
+    __device__ __forceinline__ void add(double a, double b, int lane) {
+        const double product = __dmul_rn(a, b);
+        const double product_error = __fma_rn(a, b, -product);
+        const double running_sum = __dadd_rn(sums[lane], product);
+        const double recovered_addend = __dsub_rn(running_sum, sums[lane]);
+        const double sum_error = __dadd_rn(__dsub_rn(sums[lane], __dsub_rn(running_sum, recovered_addend)),
+                                           __dsub_rn(product, recovered_addend));
+        sums[lane] = running_sum;
+        compensations[lane] = __dadd_rn(compensations[lane], __dadd_rn(sum_error, product_error));
+    }
+    __device__ __forceinline__ double total() const {
+        double running_sum = 0.0, accumulated_error = 0.0;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const double values[2] = {sums[i], compensations[i]};
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+                const double tentative_sum = __dadd_rn(running_sum, values[part]);
+                const double virtual_addend = __dsub_rn(tentative_sum, running_sum);
+                accumulated_error = __dadd_rn(accumulated_error,
+                                              __dadd_rn(__dsub_rn(running_sum, __dsub_rn(tentative_sum, virtual_addend)),
+                                                        __dsub_rn(values[part], virtual_addend)));
+                running_sum = tentative_sum;
+            }
+        }
+        return __dadd_rn(running_sum, accumulated_error);
+    }
+};
+
+template <int kEpi, typename In>
 __global__ void __launch_bounds__(256)
-gemm_f32_kernel(const uint8_t *__restrict__ a, uint64_t a_stride, const float *__restrict__ b, uint64_t b_stride_elems,
-                const double *__restrict__ b_norms, const double *__restrict__ a_norms, uint8_t *__restrict__ c,
-                uint64_t c_stride, uint32_t m, uint32_t n, uint32_t k, int32_t tri_diag) {
+gemm_fp64_kernel(const uint8_t *__restrict__ a, uint64_t a_stride, const In *__restrict__ b, uint64_t b_stride_elems,
+                 const double *__restrict__ b_norms, const double *__restrict__ a_norms, uint8_t *__restrict__ c,
+                 uint64_t c_stride, uint32_t m, uint32_t n, uint32_t k, int32_t tri_diag) {
+    constexpr int kRows = sizeof(In) == 8 ? 2 : 4;  // output rows per thread: the Dot2 cells are four doubles each
+    constexpr int kTileRows = 16 * kRows;
     // Triangular mode (A x A^T): only cells with column >= row + tri_diag are wanted; blocks wholly below that line leave.
-    if (tri_diag >= 0 && (blockIdx.x + 1) * kTile <= blockIdx.y * kTile + (uint32_t)tri_diag) return;
-    __shared__ float a_s[kDepth][kTile + 1];
-    __shared__ float b_s[kDepth][kTile + 1];
-    const uint32_t m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, 4 x 4 outputs each
-    double acc[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
+    if (tri_diag >= 0 && (blockIdx.x + 1) * kTile <= blockIdx.y * kTileRows + (uint32_t)tri_diag) return;
+    __shared__ In a_s[kDepth][kTileRows + 1];
+    __shared__ In b_s[kDepth][kTile + 1];
+    const uint32_t m0 = blockIdx.y * kTileRows, n0 = blockIdx.x * kTile;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, kRows x 4 outputs each
+    Cell<In> acc[kRows][4];
 
     for (uint32_t k0 = 0; k0 < k; k0 += kDepth) {
-        // 64 rows x 16 depth values per operand = 1024 values, 4 per thread.
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            int idx = threadIdx.x + t * 256;
-            int r = idx >> 4, d = idx & 15;
-            float av = 0.0f, bv = 0.0f;
-            if (m0 + r < m && k0 + d < k)
-                av = *reinterpret_cast<const float *>(a + (uint64_t)(m0 + r) * a_stride + (uint64_t)(k0 + d) * 4);
+        for (int idx = threadIdx.x; idx < kTile * kDepth; idx += 256) {
+            const int r = idx >> 4, d = idx & 15;
+            In bv = 0;
             if (n0 + r < n && k0 + d < k) bv = b[(uint64_t)(n0 + r) * b_stride_elems + k0 + d];
-            a_s[d][r] = av;
             b_s[d][r] = bv;
+            if (r < kTileRows) {
+                In av = 0;
+                if (m0 + r < m && k0 + d < k)
+                    av = *reinterpret_cast<const In *>(a + (uint64_t)(m0 + r) * a_stride + (uint64_t)(k0 + d) * sizeof(In));
+                a_s[d][r] = av;
+            }
         }
         __syncthreads();
 #pragma unroll
         for (int d = 0; d < kDepth; ++d) {
-            double av[4], bv[4];
+            double av[kRows], bv[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) av[i] = (double)a_s[d][ty * 4 + i];
+            for (int i = 0; i < kRows; ++i) av[i] = (double)a_s[d][ty * kRows + i];
 #pragma unroll
             for (int j = 0; j < 4; ++j) bv[j] = (double)b_s[d][tx * 4 + j];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < kRows; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fma(av[i], bv[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) acc[i][j].add(av[i], bv[j], d & 1);
         }
         __syncthreads();
     }
 
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint32_t row = m0 + ty * 4 + i;
+    for (int i = 0; i < kRows; ++i) {
+        uint32_t row = m0 + ty * kRows + i;
         if (row >= m) continue;
         double *c_row = reinterpret_cast<double *>(c + (uint64_t)row * c_stride);
         double an = 0.0;
@@ -69,7 +116,7 @@ gemm_f32_kernel(const uint8_t *__restrict__ a, uint64_t a_stride, const float *_
         for (int j = 0; j < 4; ++j) {
             uint32_t col = n0 + tx * 4 + j;
             if (col >= n || (tri_diag >= 0 && col < row + (uint32_t)tri_diag)) continue;
-            double v = acc[i][j];
+            double v = acc[i][j].total();
             if constexpr (kEpi == kEpiAngular) {
                 double product = an * b_norms[col];
                 if (product > 0.0) {
@@ -86,31 +133,46 @@ gemm_f32_kernel(const uint8_t *__restrict__ a, uint64_t a_stride, const float *_
     }
 }
 
+template <typename In>
+cudaError_t launch_fp64(int epilogue, const void *a, uint64_t a_stride, const void *b, uint64_t b_stride, const double *b_norms,
+                        const double *a_norms, double *c, uint64_t c_stride, uint64_t m, uint64_t n, uint64_t k,
+                        cudaStream_t stream, int32_t tri_diag) {
+    if (m == 0 || n == 0) return cudaSuccess;
+    if (m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull) return cudaErrorInvalidValue;
+    constexpr int kTileRows = sizeof(In) == 8 ? 32 : 64;
+    dim3 grid((unsigned)((n + kTile - 1) / kTile), (unsigned)((m + kTileRows - 1) / kTileRows));
+    if (grid.y > 65535) return cudaErrorInvalidValue;
+    const uint8_t *ab = static_cast<const uint8_t *>(a);
+    const In *bp = static_cast<const In *>(b);
+    uint8_t *cb = reinterpret_cast<uint8_t *>(c);
+    const uint64_t bse = b_stride / sizeof(In);
+    switch (epilogue) {
+    case kEpiDot:
+        gemm_fp64_kernel<kEpiDot, In><<<grid, 256, 0, stream>>>(ab, a_stride, bp, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k, tri_diag);
+        break;
+    case kEpiAngular:
+        gemm_fp64_kernel<kEpiAngular, In><<<grid, 256, 0, stream>>>(ab, a_stride, bp, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k, tri_diag);
+        break;
+    case kEpiEuclidean:
+        gemm_fp64_kernel<kEpiEuclidean, In><<<grid, 256, 0, stream>>>(ab, a_stride, bp, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k, tri_diag);
+        break;
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
 } // namespace
 
 cudaError_t launch_gemm_f32(int epilogue, const float *a, uint64_t a_stride, const float *b, uint64_t b_stride,
                             const double *b_norms, const double *a_norms, double *c, uint64_t c_stride, uint64_t m,
                             uint64_t n, uint64_t k, cudaStream_t stream, int32_t tri_diag) {
-    if (m == 0 || n == 0) return cudaSuccess;
-    if (m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull) return cudaErrorInvalidValue;
-    dim3 grid((unsigned)((n + kTile - 1) / kTile), (unsigned)((m + kTile - 1) / kTile));
-    if (grid.y > 65535) return cudaErrorInvalidValue;
-    const uint8_t *ab = reinterpret_cast<const uint8_t *>(a);
-    uint8_t *cb = reinterpret_cast<uint8_t *>(c);
-    const uint64_t bse = b_stride / 4;
-    switch (epilogue) {
-    case kEpiDot:
-        gemm_f32_kernel<kEpiDot><<<grid, 256, 0, stream>>>(ab, a_stride, b, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k, tri_diag);
-        break;
-    case kEpiAngular:
-        gemm_f32_kernel<kEpiAngular><<<grid, 256, 0, stream>>>(ab, a_stride, b, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k, tri_diag);
-        break;
-    case kEpiEuclidean:
-        gemm_f32_kernel<kEpiEuclidean><<<grid, 256, 0, stream>>>(ab, a_stride, b, bse, b_norms, a_norms, cb, c_stride, (uint32_t)m, (uint32_t)n, (uint32_t)k, tri_diag);
-        break;
-    default: return cudaErrorInvalidValue;
-    }
-    return cudaGetLastError();
+    return launch_fp64<float>(epilogue, a, a_stride, b, b_stride, b_norms, a_norms, c, c_stride, m, n, k, stream, tri_diag);
+}
+
+cudaError_t launch_gemm_f64(int epilogue, const double *a, uint64_t a_stride, const double *b, uint64_t b_stride,
+                            const double *b_norms, const double *a_norms, double *c, uint64_t c_stride, uint64_t m,
+                            uint64_t n, uint64_t k, cudaStream_t stream, int32_t tri_diag) {
+    return launch_fp64<double>(epilogue, a, a_stride, b, b_stride, b_norms, a_norms, c, c_stride, m, n, k, stream, tri_diag);
 }
 
 } // namespace nkb

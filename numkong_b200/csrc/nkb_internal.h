@@ -13,6 +13,7 @@ enum Dtype : uint32_t {
     kU1 = 1u << 1,    // eight one-bit values per byte (include/numkong/types.h:925)
     kI8 = 1u << 2,
     kU8 = 1u << 6,
+    kF64 = 1u << 10,
     kF32 = 1u << 11,
     kF16 = 1u << 12,
     kBF16 = 1u << 13,
@@ -66,18 +67,21 @@ static_assert(sizeof(PackedHeader) == 128, "header must be 128 bytes");
 
 inline uint32_t dtype_bytes(uint32_t dt) {
     switch (dt) {
+    case kF64: return 8;
     case kF32: return 4;
     case kF16: case kBF16: return 2;
     default: return 1;
     }
 }
-// Bytes of one stored norm: u32 for integers, f64 for f32, f32 otherwise.
-inline uint32_t norm_bytes(uint32_t dt) { return dt == kF32 ? 8 : 4; }
-// Bytes of one output cell of dots_packed: f64 for f32 inputs, 4 bytes otherwise.
-inline uint32_t dot_out_bytes(uint32_t dt) { return dt == kF32 ? 8 : 4; }
+// Bytes of one stored norm: u32 for integers, f64 for f32 / f64, f32 otherwise.
+inline uint32_t norm_bytes(uint32_t dt) { return (dt == kF32 || dt == kF64) ? 8 : 4; }
+// Bytes of one output cell of dots_packed: f64 for f32 / f64 inputs, 4 bytes otherwise.
+inline uint32_t dot_out_bytes(uint32_t dt) { return (dt == kF32 || dt == kF64) ? 8 : 4; }
+// f32 and f64 inputs run on CUDA cores with f64 results; their packed payload is plain row-major.
+inline bool is_cuda_core_dtype(uint32_t dt) { return dt == kF32 || dt == kF64; }
 inline bool dtype_supported(uint32_t dt) {
     switch (dt) {
-    case kI8: case kU8: case kF32: case kF16: case kBF16: case kE4M3: case kE5M2: case kE2M3: case kE3M2: case kI4: case kU4: case kU1: return true;
+    case kI8: case kU8: case kF32: case kF16: case kBF16: case kE4M3: case kE5M2: case kE2M3: case kE3M2: case kI4: case kU4: case kU1: case kF64: return true;
     default: return false;
     }
 }
@@ -198,6 +202,10 @@ int gemm_tc_launch_count(const GemmArgs &args);
 
 // f32 x f32 -> f64 on CUDA cores. `b` is the padded row-major f32 payload.
 cudaError_t launch_gemm_f32(int epilogue, const float *a, uint64_t a_stride, const float *b, uint64_t b_stride,
+                            const double *b_norms, const double *a_norms, double *c, uint64_t c_stride,
+                            uint64_t m, uint64_t n, uint64_t k, cudaStream_t stream, int32_t tri_diag = -1);
+// f64 x f64 -> f64 with the reference's two-lane Dot2 accumulation (bit-identical dots). Same layout rules.
+cudaError_t launch_gemm_f64(int epilogue, const double *a, uint64_t a_stride, const double *b, uint64_t b_stride,
                             const double *b_norms, const double *a_norms, double *c, uint64_t c_stride,
                             uint64_t m, uint64_t n, uint64_t k, cudaStream_t stream, int32_t tri_diag = -1);
 

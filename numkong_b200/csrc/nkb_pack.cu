@@ -174,6 +174,15 @@ struct SumSq {
     }
 };
 template <>
+struct SumSq<kF64> {
+    using Acc = double;
+    static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) {
+        double v;
+        memcpy(&v, p, 8);
+        acc += v * v;
+    }
+};
+template <>
 struct SumSq<kI8> {
     using Acc = unsigned long long;
     static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) {
@@ -218,7 +227,7 @@ struct SumSq<kU1> {  // a bit squared is the bit: the "norm" of a bit row is its
 template <uint32_t kDtype>
 __global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, uint64_t depth, uint64_t stride,
                                  void *__restrict__ out, int out_mode /*0 native, 1 f32*/, int inverse) {
-    constexpr uint32_t eb = kDtype == kF32 ? 4 : (kDtype == kF16 || kDtype == kBF16) ? 2 : 1;
+    constexpr uint32_t eb = kDtype == kF64 ? 8 : kDtype == kF32 ? 4 : (kDtype == kF16 || kDtype == kBF16) ? 2 : 1;
     constexpr uint32_t per16 = 16 / eb;
     using Acc = typename SumSq<kDtype>::Acc;
     const int lane = threadIdx.x & 31;
@@ -238,7 +247,7 @@ __global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, u
             done = vecs * per16;
         }
         for (uint64_t i = done + lane; i < depth; i += 32) {
-            uint8_t tmp[4];
+            uint8_t tmp[8];
             for (uint32_t bidx = 0; bidx < eb; ++bidx) tmp[bidx] = p[i * eb + bidx];
             SumSq<kDtype>::add(acc, tmp);
         }
@@ -251,7 +260,7 @@ __global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, u
                     static_cast<float *>(out)[row] = s > 0.0f ? (float)(1.0 / sqrt((double)s)) : 0.0f;
                 } else if (out_mode == 1) static_cast<float *>(out)[row] = (float)(uint32_t)acc;
                 else static_cast<uint32_t *>(out)[row] = (uint32_t)acc;
-            } else if constexpr (kDtype == kF32) {
+            } else if constexpr (kDtype == kF32 || kDtype == kF64) {
                 if (inverse) static_cast<float *>(out)[row] = acc > 0.0 ? (float)(1.0 / sqrt(acc)) : 0.0f;  // MaxSim keeps f32 inverse norms
                 else static_cast<double *>(out)[row] = acc;
             } else {
@@ -283,7 +292,7 @@ cudaError_t launch_row_sumsq(uint32_t dt, const void *x, uint64_t rows, uint64_t
 #define NKB_CASE(DT) case DT: row_sumsq_kernel<DT><<<grid, block, 0, stream>>>(p, rows, depth, stride_bytes, out, mode, inv); break
     switch (dt) {
         NKB_CASE(kI8); NKB_CASE(kU8); NKB_CASE(kF32); NKB_CASE(kF16); NKB_CASE(kBF16);
-        NKB_CASE(kE4M3); NKB_CASE(kE5M2); NKB_CASE(kE2M3); NKB_CASE(kE3M2); NKB_CASE(kI4); NKB_CASE(kU4); NKB_CASE(kU1);
+        NKB_CASE(kE4M3); NKB_CASE(kE5M2); NKB_CASE(kE2M3); NKB_CASE(kE3M2); NKB_CASE(kI4); NKB_CASE(kU4); NKB_CASE(kU1); NKB_CASE(kF64);
     default: return cudaErrorInvalidValue;
     }
 #undef NKB_CASE
@@ -298,7 +307,7 @@ cudaError_t launch_pack_payload(uint32_t dt, const void *b, uint64_t rows, uint6
     const int block = 256;
     const int grid = grid_for(pieces, block, 148 * 32);
     const uint64_t row_bytes = source_row_bytes(dt, depth);
-    if (dt == kF32)
+    if (is_cuda_core_dtype(dt))
         pack_payload_kernel<false><<<grid, block, 0, stream>>>(static_cast<const uint8_t *>(b), rows, row_bytes, stride_bytes,
                                                                static_cast<uint4 *>(payload), pieces, kblocks, kPieceNone);
     else

@@ -84,7 +84,7 @@ void symmetric_impl(uint32_t dt, int epilogue, const void *vectors, uint64_t cou
     void *a_norms = nullptr;
     if (epilogue != kEpiDot) {
         a_norms = scratch(kSlotNorms, m * 8);
-        ok = a_norms && cuda_ok(launch_row_sumsq(op_dt, a_raw, m, op_depth, a_pitch, a_norms, dt != kF32, false, stream), "row norm kernel");
+        ok = a_norms && cuda_ok(launch_row_sumsq(op_dt, a_raw, m, op_depth, a_pitch, a_norms, !is_cuda_core_dtype(dt), false, stream), "row norm kernel");
         g_launches++;
     }
     const void *a_dev = a_raw;
@@ -121,6 +121,12 @@ void symmetric_impl(uint32_t dt, int epilogue, const void *vectors, uint64_t cou
                                      g.depth_padded_bytes, reinterpret_cast<const double *>(blob + g.norms_offset),
                                      static_cast<const double *>(a_norms), reinterpret_cast<double *>(c_dev), c_pitch, m, cols, depth, stream,
                                      tri_diag), "f32 GEMM kernel");
+        g_launches++;
+    } else if (ok && dt == kF64) {
+        ok = cuda_ok(launch_gemm_f64(epilogue, static_cast<const double *>(a_dev), a_pitch, reinterpret_cast<const double *>(blob + g.payload_offset),
+                                     g.depth_padded_bytes, reinterpret_cast<const double *>(blob + g.norms_offset),
+                                     static_cast<const double *>(a_norms), reinterpret_cast<double *>(c_dev), c_pitch, m, cols, depth, stream,
+                                     tri_diag), "f64 GEMM kernel");
         g_launches++;
     } else if (ok) {
         GemmArgs args;
@@ -178,6 +184,7 @@ NKB_DEFINE_SYMMETRIC(e2m3, kE2M3)
 NKB_DEFINE_SYMMETRIC(e3m2, kE3M2)
 NKB_DEFINE_SYMMETRIC(i4, kI4)
 NKB_DEFINE_SYMMETRIC(u4, kU4)
+NKB_DEFINE_SYMMETRIC(f64, kF64)
 
 // One-bit vectors (include/numkong/dots.h:357, include/numkong/sets.h:84-117).
 NKB_API void nk_dots_symmetric_u1(void const *vectors, nk_size_t count, nk_size_t depth, nk_size_t stride, void *result,

@@ -20,10 +20,10 @@ REF_SO = _HERE / "_ref" / "libnumkong.so"
 REF_SERIAL_SO = _HERE / "_ref" / "libnkref_serial.so"
 
 CODES = {"i8": 1 << 2, "u8": 1 << 6, "f32": 1 << 11, "f16": 1 << 12, "bf16": 1 << 13,
-         "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17, "u1": 1 << 1}
-BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i4": 1, "u4": 1, "u1": 1}
+         "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17, "u1": 1 << 1, "f64": 1 << 10}
+BYTES = {"i8": 1, "u8": 1, "f32": 4, "f16": 2, "bf16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i4": 1, "u4": 1, "u1": 1, "f64": 8}
 STORAGE = {"i8": np.int8, "u8": np.uint8, "f32": np.float32, "f16": np.uint16, "bf16": np.uint16,
-           "e4m3": np.uint8, "e5m2": np.uint8, "e2m3": np.uint8, "e3m2": np.uint8, "i4": np.uint8, "u4": np.uint8, "u1": np.uint8}
+           "e4m3": np.uint8, "e5m2": np.uint8, "e2m3": np.uint8, "e3m2": np.uint8, "i4": np.uint8, "u4": np.uint8, "u1": np.uint8, "f64": np.float64}
 
 
 def _depth(x: np.ndarray, dtype: str, depth: Optional[int]) -> int:
@@ -91,7 +91,7 @@ def decode(x: np.ndarray, dtype: str) -> np.ndarray:
 
 
 def out_dtype(dtype: str, op: str = "dots"):
-    if dtype == "f32":
+    if dtype in ("f32", "f64"):
         return np.float64
     if op == "dots" and dtype in ("i8", "i4"):
         return np.int32

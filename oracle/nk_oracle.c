@@ -26,6 +26,7 @@ enum {
     ORC_E4M3 = 1 << 14, ORC_E5M2 = 1 << 15, ORC_E2M3 = 1 << 18, ORC_E3M2 = 1 << 19,
     ORC_I4 = 1 << 16, ORC_U4 = 1 << 17, /* two values per byte, low nibble first; depth counts values */
     ORC_U1 = 1 << 1,                    /* eight values per byte; depth counts bits */
+    ORC_F64 = 1 << 10,
 };
 #define ORC_IS_INT(dt) ((dt) == ORC_I8 || (dt) == ORC_U8 || (dt) == ORC_I4 || (dt) == ORC_U4 || (dt) == ORC_U1)
 #define ORC_IS_SIGNED_INT(dt) ((dt) == ORC_I8 || (dt) == ORC_I4)
@@ -80,7 +81,7 @@ static float dec_e3m2(const uint8_t *p) {
     return (b & 0x20u) ? -v : v;
 }
 
-static int elem_bytes(int dt) { return dt == ORC_F32 ? 4 : (dt == ORC_F16 || dt == ORC_BF16) ? 2 : 1; }
+static int elem_bytes(int dt) { return dt == ORC_F64 ? 8 : dt == ORC_F32 ? 4 : (dt == ORC_F16 || dt == ORC_BF16) ? 2 : 1; }
 
 static float dec(int dt, const uint8_t *p) {
     switch (dt) {
@@ -153,6 +154,36 @@ static int nibble(int dt, uint8_t byte, int high) {
     int x = high ? (byte >> 4) & 0xf : byte & 0xf;
     return dt == ORC_I4 ? (x ^ 8) - 8 : x;
 }
+/* f64 inputs: Dot2 - error-free product (FMA) and error-free sum (TwoSum), the errors gathered in a compensation term
+ * (include/numkong/scalar/serial.h:128-136) - in two lanes, even and odd depth indices (dot/serial.h:274-296), folded by
+ * the compensated lane reduction of include/numkong/reduce/serial.h:33-48. */
+static void dot2(double *sum, double *compensation, double a, double b) {
+    double product = a * b;
+    double product_error = fma(a, b, -product);
+    double running_sum = *sum + product;
+    double recovered_addend = running_sum - *sum;
+    double sum_error = (*sum - (running_sum - recovered_addend)) + (product - recovered_addend);
+    *sum = running_sum;
+    *compensation += sum_error + product_error;
+}
+static double dot_f64_dot2(const uint8_t *a, const uint8_t *b, uint64_t k) {
+    double sums[2] = {0, 0}, comps[2] = {0, 0};
+    for (uint64_t l = 0; l < k; ++l) {
+        double x, y; memcpy(&x, a + 8 * l, 8); memcpy(&y, b + 8 * l, 8);
+        dot2(&sums[l & 1], &comps[l & 1], x, y);
+    }
+    double running_sum = 0, accumulated_error = 0;
+    for (int i = 0; i < 2; ++i) {
+        double parts[2] = {sums[i], comps[i]};
+        for (int p = 0; p < 2; ++p) {
+            double tentative_sum = running_sum + parts[p];
+            double virtual_addend = tentative_sum - running_sum;
+            accumulated_error += (running_sum - (tentative_sum - virtual_addend)) + (parts[p] - virtual_addend);
+            running_sum = tentative_sum;
+        }
+    }
+    return running_sum + accumulated_error;
+}
 static int64_t dot_int(int dt, const uint8_t *a, const uint8_t *b, uint64_t k) {
     int64_t s = 0;
     if (dt == ORC_U1) { /* AND-popcount over whole bytes (include/numkong/dots/serial.h u1 instantiation, set/serial.h) */
@@ -179,6 +210,7 @@ ORC_API void orc_dots(int dt, const void *a, uint64_t a_stride, const void *b, u
             const uint8_t *x = ap + i * a_stride, *y = bp + j * b_stride;
             if (ORC_IS_INT(dt)) ((int32_t *)row)[j] = (int32_t)dot_int(dt, x, y, k);
             else if (dt == ORC_F32) ((double *)row)[j] = dot_f64lanes(x, y, k);
+            else if (dt == ORC_F64) ((double *)row)[j] = dot_f64_dot2(x, y, k);
             else ((float *)row)[j] = dot_f32lanes(dt, x, y, k);
         }
     }
@@ -203,12 +235,13 @@ static float sumsq_f32_neumaier(int dt, const uint8_t *x, uint64_t k) {
 ORC_API double orc_sumsq(int dt, const void *x, uint64_t k) {
     const uint8_t *p = (const uint8_t *)x;
     if (ORC_IS_INT(dt)) return (double)(uint32_t)(uint64_t)dot_int(dt, p, p, k);
-    if (dt == ORC_F32) {
-        /* the same compensated sum carried in f64 (reduce/serial.h:50-70) */
+    if (dt == ORC_F32 || dt == ORC_F64) {
+        /* the same compensated sum carried in f64 (reduce/serial.h:50-92) */
         double run = 0, comp = 0;
         for (uint64_t l = 0; l < k; ++l) {
-            float v; memcpy(&v, p + 4 * l, 4);
-            double sq = (double)v * (double)v, t = run + sq;
+            double v;
+            if (dt == ORC_F32) { float f; memcpy(&f, p + 4 * l, 4); v = f; } else memcpy(&v, p + 8 * l, 8);
+            double sq = v * v, t = run + sq;
             if (run >= sq) comp += (run - t) + sq; else comp += (sq - t) + run;
             run = t;
         }
@@ -244,8 +277,8 @@ ORC_API void orc_spatials(int kind, int dt, const void *a, uint64_t a_stride, co
         double an = orc_sumsq(dt, x, k);
         for (uint64_t j = 0; j < n; ++j) {
             const uint8_t *y = bp + j * b_stride;
-            if (dt == ORC_F32) {
-                double dot = dot_f64lanes(x, y, k), r;
+            if (dt == ORC_F32 || dt == ORC_F64) {
+                double dot = dt == ORC_F32 ? dot_f64lanes(x, y, k) : dot_f64_dot2(x, y, k), r;
                 if (kind == 0) {
                     double product = an * bn[j];
                     if (product > 0) { r = 1.0 - dot * rsqrt_f64(product); r = r > 0 ? r : 0; }

@@ -37,6 +37,7 @@ REF_PACKED_FAMILY(e3m2, nk_e3m2_t, nk_f32_t, nk_f32_t)
 REF_PACKED_FAMILY(f32, nk_f32_t, nk_f64_t, nk_f64_t)
 REF_PACKED_FAMILY(i4, nk_i4x2_t, nk_i32_t, nk_f32_t)
 REF_PACKED_FAMILY(u4, nk_u4x2_t, nk_u32_t, nk_f32_t)
+REF_PACKED_FAMILY(f64, nk_f64_t, nk_f64_t, nk_f64_t)
 
 /* one-bit vectors: AND-popcount product and the two set distances */
 REF_API nk_size_t ref_dots_packed_size_u1(nk_size_t n, nk_size_t k) { return nk_dots_packed_size_u1_serial(n, k); }

@@ -51,7 +51,7 @@ def main():
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "packed_path.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
-    # Sub-byte types (file nibble_path.npz). 4-bit types: uniformly random bytes (every nibble value), depths counted in values - odd ones included, where the
+    # Types added after the first nine (file nibble_path.npz): sub-byte integers, bit vectors, f64. 4-bit types: uniformly random bytes (every nibble value), depths counted in values - odd ones included, where the
     # reference lets the second nibble of the last byte take part.
     out = {}
     for dt in ("i4", "u4"):
@@ -74,6 +74,16 @@ def main():
         for op in ("dots", "hammings", "jaccards"):
             out[f"{key}_{op}_serial"] = getattr(serial, op)(a, b, "u1", depth=k)
             out[f"{key}_{op}_dispatch"] = getattr(dispatch, op)(a, b, "u1", depth=k)
+    # f64: N(0,1) values spread over forty binades, so that the compensated (Dot2) accumulation matters.
+    for si, (m, n, k) in enumerate(SHAPES):
+        rng = np.random.default_rng(4000 + si)
+        a = rng.standard_normal((m, k)) * np.exp2(rng.integers(-20, 21, (m, k)))
+        b = rng.standard_normal((n, k)) * np.exp2(rng.integers(-20, 21, (n, k)))
+        key = f"f64_{m}x{n}x{k}"
+        out[key + "_a"], out[key + "_b"] = a, b
+        for op in ("dots", "angulars", "euclideans"):
+            out[f"{key}_{op}_serial"] = getattr(serial, op)(a, b, "f64")
+            out[f"{key}_{op}_dispatch"] = getattr(dispatch, op)(a, b, "f64")
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "nibble_path.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")

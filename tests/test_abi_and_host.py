@@ -50,7 +50,7 @@ def test_packed_size_is_pure_and_bounds_the_payload():
     for dt in nk.MAXSIM_DTYPES:
         assert nk.MaxSimPackedMatrix.packed_size(180, 128, dt) >= 180 * 128 * nk.DTYPE_BYTES[dt]
     with pytest.raises(LookupError):
-        nk.PackedMatrix.packed_size(4, 4, "f64")
+        nk.PackedMatrix.packed_size(4, 4, "f64c")
 
 
 def test_find_kernel_punned_contract():
@@ -73,7 +73,7 @@ def test_find_kernel_punned_contract():
             assert fn.value and cap.value
     lib.nk_find_kernel_punned(ord("T"), nk.DTYPE_CODES["i8"], (1 << 64) - 1, ctypes.byref(fn), ctypes.byref(cap))
     assert not fn.value and cap.value == 0
-    lib.nk_find_kernel_punned(ord("G"), 1 << 10, (1 << 64) - 1, ctypes.byref(fn), ctypes.byref(cap))  # f64: not on this path
+    lib.nk_find_kernel_punned(ord("G"), 1 << 20, (1 << 64) - 1, ctypes.byref(fn), ctypes.byref(cap))  # a complex type: not on this path
     assert not fn.value and cap.value == 0
     lib.nk_find_kernel_punned(ord("G"), nk.DTYPE_CODES["i8"], 0x3, ctypes.byref(fn), ctypes.byref(cap))  # capability masked out
     assert not fn.value and cap.value == 0
@@ -84,7 +84,7 @@ def test_python_mirror_argument_checks():
     with pytest.raises(ValueError):
         nk.dots_pack(np.zeros(8, dtype=np.int8))                      # not 2-D
     with pytest.raises(TypeError):
-        nk.dots_pack(np.zeros((2, 2), dtype=np.float64))              # f64 is not on this path
+        nk.dots_pack(np.zeros((2, 2), dtype=np.complex128))           # complex types are not on this path
     with pytest.raises(TypeError):
         nk.dots_pack(np.zeros((2, 2), dtype=np.uint8), dtype="bf16")  # wrong storage width
     with pytest.raises(ValueError):

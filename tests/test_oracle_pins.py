@@ -205,3 +205,19 @@ def test_one_bit_known_answers():
     assert oracle.hammings(a, b).tolist() == [[1, 4]]
     assert np.allclose(oracle.jaccards(a, b), [[1 - 3 / 4, 1.0]])
     assert oracle.jaccards(b[1:], b[1:])[0, 0] == 0.0  # two empty sets
+
+
+@pytest.mark.parametrize("shape", GOLDEN_SHAPES)
+def test_f64_oracle_matches_reference_golden(shape):
+    """f64: two-lane Dot2 accumulation restated operation by operation - bit for bit against the reference's scalar kernels
+    (dots, angular, Euclidean) and against its dispatched back end on the dots."""
+    m, n, k = shape
+    key = f"f64_{m}x{n}x{k}"
+    a, b = NIBBLE_GOLDEN[key + "_a"], NIBBLE_GOLDEN[key + "_b"]
+    for op in ("dots", "angulars", "euclideans"):
+        assert _bits_equal(getattr(oracle, op)(a, b, "f64"), NIBBLE_GOLDEN[f"{key}_{op}_serial"])
+    assert _bits_equal(oracle.dots(a, b, "f64"), NIBBLE_GOLDEN[key + "_dots_dispatch"])
+    # Dot2 is worth having: on these inputs a plain f64 loop is measurably further from the exact value
+    exact = np.array([[float(sum(__import__("fractions").Fraction(x) * __import__("fractions").Fraction(y) for x, y in zip(r, c)))
+                       for c in b[:3]] for r in a[:3]])
+    assert np.max(np.abs(oracle.dots(a, b, "f64")[:3, :3] - exact)) <= np.max(np.abs((a @ b.T)[:3, :3] - exact))
