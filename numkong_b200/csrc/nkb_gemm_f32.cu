@@ -17,7 +17,6 @@ namespace nkb {
 
 namespace {
 
-constexpr int kTile = 64;   // output tile edge
 constexpr int kDepth = 16;  // depth slice per shared-memory stage (even, so lane parity = parity inside the slice)
 
 // Accumulator of one output cell.
@@ -61,60 +60,91 @@ struct Cell<double> {  // two Dot2 lanes
     }
 };
 
+// Register tile of one thread: kTR x kTC output cells, spread with a stride of 16 over the block tile so that a warp's
+// shared-memory reads are broadcasts (rows) or consecutive words (columns) and its stores to C are contiguous.
+template <typename In> struct TileShape;
+template <> struct TileShape<float> { static constexpr int kTR = 8, kTC = 8; };    // 64 f64 accumulators
+template <> struct TileShape<double> { static constexpr int kTR = 2, kTC = 4; };   // 8 Dot2 cells = 32 doubles (4 x 4 cells: 220 registers, slower)
+
 template <int kEpi, typename In>
 __global__ void __launch_bounds__(256)
 gemm_fp64_kernel(const uint8_t *__restrict__ a, uint64_t a_stride, const In *__restrict__ b, uint64_t b_stride_elems,
                  const double *__restrict__ b_norms, const double *__restrict__ a_norms, uint8_t *__restrict__ c,
                  uint64_t c_stride, uint32_t m, uint32_t n, uint32_t k, int32_t tri_diag) {
-    constexpr int kRows = sizeof(In) == 8 ? 2 : 4;  // output rows per thread: the Dot2 cells are four doubles each
-    constexpr int kTileRows = 16 * kRows;
+    constexpr int kTR = TileShape<In>::kTR, kTC = TileShape<In>::kTC;
+    constexpr int kTileRows = 16 * kTR, kTileCols = 16 * kTC;
     // Triangular mode (A x A^T): only cells with column >= row + tri_diag are wanted; blocks wholly below that line leave.
-    if (tri_diag >= 0 && (blockIdx.x + 1) * kTile <= blockIdx.y * kTileRows + (uint32_t)tri_diag) return;
-    __shared__ In a_s[kDepth][kTileRows + 1];
-    __shared__ In b_s[kDepth][kTile + 1];
-    const uint32_t m0 = blockIdx.y * kTileRows, n0 = blockIdx.x * kTile;
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, kRows x 4 outputs each
-    Cell<In> acc[kRows][4];
+    if (tri_diag >= 0 && (blockIdx.x + 1) * kTileCols <= blockIdx.y * kTileRows + (uint32_t)tri_diag) return;
+    // Operands are widened to f64 once, on their way into shared memory.
+    __shared__ double a_s[kDepth][kTileRows + 2];
+    __shared__ double b_s[kDepth][kTileCols + 2];
+    const uint32_t m0 = blockIdx.y * kTileRows, n0 = blockIdx.x * kTileCols;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    Cell<In> acc[kTR][kTC];
 
-    for (uint32_t k0 = 0; k0 < k; k0 += kDepth) {
-        for (int idx = threadIdx.x; idx < kTile * kDepth; idx += 256) {
-            const int r = idx >> 4, d = idx & 15;
-            In bv = 0;
-            if (n0 + r < n && k0 + d < k) bv = b[(uint64_t)(n0 + r) * b_stride_elems + k0 + d];
-            b_s[d][r] = bv;
-            if (r < kTileRows) {
-                In av = 0;
-                if (m0 + r < m && k0 + d < k)
-                    av = *reinterpret_cast<const In *>(a + (uint64_t)(m0 + r) * a_stride + (uint64_t)(k0 + d) * sizeof(In));
-                a_s[d][r] = av;
-            }
+    // The next depth slice travels from global memory into registers while the current one is being multiplied.
+    constexpr int kAPer = kTileRows * kDepth / 256, kBPer = kTileCols * kDepth / 256;
+    In a_next[kAPer], b_next[kBPer];
+    auto fetch = [&](uint32_t k0) {
+#pragma unroll
+        for (int t = 0; t < kAPer; ++t) {
+            const int idx = threadIdx.x + t * 256, r = idx >> 4, d = idx & 15;
+            a_next[t] = (m0 + r < m && k0 + d < k)
+                            ? *reinterpret_cast<const In *>(a + (uint64_t)(m0 + r) * a_stride + (uint64_t)(k0 + d) * sizeof(In)) : In(0);
         }
-        __syncthreads();
+#pragma unroll
+        for (int t = 0; t < kBPer; ++t) {
+            const int idx = threadIdx.x + t * 256, r = idx >> 4, d = idx & 15;
+            b_next[t] = (n0 + r < n && k0 + d < k) ? b[(uint64_t)(n0 + r) * b_stride_elems + k0 + d] : In(0);
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int t = 0; t < kAPer; ++t) {
+            const int idx = threadIdx.x + t * 256;
+            a_s[idx & 15][idx >> 4] = (double)a_next[t];
+        }
+#pragma unroll
+        for (int t = 0; t < kBPer; ++t) {
+            const int idx = threadIdx.x + t * 256;
+            b_s[idx & 15][idx >> 4] = (double)b_next[t];
+        }
+    };
+    fetch(0);
+    stash();
+    __syncthreads();
+    for (uint32_t k0 = 0; k0 < k; k0 += kDepth) {
+        const bool more = k0 + kDepth < k;
+        if (more) fetch(k0 + kDepth);
 #pragma unroll
         for (int d = 0; d < kDepth; ++d) {
-            double av[kRows], bv[4];
+            double av[kTR], bv[kTC];
 #pragma unroll
-            for (int i = 0; i < kRows; ++i) av[i] = (double)a_s[d][ty * kRows + i];
+            for (int i = 0; i < kTR; ++i) av[i] = a_s[d][ty + 16 * i];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) bv[j] = (double)b_s[d][tx * 4 + j];
+            for (int j = 0; j < kTC; ++j) bv[j] = b_s[d][tx + 16 * j];
 #pragma unroll
-            for (int i = 0; i < kRows; ++i)
+            for (int i = 0; i < kTR; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j].add(av[i], bv[j], d & 1);
+                for (int j = 0; j < kTC; ++j) acc[i][j].add(av[i], bv[j], d & 1);
         }
         __syncthreads();
+        if (more) {
+            stash();
+            __syncthreads();
+        }
     }
 
 #pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-        uint32_t row = m0 + ty * kRows + i;
+    for (int i = 0; i < kTR; ++i) {
+        const uint32_t row = m0 + ty + 16 * i;
         if (row >= m) continue;
         double *c_row = reinterpret_cast<double *>(c + (uint64_t)row * c_stride);
         double an = 0.0;
         if constexpr (kEpi != kEpiDot) an = a_norms[row];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint32_t col = n0 + tx * 4 + j;
+        for (int j = 0; j < kTC; ++j) {
+            const uint32_t col = n0 + tx + 16 * j;
             if (col >= n || (tri_diag >= 0 && col < row + (uint32_t)tri_diag)) continue;
             double v = acc[i][j].total();
             if constexpr (kEpi == kEpiAngular) {
@@ -139,8 +169,8 @@ cudaError_t launch_fp64(int epilogue, const void *a, uint64_t a_stride, const vo
                         cudaStream_t stream, int32_t tri_diag) {
     if (m == 0 || n == 0) return cudaSuccess;
     if (m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull) return cudaErrorInvalidValue;
-    constexpr int kTileRows = sizeof(In) == 8 ? 32 : 64;
-    dim3 grid((unsigned)((n + kTile - 1) / kTile), (unsigned)((m + kTileRows - 1) / kTileRows));
+    constexpr int kTileRows = 16 * TileShape<In>::kTR, kTileCols = 16 * TileShape<In>::kTC;
+    dim3 grid((unsigned)((n + kTileCols - 1) / kTileCols), (unsigned)((m + kTileRows - 1) / kTileRows));
     if (grid.y > 65535) return cudaErrorInvalidValue;
     const uint8_t *ab = static_cast<const uint8_t *>(a);
     const In *bp = static_cast<const In *>(b);
