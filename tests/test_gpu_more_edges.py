@@ -1,0 +1,63 @@
+"""Edge cases of the later additions: padded result matrices and tiny inputs of the symmetric family, sub-byte operands on
+the row-pipelined host path, wide-store (short depth) products with ragged shapes and strides."""
+import numpy as np
+import pytest
+
+import numkong_b200 as nk
+import oracle
+from numkong_b200 import synthetic as syn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n", [1, 2, 31, 257])
+def test_symmetric_tiny_and_padded_result(n):
+    v = np.random.default_rng(n).integers(-128, 128, (n, 40), dtype=np.int8)
+    wide = np.full((n, n + 5), -3, dtype=np.int32)           # result rows are longer than the matrix
+    out = wide[:, :n]
+    nk.dots_symmetric(v, out=out)
+    want = oracle.dots(v, v, "i8")
+    upper = np.triu(np.ones((n, n), dtype=bool))
+    assert np.array_equal(out[upper], want[upper])
+    assert np.all(out[~upper] == -3) and np.all(wide[:, n:] == -3)
+
+
+@pytest.mark.parametrize("dtype,per", [("i4", 2), ("u4", 2), ("u1", 8)])
+def test_sub_byte_operands_on_the_pipelined_host_path(dtype, per):
+    m, n, k = 4500, 300, 1024                                  # m >= 2048 host rows: uploaded and multiplied block by block
+    rng = np.random.default_rng(3)
+    a = rng.integers(0, 256, (m, k // per), dtype=np.uint8)
+    b = rng.integers(0, 256, (n, k // per), dtype=np.uint8)
+    c = nk.dots_packed(a, nk.dots_pack(b, dtype), dtype=dtype)
+    rows = rng.integers(0, m, 64)
+    assert np.array_equal(c[rows], oracle.dots(a[rows], b, dtype))
+    assert np.array_equal(c[-3:], oracle.dots(a[-3:], b, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "i8", "e5m2"])
+@pytest.mark.parametrize("k", [1, 64, 200, 256])
+def test_short_depth_products_with_ragged_shapes(dtype, k):
+    """Depths of at most 512 bytes per row take the three-stage kernel with 64-column staged stores."""
+    m, n = 300, 1000
+    a, b = syn.normal_matrix(m, k, dtype, 5), syn.normal_matrix(n, k, dtype, 6)
+    wide = np.zeros((m, n + 3), dtype=np.int32 if dtype == "i8" else np.float32)
+    out = wide[:, 1:n + 1]                                     # rows start 4 bytes off a 16-byte boundary
+    nk.dots_packed(a, nk.dots_pack(b, dtype), out=out, dtype=dtype)
+    want = oracle.dots(a, b, dtype)
+    if dtype == "i8":
+        assert np.array_equal(out, want)
+    else:
+        exact = oracle.exact_dots_f64(a, b, dtype)
+        scale = np.abs(oracle.decode(a, dtype).astype(np.float64)) @ np.abs(oracle.decode(b, dtype).astype(np.float64)).T
+        assert np.max(np.abs(out - exact) / np.maximum(scale, 1e-30)) <= 2.5e-7
+    assert np.all(wide[:, 0] == 0) and np.all(wide[:, n + 1:] == 0)
+    import torch
+    ta, tb = torch.from_numpy(a.view(np.int16) if dtype == "bf16" else a).cuda(), torch.from_numpy(b.view(np.int16) if dtype == "bf16" else b).cuda()
+    for op in ("angulars", "euclideans"):
+        got = getattr(nk, op + "_packed")(ta, nk.dots_pack(tb, dtype), dtype=dtype)
+        assert nk.synchronize() == 0
+        ref = getattr(oracle, op)(a, b, dtype)
+        if op == "angulars":
+            assert np.max(np.abs(got.cpu().numpy() - ref)) <= 5e-7
+        else:
+            assert np.max(np.abs(got.cpu().numpy() - ref) / np.maximum(np.abs(ref), 1e-3)) <= 4e-6
