@@ -142,6 +142,19 @@ NKB_API void nk_jaccards_packed_u1(void const *v, void const *q_packed, void *re
 NKB_API void nk_jaccards_symmetric_u1(void const *vectors, nk_size_t vectors_count, nk_size_t d, nk_size_t stride,
                                       void *result, nk_size_t result_stride, nk_size_t row_start, nk_size_t row_count);
 
+/* ---- In-place down-casts of a finished dots matrix -----------------------------------------------
+ * replace the header-level helpers include/numkong/dots/serial.h:2707-2754 (nk_dots_compact_bf16_serial,
+ * nk_dots_compact_i8_serial; AMX twins dots/sapphireamx.h:1301, :1834). The matrix `c` (rows `c_stride_in_bytes`
+ * apart) is overwritten from its first byte with the tightly packed result: row r starts at byte
+ * r * column_count * sizeof(out).
+ *   bf16: every f32 cell rounded to nearest even.
+ *   i8:   every i32 cell c[i][j] * 127 / sqrt(a_squared_norms[i] * b_squared_norms[j]), computed in f32 with the
+ *         reference's own reciprocal square root, truncated toward zero, clamped to [-128, 127]; 0 when a norm is 0.
+ * Host or device pointers (the norm vectors too). */
+NKB_API void nk_dots_compact_bf16(void *c, nk_size_t row_count, nk_size_t column_count, nk_size_t c_stride_in_bytes);
+NKB_API void nk_dots_compact_i8(void *c, nk_size_t row_count, nk_size_t column_count, nk_size_t c_stride_in_bytes,
+                                int32_t const *a_squared_norms, int32_t const *b_squared_norms);
+
 /* ---- MaxSim late interaction -------------------------------------------------------------------
  * replaces include/numkong/maxsim.h:72-114 (wrappers c/numkong.c:738-765). Both sides are packed
  * with the same function. result: f32 for bf16/f16, f64 for f32 (maxsim.h:350-357):

@@ -344,6 +344,43 @@ def jaccards_symmetric(vectors: Any, *, dtype: Optional[str] = "u1", out: Any = 
     return _symmetric_call("jaccards", vectors, out, dtype, start_row, end_row)
 
 
+def dots_compact(c: Any, a_squared_norms: Any = None, b_squared_norms: Any = None):
+    """Down-casts a finished dots matrix IN PLACE and returns the tightly packed result as a view of `c`'s memory:
+    f32 cells become bf16 (round to nearest even; returned as torch.bfloat16 or uint16 storage), i32 cells become i8
+    rescaled by 127 / (|a_i| |b_j|) from the two squared-norm vectors (int32). Mirrors nk_dots_compact_bf16_serial /
+    nk_dots_compact_i8_serial (include/numkong/dots/serial.h:2707-2754). `c` is overwritten from its first byte."""
+    cells = str(c.dtype).replace("torch.", "") if hasattr(c, "dtype") else ""
+    if cells not in ("float32", "int32"):
+        raise TypeError("dots_compact takes the f32 result of a bf16 product or the i32 result of an i8 product")
+    to_i8 = cells == "int32"
+    v = _View(c, "f32")  # four-byte cells either way
+    if to_i8:
+        norms = []
+        for vec, count in ((a_squared_norms, v.rows), (b_squared_norms, v.cols)):
+            if vec is None:
+                raise ValueError("the i8 form needs the squared norms of both operands")
+            if _is_torch(vec):
+                if str(vec.dtype) != "torch.int32" or vec.numel() != count or not vec.is_contiguous():
+                    raise ValueError("squared norms must be contiguous int32 vectors, one entry per row / column")
+            else:
+                vec = np.ascontiguousarray(vec, dtype=np.int32)
+                if vec.size != count:
+                    raise ValueError("squared norms must hold one entry per row / column")
+            norms.append(vec)
+        lib.nk_dots_compact_i8(v.ptr, v.rows, v.cols, v.stride, _ptr(norms[0]), _ptr(norms[1]))
+    else:
+        lib.nk_dots_compact_bf16(v.ptr, v.rows, v.cols, v.stride)
+    check("dots_compact")
+    if _is_torch(v.obj):
+        import torch
+        flat = v.obj.view(torch.int8 if to_i8 else torch.bfloat16)
+        return torch.as_strided(flat, (v.rows, v.cols), (v.cols, 1), flat.storage_offset())
+    if isinstance(v.obj, np.ndarray):
+        flat = v.obj.view(np.int8 if to_i8 else np.uint16)
+        return np.lib.stride_tricks.as_strided(flat, shape=(v.rows, v.cols), strides=(v.cols * flat.itemsize, flat.itemsize))
+    return None
+
+
 def maxsim_pack(vectors: Any, dtype: Optional[str] = None) -> MaxSimPackedMatrix:
     """Packs the token vectors of a query or a document. Mirrors nk.maxsim_pack."""
     v = _View(vectors, dtype)

@@ -72,6 +72,8 @@ def _load() -> ctypes.CDLL:
     for t in ("bf16", "f16"):
         f = getattr(lib, f"nkb_maxsims_packed_{t}")
         f.restype, f.argtypes = None, [vp, vp, sz, vp, vp, sz, sz, vp, sz]
+    lib.nk_dots_compact_bf16.restype, lib.nk_dots_compact_bf16.argtypes = None, [vp, sz, sz, sz]
+    lib.nk_dots_compact_i8.restype, lib.nk_dots_compact_i8.argtypes = None, [vp, sz, sz, sz, vp, vp]
     lib.nkb_topk_smallest_f32.restype = None
     lib.nkb_topk_smallest_f32.argtypes = [vp, sz, sz, sz, sz, sz, vp, vp]
     return lib

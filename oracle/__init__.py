@@ -56,6 +56,8 @@ def _load() -> ctypes.CDLL:
     lib.orc_sumsq.restype, lib.orc_sumsq.argtypes = ctypes.c_double, [i32, vp, u64]
     lib.orc_sets.restype, lib.orc_sets.argtypes = None, [i32, vp, u64, vp, u64, vp, u64, u64, u64, u64]
     lib.orc_rsqrt_f32.restype, lib.orc_rsqrt_f32.argtypes = ctypes.c_float, [ctypes.c_float]
+    lib.orc_compact_bf16.restype, lib.orc_compact_bf16.argtypes = None, [vp, u64, u64, u64]
+    lib.orc_compact_i8.restype, lib.orc_compact_i8.argtypes = None, [vp, u64, u64, u64, vp, vp]
     for name in ("orc_maxsim_argmax_dot", "orc_maxsim_coarse_i8"):
         f = getattr(lib, name)
         f.restype, f.argtypes = ctypes.c_double, [i32, vp, u64, u64, vp, u64, u64, u64, vp]
@@ -140,6 +142,27 @@ def hammings(a, b, dtype: str = "u1", depth: Optional[int] = None):
 def jaccards(a, b, dtype: str = "u1", depth: Optional[int] = None):
     """Jaccard distances between bit vectors (f32)."""
     return _sets(1, a, b, depth)
+
+
+def _compact(lib_fn_bf16, lib_fn_i8, c: np.ndarray, a_norms, b_norms) -> np.ndarray:
+    """Runs an in-place compaction on a copy of `c` (f32 -> bf16 bits, or i32 -> i8 with the two squared-norm vectors)."""
+    assert c.ndim == 2 and c.strides[1] == 4 and c.dtype in (np.float32, np.int32)
+    rows, cols = c.shape
+    stride = c.strides[0]
+    work = np.zeros(max((rows - 1) * stride + cols * 4, 4), dtype=np.uint8)
+    for i in range(rows):
+        work[i * stride:i * stride + cols * 4] = np.ascontiguousarray(c[i]).view(np.uint8)
+    if c.dtype == np.float32:
+        lib_fn_bf16(work.ctypes.data, rows, cols, stride)
+        return work[:rows * cols * 2].view(np.uint16).reshape(rows, cols).copy()
+    an, bn = np.ascontiguousarray(a_norms, dtype=np.int32), np.ascontiguousarray(b_norms, dtype=np.int32)
+    lib_fn_i8(work.ctypes.data, rows, cols, stride, an.ctypes.data, bn.ctypes.data)
+    return work[:rows * cols].view(np.int8).reshape(rows, cols).copy()
+
+
+def dots_compact(c: np.ndarray, a_norms=None, b_norms=None) -> np.ndarray:
+    """Down-cast of a dots matrix: f32 -> bf16 storage (uint16), or i32 -> i8 rescaled by 127 / (|a| |b|)."""
+    return _compact(_lib.orc_compact_bf16, _lib.orc_compact_i8, c, a_norms, b_norms)
 
 
 def sumsq(x: np.ndarray, dtype: str, depth: Optional[int] = None) -> np.ndarray:
@@ -231,6 +254,11 @@ class _Ref:
 
     def jaccards(self, a, b, dtype="u1", depth=None):
         return self.packed("jaccards", a, self.pack(b, "u1", depth=depth), np.asarray(b).shape[0], "u1", depth=depth)
+
+    def dots_compact(self, c, a_norms=None, b_norms=None):
+        u64, vp = ctypes.c_uint64, ctypes.c_void_p
+        return _compact(self._fn("dots_compact_bf16", None, [vp, u64, u64, u64]),
+                        self._fn("dots_compact_i8", None, [vp, u64, u64, u64, vp, vp]), c, a_norms, b_norms)
 
     def maxsim(self, q, d, dtype) -> float:
         q, d = _as_storage(q, dtype), _as_storage(d, dtype)

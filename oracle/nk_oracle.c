@@ -323,6 +323,36 @@ ORC_API void orc_sets(int kind, const void *a, uint64_t a_stride, const void *b,
     }
 }
 
+/* ---- in-place down-casts of a finished dots matrix ---------------------------------------------------
+ * include/numkong/dots/serial.h:2707-2724 (f32 -> bf16, rounding of include/numkong/cast/serial.h:768-784) and
+ * :2726-2754 (i32 -> i8 rescaled by 127 / (|a| |b|)). Rows are read `stride` bytes apart and written tightly packed
+ * from the first byte of the same buffer, row by row, cell by cell, so a cell is always read before it is overwritten.
+ */
+ORC_API void orc_compact_bf16(void *c, uint64_t rows, uint64_t cols, uint64_t stride) {
+    for (uint64_t i = 0; i < rows; ++i)
+        for (uint64_t j = 0; j < cols; ++j) {
+            uint32_t u; memcpy(&u, (const uint8_t *)c + i * stride + j * 4, 4);
+            u += 0x7FFFu + ((u >> 16) & 1u);
+            uint16_t h = (uint16_t)(u >> 16);
+            memcpy((uint8_t *)c + (i * cols + j) * 2, &h, 2);
+        }
+}
+
+ORC_API void orc_compact_i8(void *c, uint64_t rows, uint64_t cols, uint64_t stride, const int32_t *a_norms, const int32_t *b_norms) {
+    for (uint64_t i = 0; i < rows; ++i) {
+        float an = (float)a_norms[i], a_r = an > 0 ? 1.0f / sqrt_f32(an) : 0.0f;
+        for (uint64_t j = 0; j < cols; ++j) {
+            float bn = (float)b_norms[j], b_r = bn > 0 ? 1.0f / sqrt_f32(bn) : 0.0f;
+            int32_t v; memcpy(&v, (const uint8_t *)c + i * stride + j * 4, 4);
+            float scaled = (float)v * 127.0f * a_r * b_r;
+            int32_t q = (int32_t)scaled;
+            if (q < -128) q = -128;
+            if (q > 127) q = 127;
+            ((int8_t *)c)[i * cols + j] = (int8_t)q;
+        }
+    }
+}
+
 /* ---- MaxSim ------------------------------------------------------------------------------------
  * Inverse norm stored by pack: plain f32 running sum of v*v, then the bit-trick rsqrt, 0 for a zero
  * vector (include/numkong/maxsim/serial.h:122-141, :263).

@@ -52,6 +52,12 @@ REF_API void ref_jaccards_packed_u1(nk_u1x8_t const *a, void const *p, nk_f32_t 
     nk_jaccards_packed_u1_serial(a, p, c, m, n, k, as, cs);
 }
 
+/* in-place down-casts of a finished dots matrix (header-level helpers, not part of the dispatch table) */
+REF_API void ref_dots_compact_bf16(void *c, nk_size_t rows, nk_size_t cols, nk_size_t stride) { nk_dots_compact_bf16_serial(c, rows, cols, stride); }
+REF_API void ref_dots_compact_i8(void *c, nk_size_t rows, nk_size_t cols, nk_size_t stride, nk_i32_t const *an, nk_i32_t const *bn) {
+    nk_dots_compact_i8_serial(c, rows, cols, stride, an, bn);
+}
+
 #define REF_MAXSIM_FAMILY(T, IN, OUT)                                                                                \
     REF_API nk_size_t ref_maxsim_packed_size_##T(nk_size_t n, nk_size_t k) { return nk_maxsim_packed_size_##T##_serial(n, k); } \
     REF_API void ref_maxsim_pack_##T(IN const *v, nk_size_t n, nk_size_t k, nk_size_t s, void *p) {                   \

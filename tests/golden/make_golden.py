@@ -87,7 +87,38 @@ def main():
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "nibble_path.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
+    make_compact(serial)
+
+
+def make_compact(serial):
+    """compact_path.npz: the in-place down-casts of a dots matrix (f32 -> bf16, i32 -> i8 rescaled by the norms), from the
+    reference's scalar helpers. Matrices with padded rows included; an all-zero vector on each side of the i8 case."""
+    out = {}
+    for si, (m, n, k) in enumerate(SHAPES):
+        rng = np.random.default_rng(5000 + si)
+        a, b = rng.integers(-128, 128, (m, k), dtype=np.int8), rng.integers(-128, 128, (n, k), dtype=np.int8)
+        a[m // 2], b[n // 3] = 0, 0
+        b[0] = a[0]                                              # a pair with cosine 1: the rescaled cell sits at the clamp
+        c = np.zeros((m, n + si), dtype=np.int32)                # rows padded by `si` cells
+        c[:, :n] = a.astype(np.int32) @ b.astype(np.int32).T
+        an, bn = (a.astype(np.int32) ** 2).sum(1).astype(np.int32), (b.astype(np.int32) ** 2).sum(1).astype(np.int32)
+        key = f"i8_{m}x{n}x{k}"
+        out[key + "_c"], out[key + "_pad"], out[key + "_an"], out[key + "_bn"] = c, np.int64(si), an, bn
+        out[key + "_compact_serial"] = serial.dots_compact(c[:, :n], an, bn)
+        f = np.zeros((m, n + si), dtype=np.float32)
+        f[:, :n] = (rng.standard_normal((m, n)) * np.exp2(rng.integers(-30, 31, (m, n)))).astype(np.float32)
+        f[0, 0], f[m - 1, n - 1] = np.float32(np.inf), np.float32(-0.0)
+        f.view(np.uint32)[0, 1 % n] = 0x3F808000                 # exactly half way between two bf16 values: ties to even
+        key = f"bf16_{m}x{n}x{k}"
+        out[key + "_c"], out[key + "_pad"] = f, np.int64(si)
+        out[key + "_compact_serial"] = serial.dots_compact(f[:, :n])
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "compact_path.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
 
 
 if __name__ == "__main__":
-    main()
+    if "--only-compact" in sys.argv:
+        make_compact(oracle.ref_serial())
+    else:
+        main()

@@ -221,3 +221,34 @@ def test_f64_oracle_matches_reference_golden(shape):
     exact = np.array([[float(sum(__import__("fractions").Fraction(x) * __import__("fractions").Fraction(y) for x, y in zip(r, c)))
                        for c in b[:3]] for r in a[:3]])
     assert np.max(np.abs(oracle.dots(a, b, "f64")[:3, :3] - exact)) <= np.max(np.abs((a @ b.T)[:3, :3] - exact))
+
+
+COMPACT_GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "compact_path.npz"))
+
+
+@pytest.mark.parametrize("shape", GOLDEN_SHAPES)
+def test_compact_oracle_matches_reference_golden(shape):
+    """In-place down-casts of a dots matrix (f32 -> bf16, i32 -> i8 rescaled by the norms): bit for bit against the
+    reference's scalar helpers, padded rows, zero vectors, a cosine-1 pair and a rounding tie included."""
+    m, n, k = shape
+    for dt in ("i8", "bf16"):
+        key = f"{dt}_{m}x{n}x{k}"
+        c = COMPACT_GOLDEN[key + "_c"][:, :n]
+        assert c.strides[0] == (n + int(COMPACT_GOLDEN[key + "_pad"])) * 4
+        got = oracle.dots_compact(c, COMPACT_GOLDEN[key + "_an"], COMPACT_GOLDEN[key + "_bn"]) if dt == "i8" else oracle.dots_compact(c)
+        assert np.array_equal(got, COMPACT_GOLDEN[key + "_compact_serial"])
+    # the cosine-1 pair: 127, or 126 where the approximate reciprocal square roots leave the product just below 127
+    assert COMPACT_GOLDEN[f"i8_{m}x{n}x{k}_compact_serial"][0, 0] in (126, 127)
+
+
+def test_compact_oracle_against_live_reference():
+    serial = oracle.ref_serial()
+    if serial is None:
+        pytest.skip("reference not compiled here")
+    rng = np.random.default_rng(11)
+    a, b = rng.integers(-128, 128, (40, 96), dtype=np.int8), rng.integers(-128, 128, (70, 96), dtype=np.int8)
+    c = a.astype(np.int32) @ b.astype(np.int32).T
+    an, bn = (a.astype(np.int32) ** 2).sum(1).astype(np.int32), (b.astype(np.int32) ** 2).sum(1).astype(np.int32)
+    assert np.array_equal(oracle.dots_compact(c, an, bn), serial.dots_compact(c, an, bn))
+    f = (rng.standard_normal((40, 70)) * 1e4).astype(np.float32)
+    assert np.array_equal(oracle.dots_compact(f), serial.dots_compact(f))
