@@ -7,10 +7,10 @@
 // of the same buffer (row r of the result starts at byte r * columns * sizeof(out)).
 //
 // HBM bound: 4 bytes read and 2 (or 1) written per cell. The work is done in place, without a second matrix:
-// result row r lands inside source rows < r (for r >= 1), so the rows are converted in waves [1,2), [2,4), [4,8) ...
+// result row r lands inside source rows < r (for r >= 1), so rows are converted in waves [H,2H), [2H,4H), [4H,8H)
 // - one launch per wave; inside a wave no block writes what another block of the same or a later wave still has
-// to read, because the bytes written by rows [R, 2R) end where source row R begins. Row 0 overlaps itself and is
-// converted by a single block that finishes reading a chunk before it writes it.
+// to read, because the bytes written by rows [R, 2R) end where source row R begins. The head [0, H), H = rows / 8,
+// which holds the self-overlapping row 0, goes through a small staging buffer instead.
 #include <cstdio>
 #include <cstring>
 #include "nkb_internal.h"
@@ -59,61 +59,89 @@ __global__ void compact_factors_kernel(const int32_t *__restrict__ squared_norms
     factors[i] = factor;
 }
 
-// One wave of rows [row_begin, row_end), row_begin >= 1. A block converts 256 * kPer consecutive cells of one row.
-template <typename Convert, int kPer>
+// Converts rows [row_begin, row_begin + items / chunks_per_row) of the source matrix into tightly packed rows of
+// `destination` (row r of the source becomes row r - row_begin + destination_row). A block converts 2048 consecutive
+// cells of one row per step; kVec = 4 reads 16 bytes per thread and needs 16-byte aligned rows and columns % 4 == 0.
+template <typename Convert, int kVec>
 __global__ void __launch_bounds__(256)
-compact_rows_kernel(uint8_t *c, uint64_t stride, uint32_t columns, uint32_t row_begin, uint32_t chunks_per_row,
-                    uint64_t work_items, Convert convert) {
+compact_rows_kernel(const uint8_t *source_matrix, uint64_t stride, typename Convert::Out *destination, uint32_t columns,
+                    uint32_t row_begin, uint32_t destination_row, uint32_t chunks_per_row, uint64_t work_items, Convert convert) {
     using Out = typename Convert::Out;
+    constexpr int kChunk = 2048, kPer = kChunk / (256 * kVec);
     for (uint64_t item = blockIdx.x; item < work_items; item += gridDim.x) {
-        const uint32_t row = row_begin + (uint32_t)(item / chunks_per_row);
-        const uint32_t first = (uint32_t)(item % chunks_per_row) * (256u * kPer);
-        const uint32_t *source = reinterpret_cast<const uint32_t *>(c + (uint64_t)row * stride);
-        Out *destination = reinterpret_cast<Out *>(c) + (uint64_t)row * columns;
-        uint32_t bits[kPer];
+        const uint32_t local_row = (uint32_t)(item / chunks_per_row);
+        const uint32_t row = row_begin + local_row;
+        const uint32_t first = (uint32_t)(item % chunks_per_row) * kChunk;
+        const uint8_t *source = source_matrix + (uint64_t)row * stride;
+        Out *out_row = destination + (uint64_t)(destination_row + local_row) * columns;
+        if constexpr (kVec == 4) {
+            uint4 cells[kPer];
 #pragma unroll
-        for (int i = 0; i < kPer; ++i) {
-            const uint32_t column = first + i * 256u + threadIdx.x;
-            bits[i] = column < columns ? source[column] : 0u;
-        }
+            for (int i = 0; i < kPer; ++i) {
+                const uint32_t column = first + (i * 256u + threadIdx.x) * 4u;
+                cells[i] = column < columns ? *reinterpret_cast<const uint4 *>(source + (uint64_t)column * 4) : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-        for (int i = 0; i < kPer; ++i) {
-            const uint32_t column = first + i * 256u + threadIdx.x;
-            if (column < columns) destination[column] = convert(bits[i], row, column);
+            for (int i = 0; i < kPer; ++i) {
+                const uint32_t column = first + (i * 256u + threadIdx.x) * 4u;
+                if (column >= columns) continue;
+                const Out o0 = convert(cells[i].x, row, column), o1 = convert(cells[i].y, row, column + 1);
+                const Out o2 = convert(cells[i].z, row, column + 2), o3 = convert(cells[i].w, row, column + 3);
+                if constexpr (sizeof(Out) == 2) {
+                    *reinterpret_cast<uint2 *>(out_row + column) = make_uint2((uint32_t)(uint16_t)o0 | ((uint32_t)(uint16_t)o1 << 16),
+                                                                              (uint32_t)(uint16_t)o2 | ((uint32_t)(uint16_t)o3 << 16));
+                } else {
+                    *reinterpret_cast<uint32_t *>(out_row + column) = (uint32_t)(uint8_t)o0 | ((uint32_t)(uint8_t)o1 << 8) |
+                                                                      ((uint32_t)(uint8_t)o2 << 16) | ((uint32_t)(uint8_t)o3 << 24);
+                }
+            }
+        } else {
+            uint32_t bits[kPer];
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const uint32_t column = first + i * 256u + threadIdx.x;
+                bits[i] = column < columns ? reinterpret_cast<const uint32_t *>(source)[column] : 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const uint32_t column = first + i * 256u + threadIdx.x;
+                if (column < columns) out_row[column] = convert(bits[i], row, column);
+            }
         }
     }
 }
 
-// Row 0: the result overlaps its own source. One block; a chunk is read completely before any of it is written, and
-// the bytes a chunk writes lie before the start of the next chunk's source.
 template <typename Convert>
-__global__ void __launch_bounds__(1024) compact_first_row_kernel(uint8_t *c, uint32_t columns, Convert convert) {
-    using Out = typename Convert::Out;
-    const uint32_t *source = reinterpret_cast<const uint32_t *>(c);
-    Out *destination = reinterpret_cast<Out *>(c);
-    for (uint32_t first = 0; first < columns; first += 1024u) {
-        const uint32_t column = first + threadIdx.x;
-        const uint32_t bits = column < columns ? source[column] : 0u;
-        __syncthreads();
-        if (column < columns) destination[column] = convert(bits, 0u, column);
-        __syncthreads();
-    }
+bool launch_rows(const uint8_t *source, uint64_t stride, typename Convert::Out *destination, uint64_t columns, uint64_t row_begin,
+                 uint64_t row_end, uint64_t destination_row, bool vectors, Convert convert, cudaStream_t stream) {
+    const uint32_t chunks_per_row = (uint32_t)((columns + 2047) / 2048);
+    const uint64_t items = (row_end - row_begin) * chunks_per_row;
+    const unsigned grid = (unsigned)(items < 148ull * 16 ? items : 148ull * 16);
+    if (vectors)
+        compact_rows_kernel<Convert, 4><<<grid, 256, 0, stream>>>(source, stride, destination, (uint32_t)columns, (uint32_t)row_begin,
+                                                                  (uint32_t)destination_row, chunks_per_row, items, convert);
+    else
+        compact_rows_kernel<Convert, 1><<<grid, 256, 0, stream>>>(source, stride, destination, (uint32_t)columns, (uint32_t)row_begin,
+                                                                  (uint32_t)destination_row, chunks_per_row, items, convert);
+    g_launches++;
+    return cuda_ok(cudaGetLastError(), "compact kernel");
 }
 
+// The whole matrix, in place. The first eighth of the rows (the "head", which holds row 0 - the one row whose result
+// overlaps its own source) is converted into a staging buffer and copied back; the rest follows in doubling waves.
 template <typename Convert>
 bool compact_on_device(uint8_t *c, uint64_t rows, uint64_t columns, uint64_t stride, Convert convert, cudaStream_t stream) {
-    constexpr int kPer = 8;
-    compact_first_row_kernel<Convert><<<1, 1024, 0, stream>>>(c, (uint32_t)columns, convert);
-    g_launches++;
-    const uint32_t chunks_per_row = (uint32_t)((columns + 256 * kPer - 1) / (256 * kPer));
-    for (uint64_t begin = 1; begin < rows; begin *= 2) {
-        const uint64_t end = begin * 2 < rows ? begin * 2 : rows;
-        const uint64_t items = (end - begin) * chunks_per_row;
-        const unsigned grid = (unsigned)(items < 148ull * 16 ? items : 148ull * 16);
-        compact_rows_kernel<Convert, kPer><<<grid, 256, 0, stream>>>(c, stride, (uint32_t)columns, (uint32_t)begin, chunks_per_row, items, convert);
-        g_launches++;
-    }
-    return cuda_ok(cudaGetLastError(), "compact kernels");
+    using Out = typename Convert::Out;
+    const bool vectors = columns % 4 == 0 && stride % 16 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0;
+    const uint64_t head = (rows + 7) / 8;
+    Out *staging = static_cast<Out *>(scratch(kSlotAux2, head * columns * sizeof(Out)));
+    if (!staging) return false;
+    bool ok = launch_rows(c, stride, staging, columns, 0, head, 0, vectors, convert, stream) &&
+              cuda_ok(cudaMemcpyAsync(c, staging, head * columns * sizeof(Out), cudaMemcpyDeviceToDevice, stream), "compact: head copy");
+    for (uint64_t begin = head; ok && begin < rows; begin *= 2)
+        ok = launch_rows(c, stride, reinterpret_cast<Out *>(c), columns, begin, begin * 2 < rows ? begin * 2 : rows, begin, vectors,
+                         convert, stream);
+    return ok;
 }
 
 void compact_impl(bool to_i8, void *c, uint64_t rows, uint64_t columns, uint64_t stride, const int32_t *a_norms,
