@@ -155,6 +155,16 @@ NKB_API void nk_dots_compact_bf16(void *c, nk_size_t row_count, nk_size_t column
 NKB_API void nk_dots_compact_i8(void *c, nk_size_t row_count, nk_size_t column_count, nk_size_t c_stride_in_bytes,
                                 int32_t const *a_squared_norms, int32_t const *b_squared_norms);
 
+/* ---- Bulk type conversion ----------------------------------------------------------------------------
+ * replaces nk_cast (include/numkong/cast.h:55, dispatch c/numkong.c:770) with the rules of nk_cast_serial
+ * (include/numkong/cast/serial.h:2250-2311): `n` values of `from_type` become `n` values of `to_type`; every real
+ * scalar type of nk_dtype_t (f64 f32 f16 bf16 e4m3 e5m2 e2m3 e3m2, i8..i64, u8..u64, i4 u4 u1). Floats round to
+ * nearest even (e4m3 / e2m3 / e3m2 saturate, e5m2 and f16 overflow to infinity), integers saturate, float -> integer
+ * rounds to nearest even after clamping, NaN -> 0. u1 is most-significant-bit first and i4 / u4 keep the even index in
+ * the high nibble here. Host or device pointers. Pairs the reference leaves undefined (u1 -> signed integer, signed
+ * integer -> u4 / u1, complex types) set the error text and write nothing. */
+NKB_API void nk_cast(void const *from, uint32_t from_type, nk_size_t n, void *to, uint32_t to_type);
+
 /* ---- MaxSim late interaction -------------------------------------------------------------------
  * replaces include/numkong/maxsim.h:72-114 (wrappers c/numkong.c:738-765). Both sides are packed
  * with the same function. result: f32 for bf16/f16, f64 for f32 (maxsim.h:350-357):

@@ -29,7 +29,7 @@ __all__ = [
     "dots_symmetric", "angulars_symmetric", "euclideans_symmetric",
     "hammings_packed", "jaccards_packed", "hammings_symmetric", "jaccards_symmetric",
     "maxsim_pack", "maxsim_packed", "maxsim", "maxsims_packed", "angulars_packed_topk", "euclideans_packed_topk",
-    "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error",
+    "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error", "dots_compact", "cast",
 ]
 
 _NUMPY_NAMES = {
@@ -379,6 +379,58 @@ def dots_compact(c: Any, a_squared_norms: Any = None, b_squared_norms: Any = Non
         flat = v.obj.view(np.int8 if to_i8 else np.uint16)
         return np.lib.stride_tricks.as_strided(flat, shape=(v.rows, v.cols), strides=(v.cols * flat.itemsize, flat.itemsize))
     return None
+
+
+# ---- bulk type conversion -------------------------------------------------------------------------------------------
+CAST_CODES = dict(DTYPE_CODES, i16=1 << 3, i32=1 << 4, i64=1 << 5, u16=1 << 7, u32=1 << 8, u64=1 << 9)
+CAST_BITS = {"u1": 1, "i4": 4, "u4": 4, "i8": 8, "u8": 8, "e4m3": 8, "e5m2": 8, "e2m3": 8, "e3m2": 8, "i16": 16, "u16": 16,
+             "f16": 16, "bf16": 16, "i32": 32, "u32": 32, "f32": 32, "i64": 64, "u64": 64, "f64": 64}
+_CAST_NUMPY = {"i8": np.int8, "u8": np.uint8, "i16": np.int16, "u16": np.uint16, "i32": np.int32, "u32": np.uint32, "i64": np.int64,
+               "u64": np.uint64, "f16": np.float16, "f32": np.float32, "f64": np.float64, "bf16": np.uint16}
+_CAST_TORCH = {"i8": "int8", "u8": "uint8", "i16": "int16", "u16": "uint16", "i32": "int32", "u32": "uint32", "i64": "int64",
+               "u64": "uint64", "f16": "float16", "f32": "float32", "f64": "float64", "bf16": "bfloat16", "e4m3": "float8_e4m3fn",
+               "e5m2": "float8_e5m2"}
+_CAST_NAMES = {"int16": "i16", "uint16": "u16", "int32": "i32", "uint32": "u32", "int64": "i64", "uint64": "u64"}
+
+
+def cast(x: Any, to_dtype: str, *, dtype: Optional[str] = None, count: Optional[int] = None, out: Any = None):
+    """Converts the values of a contiguous array to another element type with the rules of the reference's nk_cast
+    (include/numkong/cast.h:55, scalar back end include/numkong/cast/serial.h:2250-2311). `dtype` names the source type
+    where the storage cannot (bf16 / fp8 / fp6 words, packed i4 / u4 / u1 bytes); `count` is the number of VALUES
+    (default: all the storage holds). NumPy in, NumPy out; CUDA tensor in, CUDA tensor out. Types NumPy or torch cannot
+    name come back as uint8 / uint16 storage."""
+    is_torch = _is_torch(x)
+    if not is_torch:
+        x = np.asarray(x)
+    name = dtype or (_TORCH_NAMES.get(str(x.dtype)) or _CAST_NAMES.get(str(x.dtype).replace("torch.", "")) if is_torch
+                     else _NUMPY_NAMES.get(x.dtype.name) or _CAST_NAMES.get(x.dtype.name))
+    if name not in CAST_CODES or to_dtype not in CAST_CODES:
+        raise TypeError(f"cannot cast {name!r} to {to_dtype!r}")
+    contiguous = x.is_contiguous() if is_torch else x.flags.c_contiguous
+    if not contiguous:
+        raise ValueError("cast needs a contiguous array")
+    nbytes = x.numel() * x.element_size() if is_torch else x.nbytes
+    n = int(count) if count is not None else nbytes * 8 // CAST_BITS[name]
+    if n * CAST_BITS[name] > nbytes * 8:
+        raise ValueError("count exceeds what the array holds")
+    out_bytes = (n * CAST_BITS[to_dtype] + 7) // 8
+    if out is None:
+        if is_torch:
+            import torch
+            tdt = getattr(torch, _CAST_TORCH.get(to_dtype, "uint8"))
+            shape = tuple(x.shape) if (CAST_BITS[to_dtype] >= 8 and count is None and CAST_BITS[name] >= 8) else (out_bytes * 8 // max(CAST_BITS[to_dtype], 8),)
+            out = torch.empty(shape, dtype=tdt, device=x.device)
+        else:
+            ndt = _CAST_NUMPY.get(to_dtype, np.uint8)
+            shape = x.shape if (CAST_BITS[to_dtype] >= 8 and count is None and CAST_BITS[name] >= 8) else (out_bytes * 8 // max(CAST_BITS[to_dtype], 8),)
+            out = np.empty(shape, dtype=ndt)
+    else:
+        have = out.numel() * out.element_size() if _is_torch(out) else out.nbytes
+        if have < out_bytes or not (out.is_contiguous() if _is_torch(out) else out.flags.c_contiguous):
+            raise ValueError("out is too small or not contiguous")
+    lib.nk_cast(_ptr(x), CAST_CODES[name], n, _ptr(out), CAST_CODES[to_dtype])
+    check("cast")
+    return out
 
 
 def maxsim_pack(vectors: Any, dtype: Optional[str] = None) -> MaxSimPackedMatrix:

@@ -72,6 +72,7 @@ def _load() -> ctypes.CDLL:
     for t in ("bf16", "f16"):
         f = getattr(lib, f"nkb_maxsims_packed_{t}")
         f.restype, f.argtypes = None, [vp, vp, sz, vp, vp, sz, sz, vp, sz]
+    lib.nk_cast.restype, lib.nk_cast.argtypes = None, [vp, ctypes.c_uint32, sz, vp, ctypes.c_uint32]
     lib.nk_dots_compact_bf16.restype, lib.nk_dots_compact_bf16.argtypes = None, [vp, sz, sz, sz]
     lib.nk_dots_compact_i8.restype, lib.nk_dots_compact_i8.argtypes = None, [vp, sz, sz, sz, vp, vp]
     lib.nkb_topk_smallest_f32.restype = None

@@ -133,3 +133,37 @@ def lognormal_matrix(rows: int, cols: int, dtype: str, seed: int) -> np.ndarray:
     if dtype in ("i8", "u8"):
         x = np.minimum(x * 16, 127)
     return encode(x, dtype)
+
+
+# Values every float source of a conversion test starts with: zeros, rounding ties of the integer targets, the largest
+# values and rounding ties of the small float formats, a binary16 underflow tie, an f32 subnormal, large magnitudes.
+_CAST_SPECIALS = [0.0, -0.0, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 126.5, 127.5, -128.5, 254.5, 255.5, 448.0, 464.0, 480.0, -464.0,
+                  57344.0, 61440.0, 61439.0, 7.5, 7.75, 7.25, 28.0, 30.0, 26.0, 65504.0, 65520.0, 65519.0, 2.0 ** -25, 2.0 ** -24 * 1.5,
+                  1e-40, 0.0009765625, 0.001953125 * 1.5, 3e9, -3e9, 1e30, -1e30, 32767.5, -32768.5, 65535.5, 15.9, -8.9, 0.9]
+
+
+def cast_samples(dtype: str, n: int, seed: int) -> np.ndarray:
+    """Storage of `n` finite values of `dtype` for conversion tests: floats spread over forty binades behind the list of
+    special cases above, 16-bit and smaller floats as uniformly random finite codes, integers half full-range and half
+    small, sub-byte types as random bytes."""
+    rng = np.random.default_rng(seed)
+    if dtype in ("f64", "f32"):
+        v = rng.standard_normal(n) * np.exp2(rng.integers(-20, 20, n))
+        k = min(n, len(_CAST_SPECIALS))
+        v[:k] = _CAST_SPECIALS[:k]
+        return v if dtype == "f64" else v.astype(np.float32)
+    if dtype in ("f16", "bf16"):
+        v = rng.integers(0, 65536, n).astype(np.uint16)
+        all_ones = 0x7C00 if dtype == "f16" else 0x7F80
+        v[(v & all_ones) == all_ones] &= np.uint16(0xBFFF)   # clear one exponent bit of infinities and NaN
+        return v
+    if dtype in ("e4m3", "e5m2", "e2m3", "e3m2"):
+        return finite_codes_matrix(1, n, dtype, seed, max_abs=1e9).ravel()
+    if dtype in ("i4", "u4", "u1"):
+        return rng.integers(0, 256, (n * (1 if dtype == "u1" else 4) + 7) // 8).astype(np.uint8)
+    storage = {"i8": np.int8, "u8": np.uint8, "i16": np.int16, "u16": np.uint16, "i32": np.int32, "u32": np.uint32,
+               "i64": np.int64, "u64": np.uint64}[dtype]
+    info = np.iinfo(storage)
+    v = rng.integers(info.min, info.max, n, dtype=storage, endpoint=True)
+    v[: n // 2] = rng.integers(max(info.min, -300), min(info.max, 300), n // 2).astype(storage)
+    return v

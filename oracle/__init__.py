@@ -26,6 +26,26 @@ STORAGE = {"i8": np.int8, "u8": np.uint8, "f32": np.float32, "f16": np.uint16, "
            "e4m3": np.uint8, "e5m2": np.uint8, "e2m3": np.uint8, "e3m2": np.uint8, "i4": np.uint8, "u4": np.uint8, "u1": np.uint8, "f64": np.float64}
 
 
+# Every real type nk_cast converts (numerically nk_dtype_t), bits per value, NumPy storage of a buffer of them.
+CAST_CODES = dict(CODES, i16=1 << 3, i32=1 << 4, i64=1 << 5, u16=1 << 7, u32=1 << 8, u64=1 << 9)
+CAST_BITS = {"u1": 1, "i4": 4, "u4": 4, "i8": 8, "u8": 8, "e4m3": 8, "e5m2": 8, "e2m3": 8, "e3m2": 8, "i16": 16, "u16": 16, "f16": 16,
+             "bf16": 16, "i32": 32, "u32": 32, "f32": 32, "i64": 64, "u64": 64, "f64": 64}
+CAST_STORAGE = dict(STORAGE, i16=np.int16, i32=np.int32, i64=np.int64, u16=np.uint16, u32=np.uint32, u64=np.uint64)
+
+
+def _cast_with(fn, x: np.ndarray, from_dtype: str, to_dtype: str, n: Optional[int]) -> np.ndarray:
+    x = np.ascontiguousarray(x)
+    n = int(n) if n is not None else x.nbytes * 8 // CAST_BITS[from_dtype]
+    out = np.zeros(max((n * CAST_BITS[to_dtype] + 7) // 8, 1) + 8, dtype=np.uint8)   # slack: the reference writes whole batches
+    fn(x.ctypes.data, CAST_CODES[from_dtype], n, out.ctypes.data, CAST_CODES[to_dtype])
+    return out[:(n * CAST_BITS[to_dtype] + 7) // 8].view(CAST_STORAGE[to_dtype]).copy()
+
+
+def cast(x: np.ndarray, from_dtype: str, to_dtype: str, n: Optional[int] = None) -> np.ndarray:
+    """Bulk conversion of `n` values (default: all of `x`) with the reference's rules; returns the result's storage."""
+    return _cast_with(_lib.orc_cast, x, from_dtype, to_dtype, n)
+
+
 def _depth(x: np.ndarray, dtype: str, depth: Optional[int]) -> int:
     """Logical dimensions of a row: 4-bit types hold two per byte (an explicit `depth` may be odd)."""
     return int(depth) if depth is not None else x.shape[1] * {"i4": 2, "u4": 2, "u1": 8}.get(dtype, 1)
@@ -56,6 +76,7 @@ def _load() -> ctypes.CDLL:
     lib.orc_sumsq.restype, lib.orc_sumsq.argtypes = ctypes.c_double, [i32, vp, u64]
     lib.orc_sets.restype, lib.orc_sets.argtypes = None, [i32, vp, u64, vp, u64, vp, u64, u64, u64, u64]
     lib.orc_rsqrt_f32.restype, lib.orc_rsqrt_f32.argtypes = ctypes.c_float, [ctypes.c_float]
+    lib.orc_cast.restype, lib.orc_cast.argtypes = ctypes.c_int, [vp, i32, u64, vp, i32]
     lib.orc_compact_bf16.restype, lib.orc_compact_bf16.argtypes = None, [vp, u64, u64, u64]
     lib.orc_compact_i8.restype, lib.orc_compact_i8.argtypes = None, [vp, u64, u64, u64, vp, vp]
     for name in ("orc_maxsim_argmax_dot", "orc_maxsim_coarse_i8"):
@@ -259,6 +280,10 @@ class _Ref:
         u64, vp = ctypes.c_uint64, ctypes.c_void_p
         return _compact(self._fn("dots_compact_bf16", None, [vp, u64, u64, u64]),
                         self._fn("dots_compact_i8", None, [vp, u64, u64, u64, vp, vp]), c, a_norms, b_norms)
+
+    def cast(self, x, from_dtype, to_dtype, n=None):
+        u64, vp = ctypes.c_uint64, ctypes.c_void_p
+        return _cast_with(self._fn("cast", None, [vp, ctypes.c_int, u64, vp, ctypes.c_int]), x, from_dtype, to_dtype, n)
 
     def maxsim(self, q, d, dtype) -> float:
         q, d = _as_storage(q, dtype), _as_storage(d, dtype)

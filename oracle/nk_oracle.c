@@ -487,3 +487,232 @@ ORC_API double orc_maxsim_coarse_i8(int dt, const void *q, uint64_t q_stride, ui
 
 /* ---- multi-threaded driver for the CPU-baseline timing (rows of A split across threads, as the
  * reference's callers do: README.md:199-212) is in Python (threads release the GIL inside ctypes). */
+
+/* ---- bulk type conversion --------------------------------------------------------------------------
+ * Restates nk_cast_serial (include/numkong/cast/serial.h:2250-2311): equal types are copied; two unsigned
+ * integer types go through u64, two integer types with a signed one through i64, everything else through f64.
+ * Values travel in batches of eight. Sub-byte conventions of the cast (cast/serial.h:1846-1871, :1966-1995):
+ * u1 is most-significant-bit first, i4 / u4 keep the even index in the HIGH nibble - unlike the dots family.
+ *
+ * Narrowing rules restated:
+ *   float -> f32: C cast of the f64 hub value; -> f16 / bf16 / e4m3 / e5m2 / e2m3 / e3m2: that f32, then round to
+ *     nearest even onto the format's grid. e4m3 saturates at +-448 (infinity too) and keeps NaN as 0x7F | sign
+ *     (cast/serial.h:866-943); e5m2 overflows to infinity, NaN is 0x7D | sign (:1108-1188); e2m3 / e3m2 saturate
+ *     at +-7.5 / +-28, NaN included (:1340-1416, :1481-1560); f16 is IEEE (:669-741), bf16 too (:768-784).
+ *   float -> integer: NaN gives 0, the value is clamped to the target range and rounded to nearest even
+ *     (cast/serial.h:1583-1666). float -> i4 / u4: clamped, then truncated toward zero (:1973-1995); float -> u1:
+ *     non-zero gives 1.
+ *   integer -> integer: saturating; a u64 source that meets a signed type is first reinterpreted as i64
+ *     (cast/serial.h:2043-2046), so values >= 2^63 come out as the target's minimum.
+ * Pairs the reference leaves undefined (u1 -> signed integers; signed integers -> u4 / u1; complex types)
+ * return 0 and write nothing. Tails: only whole result bytes that hold a converted value are written, missing
+ * values of a partial sub-byte batch count as 0.
+ */
+enum { ORC_I16 = 1 << 3, ORC_I32 = 1 << 4, ORC_I64 = 1 << 5, ORC_U16 = 1 << 7, ORC_U32 = 1 << 8, ORC_U64 = 1 << 9 };
+enum { FAMILY_NONE = 0, FAMILY_FLOAT, FAMILY_INT, FAMILY_UINT };
+
+static int cast_family(int dt) {
+    switch (dt) {
+    case ORC_F64: case ORC_F32: case ORC_F16: case ORC_BF16: case ORC_E4M3: case ORC_E5M2: case ORC_E2M3: case ORC_E3M2: return FAMILY_FLOAT;
+    case ORC_I4: case ORC_I8: case ORC_I16: case ORC_I32: case ORC_I64: return FAMILY_INT;
+    case ORC_U1: case ORC_U4: case ORC_U8: case ORC_U16: case ORC_U32: case ORC_U64: return FAMILY_UINT;
+    default: return FAMILY_NONE;
+    }
+}
+static int cast_bits(int dt) {
+    switch (dt) {
+    case ORC_F64: case ORC_I64: case ORC_U64: return 64;
+    case ORC_F32: case ORC_I32: case ORC_U32: return 32;
+    case ORC_F16: case ORC_BF16: case ORC_I16: case ORC_U16: return 16;
+    case ORC_I4: case ORC_U4: return 4;
+    case ORC_U1: return 1;
+    default: return cast_family(dt) == FAMILY_NONE ? 0 : 8;
+    }
+}
+
+/* Round-to-nearest-even of an f32 onto a small binary format: `man_bits` fraction bits, exponent `bias`; returns the
+ * magnitude code, possibly above the format's largest one (the caller applies the overflow rule). */
+static uint32_t round_to_grid(uint32_t abs_bits, int man_bits, int bias) {
+    int e = (int)(abs_bits >> 23) - 127, emin = 1 - bias;
+    if ((abs_bits >> 23) == 0) return 0;                       /* f32 subnormals are far below every grid */
+    uint32_t sig = 0x800000u | (abs_bits & 0x7fffffu);
+    int shift = 23 - man_bits + (e < emin ? emin - e : 0);
+    uint32_t r = 0;
+    if (shift <= 24) {
+        uint32_t rem = sig & ((1u << shift) - 1), half = 1u << (shift - 1);
+        r = sig >> shift;
+        if (rem > half || (rem == half && (r & 1))) ++r;
+    }
+    return ((uint32_t)(e < emin ? 0 : e - emin) << man_bits) + r;
+}
+
+static uint16_t enc_f16(float x) {
+    uint32_t u = f32_to_bits(x), sign = (u >> 16) & 0x8000u, a = u & 0x7fffffffu;
+    if (a > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);
+    if (a == 0x7f800000u || (int)(a >> 23) - 127 > 16) return (uint16_t)(sign | 0x7c00u);
+    uint32_t code = round_to_grid(a, 10, 15);
+    return (uint16_t)(sign | (code > 0x7c00u ? 0x7c00u : code));
+}
+static uint16_t enc_bf16(float x) {
+    uint32_t u = f32_to_bits(x);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40u);
+    return (uint16_t)((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
+}
+static uint8_t enc_e4m3(float x) {
+    uint32_t u = f32_to_bits(x), sign = (u >> 24) & 0x80u, a = u & 0x7fffffffu;
+    if (a > 0x7f800000u) return (uint8_t)(sign | 0x7fu);
+    if ((int)(a >> 23) - 127 > 9) return (uint8_t)(sign | 0x7eu);
+    uint32_t code = round_to_grid(a, 3, 7);
+    return (uint8_t)(sign | (code > 0x7eu ? 0x7eu : code));
+}
+static uint8_t enc_e5m2(float x) {
+    uint32_t u = f32_to_bits(x), sign = (u >> 24) & 0x80u, a = u & 0x7fffffffu;
+    if (a > 0x7f800000u) return (uint8_t)(sign | 0x7du);
+    if ((int)(a >> 23) - 127 > 16) return (uint8_t)(sign | 0x7cu);
+    uint32_t code = round_to_grid(a, 2, 15);
+    return (uint8_t)(sign | (code > 0x7cu ? 0x7cu : code));
+}
+static uint8_t enc_fp6(float x, int man_bits, int bias) {
+    uint32_t u = f32_to_bits(x), sign = (u >> 26) & 0x20u, a = u & 0x7fffffffu;
+    if ((int)(a >> 23) - 127 > 5) return (uint8_t)(sign | 0x1fu);   /* far above the range, infinities and NaN */
+    uint32_t code = round_to_grid(a, man_bits, bias);
+    return (uint8_t)(sign | (code > 0x1fu ? 0x1fu : code));
+}
+
+static double rint_even(double x) {  /* cast/serial.h:1583-1596, for |x| < 2^63 */
+    double t = trunc(x), f = x - t;
+    if (f > 0.5 || (f == 0.5 && fmod(t, 2.0) != 0.0)) return t + 1.0;
+    if (f < -0.5 || (f == -0.5 && fmod(t, 2.0) != 0.0)) return t - 1.0;
+    return t;
+}
+static double clamp_f64(double x, double lo, double hi) { return x > hi ? hi : (x < lo ? lo : x); }
+
+static double load_f64(int dt, const uint8_t *p) {
+    switch (dt) {
+    case ORC_F64: { double v; memcpy(&v, p, 8); return v; }
+    case ORC_I64: { int64_t v; memcpy(&v, p, 8); return (double)v; }
+    case ORC_U64: { uint64_t v; memcpy(&v, p, 8); return (double)v; }
+    case ORC_I32: { int32_t v; memcpy(&v, p, 4); return (double)v; }
+    case ORC_U32: { uint32_t v; memcpy(&v, p, 4); return (double)v; }
+    case ORC_I16: { int16_t v; memcpy(&v, p, 2); return (double)v; }
+    case ORC_U16: { uint16_t v; memcpy(&v, p, 2); return (double)v; }
+    default: return (double)dec(dt, p);   /* f32 and the small floats (through f32), i8, u8 */
+    }
+}
+static void store_f64(int dt, double v, uint8_t *p) {
+    float f = (float)v;
+    switch (dt) {
+    case ORC_F64: memcpy(p, &v, 8); break;
+    case ORC_F32: memcpy(p, &f, 4); break;
+    case ORC_F16: { uint16_t h = enc_f16(f); memcpy(p, &h, 2); } break;
+    case ORC_BF16: { uint16_t h = enc_bf16(f); memcpy(p, &h, 2); } break;
+    case ORC_E4M3: p[0] = enc_e4m3(f); break;
+    case ORC_E5M2: p[0] = enc_e5m2(f); break;
+    case ORC_E2M3: p[0] = enc_fp6(f, 3, 1); break;
+    case ORC_E3M2: p[0] = enc_fp6(f, 2, 3); break;
+    case ORC_I8: { int8_t o = v != v ? 0 : (int8_t)rint_even(clamp_f64(v, -128.0, 127.0)); memcpy(p, &o, 1); } break;
+    case ORC_U8: { uint8_t o = v != v ? 0 : (uint8_t)rint_even(clamp_f64(v, 0.0, 255.0)); memcpy(p, &o, 1); } break;
+    case ORC_I16: { int16_t o = v != v ? 0 : (int16_t)rint_even(clamp_f64(v, -32768.0, 32767.0)); memcpy(p, &o, 2); } break;
+    case ORC_U16: { uint16_t o = v != v ? 0 : (uint16_t)rint_even(clamp_f64(v, 0.0, 65535.0)); memcpy(p, &o, 2); } break;
+    case ORC_I32: { int32_t o = v != v ? 0 : (int32_t)rint_even(clamp_f64(v, -2147483648.0, 2147483647.0)); memcpy(p, &o, 4); } break;
+    case ORC_U32: { uint32_t o = v != v ? 0 : (uint32_t)rint_even(clamp_f64(v, 0.0, 4294967295.0)); memcpy(p, &o, 4); } break;
+    case ORC_I64: {  /* values at or beyond +-2^63 saturate (the reference leaves the upper end to the C cast) */
+        int64_t o = v != v ? 0 : v >= 9223372036854775808.0 ? INT64_MAX : v <= -9223372036854775808.0 ? INT64_MIN : (int64_t)rint_even(v);
+        memcpy(p, &o, 8);
+    } break;
+    case ORC_U64: {
+        uint64_t o = v != v || v <= 0 ? 0 : v >= 18446744073709551616.0 ? UINT64_MAX
+                     : (v < 9007199254740992.0 ? (uint64_t)rint_even(v) : (uint64_t)v);
+        memcpy(p, &o, 8);
+    } break;
+    }
+}
+static int64_t load_i64(int dt, const uint8_t *p) {
+    switch (dt) {
+    case ORC_I64: case ORC_U64: { int64_t v; memcpy(&v, p, 8); return v; }   /* u64: reinterpreted */
+    case ORC_I32: { int32_t v; memcpy(&v, p, 4); return v; }
+    case ORC_U32: { uint32_t v; memcpy(&v, p, 4); return v; }
+    case ORC_I16: { int16_t v; memcpy(&v, p, 2); return v; }
+    case ORC_U16: { uint16_t v; memcpy(&v, p, 2); return v; }
+    case ORC_I8: return (int8_t)p[0];
+    default: return p[0];
+    }
+}
+static int64_t clamp_i64(int64_t x, int64_t lo, int64_t hi) { return x > hi ? hi : (x < lo ? lo : x); }
+static void store_i64(int dt, int64_t v, uint8_t *p) {
+    switch (dt) {
+    case ORC_I64: memcpy(p, &v, 8); break;
+    case ORC_U64: { uint64_t o = v < 0 ? 0 : (uint64_t)v; memcpy(p, &o, 8); } break;
+    case ORC_I32: { int32_t o = (int32_t)clamp_i64(v, INT32_MIN, INT32_MAX); memcpy(p, &o, 4); } break;
+    case ORC_U32: { uint32_t o = (uint32_t)clamp_i64(v, 0, UINT32_MAX); memcpy(p, &o, 4); } break;
+    case ORC_I16: { int16_t o = (int16_t)clamp_i64(v, INT16_MIN, INT16_MAX); memcpy(p, &o, 2); } break;
+    case ORC_U16: { uint16_t o = (uint16_t)clamp_i64(v, 0, UINT16_MAX); memcpy(p, &o, 2); } break;
+    case ORC_I8: { int8_t o = (int8_t)clamp_i64(v, INT8_MIN, INT8_MAX); memcpy(p, &o, 1); } break;
+    case ORC_U8: p[0] = (uint8_t)clamp_i64(v, 0, UINT8_MAX); break;
+    }
+}
+static uint64_t load_u64(int dt, const uint8_t *p) {
+    switch (dt) {
+    case ORC_U64: { uint64_t v; memcpy(&v, p, 8); return v; }
+    case ORC_U32: { uint32_t v; memcpy(&v, p, 4); return v; }
+    case ORC_U16: { uint16_t v; memcpy(&v, p, 2); return v; }
+    default: return p[0];
+    }
+}
+static void store_u64(int dt, uint64_t v, uint8_t *p) {
+    switch (dt) {
+    case ORC_U64: memcpy(p, &v, 8); break;
+    case ORC_U32: { uint32_t o = v > UINT32_MAX ? UINT32_MAX : (uint32_t)v; memcpy(p, &o, 4); } break;
+    case ORC_U16: { uint16_t o = v > UINT16_MAX ? UINT16_MAX : (uint16_t)v; memcpy(p, &o, 2); } break;
+    case ORC_U8: p[0] = v > UINT8_MAX ? UINT8_MAX : (uint8_t)v; break;
+    }
+}
+
+ORC_API int orc_cast(const void *from, int from_type, uint64_t n, void *to, int to_type) {
+    const int from_family = cast_family(from_type), to_family = cast_family(to_type);
+    const int from_bits = cast_bits(from_type), to_bits = cast_bits(to_type);
+    if (!from_family || !to_family) return 0;
+    if (from_type == to_type) { memcpy(to, from, (n * (uint64_t)from_bits + 7) / 8); return 1; }
+    const int hub = (from_family == FAMILY_UINT && to_family == FAMILY_UINT) ? FAMILY_UINT
+                    : (from_family != FAMILY_FLOAT && to_family != FAMILY_FLOAT) ? FAMILY_INT : FAMILY_FLOAT;
+    if (hub == FAMILY_INT && (from_type == ORC_U1 || to_type == ORC_U4 || to_type == ORC_U1)) return 0;
+    const uint8_t *src = (const uint8_t *)from;
+    uint8_t *dst = (uint8_t *)to;
+    for (uint64_t first = 0; first < n; first += 8) {
+        const int count = n - first < 8 ? (int)(n - first) : 8;
+        const uint8_t *s = src + first * (uint64_t)from_bits / 8;
+        uint8_t *d = dst + first * (uint64_t)to_bits / 8;
+        double f[8] = {0}; int64_t i[8] = {0}; uint64_t u[8] = {0};
+        for (int l = 0; l < count; ++l) {
+            int64_t small = 0;   /* value of a sub-byte source element */
+            if (from_type == ORC_U1) small = (s[0] >> (7 - l)) & 1;
+            else if (from_type == ORC_U4) small = (l & 1) ? (s[l / 2] & 0xF) : (s[l / 2] >> 4);
+            else if (from_type == ORC_I4) { small = (l & 1) ? (s[l / 2] & 0xF) : (s[l / 2] >> 4); small = (small ^ 8) - 8; }
+            if (from_bits < 8) f[l] = (double)small, i[l] = small, u[l] = (uint64_t)small;
+            else if (hub == FAMILY_FLOAT) f[l] = load_f64(from_type, s + l * (from_bits / 8));
+            else if (hub == FAMILY_INT) i[l] = load_i64(from_type, s + l * (from_bits / 8));
+            else u[l] = load_u64(from_type, s + l * (from_bits / 8));
+        }
+        if (to_bits >= 8) {
+            for (int l = 0; l < count; ++l) {
+                uint8_t *cell = d + l * (to_bits / 8);
+                if (hub == FAMILY_FLOAT) store_f64(to_type, f[l], cell);
+                else if (hub == FAMILY_INT) store_i64(to_type, i[l], cell);
+                else store_u64(to_type, u[l], cell);
+            }
+            continue;
+        }
+        uint8_t bytes[4] = {0, 0, 0, 0};
+        for (int l = 0; l < count; ++l) {
+            if (to_type == ORC_U1) bytes[0] |= (uint8_t)((hub == FAMILY_FLOAT ? f[l] != 0 : u[l] != 0) << (7 - l));
+            else {
+                int64_t v;
+                if (to_type == ORC_I4) v = hub == FAMILY_FLOAT ? (int64_t)(int8_t)clamp_f64(f[l], -8.0, 7.0) : clamp_i64(i[l], -8, 7);
+                else v = hub == FAMILY_FLOAT ? (int64_t)(uint8_t)clamp_f64(f[l], 0.0, 15.0) : (int64_t)(u[l] > 15 ? 15 : u[l]);
+                bytes[l / 2] |= (uint8_t)((v & 0xF) << ((l & 1) ? 0 : 4));
+            }
+        }
+        memcpy(d, bytes, ((uint64_t)count * (uint64_t)to_bits + 7) / 8);
+    }
+    return 1;
+}

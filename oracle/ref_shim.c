@@ -58,6 +58,9 @@ REF_API void ref_dots_compact_i8(void *c, nk_size_t rows, nk_size_t cols, nk_siz
     nk_dots_compact_i8_serial(c, rows, cols, stride, an, bn);
 }
 
+/* bulk type conversion, scalar back end */
+REF_API void ref_cast(void const *from, int from_type, nk_size_t n, void *to, int to_type) { nk_cast_serial(from, (nk_dtype_t)from_type, n, to, (nk_dtype_t)to_type); }
+
 #define REF_MAXSIM_FAMILY(T, IN, OUT)                                                                                \
     REF_API nk_size_t ref_maxsim_packed_size_##T(nk_size_t n, nk_size_t k) { return nk_maxsim_packed_size_##T##_serial(n, k); } \
     REF_API void ref_maxsim_pack_##T(IN const *v, nk_size_t n, nk_size_t k, nk_size_t s, void *p) {                   \

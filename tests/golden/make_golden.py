@@ -88,6 +88,7 @@ def main():
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
     make_compact(serial)
+    make_cast(serial)
 
 
 def make_compact(serial):
@@ -117,8 +118,33 @@ def make_compact(serial):
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
 
 
+CAST_TYPES = ["f64", "f32", "f16", "bf16", "e4m3", "e5m2", "e2m3", "e3m2", "i8", "i16", "i32", "i64", "u8", "u16", "u32", "u64", "i4", "u4", "u1"]
+
+
+def cast_pair_defined(a: str, b: str) -> bool:
+    """Pairs of the bulk conversion the reference defines (its integer hub has no u1 source and no u4 / u1 target)."""
+    signed = ("i8", "i16", "i32", "i64", "i4")
+    return not ((a == "u1" and b in signed) or (a in signed and b in ("u4", "u1")))
+
+
+def make_cast(serial):
+    """cast_path.npz: nk_cast_serial on 136 values (seventeen whole batches) of every source type to every target type."""
+    out = {}
+    for si, a in enumerate(CAST_TYPES):
+        x = syn.cast_samples(a, 136, 6000 + si)
+        out["from_" + a] = x
+        for b in CAST_TYPES:
+            if a != b and cast_pair_defined(a, b):
+                out[f"{a}_to_{b}"] = serial.cast(x, a, b, 136)
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cast_path.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
+
+
 if __name__ == "__main__":
     if "--only-compact" in sys.argv:
         make_compact(oracle.ref_serial())
+    elif "--only-cast" in sys.argv:
+        make_cast(oracle.ref_serial())
     else:
         main()
