@@ -16,8 +16,10 @@
 // refused: the error text is set and nothing is written. A partial last batch writes only the bytes that hold
 // converted values; the missing values of a partial sub-byte batch count as 0. NaN payloads are not preserved.
 //
-// HBM bound. One thread converts one batch: it reads the batch's `from_bits` bytes (1 to 64) with 16-byte accesses
-// where the pointers allow, decodes into eight 64-bit hub registers, encodes, and writes `to_bits` bytes.
+// HBM bound. General kernel: one thread converts one batch - it reads the batch's `from_bits` bytes (1 to 64) with
+// 16-byte accesses where the pointers allow, decodes into eight 64-bit hub registers, encodes, and writes `to_bits`
+// bytes. Pairs of types of at most 32 bits with a float among them (the quantisation pairs: f32 / f16 / bf16 / fp8 /
+// fp6 / i8 / u8) take a kernel compiled for the pair, with f32 in the middle and fully coalesced 16-byte vectors.
 #include <cstdio>
 #include <cstring>
 #include <cuda_fp16.h>
@@ -304,6 +306,224 @@ cast_kernel(const uint8_t *__restrict__ from, uint8_t *__restrict__ to, uint64_t
     }
 }
 
+// ---- fast path: both types at most 32 bits wide and at least one of them a float ------------------------------------
+// Such a pair never needs more than f32 in the middle: every source value is exactly an f32, and the reference narrows
+// the f64 hub value to f32 before it encodes a small float anyway; for the 8-bit integer targets clamping and rounding
+// an f32 gives what clamping and rounding its f64 image gives. With both types known at compile time a thread moves one
+// 16-byte vector of the wider type per step and every access of a warp is contiguous.
+// Two f32 values to two 8-bit codes with the conversion unit (round to nearest even, saturating to the largest finite
+// value): low byte = first value. The reference's rules that differ from the instruction's are patched per value:
+// a NaN keeps its sign (0x7F / 0x7D / largest value), and e5m2 overflows to infinity from the rounding boundary 61440 on.
+#define NKB_HW_PAIR(NAME, FORMAT)                                                                          \
+    __device__ __forceinline__ uint32_t NAME(float first, float second) {                                  \
+        unsigned short packed;                                                                             \
+        asm("cvt.rn.satfinite." FORMAT ".f32 %0, %1, %2;" : "=h"(packed) : "f"(second), "f"(first));      \
+        return packed;                                                                                     \
+    }
+NKB_HW_PAIR(hw_pair_e4m3, "e4m3x2")
+NKB_HW_PAIR(hw_pair_e5m2, "e5m2x2")
+NKB_HW_PAIR(hw_pair_e2m3, "e2m3x2")
+NKB_HW_PAIR(hw_pair_e3m2, "e3m2x2")
+#undef NKB_HW_PAIR
+
+__device__ __forceinline__ uint32_t patch_e4m3(uint32_t code, float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x7fffffffu) > 0x7f800000u ? ((u >> 24) & 0x80u) | 0x7fu : code;
+}
+__device__ __forceinline__ uint32_t patch_e5m2(uint32_t code, float x) {
+    const uint32_t u = __float_as_uint(x), a = u & 0x7fffffffu, sign = (u >> 24) & 0x80u;
+    return a > 0x7f800000u ? sign | 0x7du : (a >= 0x47700000u ? sign | 0x7cu : code);
+}
+__device__ __forceinline__ uint32_t patch_fp6(uint32_t code, float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x7fffffffu) > 0x7f800000u ? ((u >> 26) & 0x20u) | 0x1fu : code;
+}
+
+template <uint32_t kType> struct Scalar32;
+template <> struct Scalar32<kF32> {
+    static constexpr int kBytes = 4;
+    static __device__ __forceinline__ float decode(uint32_t b) { return __uint_as_float(b); }
+    static __device__ __forceinline__ uint32_t encode(float x) { return __float_as_uint(x); }
+    static __device__ __forceinline__ uint32_t encode2(float a, float) { return encode(a); }
+};
+template <> struct Scalar32<kF16> {
+    static constexpr int kBytes = 2;
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_f16(b); }
+    static __device__ __forceinline__ uint32_t encode(float x) { return encode_f16(x); }
+    static __device__ __forceinline__ uint32_t encode2(float a, float b) { return encode(a) | (encode(b) << (8 * kBytes)); }
+};
+template <> struct Scalar32<kBF16> {
+    static constexpr int kBytes = 2;
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_bf16(b); }
+    static __device__ __forceinline__ uint32_t encode(float x) { return encode_bf16(x); }
+    static __device__ __forceinline__ uint32_t encode2(float a, float b) { return encode(a) | (encode(b) << (8 * kBytes)); }
+};
+template <> struct Scalar32<kE4M3> {
+    static constexpr int kBytes = 1;
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_e4m3(b); }
+    static __device__ __forceinline__ uint32_t encode(float x) { return encode_e4m3(x); }
+    static __device__ __forceinline__ uint32_t encode2(float a, float b) {
+        const uint32_t packed = hw_pair_e4m3(a, b);
+        return patch_e4m3(packed & 0xffu, a) | (patch_e4m3(packed >> 8, b) << 8);
+    }
+};
+template <> struct Scalar32<kE5M2> {
+    static constexpr int kBytes = 1;
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_e5m2(b); }
+    static __device__ __forceinline__ uint32_t encode(float x) { return encode_e5m2(x); }
+    static __device__ __forceinline__ uint32_t encode2(float a, float b) {
+        const uint32_t packed = hw_pair_e5m2(a, b);
+        return patch_e5m2(packed & 0xffu, a) | (patch_e5m2(packed >> 8, b) << 8);
+    }
+};
+template <> struct Scalar32<kE2M3> {
+    static constexpr int kBytes = 1;
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_e2m3(b); }
+    static __device__ __forceinline__ uint32_t encode(float x) { return encode_fp6(x, 3, 1); }
+    static __device__ __forceinline__ uint32_t encode2(float a, float b) {
+        const uint32_t packed = hw_pair_e2m3(a, b);
+        return patch_fp6(packed & 0xffu, a) | (patch_fp6(packed >> 8, b) << 8);
+    }
+};
+template <> struct Scalar32<kE3M2> {
+    static constexpr int kBytes = 1;
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_e3m2(b); }
+    static __device__ __forceinline__ uint32_t encode(float x) { return encode_fp6(x, 2, 3); }
+    static __device__ __forceinline__ uint32_t encode2(float a, float b) {
+        const uint32_t packed = hw_pair_e3m2(a, b);
+        return patch_fp6(packed & 0xffu, a) | (patch_fp6(packed >> 8, b) << 8);
+    }
+};
+template <> struct Scalar32<kI8> {
+    static constexpr int kBytes = 1;
+    static __device__ __forceinline__ float decode(uint32_t b) { return (float)(signed char)b; }
+    static __device__ __forceinline__ uint32_t encode(float x) { return x != x ? 0u : (uint32_t)__float2int_rn(fminf(fmaxf(x, -128.0f), 127.0f)) & 0xffu; }
+    static __device__ __forceinline__ uint32_t encode2(float a, float b) { return encode(a) | (encode(b) << (8 * kBytes)); }
+};
+template <> struct Scalar32<kU8> {
+    static constexpr int kBytes = 1;
+    static __device__ __forceinline__ float decode(uint32_t b) { return (float)(b & 0xffu); }
+    static __device__ __forceinline__ uint32_t encode(float x) { return x != x ? 0u : (uint32_t)__float2int_rn(fminf(fmaxf(x, 0.0f), 255.0f)); }
+    static __device__ __forceinline__ uint32_t encode2(float a, float b) { return encode(a) | (encode(b) << (8 * kBytes)); }
+};
+
+template <int kBytes>
+__device__ __forceinline__ uint32_t vector_element(const uint32_t (&words)[4], int j) {
+    if constexpr (kBytes == 4) return words[j];
+    else if constexpr (kBytes == 2) return (words[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+    else return (words[j >> 2] >> (8 * (j & 3))) & 0xffu;
+}
+template <int kBytes>
+__device__ __forceinline__ void set_vector_element(uint32_t (&words)[4], int j, uint32_t v) {
+    if constexpr (kBytes == 4) words[j] = v;
+    else if constexpr (kBytes == 2) words[j >> 1] |= (v & 0xffffu) << (16 * (j & 1));
+    else words[j >> 2] |= (v & 0xffu) << (8 * (j & 3));
+}
+template <int kVectorBytes>
+__device__ __forceinline__ void load_vector(const uint8_t *p, uint32_t (&words)[4]) {
+    if constexpr (kVectorBytes == 16) { const uint4 v = *reinterpret_cast<const uint4 *>(p); words[0] = v.x, words[1] = v.y, words[2] = v.z, words[3] = v.w; }
+    else if constexpr (kVectorBytes == 8) { const uint2 v = *reinterpret_cast<const uint2 *>(p); words[0] = v.x, words[1] = v.y; }
+    else words[0] = *reinterpret_cast<const uint32_t *>(p);
+}
+template <int kVectorBytes>
+__device__ __forceinline__ void store_vector(uint8_t *p, const uint32_t (&words)[4]) {
+    if constexpr (kVectorBytes == 16) *reinterpret_cast<uint4 *>(p) = make_uint4(words[0], words[1], words[2], words[3]);
+    else if constexpr (kVectorBytes == 8) *reinterpret_cast<uint2 *>(p) = make_uint2(words[0], words[1]);
+    else *reinterpret_cast<uint32_t *>(p) = words[0];
+}
+
+template <uint32_t kFrom, uint32_t kTo>
+__global__ void __launch_bounds__(256) cast_pair_kernel(const uint8_t *__restrict__ from, uint8_t *__restrict__ to, uint64_t n) {
+    using In = Scalar32<kFrom>;
+    using Out = Scalar32<kTo>;
+    constexpr int kWide = In::kBytes > Out::kBytes ? In::kBytes : Out::kBytes;
+    constexpr int kNarrow = In::kBytes < Out::kBytes ? In::kBytes : Out::kBytes;
+    // Values per vector: the wider side moves 16 bytes, unless that leaves the narrower side under 4 bytes.
+    constexpr int kVec = (16 / kWide) * kNarrow >= 4 ? 16 / kWide : 4 / kNarrow;
+    static_assert(kVec * kWide <= 16 && kVec * kNarrow >= 4, "vector shape");
+    const uint64_t vectors = n / kVec;
+    for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < vectors; i += (uint64_t)gridDim.x * 256) {
+        uint32_t in_words[4] = {0, 0, 0, 0}, out_words[4] = {0, 0, 0, 0};
+        load_vector<kVec * In::kBytes>(from + i * (kVec * In::kBytes), in_words);
+        if constexpr (Out::kBytes == 4) {
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) out_words[j] = Out::encode(In::decode(vector_element<In::kBytes>(in_words, j)));
+        } else {  // two values per step: the 8-bit float formats convert in pairs
+#pragma unroll
+            for (int j = 0; j < kVec; j += 2) {
+                const uint32_t two = Out::encode2(In::decode(vector_element<In::kBytes>(in_words, j)),
+                                                  In::decode(vector_element<In::kBytes>(in_words, j + 1)));
+                if constexpr (Out::kBytes == 2) out_words[j >> 1] = two;
+                else out_words[j >> 2] |= two << (16 * ((j >> 1) & 1));
+            }
+        }
+        store_vector<kVec * Out::kBytes>(to + i * (kVec * Out::kBytes), out_words);
+    }
+    // ragged end: fewer than kVec values, one thread each
+    const uint64_t done = vectors * kVec;
+    if (blockIdx.x == 0 && threadIdx.x < n - done) {
+        const uint64_t e = done + threadIdx.x;
+        // Whole-element accesses (the launch checked that both buffers are aligned to a vector). Storing the two bytes of
+        // a fresh binary16 conversion one by one came out wrong on sm_100a with nvcc 12.9: the low byte held the VALUE
+        // converted to an integer.
+        uint32_t bits;
+        if constexpr (In::kBytes == 4) bits = reinterpret_cast<const uint32_t *>(from)[e];
+        else if constexpr (In::kBytes == 2) bits = reinterpret_cast<const uint16_t *>(from)[e];
+        else bits = from[e];
+        const uint32_t code = Out::encode(In::decode(bits));
+        if constexpr (Out::kBytes == 4) reinterpret_cast<uint32_t *>(to)[e] = code;
+        else if constexpr (Out::kBytes == 2) reinterpret_cast<uint16_t *>(to)[e] = (uint16_t)code;
+        else to[e] = (uint8_t)code;
+    }
+}
+
+template <uint32_t kFrom, uint32_t kTo>
+bool launch_pair(const uint8_t *from, uint8_t *to, uint64_t n, cudaStream_t stream) {
+    if constexpr (kFrom == kTo || ((kFrom == kI8 || kFrom == kU8) && (kTo == kI8 || kTo == kU8))) return false;
+    else {
+        using In = Scalar32<kFrom>;
+        using Out = Scalar32<kTo>;
+        constexpr int kWide = In::kBytes > Out::kBytes ? In::kBytes : Out::kBytes;
+        constexpr int kNarrow = In::kBytes < Out::kBytes ? In::kBytes : Out::kBytes;
+        constexpr int kVec = (16 / kWide) * kNarrow >= 4 ? 16 / kWide : 4 / kNarrow;
+        if (reinterpret_cast<uintptr_t>(from) % (kVec * In::kBytes) || reinterpret_cast<uintptr_t>(to) % (kVec * Out::kBytes)) return false;
+        const uint64_t vectors = n / kVec, wanted = (vectors + 255) / 256;
+        const unsigned grid = (unsigned)(wanted < 1 ? 1 : (wanted > 148ull * 32 ? 148ull * 32 : wanted));
+        cast_pair_kernel<kFrom, kTo><<<grid, 256, 0, stream>>>(from, to, n);
+        return true;
+    }
+}
+template <uint32_t kFrom>
+bool launch_pair_to(uint32_t to_type, const uint8_t *from, uint8_t *to, uint64_t n, cudaStream_t stream) {
+    switch (to_type) {
+    case kF32: return launch_pair<kFrom, kF32>(from, to, n, stream);
+    case kF16: return launch_pair<kFrom, kF16>(from, to, n, stream);
+    case kBF16: return launch_pair<kFrom, kBF16>(from, to, n, stream);
+    case kE4M3: return launch_pair<kFrom, kE4M3>(from, to, n, stream);
+    case kE5M2: return launch_pair<kFrom, kE5M2>(from, to, n, stream);
+    case kE2M3: return launch_pair<kFrom, kE2M3>(from, to, n, stream);
+    case kE3M2: return launch_pair<kFrom, kE3M2>(from, to, n, stream);
+    case kI8: return launch_pair<kFrom, kI8>(from, to, n, stream);
+    case kU8: return launch_pair<kFrom, kU8>(from, to, n, stream);
+    default: return false;
+    }
+}
+// Launches the compile-time pair kernel when there is one for (from_type, to_type) and the pointers allow vectors.
+bool launch_fast_pair(uint32_t from_type, uint32_t to_type, const uint8_t *from, uint8_t *to, uint64_t n, cudaStream_t stream) {
+    switch (from_type) {
+    case kF32: return launch_pair_to<kF32>(to_type, from, to, n, stream);
+    case kF16: return launch_pair_to<kF16>(to_type, from, to, n, stream);
+    case kBF16: return launch_pair_to<kBF16>(to_type, from, to, n, stream);
+    case kE4M3: return launch_pair_to<kE4M3>(to_type, from, to, n, stream);
+    case kE5M2: return launch_pair_to<kE5M2>(to_type, from, to, n, stream);
+    case kE2M3: return launch_pair_to<kE2M3>(to_type, from, to, n, stream);
+    case kE3M2: return launch_pair_to<kE3M2>(to_type, from, to, n, stream);
+    case kI8: return launch_pair_to<kI8>(to_type, from, to, n, stream);
+    case kU8: return launch_pair_to<kU8>(to_type, from, to, n, stream);
+    default: return false;
+    }
+}
+
 void cast_impl(const void *from, uint32_t from_type, uint64_t n, void *to, uint32_t to_type) {
     clear_error();
     if (n == 0) return;
@@ -341,7 +561,8 @@ void cast_impl(const void *from, uint32_t from_type, uint64_t n, void *to, uint3
         const bool from_vectors = aligned(src, cast_bits(from_type)), to_vectors = aligned(dst, cast_bits(to_type));
         const uint64_t batches = (n + 7) / 8, blocks = (batches + 255) / 256;
         if (blocks > 0x7fffffffull) { set_error("cast: too many values for one call%s", ""); return; }
-        if (hub == kFamilyFloat) cast_kernel<kFamilyFloat><<<(unsigned)blocks, 256, 0, stream>>>(src, dst, n, from_type, to_type, from_vectors, to_vectors);
+        if (launch_fast_pair(from_type, to_type, src, dst, n, stream)) {}
+        else if (hub == kFamilyFloat) cast_kernel<kFamilyFloat><<<(unsigned)blocks, 256, 0, stream>>>(src, dst, n, from_type, to_type, from_vectors, to_vectors);
         else if (hub == kFamilyInt) cast_kernel<kFamilyInt><<<(unsigned)blocks, 256, 0, stream>>>(src, dst, n, from_type, to_type, from_vectors, to_vectors);
         else cast_kernel<kFamilyUint><<<(unsigned)blocks, 256, 0, stream>>>(src, dst, n, from_type, to_type, from_vectors, to_vectors);
         g_launches++;

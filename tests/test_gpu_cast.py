@@ -131,3 +131,28 @@ def test_quantise_then_pack_chain():
     exact = oracle.exact_dots_f64(ha, hb, "e4m3")
     scale = np.abs(oracle.decode(ha, "e4m3").astype(np.float64)) @ np.abs(oracle.decode(hb, "e4m3").astype(np.float64)).T
     assert np.max(np.abs(c.cpu().numpy() - exact) / scale) <= 1e-7
+
+
+def test_cast_sweep_of_the_f32_bit_space():
+    """Every 4099th f32 bit pattern (subnormals, infinities and NaN included) to the narrow types: the kernel compiled for
+    the pair (aligned buffers; hardware fp8 / fp6 conversions) and the general kernel (a source 4 bytes off a 16-byte
+    boundary) must both give the oracle's bytes; for f16 / bf16 a NaN only has to stay a NaN."""
+    bits = np.arange(0, 2 ** 32, 4099, dtype=np.uint64).astype(np.uint32)
+    n = bits.size
+    store = torch.zeros(n * 4 + 16, dtype=torch.uint8, device="cuda")
+    aligned, shifted = store[:n * 4], torch.zeros(n * 4 + 16, dtype=torch.uint8, device="cuda")[4:4 + n * 4]
+    aligned.copy_(torch.from_numpy(bits.view(np.uint8)).cuda())
+    shifted.copy_(aligned)
+    nan = np.isnan(bits.view(np.float32))
+    for target in ("e4m3", "e5m2", "e2m3", "e3m2", "f16", "bf16", "i8", "u8"):
+        want = oracle.cast(bits.view(np.float32), "f32", target)
+        for source in (aligned, shifted):
+            before = nk.launch_count()
+            got = nk.cast(source, target, dtype="f32", count=n)
+            assert nk.synchronize() == 0 and nk.launch_count() == before + 1
+            got = got.view(torch.uint8).cpu().numpy().view(want.dtype)
+            if target in ("f16", "bf16"):
+                assert np.array_equal(got[~nan], want[~nan]), target
+                assert np.all(np.isnan(oracle.decode(got[nan].view(np.uint16).reshape(1, -1), target))), target
+            else:
+                assert np.array_equal(got, want), target
