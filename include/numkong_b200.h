@@ -165,6 +165,31 @@ NKB_API void nk_dots_compact_i8(void *c, nk_size_t row_count, nk_size_t column_c
  * integer -> u4 / u1, complex types) set the error text and write nothing. */
 NKB_API void nk_cast(void const *from, uint32_t from_type, nk_size_t n, void *to, uint32_t to_type);
 
+/* ---- Moments: sum and sum of squares of a strided vector -------------------------------------------------
+ * replace nk_reduce_moments_<t> (include/numkong/reduce.h:120-279, scalar back end reduce/serial.h:52-416): `count`
+ * values `stride_bytes` apart (sub-byte types: whole bytes, the stride steps from byte to byte). Integers are exact,
+ * with the reference's saturation rules for 32 / 64-bit types; floats are summed in f64 and rounded once to the
+ * result type. `data` and the two result pointers may each be host or device memory. */
+NKB_API void nk_reduce_moments_f64(double const *data, nk_size_t count, nk_size_t stride_bytes, double *sum, double *sumsq);
+NKB_API void nk_reduce_moments_f32(float const *data, nk_size_t count, nk_size_t stride_bytes, double *sum, double *sumsq);
+NKB_API void nk_reduce_moments_f16(void const *data, nk_size_t count, nk_size_t stride_bytes, float *sum, float *sumsq);
+NKB_API void nk_reduce_moments_bf16(void const *data, nk_size_t count, nk_size_t stride_bytes, float *sum, float *sumsq);
+NKB_API void nk_reduce_moments_e4m3(void const *data, nk_size_t count, nk_size_t stride_bytes, float *sum, float *sumsq);
+NKB_API void nk_reduce_moments_e5m2(void const *data, nk_size_t count, nk_size_t stride_bytes, float *sum, float *sumsq);
+NKB_API void nk_reduce_moments_e2m3(void const *data, nk_size_t count, nk_size_t stride_bytes, float *sum, float *sumsq);
+NKB_API void nk_reduce_moments_e3m2(void const *data, nk_size_t count, nk_size_t stride_bytes, float *sum, float *sumsq);
+NKB_API void nk_reduce_moments_i8(int8_t const *data, nk_size_t count, nk_size_t stride_bytes, int64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_u8(uint8_t const *data, nk_size_t count, nk_size_t stride_bytes, uint64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_i16(int16_t const *data, nk_size_t count, nk_size_t stride_bytes, int64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_u16(uint16_t const *data, nk_size_t count, nk_size_t stride_bytes, uint64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_i32(int32_t const *data, nk_size_t count, nk_size_t stride_bytes, int64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_u32(uint32_t const *data, nk_size_t count, nk_size_t stride_bytes, uint64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_i64(int64_t const *data, nk_size_t count, nk_size_t stride_bytes, int64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_u64(uint64_t const *data, nk_size_t count, nk_size_t stride_bytes, uint64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_i4(void const *data, nk_size_t count, nk_size_t stride_bytes, int64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_u4(void const *data, nk_size_t count, nk_size_t stride_bytes, uint64_t *sum, uint64_t *sumsq);
+NKB_API void nk_reduce_moments_u1(void const *data, nk_size_t count, nk_size_t stride_bytes, uint64_t *sum, uint64_t *sumsq);
+
 /* ---- MaxSim late interaction -------------------------------------------------------------------
  * replaces include/numkong/maxsim.h:72-114 (wrappers c/numkong.c:738-765). Both sides are packed
  * with the same function. result: f32 for bf16/f16, f64 for f32 (maxsim.h:350-357):

@@ -29,7 +29,7 @@ __all__ = [
     "dots_symmetric", "angulars_symmetric", "euclideans_symmetric",
     "hammings_packed", "jaccards_packed", "hammings_symmetric", "jaccards_symmetric",
     "maxsim_pack", "maxsim_packed", "maxsim", "maxsims_packed", "angulars_packed_topk", "euclideans_packed_topk",
-    "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error", "dots_compact", "cast",
+    "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error", "dots_compact", "cast", "moments",
 ]
 
 _NUMPY_NAMES = {
@@ -431,6 +431,37 @@ def cast(x: Any, to_dtype: str, *, dtype: Optional[str] = None, count: Optional[
     lib.nk_cast(_ptr(x), CAST_CODES[name], n, _ptr(out), CAST_CODES[to_dtype])
     check("cast")
     return out
+
+
+def moments(x: Any, *, dtype: Optional[str] = None, count: Optional[int] = None, stride: Optional[int] = None) -> Tuple[Any, Any]:
+    """(sum, sum of squares) of the values of a flat array - nk_reduce_moments_<dtype> (include/numkong/reduce.h:120-279).
+    `count` values `stride` bytes apart (default: all of `x`, contiguous; sub-byte types count whole bytes). Python ints
+    for integer types, floats otherwise (f32 precision for the 16-bit and smaller floats, as in the reference)."""
+    is_torch = _is_torch(x)
+    if not is_torch:
+        x = np.asarray(x)
+    name = dtype or (_TORCH_NAMES.get(str(x.dtype)) or _CAST_NAMES.get(str(x.dtype).replace("torch.", "")) if is_torch
+                     else _NUMPY_NAMES.get(x.dtype.name) or _CAST_NAMES.get(x.dtype.name))
+    if name not in CAST_CODES:
+        raise TypeError(f"no moments kernel for {name!r}")
+    if not (x.is_contiguous() if is_torch else x.flags.c_contiguous):
+        raise ValueError("moments needs a contiguous array (use `stride` to skip values)")
+    nbytes = x.numel() * x.element_size() if is_torch else x.nbytes
+    unit = max(CAST_BITS[name] // 8, 1)
+    step = int(stride) if stride is not None else unit
+    per_unit = 8 // CAST_BITS[name] if CAST_BITS[name] < 8 else 1
+    n = int(count) if count is not None else (nbytes // step) * per_unit
+    units = (n + per_unit - 1) // per_unit
+    if units and (units - 1) * step + unit > nbytes:
+        raise ValueError("count and stride reach beyond the array")
+    floats = name in ("f64", "f32", "f16", "bf16", "e4m3", "e5m2", "e2m3", "e3m2")
+    narrow = floats and name not in ("f64", "f32")
+    signed = name in ("i8", "i16", "i32", "i64", "i4")
+    total = (ctypes.c_float if narrow else ctypes.c_double if floats else ctypes.c_int64 if signed else ctypes.c_uint64)()
+    squares = (ctypes.c_float if narrow else ctypes.c_double if floats else ctypes.c_uint64)()
+    getattr(lib, f"nk_reduce_moments_{name}")(_ptr(x), n, step, ctypes.byref(total), ctypes.byref(squares))
+    check("moments")
+    return total.value, squares.value
 
 
 def maxsim_pack(vectors: Any, dtype: Optional[str] = None) -> MaxSimPackedMatrix:

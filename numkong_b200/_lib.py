@@ -73,6 +73,9 @@ def _load() -> ctypes.CDLL:
         f = getattr(lib, f"nkb_maxsims_packed_{t}")
         f.restype, f.argtypes = None, [vp, vp, sz, vp, vp, sz, sz, vp, sz]
     lib.nk_cast.restype, lib.nk_cast.argtypes = None, [vp, ctypes.c_uint32, sz, vp, ctypes.c_uint32]
+    for t in ("f64", "f32", "f16", "bf16", "e4m3", "e5m2", "e2m3", "e3m2", "i8", "u8", "i16", "u16", "i32", "u32", "i64", "u64", "i4", "u4", "u1"):
+        f = getattr(lib, f"nk_reduce_moments_{t}")
+        f.restype, f.argtypes = None, [vp, sz, sz, vp, vp]
     lib.nk_dots_compact_bf16.restype, lib.nk_dots_compact_bf16.argtypes = None, [vp, sz, sz, sz]
     lib.nk_dots_compact_i8.restype, lib.nk_dots_compact_i8.argtypes = None, [vp, sz, sz, sz, vp, vp]
     lib.nkb_topk_smallest_f32.restype = None

@@ -167,3 +167,14 @@ def cast_samples(dtype: str, n: int, seed: int) -> np.ndarray:
     v = rng.integers(info.min, info.max, n, dtype=storage, endpoint=True)
     v[: n // 2] = rng.integers(max(info.min, -300), min(info.max, 300), n // 2).astype(storage)
     return v
+
+
+def moments_samples(dtype: str, n: int, seed: int) -> np.ndarray:
+    """`cast_samples` with magnitudes bounded so that sums of squares stay finite in the result type: f32 / f64 clipped to
+    +-1e6, bf16 kept below 2 (top exponent bit cleared)."""
+    x = cast_samples(dtype, n, seed)
+    if dtype in ("f64", "f32"):
+        return np.clip(x, -1e6, 1e6).astype(x.dtype)
+    if dtype == "bf16":
+        return x & np.uint16(0xBFFF)
+    return x

@@ -46,6 +46,32 @@ def cast(x: np.ndarray, from_dtype: str, to_dtype: str, n: Optional[int] = None)
     return _cast_with(_lib.orc_cast, x, from_dtype, to_dtype, n)
 
 
+def moments_result_dtype(dtype: str):
+    """(sum, sum of squares) types of nk_reduce_moments_<dtype> (include/numkong/reduce.h:120-279)."""
+    if dtype in ("f64", "f32"):
+        return np.float64, np.float64
+    if dtype in ("f16", "bf16", "e4m3", "e5m2", "e2m3", "e3m2"):
+        return np.float32, np.float32
+    return (np.int64 if dtype in ("i8", "i16", "i32", "i64", "i4") else np.uint64), np.uint64
+
+
+def _moments_with(fn, x: np.ndarray, dtype: str, count: Optional[int], stride: Optional[int]):
+    x = np.ascontiguousarray(x)
+    unit = max(CAST_BITS[dtype] // 8, 1)
+    stride = int(stride) if stride is not None else unit
+    count = int(count) if count is not None else (x.nbytes // stride) * (8 // CAST_BITS[dtype] if CAST_BITS[dtype] < 8 else 1)
+    s, q = np.zeros(1, dtype=np.uint64), np.zeros(1, dtype=np.uint64)
+    fn(x.ctypes.data, count, stride, s.ctypes.data, q.ctypes.data)
+    st, qt = moments_result_dtype(dtype)
+    return s.view(np.uint8)[:np.dtype(st).itemsize].view(st)[0], q.view(np.uint8)[:np.dtype(qt).itemsize].view(qt)[0]
+
+
+def moments(x: np.ndarray, dtype: str, count: Optional[int] = None, stride: Optional[int] = None):
+    """Sum and sum of squares of `count` values of `dtype` taken `stride` bytes apart, with the reference's scalar rules."""
+    code = CAST_CODES[dtype]
+    return _moments_with(lambda p, n, st, s, q: _lib.orc_moments(code, p, n, st, s, q), x, dtype, count, stride)
+
+
 def _depth(x: np.ndarray, dtype: str, depth: Optional[int]) -> int:
     """Logical dimensions of a row: 4-bit types hold two per byte (an explicit `depth` may be odd)."""
     return int(depth) if depth is not None else x.shape[1] * {"i4": 2, "u4": 2, "u1": 8}.get(dtype, 1)
@@ -77,6 +103,7 @@ def _load() -> ctypes.CDLL:
     lib.orc_sets.restype, lib.orc_sets.argtypes = None, [i32, vp, u64, vp, u64, vp, u64, u64, u64, u64]
     lib.orc_rsqrt_f32.restype, lib.orc_rsqrt_f32.argtypes = ctypes.c_float, [ctypes.c_float]
     lib.orc_cast.restype, lib.orc_cast.argtypes = ctypes.c_int, [vp, i32, u64, vp, i32]
+    lib.orc_moments.restype, lib.orc_moments.argtypes = ctypes.c_int, [i32, vp, u64, u64, vp, vp]
     lib.orc_compact_bf16.restype, lib.orc_compact_bf16.argtypes = None, [vp, u64, u64, u64]
     lib.orc_compact_i8.restype, lib.orc_compact_i8.argtypes = None, [vp, u64, u64, u64, vp, vp]
     for name in ("orc_maxsim_argmax_dot", "orc_maxsim_coarse_i8"):
@@ -284,6 +311,10 @@ class _Ref:
     def cast(self, x, from_dtype, to_dtype, n=None):
         u64, vp = ctypes.c_uint64, ctypes.c_void_p
         return _cast_with(self._fn("cast", None, [vp, ctypes.c_int, u64, vp, ctypes.c_int]), x, from_dtype, to_dtype, n)
+
+    def moments(self, x, dtype, count=None, stride=None):
+        u64, vp = ctypes.c_uint64, ctypes.c_void_p
+        return _moments_with(self._fn(f"reduce_moments_{dtype}", None, [vp, u64, u64, vp, vp]), x, dtype, count, stride)
 
     def maxsim(self, q, d, dtype) -> float:
         q, d = _as_storage(q, dtype), _as_storage(d, dtype)

@@ -716,3 +716,87 @@ ORC_API int orc_cast(const void *from, int from_type, uint64_t n, void *to, int 
     }
     return 1;
 }
+
+/* ---- moments: sum and sum of squares of a strided vector ----------------------------------------------
+ * Restates nk_reduce_moments_<t>_serial (include/numkong/reduce/serial.h:52-416).
+ *   f32 / f64: every value widened to f64, Neumaier-compensated running sums of the values and of their rounded
+ *     squares, result = running + compensation (:52-94). f16 bf16 e4m3 e5m2 e2m3 e3m2: the same in f32 (:232-371).
+ *   i8 u8 i16 u16 i4 u4 u1: plain 64-bit sums (:96-146, :373-416); sub-byte types count whole bytes, `stride`
+ *     steps from byte to byte. i32 / i64: the sum is kept in 128 bits and saturated to i64 at the end; squares (for
+ *     i64 saturated at 2^63 - 1) are added with unsigned saturation (:148-167, :182-205). u32 / u64: saturating
+ *     unsigned sums of values and (saturated) squares (:169-180, :207-219).
+ * `sum` and `sumsq` receive 8 bytes each: f64, or an f32 in the first four bytes, or i64 / u64.
+ */
+static uint64_t sat_add_u64(uint64_t a, uint64_t b) { return a + b < a ? UINT64_MAX : a + b; }
+static uint64_t sat_square_u64(uint64_t a) { unsigned __int128 p = (unsigned __int128)a * a; return p > UINT64_MAX ? UINT64_MAX : (uint64_t)p; }
+
+ORC_API int orc_moments(int dt, const void *data, uint64_t count, uint64_t stride, void *sum_out, void *sumsq_out) {
+    const uint8_t *p = (const uint8_t *)data;
+    if (dt == ORC_F64 || dt == ORC_F32) {
+        double s = 0, sc = 0, q = 0, qc = 0;
+        for (uint64_t i = 0; i < count; ++i, p += stride) {
+            double v;
+            if (dt == ORC_F64) memcpy(&v, p, 8); else { float f; memcpy(&f, p, 4); v = (double)f; }
+            double t = s + v;
+            if (fabs(s) >= fabs(v)) sc += (s - t) + v; else sc += (v - t) + s;
+            s = t;
+            double sq = v * v, tq = q + sq;
+            if (q >= sq) qc += (q - tq) + sq; else qc += (sq - tq) + q;
+            q = tq;
+        }
+        double rs = s + sc, rq = q + qc;
+        memcpy(sum_out, &rs, 8); memcpy(sumsq_out, &rq, 8);
+        return 1;
+    }
+    if (cast_family(dt) == FAMILY_FLOAT) {
+        float s = 0, sc = 0, q = 0, qc = 0;
+        for (uint64_t i = 0; i < count; ++i, p += stride) {
+            float v = dec(dt, p), t = s + v;
+            if (fabsf(s) >= fabsf(v)) sc += (s - t) + v; else sc += (v - t) + s;
+            s = t;
+            float sq = v * v, tq = q + sq;
+            if (q >= sq) qc += (q - tq) + sq; else qc += (sq - tq) + q;
+            q = tq;
+        }
+        float rs = s + sc, rq = q + qc;
+        memset(sum_out, 0, 8); memset(sumsq_out, 0, 8);
+        memcpy(sum_out, &rs, 4); memcpy(sumsq_out, &rq, 4);
+        return 1;
+    }
+    if (dt == ORC_U1 || dt == ORC_I4 || dt == ORC_U4) {
+        const uint64_t bytes = dt == ORC_U1 ? (count + 7) / 8 : (count + 1) / 2;
+        int64_t s = 0; uint64_t q = 0;
+        for (uint64_t i = 0; i < bytes; ++i, p += stride) {
+            if (dt == ORC_U1) { int c = __builtin_popcount(p[0]); s += c; q += (uint64_t)c; continue; }
+            int64_t lo = p[0] & 0xF, hi = p[0] >> 4;
+            if (dt == ORC_I4) lo = (lo ^ 8) - 8, hi = (hi ^ 8) - 8;
+            s += lo + hi; q += (uint64_t)(lo * lo) + (uint64_t)(hi * hi);
+        }
+        memcpy(sum_out, &s, 8); memcpy(sumsq_out, &q, 8);
+        return 1;
+    }
+    if (cast_family(dt) == FAMILY_INT) {
+        __int128 s = 0; uint64_t q = 0;
+        for (uint64_t i = 0; i < count; ++i, p += stride) {
+            int64_t v = load_i64(dt, p);
+            s += v;
+            if (dt == ORC_I64) { uint64_t a = v < 0 ? 0 - (uint64_t)v : (uint64_t)v, sq = sat_square_u64(a); q = sat_add_u64(q, sq > INT64_MAX ? INT64_MAX : sq); }
+            else if (dt == ORC_I32) q = sat_add_u64(q, (uint64_t)(v * v));
+            else q += (uint64_t)(v * v);
+        }
+        int64_t rs = (dt == ORC_I32 || dt == ORC_I64) ? (s > INT64_MAX ? INT64_MAX : s < INT64_MIN ? INT64_MIN : (int64_t)s) : (int64_t)s;
+        memcpy(sum_out, &rs, 8); memcpy(sumsq_out, &q, 8);
+        return 1;
+    }
+    if (cast_family(dt) == FAMILY_UINT) {
+        uint64_t s = 0, q = 0;
+        for (uint64_t i = 0; i < count; ++i, p += stride) {
+            uint64_t v = load_u64(dt, p);
+            if (dt == ORC_U32 || dt == ORC_U64) s = sat_add_u64(s, v), q = sat_add_u64(q, sat_square_u64(v));
+            else s += v, q += v * v;
+        }
+        memcpy(sum_out, &s, 8); memcpy(sumsq_out, &q, 8);
+        return 1;
+    }
+    return 0;
+}

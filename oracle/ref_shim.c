@@ -61,6 +61,31 @@ REF_API void ref_dots_compact_i8(void *c, nk_size_t rows, nk_size_t cols, nk_siz
 /* bulk type conversion, scalar back end */
 REF_API void ref_cast(void const *from, int from_type, nk_size_t n, void *to, int to_type) { nk_cast_serial(from, (nk_dtype_t)from_type, n, to, (nk_dtype_t)to_type); }
 
+/* moments (sum, sum of squares), scalar back end */
+#define REF_MOMENTS(T, IN, SUM, SQ)                                                                                  \
+    REF_API void ref_reduce_moments_##T(IN const *x, nk_size_t n, nk_size_t stride, SUM *s, SQ *q) {                 \
+        nk_reduce_moments_##T##_serial(x, n, stride, s, q);                                                          \
+    }
+REF_MOMENTS(f64, nk_f64_t, nk_f64_t, nk_f64_t)
+REF_MOMENTS(f32, nk_f32_t, nk_f64_t, nk_f64_t)
+REF_MOMENTS(f16, nk_f16_t, nk_f32_t, nk_f32_t)
+REF_MOMENTS(bf16, nk_bf16_t, nk_f32_t, nk_f32_t)
+REF_MOMENTS(e4m3, nk_e4m3_t, nk_f32_t, nk_f32_t)
+REF_MOMENTS(e5m2, nk_e5m2_t, nk_f32_t, nk_f32_t)
+REF_MOMENTS(e2m3, nk_e2m3_t, nk_f32_t, nk_f32_t)
+REF_MOMENTS(e3m2, nk_e3m2_t, nk_f32_t, nk_f32_t)
+REF_MOMENTS(i8, nk_i8_t, nk_i64_t, nk_u64_t)
+REF_MOMENTS(u8, nk_u8_t, nk_u64_t, nk_u64_t)
+REF_MOMENTS(i16, nk_i16_t, nk_i64_t, nk_u64_t)
+REF_MOMENTS(u16, nk_u16_t, nk_u64_t, nk_u64_t)
+REF_MOMENTS(i32, nk_i32_t, nk_i64_t, nk_u64_t)
+REF_MOMENTS(u32, nk_u32_t, nk_u64_t, nk_u64_t)
+REF_MOMENTS(i64, nk_i64_t, nk_i64_t, nk_u64_t)
+REF_MOMENTS(u64, nk_u64_t, nk_u64_t, nk_u64_t)
+REF_MOMENTS(i4, nk_i4x2_t, nk_i64_t, nk_u64_t)
+REF_MOMENTS(u4, nk_u4x2_t, nk_u64_t, nk_u64_t)
+REF_MOMENTS(u1, nk_u1x8_t, nk_u64_t, nk_u64_t)
+
 #define REF_MAXSIM_FAMILY(T, IN, OUT)                                                                                \
     REF_API nk_size_t ref_maxsim_packed_size_##T(nk_size_t n, nk_size_t k) { return nk_maxsim_packed_size_##T##_serial(n, k); } \
     REF_API void ref_maxsim_pack_##T(IN const *v, nk_size_t n, nk_size_t k, nk_size_t s, void *p) {                   \

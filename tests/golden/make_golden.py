@@ -89,6 +89,7 @@ def main():
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
     make_compact(serial)
     make_cast(serial)
+    make_moments(serial)
 
 
 def make_compact(serial):
@@ -141,8 +142,35 @@ def make_cast(serial):
     print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
 
 
+def make_moments(serial):
+    """moments_path.npz: nk_reduce_moments_<t>_serial on 1000 contiguous values and on every third of 999, all nineteen types;
+    plus the saturating cases of the 32 / 64-bit integers. Results are stored in their own types (`_sum`, `_sumsq`)."""
+    out = {}
+
+    def keep(key, pair):
+        out[key + "_sum"], out[key + "_sumsq"] = np.array([pair[0]]), np.array([pair[1]])
+
+    for si, t in enumerate(CAST_TYPES):
+        x = syn.moments_samples(t, 1000, 9000 + si)
+        out["from_" + t] = x
+        per_unit = 8 // oracle.CAST_BITS[t] if oracle.CAST_BITS[t] < 8 else 1
+        keep(t + "_all", serial.moments(x, t, 1000 if per_unit > 1 else None))
+        keep(t + "_strided", serial.moments(x, t, 333 * per_unit if per_unit == 1 else 40 * per_unit, 3 * max(oracle.CAST_BITS[t] // 8, 1)))
+    big = {"i32": np.full(5, -2 ** 31, dtype=np.int32), "u32": np.full(5, 2 ** 32 - 1, dtype=np.uint32),
+           "i64": np.array([2 ** 63 - 1, 2 ** 63 - 1, 5, -7], dtype=np.int64), "u64": np.array([2 ** 64 - 1, 2 ** 64 - 1, 3], dtype=np.uint64),
+           "i64_negative": np.array([-2 ** 63, -2 ** 63, -1], dtype=np.int64)}
+    for key, x in big.items():
+        out["big_" + key] = x
+        keep("big_" + key, serial.moments(x, key.split("_")[0]))
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "moments_path.npz")
+    np.savez_compressed(path, **out)
+    print(path, os.path.getsize(path), "bytes,", len(out), "arrays")
+
+
 if __name__ == "__main__":
-    if "--only-compact" in sys.argv:
+    if "--only-moments" in sys.argv:
+        make_moments(oracle.ref_serial())
+    elif "--only-compact" in sys.argv:
         make_compact(oracle.ref_serial())
     elif "--only-cast" in sys.argv:
         make_cast(oracle.ref_serial())

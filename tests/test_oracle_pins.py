@@ -295,3 +295,38 @@ def test_cast_oracle_against_live_reference():
                 if b == "e5m2" or (b == "u64" and a in ("i8", "i16", "i32", "i64")):
                     continue
                 assert np.array_equal(got, dispatch.cast(x, a, b, n).view(np.uint8)), (a, b, n, "dispatch")
+
+
+MOMENTS_GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "moments_path.npz"))
+
+
+def _same_bits(pair, key):
+    return all(np.array(v).tobytes() == MOMENTS_GOLDEN[f"{key}_{name}"].tobytes() for v, name in zip(pair, ("sum", "sumsq")))
+
+
+@pytest.mark.parametrize("dtype", CAST_TYPES)
+def test_moments_oracle_matches_reference_golden(dtype):
+    """Sum and sum of squares: bit for bit against the reference's scalar reductions (compensated serial sums for the
+    floats, exact and saturating integer rules), contiguous and strided."""
+    x = MOMENTS_GOLDEN["from_" + dtype]
+    per_unit = 8 // oracle.CAST_BITS[dtype] if oracle.CAST_BITS[dtype] < 8 else 1
+    assert _same_bits(oracle.moments(x, dtype, 1000 if per_unit > 1 else None), dtype + "_all")
+    strided = oracle.moments(x, dtype, 333 if per_unit == 1 else 40 * per_unit, 3 * max(oracle.CAST_BITS[dtype] // 8, 1))
+    assert _same_bits(strided, dtype + "_strided")
+
+
+def test_moments_oracle_saturation_cases():
+    for key in ("i32", "u32", "i64", "u64", "i64_negative"):
+        assert _same_bits(oracle.moments(MOMENTS_GOLDEN["big_" + key], key.split("_")[0]), "big_" + key), key
+
+
+def test_moments_oracle_against_live_reference():
+    serial = oracle.ref_serial()
+    if serial is None:
+        pytest.skip("reference not compiled here")
+    for si, t in enumerate(CAST_TYPES):
+        for n in (1, 9, 2500):
+            x = syn.moments_samples(t, n, 9500 + si)
+            count = n if oracle.CAST_BITS[t] < 8 else None
+            mine, theirs = oracle.moments(x, t, count), serial.moments(x, t, count)
+            assert all(np.array(a).tobytes() == np.array(b).tobytes() for a, b in zip(mine, theirs)), (t, n)
