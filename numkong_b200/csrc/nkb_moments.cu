@@ -114,28 +114,87 @@ template <> struct Moments<kF16> : FloatMoments<2, false> {
 template <> struct Moments<kBF16> : FloatMoments<2, false> {
     static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)__uint_as_float((uint32_t)bits << 16)); }
 };
+// The sixteen values of a vector of e4m3 / e2m3 / e3m2 add up EXACTLY in f32 (values are multiples of 2^-9 / 2^-3 / 2^-4
+// and sixteen of them stay below 2^13 / 2^7 / 2^9), and so do their squares for the two 6-bit formats. e4m3 squares span
+// 36 bits, so they are added in two classes: |v| < 2 (multiples of 2^-18 below 4: exact over the sixteen values) and
+// |v| >= 2 (multiples of 2^-4 up to 2^17.6: exact over the four values of a word). Only these partial sums go through
+// f64 additions. Two codes are decoded at a time: their bits are moved into a binary16 pair (value / kScale), which
+// converts to f32 exactly; the power-of-two scale is applied to the partial sums.
+struct E4M3Format {
+    static constexpr float kScale = 256.0f;
+    static __device__ __forceinline__ uint32_t half_pair(uint32_t x) { return (x & 0x80008000u) | ((x >> 1) & 0x3f803f80u); }
+    static __device__ __forceinline__ float decode(uint32_t c) {
+        return (c & 0x7fu) == 0x7fu ? __uint_as_float(0x7fc00000u) : half_bits_to_f32(((c & 0x80u) << 8) | ((c & 0x7fu) << 7)) * 256.0f;
+    }
+};
+struct E2M3Format {
+    static constexpr float kScale = 16384.0f;
+    static __device__ __forceinline__ uint32_t half_pair(uint32_t x) { return ((x & 0x20002000u) << 2) | ((x >> 1) & 0x0f800f80u); }
+    static __device__ __forceinline__ float decode(uint32_t c) { return half_bits_to_f32(((c & 0x20u) << 10) | ((c & 0x1fu) << 7)) * 16384.0f; }
+};
+struct E3M2Format {
+    static constexpr float kScale = 4096.0f;
+    static __device__ __forceinline__ uint32_t half_pair(uint32_t x) { return ((x & 0x20002000u) << 2) | (x & 0x1f001f00u); }
+    static __device__ __forceinline__ float decode(uint32_t c) { return half_bits_to_f32(((c & 0x20u) << 10) | ((c & 0x1fu) << 8)) * 4096.0f; }
+};
+// Codes 2p and 2p+1 of a word as f32 values divided by kScale.
+template <typename Format>
+__device__ __forceinline__ float2 scaled_pair(uint32_t word, int p) {
+    const uint32_t x = __byte_perm(word, 0u, p ? 0x3424u : 0x1404u);  // the two codes in the high bytes of the two halves
+    const uint32_t bits = Format::half_pair(x);
+    return __half22float2(*reinterpret_cast<const __half2 *>(&bits));
+}
+
 template <> struct Moments<kE4M3> : FloatMoments<1, false> {
-    static __device__ __forceinline__ void add(State &s, unsigned long long bits) {
-        const uint32_t c = (uint32_t)bits;
-        const float v = (c & 0x7fu) == 0x7fu ? __uint_as_float(0x7fc00000u) : half_bits_to_f32(((c & 0x80u) << 8) | ((c & 0x7fu) << 7)) * 256.0f;
-        add_value(s, (double)v);
+    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)E4M3Format::decode((uint32_t)bits)); }
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+        float total = 0.0f, small_squares = 0.0f, large_squares[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        uint32_t nan_bytes = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            nan_bytes |= ((w[i] & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u;  // a byte of 0x7F / 0xFF is the format's NaN
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const float2 v = scaled_pair<E4M3Format>(w[i], p);
+                const uint32_t large_bits = w[i] >> (16 * p);                  // bit 6 of a code: exponent field >= 8, |v| >= 2
+                const float large_x = (large_bits & 0x40u) ? v.x : 0.0f, large_y = (large_bits & 0x4000u) ? v.y : 0.0f;
+                const float small_x = v.x - large_x, small_y = v.y - large_y;
+                total += v.x, total += v.y;
+                small_squares = fmaf(small_x, small_x, small_squares), small_squares = fmaf(small_y, small_y, small_squares);
+                large_squares[i] = fmaf(large_x, large_x, large_squares[i]), large_squares[i] = fmaf(large_y, large_y, large_squares[i]);
+            }
+        }
+        if (nan_bytes) total = __uint_as_float(0x7fc00000u), small_squares = total;
+        constexpr double kScale = E4M3Format::kScale, kScaleSquared = kScale * kScale;
+        s.sum += (double)total * kScale;
+        s.squares += (double)small_squares * kScaleSquared;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s.squares += (double)large_squares[i] * kScaleSquared;
     }
 };
 template <> struct Moments<kE5M2> : FloatMoments<1, false> {
     static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)half_bits_to_f32(((uint32_t)bits & 0xffu) << 8)); }
 };
-template <> struct Moments<kE2M3> : FloatMoments<1, false> {
-    static __device__ __forceinline__ void add(State &s, unsigned long long bits) {
-        const uint32_t c = (uint32_t)bits;
-        add_value(s, (double)(half_bits_to_f32(((c & 0x20u) << 10) | ((c & 0x1fu) << 7)) * 16384.0f));
+template <typename Format>
+struct Fp6Moments : FloatMoments<1, false> {
+    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)Format::decode((uint32_t)bits)); }
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+        float total = 0.0f, squares = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const float2 v = scaled_pair<Format>(w[i], p);
+                total += v.x, total += v.y;
+                squares = fmaf(v.x, v.x, squares), squares = fmaf(v.y, v.y, squares);
+            }
+        constexpr double kScale = Format::kScale;
+        s.sum += (double)total * kScale;
+        s.squares += (double)squares * (kScale * kScale);
     }
 };
-template <> struct Moments<kE3M2> : FloatMoments<1, false> {
-    static __device__ __forceinline__ void add(State &s, unsigned long long bits) {
-        const uint32_t c = (uint32_t)bits;
-        add_value(s, (double)(half_bits_to_f32(((c & 0x20u) << 10) | ((c & 0x1fu) << 8)) * 4096.0f));
-    }
-};
+template <> struct Moments<kE2M3> : Fp6Moments<E2M3Format> {};
+template <> struct Moments<kE3M2> : Fp6Moments<E3M2Format> {};
 
 // ---- integers ----
 struct IntState {
@@ -160,24 +219,51 @@ struct IntMoments {
 };
 template <> struct Moments<kI8> : IntMoments<1> {
     static __device__ __forceinline__ void add(State &s, unsigned long long bits) { const long long v = (signed char)bits; s.sum.add_signed(v), s.squares.add_unsigned((unsigned long long)(v * v)); }
-    // four values at once with the byte dot-product instruction
-    static __device__ __forceinline__ void add_word(State &s, uint32_t word) {
-        s.sum.add_signed(__dp4a((int)word, 0x01010101, 0));
-        s.squares.add_unsigned((unsigned long long)(unsigned)__dp4a((int)word, (int)word, 0));
+    // sixteen values at once with the byte dot-product instruction; the 32-bit partial sums cannot overflow
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+        int total = 0, squares = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) total = __dp4a((int)w[i], 0x01010101, total), squares = __dp4a((int)w[i], (int)w[i], squares);
+        s.sum.add_signed(total), s.squares.add_unsigned((unsigned long long)(unsigned)squares);
     }
 };
 template <> struct Moments<kU8> : IntMoments<1> {
     static __device__ __forceinline__ void add(State &s, unsigned long long bits) { const unsigned long long v = bits & 0xffu; s.sum.add_unsigned(v), s.squares.add_unsigned(v * v); }
-    static __device__ __forceinline__ void add_word(State &s, uint32_t word) {
-        s.sum.add_unsigned(__dp4a(word, 0x01010101u, 0u));
-        s.squares.add_unsigned(__dp4a(word, word, 0u));
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+        uint32_t total = 0, squares = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) total = __dp4a(w[i], 0x01010101u, total), squares = __dp4a(w[i], w[i], squares);
+        s.sum.add_unsigned(total), s.squares.add_unsigned(squares);
     }
 };
 template <> struct Moments<kI16> : IntMoments<2> {
     static __device__ __forceinline__ void add(State &s, unsigned long long bits) { const long long v = (short)bits; s.sum.add_signed(v), s.squares.add_unsigned((unsigned long long)(v * v)); }
+    // eight values: their sum fits 32 bits, the sum of their squares (each at most 2^30) fits 64
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+        int total = 0;
+        unsigned long long squares = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int low = (short)(w[i] & 0xffffu), high = (int)w[i] >> 16;
+            total += low + high;
+            squares += (unsigned long long)(unsigned)(low * low) + (unsigned long long)(unsigned)(high * high);
+        }
+        s.sum.add_signed(total), s.squares.add_unsigned(squares);
+    }
 };
 template <> struct Moments<kU16> : IntMoments<2> {
     static __device__ __forceinline__ void add(State &s, unsigned long long bits) { const unsigned long long v = bits & 0xffffu; s.sum.add_unsigned(v), s.squares.add_unsigned(v * v); }
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+        uint32_t total = 0;
+        unsigned long long squares = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t low = w[i] & 0xffffu, high = w[i] >> 16;
+            total += low + high;
+            squares += (unsigned long long)(low * low) + (unsigned long long)(high * high);
+        }
+        s.sum.add_unsigned(total), s.squares.add_unsigned(squares);
+    }
 };
 template <> struct Moments<kI32> : IntMoments<4> {
     static __device__ __forceinline__ void add(State &s, unsigned long long bits) { const long long v = (int)bits; s.sum.add_signed(v), s.squares.add_unsigned((unsigned long long)(v * v)); }
@@ -200,34 +286,54 @@ template <> struct Moments<kU64> : IntMoments<8> {
 };
 // Sub-byte types: a byte holds two nibbles or eight bits, every one of them counts.
 template <> struct Moments<kU4> : IntMoments<1> {
-    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_word(s, (uint32_t)bits & 0xffu); }
-    static __device__ __forceinline__ void add_word(State &s, uint32_t word) {
+    static __device__ __forceinline__ void nibble_sums(uint32_t word, uint32_t &total, uint32_t &squares) {
         const uint32_t lo = word & 0x0f0f0f0fu, hi = (word >> 4) & 0x0f0f0f0fu;
-        s.sum.add_unsigned(__dp4a(lo, 0x01010101u, __dp4a(hi, 0x01010101u, 0u)));
-        s.squares.add_unsigned(__dp4a(lo, lo, __dp4a(hi, hi, 0u)));
+        total = __dp4a(lo, 0x01010101u, __dp4a(hi, 0x01010101u, total));
+        squares = __dp4a(lo, lo, __dp4a(hi, hi, squares));
+    }
+    static __device__ __forceinline__ void add(State &s, unsigned long long bits) {
+        uint32_t total = 0, squares = 0;
+        nibble_sums((uint32_t)bits & 0xffu, total, squares);
+        s.sum.add_unsigned(total), s.squares.add_unsigned(squares);
+    }
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+        uint32_t total = 0, squares = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) nibble_sums(w[i], total, squares);
+        s.sum.add_unsigned(total), s.squares.add_unsigned(squares);
     }
 };
 template <> struct Moments<kI4> : IntMoments<1> {
-    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { accumulate(s, (uint32_t)bits & 0xffu, 2); }
-    static __device__ __forceinline__ void add_word(State &s, uint32_t word) { accumulate(s, word, 8); }
     // A signed nibble n is (n ^ 8) - 8 = m - 8 with m in [0, 15]: sum = S1 - 8 k, squares = S2 - 16 S1 + 64 k over k nibbles.
-    static __device__ __forceinline__ void accumulate(State &s, uint32_t word, int nibbles) {
-        const uint32_t lo = (word & 0x0f0f0f0fu) ^ (nibbles == 8 ? 0x08080808u : 0x08u), hi = ((word >> 4) & 0x0f0f0f0fu) ^ (nibbles == 8 ? 0x08080808u : 0x08u);
-        const uint32_t s1 = __dp4a(lo, 0x01010101u, __dp4a(hi, 0x01010101u, 0u)), s2 = __dp4a(lo, lo, __dp4a(hi, hi, 0u));
+    static __device__ __forceinline__ void finish(State &s, uint32_t s1, uint32_t s2, int nibbles) {
         s.sum.add_signed((long long)s1 - 8 * nibbles);
         s.squares.add_unsigned((unsigned long long)((long long)s2 - 16ll * s1 + 64ll * nibbles));
     }
+    static __device__ __forceinline__ void add(State &s, unsigned long long bits) {
+        uint32_t s1 = 0, s2 = 0;
+        Moments<kU4>::nibble_sums(((uint32_t)bits & 0xffu) ^ 0x88u, s1, s2);
+        finish(s, s1, s2, 2);
+    }
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+        uint32_t s1 = 0, s2 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) Moments<kU4>::nibble_sums(w[i] ^ 0x88888888u, s1, s2);
+        finish(s, s1, s2, 32);
+    }
 };
 template <> struct Moments<kU1> : IntMoments<1> {
-    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_word(s, (uint32_t)bits & 0xffu); }
-    static __device__ __forceinline__ void add_word(State &s, uint32_t word) {
-        const unsigned long long ones = (unsigned long long)__popc(word);
+    static __device__ __forceinline__ void add(State &s, unsigned long long bits) {
+        const unsigned long long ones = (unsigned long long)__popc((uint32_t)bits & 0xffu);
+        s.sum.add_unsigned(ones), s.squares.add_unsigned(ones);
+    }
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+        const unsigned long long ones = (unsigned long long)(__popc(w[0]) + __popc(w[1]) + __popc(w[2]) + __popc(w[3]));
         s.sum.add_unsigned(ones), s.squares.add_unsigned(ones);
     }
 };
 
-template <typename T, typename = void> struct HasWordPath : std::false_type {};
-template <typename T> struct HasWordPath<T, std::void_t<decltype(&T::add_word)>> : std::true_type {};
+template <typename T, typename = void> struct HasVectorPath : std::false_type {};
+template <typename T> struct HasVectorPath<T, std::void_t<decltype(&T::add_vector)>> : std::true_type {};
 
 template <typename State>
 __device__ __forceinline__ State shuffle_down(const State &s, int delta) {
@@ -281,9 +387,8 @@ moments_partial_kernel(const uint8_t *__restrict__ data, uint64_t units, uint64_
         for (uint64_t v = thread; v < vectors; v += threads) {
             const uint4 q = base[v];
             const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-            if constexpr (HasWordPath<M>::value) {
-#pragma unroll
-                for (int w = 0; w < 4; ++w) M::add_word(state, words[w]);
+            if constexpr (HasVectorPath<M>::value) {
+                M::add_vector(state, words);
             } else if constexpr (kBytes == 8) {
                 M::add(state, (unsigned long long)words[0] | ((unsigned long long)words[1] << 32));
                 M::add(state, (unsigned long long)words[2] | ((unsigned long long)words[3] << 32));
