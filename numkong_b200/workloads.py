@@ -109,6 +109,22 @@ def run_maxsim(queries: int, docs: int, depth: int = 128, top: int = 100, q_toke
             "ms": seconds * 1e3, "gso_per_s": ops / seconds / 1e9, "steps": steps, "warmup": warmup}
 
 
+def run_quantise(values: int, dtype: str = "e4m3", steps: int = 5, seed: int = 7, warmup: int = 2):
+    """The step in front of `pack` when the source is f32: moments of the source (the scale comes from them) and the bulk
+    conversion to the storage type. Device-resident; reports both kernels in GB/s of algorithmic traffic."""
+    import torch
+    import numkong_b200 as nk
+    torch.manual_seed(seed)
+    x = torch.randn(values, device="cuda")
+    out = torch.empty(values * nk.CAST_BITS[dtype] // 8, dtype=torch.uint8, device="cuda")
+    stats = nk.moments(x)
+    s_moments = _timed(torch, lambda: nk.moments(x), steps, warmup)
+    s_cast = _timed(torch, lambda: nk.cast(x, dtype, out=out), steps, warmup)
+    return {"workload": "quantise", "values": values, "dtype": dtype, "sum": stats[0], "sumsq": stats[1],
+            "moments_ms": s_moments * 1e3, "moments_gbs": values * 4 / s_moments / 1e9,
+            "cast_ms": s_cast * 1e3, "cast_gbs": (values * 4 + out.numel()) / s_cast / 1e9}
+
+
 def _distributed(torch):
     import os
     import torch.distributed as dist
@@ -192,7 +208,8 @@ def run_maxsim_sharded(queries: int, docs: int, depth: int = 128, top: int = 100
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("workload", choices=["nearest", "maxsim"])
+    ap.add_argument("workload", choices=["nearest", "maxsim", "quantise"])
+    ap.add_argument("--values", type=int, default=1 << 26)
     ap.add_argument("--queries", type=int, default=None)
     ap.add_argument("--corpus", type=int, default=65536)
     ap.add_argument("--docs", type=int, default=20000)
@@ -203,7 +220,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--sharded", action="store_true", help="split the corpus / documents over the ranks of a torchrun launch")
     a = ap.parse_args()
-    if a.workload == "nearest":
+    if a.workload == "quantise":
+        out = run_quantise(a.values, a.dtype if a.dtype != "f16" else "e4m3", a.steps, warmup=a.warmup)
+    elif a.workload == "nearest":
         fn = run_nearest_sharded if a.sharded else run_nearest
         out = fn(a.queries or 8192, a.corpus, a.depth or 768, a.top or 10, a.dtype, a.steps, warmup=a.warmup)
     else:
