@@ -68,8 +68,52 @@ class ClockSampler:
 
     def __init__(self, device_index: int):
         self.device_index, self.proc, self.lines = device_index, None, []
+        self.nvml_samples, self.nvml_stop, self.nvml_thread, self.nvml_max = [], threading.Event(), None, None
+
+    def _start_nvml(self) -> bool:
+        """In-process NVML polling (read-only queries, about a thousand per second): the timed region of the default run
+        lasts some 15 ms, shorter than nvidia-smi's fastest sampling period."""
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.device_index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
+            self.nvml_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+
+            def poll():
+                while not self.nvml_stop.is_set():
+                    try:
+                        self.nvml_samples.append((time.time(), float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)), int(reasons_fn(handle))))
+                    except Exception:
+                        break
+                    time.sleep(0.0005)
+
+            self.nvml_thread = threading.Thread(target=poll, daemon=True)
+            self.nvml_thread.start()
+            return True
+        except Exception:
+            return False
+
+    def _stop_nvml(self, t0: float, t1: float):
+        self.nvml_stop.set()
+        self.nvml_thread.join(timeout=1.0)
+        inside = [(c, r) for (t, c, r) in self.nvml_samples if t0 <= t <= t1] or [(c, r) for (_, c, r) in self.nvml_samples]
+        sm = sorted(c for c, _ in inside)
+        # NVML reason bits: 0x4 sw_power_cap, 0x8 hw_slowdown, 0x20 sw_thermal_slowdown, 0x40 hw_thermal_slowdown
+        names = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
+        reasons = sorted({name for _, r in inside for bit, name in names.items() if r & bit})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None, "sm_max_mhz": self.nvml_max,
+                "reasons": reasons, "samples": len(sm), "source": "nvml polled inside the timed region"}
 
     def start(self):
+        if self._start_nvml():
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                           "-lms", "100", "-i", str(self.device_index)], stdout=subprocess.PIPE, text=True)
@@ -83,6 +127,8 @@ class ClockSampler:
             self.lines.append((time.time(), line.strip()))
 
     def stop(self, t0: float, t1: float):
+        if self.nvml_thread is not None:
+            return self._stop_nvml(t0, t1)
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
