@@ -24,6 +24,7 @@
 #include <cstring>
 #include <cuda_fp16.h>
 #include "nkb_internal.h"
+#include "nkb_decode.cuh"
 #include "nkb_host.h"
 #include "../../include/numkong_b200.h"
 
@@ -94,18 +95,6 @@ __device__ __forceinline__ uint32_t encode_fp6(float x, int man_bits, int bias) 
     const uint32_t code = round_to_grid(a, man_bits, bias);  // infinities and NaN land far above the range
     return sign | (code > 0x1fu ? 0x1fu : code);
 }
-
-// Decoders: every one of these formats is a binary16 with fewer bits, so its bits are moved into a binary16 pattern
-// and the exponent bias difference is made up with an exact power-of-two multiplication.
-__device__ __forceinline__ float decode_f16(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
-__device__ __forceinline__ float decode_bf16(uint32_t h) { return __uint_as_float(h << 16); }
-__device__ __forceinline__ float decode_e4m3(uint32_t c) {
-    if ((c & 0x7fu) == 0x7fu) return __uint_as_float(((c & 0x80u) << 24) | 0x7fc00000u);
-    return decode_f16(((c & 0x80u) << 8) | ((c & 0x7fu) << 7)) * 256.0f;
-}
-__device__ __forceinline__ float decode_e5m2(uint32_t c) { return decode_f16((c & 0xffu) << 8); }
-__device__ __forceinline__ float decode_e2m3(uint32_t c) { return decode_f16(((c & 0x20u) << 10) | ((c & 0x1fu) << 7)) * 16384.0f; }
-__device__ __forceinline__ float decode_e3m2(uint32_t c) { return decode_f16(((c & 0x20u) << 10) | ((c & 0x1fu) << 8)) * 4096.0f; }
 
 // ---- integers out of the f64 hub ----
 __device__ __forceinline__ long long f64_to_signed(double v, double lo, double hi) {
@@ -190,12 +179,12 @@ cast_kernel(const uint8_t *__restrict__ from, uint8_t *__restrict__ to, uint64_t
             switch (from_type) {
             case kF64: f[l] = __longlong_as_double((long long)raw_quad(raw, l)); break;
             case kF32: f[l] = (double)__uint_as_float(raw[l]); break;
-            case kF16: f[l] = (double)decode_f16(raw_half(raw, l)); break;
-            case kBF16: f[l] = (double)decode_bf16(raw_half(raw, l)); break;
-            case kE4M3: f[l] = (double)decode_e4m3(raw_byte(raw, l)); break;
-            case kE5M2: f[l] = (double)decode_e5m2(raw_byte(raw, l)); break;
-            case kE2M3: f[l] = (double)decode_e2m3(raw_byte(raw, l)); break;
-            case kE3M2: f[l] = (double)decode_e3m2(raw_byte(raw, l)); break;
+            case kF16: f[l] = (double)decode_bits<kF16>(raw_half(raw, l)); break;
+            case kBF16: f[l] = (double)decode_bits<kBF16>(raw_half(raw, l)); break;
+            case kE4M3: f[l] = (double)decode_bits<kE4M3>(raw_byte(raw, l)); break;
+            case kE5M2: f[l] = (double)decode_bits<kE5M2>(raw_byte(raw, l)); break;
+            case kE2M3: f[l] = (double)decode_bits<kE2M3>(raw_byte(raw, l)); break;
+            case kE3M2: f[l] = (double)decode_bits<kE3M2>(raw_byte(raw, l)); break;
             case kI64: f[l] = (double)(long long)raw_quad(raw, l); break;
             case kU64: f[l] = (double)raw_quad(raw, l); break;
             case kI32: f[l] = (double)(int)raw[l]; break;
@@ -348,19 +337,19 @@ template <> struct Scalar32<kF32> {
 };
 template <> struct Scalar32<kF16> {
     static constexpr int kBytes = 2;
-    static __device__ __forceinline__ float decode(uint32_t b) { return decode_f16(b); }
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_bits<kF16>(b); }
     static __device__ __forceinline__ uint32_t encode(float x) { return encode_f16(x); }
     static __device__ __forceinline__ uint32_t encode2(float a, float b) { return encode(a) | (encode(b) << (8 * kBytes)); }
 };
 template <> struct Scalar32<kBF16> {
     static constexpr int kBytes = 2;
-    static __device__ __forceinline__ float decode(uint32_t b) { return decode_bf16(b); }
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_bits<kBF16>(b); }
     static __device__ __forceinline__ uint32_t encode(float x) { return encode_bf16(x); }
     static __device__ __forceinline__ uint32_t encode2(float a, float b) { return encode(a) | (encode(b) << (8 * kBytes)); }
 };
 template <> struct Scalar32<kE4M3> {
     static constexpr int kBytes = 1;
-    static __device__ __forceinline__ float decode(uint32_t b) { return decode_e4m3(b); }
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_bits<kE4M3>(b); }
     static __device__ __forceinline__ uint32_t encode(float x) { return encode_e4m3(x); }
     static __device__ __forceinline__ uint32_t encode2(float a, float b) {
         const uint32_t packed = hw_pair_e4m3(a, b);
@@ -369,7 +358,7 @@ template <> struct Scalar32<kE4M3> {
 };
 template <> struct Scalar32<kE5M2> {
     static constexpr int kBytes = 1;
-    static __device__ __forceinline__ float decode(uint32_t b) { return decode_e5m2(b); }
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_bits<kE5M2>(b); }
     static __device__ __forceinline__ uint32_t encode(float x) { return encode_e5m2(x); }
     static __device__ __forceinline__ uint32_t encode2(float a, float b) {
         const uint32_t packed = hw_pair_e5m2(a, b);
@@ -378,7 +367,7 @@ template <> struct Scalar32<kE5M2> {
 };
 template <> struct Scalar32<kE2M3> {
     static constexpr int kBytes = 1;
-    static __device__ __forceinline__ float decode(uint32_t b) { return decode_e2m3(b); }
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_bits<kE2M3>(b); }
     static __device__ __forceinline__ uint32_t encode(float x) { return encode_fp6(x, 3, 1); }
     static __device__ __forceinline__ uint32_t encode2(float a, float b) {
         const uint32_t packed = hw_pair_e2m3(a, b);
@@ -387,7 +376,7 @@ template <> struct Scalar32<kE2M3> {
 };
 template <> struct Scalar32<kE3M2> {
     static constexpr int kBytes = 1;
-    static __device__ __forceinline__ float decode(uint32_t b) { return decode_e3m2(b); }
+    static __device__ __forceinline__ float decode(uint32_t b) { return decode_bits<kE3M2>(b); }
     static __device__ __forceinline__ uint32_t encode(float x) { return encode_fp6(x, 2, 3); }
     static __device__ __forceinline__ uint32_t encode2(float a, float b) {
         const uint32_t packed = hw_pair_e3m2(a, b);

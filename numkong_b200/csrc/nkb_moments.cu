@@ -22,6 +22,7 @@
 #include <type_traits>
 #include <cuda_fp16.h>
 #include "nkb_internal.h"
+#include "nkb_decode.cuh"
 #include "nkb_host.h"
 #include "../../include/numkong_b200.h"
 
@@ -29,8 +30,6 @@ namespace nkb {
 namespace {
 
 enum MomentsDtype : uint32_t { kI16 = 1u << 3, kI32 = 1u << 4, kI64 = 1u << 5, kU16 = 1u << 7, kU32 = 1u << 8, kU64 = 1u << 9 };
-
-__device__ __forceinline__ float half_bits_to_f32(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
 
 // 128-bit accumulator (two's complement when used for signed sums).
 struct Wide {
@@ -109,10 +108,10 @@ template <> struct Moments<kF32> : FloatMoments<4, false> {
     static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)__uint_as_float((uint32_t)bits)); }
 };
 template <> struct Moments<kF16> : FloatMoments<2, false> {
-    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)half_bits_to_f32((uint32_t)bits)); }
+    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)decode_bits<kF16>((uint32_t)bits)); }
 };
 template <> struct Moments<kBF16> : FloatMoments<2, false> {
-    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)__uint_as_float((uint32_t)bits << 16)); }
+    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)decode_bits<kBF16>((uint32_t)bits)); }
 };
 // The sixteen values of a vector of e4m3 / e2m3 / e3m2 add up EXACTLY in f32 (values are multiples of 2^-9 / 2^-3 / 2^-4
 // and sixteen of them stay below 2^13 / 2^7 / 2^9), and so do their squares for the two 6-bit formats. e4m3 squares span
@@ -123,19 +122,17 @@ template <> struct Moments<kBF16> : FloatMoments<2, false> {
 struct E4M3Format {
     static constexpr float kScale = 256.0f;
     static __device__ __forceinline__ uint32_t half_pair(uint32_t x) { return (x & 0x80008000u) | ((x >> 1) & 0x3f803f80u); }
-    static __device__ __forceinline__ float decode(uint32_t c) {
-        return (c & 0x7fu) == 0x7fu ? __uint_as_float(0x7fc00000u) : half_bits_to_f32(((c & 0x80u) << 8) | ((c & 0x7fu) << 7)) * 256.0f;
-    }
+    static __device__ __forceinline__ float decode(uint32_t c) { return decode_bits<kE4M3>(c); }
 };
 struct E2M3Format {
     static constexpr float kScale = 16384.0f;
     static __device__ __forceinline__ uint32_t half_pair(uint32_t x) { return ((x & 0x20002000u) << 2) | ((x >> 1) & 0x0f800f80u); }
-    static __device__ __forceinline__ float decode(uint32_t c) { return half_bits_to_f32(((c & 0x20u) << 10) | ((c & 0x1fu) << 7)) * 16384.0f; }
+    static __device__ __forceinline__ float decode(uint32_t c) { return decode_bits<kE2M3>(c); }
 };
 struct E3M2Format {
     static constexpr float kScale = 4096.0f;
     static __device__ __forceinline__ uint32_t half_pair(uint32_t x) { return ((x & 0x20002000u) << 2) | (x & 0x1f001f00u); }
-    static __device__ __forceinline__ float decode(uint32_t c) { return half_bits_to_f32(((c & 0x20u) << 10) | ((c & 0x1fu) << 8)) * 4096.0f; }
+    static __device__ __forceinline__ float decode(uint32_t c) { return decode_bits<kE3M2>(c); }
 };
 // Codes 2p and 2p+1 of a word as f32 values divided by kScale.
 template <typename Format>
@@ -173,7 +170,7 @@ template <> struct Moments<kE4M3> : FloatMoments<1, false> {
     }
 };
 template <> struct Moments<kE5M2> : FloatMoments<1, false> {
-    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)half_bits_to_f32(((uint32_t)bits & 0xffu) << 8)); }
+    static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)decode_bits<kE5M2>((uint32_t)bits)); }
 };
 template <typename Format>
 struct Fp6Moments : FloatMoments<1, false> {
