@@ -29,7 +29,7 @@ __all__ = [
     "dots_symmetric", "angulars_symmetric", "euclideans_symmetric",
     "hammings_packed", "jaccards_packed", "hammings_symmetric", "jaccards_symmetric",
     "maxsim_pack", "maxsim_packed", "maxsim", "maxsims_packed", "angulars_packed_topk", "euclideans_packed_topk",
-    "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error", "dots_compact", "cast", "moments",
+    "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error", "dots_compact", "cast", "moments", "set_accumulation_span",
 ]
 
 _NUMPY_NAMES = {
@@ -577,6 +577,12 @@ def synchronize() -> int:
 
 def set_stream(cuda_stream: int) -> None:
     lib.nkb_set_stream(ctypes.c_void_p(cuda_stream))
+
+
+def set_accumulation_span(stages: int) -> None:
+    """Stages (128 bytes of depth each) the tensor cores accumulate before the partial sums are added with round-to-nearest;
+    0 = automatic. Shorter spans are slower and more accurate for bf16 / f16 products (nkb_set_accumulation_span)."""
+    lib.nkb_set_accumulation_span(int(stages))
 
 
 def launch_count() -> int:

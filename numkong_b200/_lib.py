@@ -60,6 +60,7 @@ def _load() -> ctypes.CDLL:
     lib.nkb_synchronize.restype, lib.nkb_synchronize.argtypes = ctypes.c_uint32, []
     lib.nkb_launch_count.restype, lib.nkb_launch_count.argtypes = ctypes.c_uint64, []
     lib.nkb_set_gemm_variant.restype, lib.nkb_set_gemm_variant.argtypes = None, [ctypes.c_int]
+    lib.nkb_set_accumulation_span.restype, lib.nkb_set_accumulation_span.argtypes = None, [ctypes.c_int]
     lib.nkb_release_caches.restype, lib.nkb_release_caches.argtypes = None, []
     lib.nkb_set_fp6_native.restype, lib.nkb_set_fp6_native.argtypes = None, [ctypes.c_int]
     lib.nkb_set_topk_panel_rows.restype, lib.nkb_set_topk_panel_rows.argtypes = None, [sz]

@@ -583,6 +583,10 @@ NKB_API uint32_t nkb_synchronize(void) {
 }
 NKB_API uint64_t nkb_launch_count(void) { return g_launches.load(); }
 NKB_API void nkb_set_gemm_variant(int variant) { g_variant.store(variant); }
+NKB_API void nkb_set_accumulation_span(int stages) {
+    const int span = stages < 0 ? 0 : (stages > 255 ? 255 : stages);
+    g_variant.store((g_variant.load() & ~0xff00) | (span << 8));
+}
 NKB_API void nkb_set_fp6_native(int native) { g_fp6_native.store(native ? 1 : 0); }
 NKB_API void nkb_release_caches(void) {
     cudaDeviceSynchronize();

@@ -819,9 +819,11 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     // depth 1000; the 8/6-bit kinds sit ten times lower and level off at 1e-8. Reading a 128 KiB accumulator out of
     // TMEM stalls the MMAs for ~256 cycles, so spans are made as long as the error target (1e-7, NumKong's own f32
     // kernels measure 3e-8..7e-8) allows: span = 12 * sqrt(depth) values for 16-bit floats, capped at 16 stages;
-    // 16 stages for the 8/6-bit kinds. Integers are exact: one span.
-    const uint32_t forced_flush = (uint32_t)args.variant >> 8;
-    uint32_t auto_flush = 16u;
+    // 16 stages for the 8/6-bit kinds (measured at depth 8192: the same error as the reference's own kernels; 32 stages
+    // double it on wide-range inputs). e2m3 products are multiples of 2^-6 of at most 56.25, so up to 4660 of them add
+    // up exactly in f32 whatever the inputs: 32 stages (4096 values). Integers are exact: one span.
+    const uint32_t forced_flush = ((uint32_t)args.variant >> 8) & 0xffu;  // nkb_set_accumulation_span
+    uint32_t auto_flush = args.dtype == kE2M3 ? 32u : 16u;
     if (ki.kind == kKindF16) {
         uint32_t span_values = (uint32_t)(12.0 * sqrt((double)args.k));
         auto_flush = span_values / dev.elems_per_kblock;

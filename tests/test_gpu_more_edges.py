@@ -61,3 +61,24 @@ def test_short_depth_products_with_ragged_shapes(dtype, k):
             assert np.max(np.abs(got.cpu().numpy() - ref)) <= 5e-7
         else:
             assert np.max(np.abs(got.cpu().numpy() - ref) / np.maximum(np.abs(ref), 1e-3)) <= 4e-6
+
+
+def test_accumulation_span_trades_speed_for_accuracy():
+    """Same-sign bf16 data at depth 4096 (the worst case of the truncating tensor-core accumulate): shorter spans bring the
+    error down in proportion, and at 4 stages it is at the level of the reference's own scalar kernel (about 3 units in
+    the last place at this depth)."""
+    a, b = syn.lognormal_matrix(256, 4096, "bf16", 1), syn.lognormal_matrix(512, 4096, "bf16", 2)
+    exact = oracle.exact_dots_f64(a, b, "bf16")
+    nearest = exact.astype(np.float32)
+    ulp = np.spacing(np.abs(nearest)).astype(np.float64)
+    packed = nk.dots_pack(b, "bf16")
+    errors = {}
+    try:
+        for stages in (0, 8, 4):
+            nk.set_accumulation_span(stages)
+            c = nk.dots_packed(a, packed, dtype="bf16")
+            errors[stages] = float(np.mean(np.abs(c.astype(np.float64) - nearest.astype(np.float64)) / ulp))
+    finally:
+        nk.set_accumulation_span(0)
+    assert errors[4] < errors[8] < errors[0]
+    assert errors[4] <= 3.0 and errors[0] <= 25.0
