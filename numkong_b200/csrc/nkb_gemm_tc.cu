@@ -13,6 +13,7 @@
 //   warps 2..9  epilogue: tcgen05.ld of their 32-lane quarter and column half, f32/i32 summation of the
 //               accumulation spans in registers, finalisation, global stores
 #include <cmath>
+#include <type_traits>
 #include "nkb_internal.h"
 #include "nkb_ptx.cuh"
 
@@ -107,6 +108,13 @@ __device__ __forceinline__ float sqrt_approx(float x) {
     return r;
 }
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueWarps * 32) : "memory"); }
+// The same barrier, returning the OR of `flag` over the epilogue threads.
+__device__ __forceinline__ bool epilogue_barrier_any(bool flag) {
+    uint32_t any;
+    asm volatile("{\n\t.reg .pred in, out;\n\tsetp.ne.u32 in, %1, 0;\n\tbar.red.or.pred out, 1, %2, in;\n\tselp.u32 %0, 1, 0, out;\n\t}"
+                 : "=r"(any) : "r"((uint32_t)flag), "n"(kEpilogueWarps * 32) : "memory");
+    return any != 0;
+}
 
 // Column factor of one packed row for the distance epilogues: 1/|b| (0 for a zero row) for angular, |b|^2 for euclidean.
 template <int kEpi>
@@ -119,12 +127,18 @@ __device__ __forceinline__ float column_factor(const GemmDev &p, uint32_t col) {
 }
 
 // One finalised distance. Never NaN and never below -0: a NaN dot or factor falls out of fmaxf as 0.
-template <int kEpi>
+//   kFloat       the accumulator holds f32 bits (known at compile time for the float kinds; the integer kinds read `int_mode`)
+//   kZeroRule    apply the zero-norm rule of the angular distance; callers switch it off for a tile whose row and column
+//                factors are all non-zero, which is nearly every tile
+template <int kEpi, bool kFloat, bool kZeroRule = true>
 __device__ __forceinline__ float distance_value(uint32_t raw, uint32_t int_mode, float row_factor, float col_factor) {
-    const float dot = int_mode == 0 ? __uint_as_float(raw) : int_mode == 1 ? (float)(int32_t)raw : (float)raw;
+    float dot;
+    if constexpr (kFloat) dot = __uint_as_float(raw);
+    else dot = int_mode == 1 ? (float)(int32_t)raw : (float)raw;
     if constexpr (kEpi == kEpiAngular) {
         float r = fmaxf(fmaf(-(dot * row_factor), col_factor, 1.0f), 0.0f);
-        if (row_factor == 0.0f || col_factor == 0.0f) r = dot == 0.0f ? 0.0f : 1.0f;
+        if constexpr (kZeroRule)
+            if (row_factor == 0.0f || col_factor == 0.0f) r = dot == 0.0f ? 0.0f : 1.0f;
         return r;
     } else {
         return sqrt_approx(fmaxf(fmaf(-2.0f, dot, row_factor + col_factor), 0.0f));
@@ -135,7 +149,7 @@ __device__ __forceinline__ float distance_value(uint32_t raw, uint32_t int_mode,
 // AND-popcount, the factors are the two population counts, exact in f32 below 2^24) follow
 // include/numkong/set/serial.h:150-168: Hamming = |a| + |b| - 2 |a & b| in u32, Jaccard = 1 - |a & b| / (|a| + |b| - |a & b|)
 // in f32 with the reference's operation order (0 for two empty sets).
-template <int kEpi>
+template <int kEpi, bool kFloat, bool kZeroRule = true>
 __device__ __forceinline__ uint32_t cell_bits(uint32_t raw, uint32_t int_mode, float row_factor, float col_factor) {
     if constexpr (kEpi == kEpiHamming) {
         return __float2uint_rn(row_factor) + __float2uint_rn(col_factor) - 2u * raw;
@@ -144,7 +158,7 @@ __device__ __forceinline__ uint32_t cell_bits(uint32_t raw, uint32_t int_mode, f
         const float union_size = row_factor + col_factor - dot;
         return __float_as_uint(union_size != 0.0f ? 1.0f - __fdiv_rn(dot, union_size) : 0.0f);
     } else {
-        return __float_as_uint(distance_value<kEpi>(raw, int_mode, row_factor, col_factor));
+        return __float_as_uint(distance_value<kEpi, kFloat, kZeroRule>(raw, int_mode, row_factor, col_factor));
     }
 }
 
@@ -154,30 +168,34 @@ __device__ __forceinline__ uint32_t cell_bits(uint32_t raw, uint32_t int_mode, f
 // patterns is their numeric order (with -0 before +0, as the selection kernels order them) and one integer compare per
 // value decides. Pass 1 only builds a bit mask; a row then reserves all its slots with ONE atomic (a per-value atomic
 // would put its round trip on the critical path of every hit), and pass 2 recomputes and writes the few hits.
-template <int kEpi, int kCols>
+template <int kEpi, int kCols, bool kFloat>
 __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDev &p, uint32_t my_row, uint32_t col_base,
-                                            float row_factor, const float *colf, uint32_t *stage, int lane) {
+                                            float row_factor, const float *colf, uint32_t *stage, int lane, bool zero_factors) {
     static_assert(kCols % 32 == 0, "whole mask words");
     const int threshold = my_row < p.m ? (int)__ldg(p.threshold_bits + my_row) : (int)0x80000000;
     uint32_t mask[kCols / 32];
+    auto build_masks = [&](auto zero_rule) {
 #pragma unroll
-    for (int w = 0; w < kCols / 32; ++w) {
-        uint32_t bits = 0;
+        for (int w = 0; w < kCols / 32; ++w) {
+            uint32_t bits = 0;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const float4 f = *reinterpret_cast<const float4 *>(colf + w * 32 + c * 4);
-            const float cf[4] = {f.x, f.y, f.z, f.w};
+            for (int c = 0; c < 8; ++c) {
+                const float4 f = *reinterpret_cast<const float4 *>(colf + w * 32 + c * 4);
+                const float cf[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float r = distance_value<kEpi>(acc[w * 32 + c * 4 + j], p.int_mode, row_factor, cf[j]);
-                bits |= (uint32_t)((int)__float_as_uint(r) < threshold) << (c * 4 + j);
+                for (int j = 0; j < 4; ++j) {
+                    const float r = distance_value<kEpi, kFloat, decltype(zero_rule)::value>(acc[w * 32 + c * 4 + j], p.int_mode, row_factor, cf[j]);
+                    bits |= (uint32_t)((int)__float_as_uint(r) < threshold) << (c * 4 + j);
+                }
             }
+            // Columns past the end of the packed matrix are padding.
+            const uint32_t first = col_base + w * 32;
+            const uint32_t valid = first >= p.n ? 0u : (p.n - first >= 32u ? 0xffffffffu : (1u << (p.n - first)) - 1u);
+            mask[w] = bits & valid;
         }
-        // Columns past the end of the packed matrix are padding.
-        const uint32_t first = col_base + w * 32;
-        const uint32_t valid = first >= p.n ? 0u : (p.n - first >= 32u ? 0xffffffffu : (1u << (p.n - first)) - 1u);
-        mask[w] = bits & valid;
-    }
+    };
+    if (zero_factors) build_masks(std::true_type{});
+    else build_masks(std::false_type{});
     uint32_t hits = 0;
 #pragma unroll
     for (int w = 0; w < kCols / 32; ++w) hits += __popc(mask[w]);
@@ -199,7 +217,7 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
         while (m16) {
             const int j = __ffs((int)m16) - 1;
             m16 &= m16 - 1;
-            const float r = distance_value<kEpi>(mine[j], p.int_mode, row_factor, colf[c * 16 + j]);
+            const float r = distance_value<kEpi, kFloat>(mine[j], p.int_mode, row_factor, colf[c * 16 + j]);
             if (slot < p.candidate_capacity) list[slot] = make_uint2(__float_as_uint(r), col_base + c * 16 + j + p.column_id_base);
             ++slot;
         }
@@ -212,9 +230,10 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
 //   colf      this tile's column factors in shared memory, indexed by column inside the tile;  colf_off  col_base inside the tile
 // Angular: max(0, 1 - dot/(|a||b|)), and for a zero norm 0 when the dot is 0 else 1 (include/numkong/spatial/serial.h:257-269).
 // Euclidean: sqrt(max(0, |a|^2 + |b|^2 - 2 dot)) (include/numkong/spatial/serial.h:272-278).
-template <int kEpi, int kCols, int kW = 16>
+//   zero_cols  some column factor of this tile is 0 (a zero vector, or padding past the last column)
+template <int kEpi, int kCols, int kW, bool kFloat>
 __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev &p, uint32_t row_base, uint32_t col_base,
-                                           uint32_t *stage, const float *colf, uint32_t colf_off, int lane) {
+                                           uint32_t *stage, const float *colf, uint32_t colf_off, int lane, bool zero_cols) {
     constexpr int kPitch = kW + 4;          // words per staged row (keeps 16-byte accesses aligned and conflict-free)
     constexpr int kQuads = kW / 4;          // 16-byte pieces per staged row
     constexpr int kRowsPerStore = 32 / kQuads;
@@ -225,12 +244,16 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
         float an = my_row < p.m ? p.a_norms[my_row] : 0.0f;
         row_factor = kEpi == kEpiAngular ? (an > 0.0f ? rsqrt_refined(an) : 0.0f) : an;
     }
+    // The angular zero-norm rule is only compiled into the path taken when this row or some column of the tile has a zero factor.
+    // The predicate is uniform over the warp: the store loop below synchronises the warp.
+    const bool zero_factors = kEpi == kEpiAngular && (zero_cols || __any_sync(0xffffffffu, row_factor == 0.0f));
     if constexpr (kEpi == kEpiAngular || kEpi == kEpiEuclidean) {
         if (p.candidates != nullptr) {
-            filter_tile<kEpi, kCols>(acc, p, my_row, col_base, row_factor, colf + colf_off, stage, lane);
+            filter_tile<kEpi, kCols, kFloat>(acc, p, my_row, col_base, row_factor, colf + colf_off, stage, lane, zero_factors);
             return;
         }
     }
+    auto emit = [&](auto zero_rule) {
 #pragma unroll
     for (int c = 0; c < kCols / kW; ++c) {
         const uint32_t col0 = col_base + c * kW;
@@ -245,7 +268,7 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
             for (int j = 0; j < 4; ++j) {
                 const uint32_t raw = acc[c * kW + q * 4 + j];
                 if constexpr (kEpi == kEpiDot) out[j] = raw;
-                else out[j] = cell_bits<kEpi>(raw, p.int_mode, row_factor, cf[j]);
+                else out[j] = cell_bits<kEpi, kFloat, decltype(zero_rule)::value>(raw, p.int_mode, row_factor, cf[j]);
             }
             *reinterpret_cast<uint4 *>(stage + lane * kPitch + q * 4) = make_uint4(out[0], out[1], out[2], out[3]);
         }
@@ -272,6 +295,9 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
         }
         __syncwarp();
     }
+    };
+    if (zero_factors) emit(std::true_type{});
+    else emit(std::false_type{});
 }
 
 template <int kKind, int kBN, int kStages, int kEpi>
@@ -404,11 +430,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
             uint32_t mt, nt;
             tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
             if (tile_skipped(p.tri_diag, mt * kBM, (nt + 1) * kBN)) continue;
+            bool zero_cols = false;
             if constexpr (kEpi != kEpiDot) {
                 // One column factor per epilogue thread, shared by all rows of the tile (double-buffered by tile parity).
                 const uint32_t e = threadIdx.x - 64u;
-                colf[(local_tile & 1u) * 256 + e] = e < (uint32_t)kBN ? column_factor<kEpi>(p, nt * kBN + e) : 0.0f;
-                epilogue_barrier();
+                const float factor = e < (uint32_t)kBN ? column_factor<kEpi>(p, nt * kBN + e) : 1.0f;
+                colf[(local_tile & 1u) * 256 + e] = factor;
+                zero_cols = epilogue_barrier_any(factor == 0.0f);
             }
             uint32_t acc[kColsPerThread];
 #pragma unroll
@@ -418,23 +446,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                 const uint32_t buf_phase = (seq >> 1) & 1u;
                 if (!mbar_wait(tmem_full_bar(buf), buf_phase, 4, p.error_word)) { ok = false; break; }
                 tc_fence_after_sync();
+                if (kb0 == 0) {
+                    // First span of a tile: nothing to add to, so every load goes straight into the accumulators and all of
+                    // them are in flight before the one wait.
 #pragma unroll
-                for (int c = 0; c < kColsPerThread / 16; ++c) {
-                    uint32_t v[16];
-                    tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 16, v);
-                    tmem_ld_wait();
+                    for (int c = 0; c < kColsPerThread / 16; ++c)
+                        tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 16,
+                                      *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if constexpr (kKind == kKindI8) acc[c * 16 + j] += v[j];
-                        else acc[c * 16 + j] = __float_as_uint(__uint_as_float(acc[c * 16 + j]) + __uint_as_float(v[j]));
+                    for (int c = 0; c < kColsPerThread / 32; ++c) tmem_ld_wait_for(*reinterpret_cast<uint32_t(*)[32]>(&acc[c * 32]));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < kColsPerThread / 16; ++c) {
+                        uint32_t v[16];
+                        tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 16, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if constexpr (kKind == kKindI8) acc[c * 16 + j] += v[j];
+                            else acc[c * 16 + j] = __float_as_uint(__uint_as_float(acc[c * 16 + j]) + __uint_as_float(v[j]));
+                        }
                     }
                 }
                 tc_fence_before_sync();
                 mbar_arrive(tmem_empty_bar(buf));
             }
             if (!ok) continue;  // nothing valid to store; the next tile's barrier is still met
-            store_tile<kEpi, kColsPerThread, Plan::kStageCols>(acc, p, mt * kBM + quarter * 32u, nt * kBN + half * kColsPerThread,
-                                                               epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane);
+            store_tile<kEpi, kColsPerThread, Plan::kStageCols, kKind != kKindI8>(acc, p, mt * kBM + quarter * 32u, nt * kBN + half * kColsPerThread,
+                                                                                  epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane, zero_cols);
             ++local_tile;
         }
     }
@@ -578,10 +617,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
             uint32_t mt, nt;
             tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
             if (tile_skipped(p.tri_diag, mt * 256u, (nt + 1) * kBN)) continue;
+            bool zero_cols = false;
             if constexpr (kEpi != kEpiDot) {
                 const uint32_t e = threadIdx.x - 64u;
-                colf[(local_tile & 1u) * 256 + e] = column_factor<kEpi>(p, nt * kBN + e);
-                epilogue_barrier();
+                const float factor = column_factor<kEpi>(p, nt * kBN + e);
+                colf[(local_tile & 1u) * 256 + e] = factor;
+                zero_cols = epilogue_barrier_any(factor == 0.0f);
             }
             uint32_t acc[kColsPerThread];
 #pragma unroll
@@ -590,15 +631,26 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 const uint32_t buf = seq & 1u, buf_phase = (seq >> 1) & 1u;
                 if (!mbar_wait<true>(tmem_full_bar(buf), buf_phase, 4, p.error_word)) { ok = false; break; }
                 tc_fence_after_sync();
+                if (kb0 == 0) {
+                    // First span of a tile: nothing to add to, so every load goes straight into the accumulators and all of
+                    // them are in flight before the one wait.
 #pragma unroll
-                for (int c = 0; c < kColsPerThread / 16; ++c) {
-                    uint32_t v[16];
-                    tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 16, v);
-                    tmem_ld_wait();
+                    for (int c = 0; c < kColsPerThread / 16; ++c)
+                        tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 16,
+                                      *reinterpret_cast<uint32_t(*)[16]>(&acc[c * 16]));
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if constexpr (kKind == kKindI8) acc[c * 16 + j] += v[j];
-                        else acc[c * 16 + j] = __float_as_uint(__uint_as_float(acc[c * 16 + j]) + __uint_as_float(v[j]));
+                    for (int c = 0; c < kColsPerThread / 32; ++c) tmem_ld_wait_for(*reinterpret_cast<uint32_t(*)[32]>(&acc[c * 32]));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < kColsPerThread / 16; ++c) {
+                        uint32_t v[16];
+                        tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 16, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if constexpr (kKind == kKindI8) acc[c * 16 + j] += v[j];
+                            else acc[c * 16 + j] = __float_as_uint(__uint_as_float(acc[c * 16 + j]) + __uint_as_float(v[j]));
+                        }
                     }
                 }
                 tc_fence_before_sync();
@@ -606,8 +658,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(tmem_empty_bar(buf), 0));
             }
             if (!ok) continue;
-            store_tile<kEpi, kColsPerThread>(acc, p, mt * 256u + rank * 128u + quarter * 32u, nt * kBN + half * kColsPerThread,
-                                             epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane);
+            store_tile<kEpi, kColsPerThread, 16, kKind != kKindI8>(acc, p, mt * 256u + rank * 128u + quarter * 32u, nt * kBN + half * kColsPerThread,
+                                                                   epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane, zero_cols);
             ++local_tile;
         }
     }
