@@ -194,8 +194,43 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
             mask[w] = bits & valid;
         }
     };
-    if (zero_factors) build_masks(std::true_type{});
-    else build_masks(std::false_type{});
+    // Angular distances of float kinds, no zero factor in sight: a two-instruction prefilter per value. r < threshold needs
+    // dot * col_factor > (1 - threshold) / row_factor up to the rounding of the three operations behind r; with the bound
+    // lowered by 2^-18 (relative to 1 + |1 - threshold|) no value below the threshold can be missed, and the few extra ones
+    // are weeded out when pass 2 recomputes r. The sign bit of fma(-dot, col_factor, bound) is the decision; a funnel shift
+    // collects it (columns are walked downwards so that bit i ends up standing for column i).
+    bool prefiltered = false;
+    if constexpr (kEpi == kEpiAngular && kFloat) {
+        if (!zero_factors) {
+            prefiltered = true;
+            float bound;
+            if (my_row >= p.m) bound = __uint_as_float(0x7f800000u);             // nothing passes
+            else if (threshold == 0x7fffffff) bound = __uint_as_float(0xff800000u);  // no threshold yet: everything passes
+            else {
+                const float b = 1.0f - __int_as_float(threshold), w = __frcp_rn(row_factor);
+                bound = fmaf(b, w, -(fabsf(b) + 1.0f) * w * 0x1p-18f);
+            }
+#pragma unroll
+            for (int w = 0; w < kCols / 32; ++w) {
+                uint32_t bits = 0;
+#pragma unroll
+                for (int c = 7; c >= 0; --c) {
+                    const float4 f = *reinterpret_cast<const float4 *>(colf + w * 32 + c * 4);
+                    const float cf[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                    for (int j = 3; j >= 0; --j)
+                        bits = __funnelshift_l(__float_as_uint(fmaf(-__uint_as_float(acc[w * 32 + c * 4 + j]), cf[j], bound)), bits, 1);
+                }
+                const uint32_t first = col_base + w * 32;
+                const uint32_t valid = first >= p.n ? 0u : (p.n - first >= 32u ? 0xffffffffu : (1u << (p.n - first)) - 1u);
+                mask[w] = bits & valid;
+            }
+        }
+    }
+    if (!prefiltered) {
+        if (zero_factors) build_masks(std::true_type{});
+        else build_masks(std::false_type{});
+    }
     uint32_t hits = 0;
 #pragma unroll
     for (int w = 0; w < kCols / 32; ++w) hits += __popc(mask[w]);
@@ -218,7 +253,10 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
             const int j = __ffs((int)m16) - 1;
             m16 &= m16 - 1;
             const float r = distance_value<kEpi, kFloat>(mine[j], p.int_mode, row_factor, colf[c * 16 + j]);
-            if (slot < p.candidate_capacity) list[slot] = make_uint2(__float_as_uint(r), col_base + c * 16 + j + p.column_id_base);
+            // A value the prefilter let through although it is not below the threshold keeps its reserved slot as +infinity,
+            // which the selection sorts behind everything else.
+            const uint32_t value = (int)__float_as_uint(r) < threshold ? __float_as_uint(r) : 0x7f800000u;
+            if (slot < p.candidate_capacity) list[slot] = make_uint2(value, col_base + c * 16 + j + p.column_id_base);
             ++slot;
         }
     }
