@@ -287,8 +287,8 @@ NKB_API uint64_t nkb_launch_count(void);
 NKB_API void nkb_set_gemm_variant(int variant);
 /** Accuracy / speed trade of the floating-point tensor-core products. The tensor cores truncate when they add into their
  *  f32 accumulators, so the depth is cut into spans of `stages` x 128 bytes that are added with round-to-nearest in
- *  registers. 0 (default): chosen by type and depth (about 12 sqrt(depth) values for bf16 / f16, 16 stages for the 8-bit
- *  floats, 32 for e2m3). Shorter spans cost time (4 stages: about -12 % at depth 8192) and bring the error of bf16 / f16
+ *  registers. 0 (default): chosen by type and depth (about 12 sqrt(depth) values, at most 16 stages for bf16 and 4 for f16;
+ *  16 stages for the 8-bit floats, 32 for e2m3). Shorter spans cost time (4 stages: about -12 % at depth 8192) and bring the error of bf16 / f16
  *  products of same-sign data down in proportion (measured at depth 8192, bf16: 14.5 -> 1.8 units in the last place, the
  *  reference's scalar kernel 2.9). Integer products are exact and ignore the setting. Process-wide. */
 NKB_API void nkb_set_accumulation_span(int stages);

@@ -82,3 +82,15 @@ def test_accumulation_span_trades_speed_for_accuracy():
         nk.set_accumulation_span(0)
     assert errors[4] < errors[8] < errors[0]
     assert errors[4] <= 3.0 and errors[0] <= 25.0
+
+
+@pytest.mark.parametrize("dtype,limit", [("f16", 32), ("bf16", 256), ("e4m3", 4), ("e5m2", 4), ("e2m3", 4), ("e3m2", 4)])
+def test_reference_acceptance_thresholds_at_its_default_test_shape(dtype, limit):
+    """The reference's own test harness accepts a dots kernel when, on all-positive log-normal inputs at 1024 x 128 x 1536, no
+    cell is further than 32 (f16), 256 (bf16) or 4 (everything else) units in the last place from the exactly computed result
+    rounded to f32 (test/test.hpp:192-230, :207-219, :478-486). The same gate, applied to this library."""
+    a, b = syn.lognormal_matrix(1024, 1536, dtype, 42), syn.lognormal_matrix(128, 1536, dtype, 43)
+    c = nk.dots_packed(a, nk.dots_pack(b, dtype), dtype=dtype)
+    nearest = oracle.exact_dots_f64(a, b, dtype).astype(np.float32)
+    ulps = np.abs(c.view(np.int32).astype(np.int64) - nearest.view(np.int32).astype(np.int64))   # same sign: bit patterns are ordered
+    assert int(ulps.max()) <= limit, (dtype, int(ulps.max()), float(ulps.mean()))
