@@ -1,6 +1,7 @@
-"""Generates tests/golden/packed_path.npz from the REFERENCE ITSELF.
+"""Generates the fixtures under tests/golden/ (packed_path, nibble_path, compact_path, cast_path, moments_path) from the
+REFERENCE ITSELF.
 
-Run in a container that has the NumKong source tree (default /root/reference):
+Run in a container that has the NumKong source tree (where `make -C oracle ref` looks for it; REF=... overrides):
 
     make -C oracle ref            # compiles the reference's own sources into oracle/_ref/
     python tests/golden/make_golden.py
