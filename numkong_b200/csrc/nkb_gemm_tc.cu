@@ -860,11 +860,13 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     const uint32_t eb = dtype_bytes(args.dtype);
     // Tile configuration: 3 = CTA pairs sharing 256 x 256 tiles, 1 = 128 x 256 per CTA, 2 = 128 x 128 per CTA.
     const uint64_t chunk_rows_total = round_up(args.n, kRowPad) * (args.depth_padded_bytes / kBKBytes);
-    // Measured on B200 at 8192^3 the pair kernel is 5-10 % faster (bf16 1440 vs 1368, i8 3090 vs 2802 Tops); with a
-    // short depth (768) and a distance epilogue the single-CTA kernel wins (834 vs 719 Tops), so pairs are used for
-    // deep problems (>= 32 stages) that have at least one 256 x 256 tile per CTA pair.
+    // Measured on B200 at 8192^3 the pair kernel is 5-10 % faster (bf16 1440 vs 1368, i8 3090 vs 2802 Tops), and at
+    // 8192 x 8192 it leads from 8 stages of depth on (bf16 depth 512: 817 vs 790, 2048: 1290 vs 1213; i8 depth 1024:
+    // 1377 vs 1300, 4096: 2610 vs 2270; i8 at 4 stages: 720 vs 830, the other way round). With the filtering distance
+    // epilogue at depth 768 the two are level. So pairs are used from 8 stages on when there is at least one
+    // 256 x 256 tile per CTA pair.
     const uint64_t pair_tiles = ((args.m + 255) / 256) * ((args.n + 255) / 256);
-    const bool pair_by_shape = (args.variant & 0xff) == 0 && args.depth_padded_bytes / kBKBytes >= 32 &&
+    const bool pair_by_shape = (args.variant & 0xff) == 0 && args.depth_padded_bytes / kBKBytes >= 8 &&
                                pair_tiles >= (uint64_t)device_sm_count() / 2;
     const bool use_pair = ((args.variant & 0xff) == 3 || pair_by_shape) && chunk_rows_total < 0x7fffffffull;
     int bn = 256;
