@@ -94,3 +94,34 @@ def test_reference_acceptance_thresholds_at_its_default_test_shape(dtype, limit)
     nearest = oracle.exact_dots_f64(a, b, dtype).astype(np.float32)
     ulps = np.abs(c.view(np.int32).astype(np.int64) - nearest.view(np.int32).astype(np.int64))   # same sign: bit patterns are ordered
     assert int(ulps.max()) <= limit, (dtype, int(ulps.max()), float(ulps.mean()))
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "i8", "e4m3", "e2m3"])
+def test_cta_pair_kernel_at_mid_depth_with_ragged_edges(dtype):
+    """4000 x 5100 x 1000: enough 256 x 256 tiles for the CTA-pair kernel (chosen from 8 stages of depth on), none of the
+    three extents a multiple of its tile. Sampled rows (the last, partial row tile included) against the oracle."""
+    m, n, k = 4000, 5100, 1000
+    a, b = syn.normal_matrix(m, k, dtype, 21), syn.normal_matrix(n, k, dtype, 22)
+    ta, tb = (torch_from(a), torch_from(b))
+    packed = nk.dots_pack(tb, dtype)
+    rows = np.r_[0:3, 127:130, 2047:2050, m - 40:m]
+    for op in ("dots", "angulars", "euclideans"):
+        got = getattr(nk, op + "_packed")(ta, packed, dtype=dtype)
+        assert nk.synchronize() == 0
+        got = got.cpu().numpy()[rows]
+        want = getattr(oracle, op)(a[rows], b, dtype)
+        if op == "dots" and dtype == "i8":
+            assert np.array_equal(got, want)
+        elif op == "dots":
+            exact = oracle.exact_dots_f64(a[rows], b, dtype)
+            scale = np.abs(oracle.decode(a[rows], dtype).astype(np.float64)) @ np.abs(oracle.decode(b, dtype).astype(np.float64)).T
+            assert np.max(np.abs(got - exact) / scale) <= 2.5e-7
+        elif op == "angulars":
+            assert np.max(np.abs(got - want)) <= 5e-7
+        else:
+            assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-3)) <= 4e-6
+
+
+def torch_from(x):
+    import torch
+    return torch.from_numpy(x.view(np.int16) if x.dtype == np.uint16 else x).cuda()
