@@ -109,6 +109,26 @@ def run_maxsim(queries: int, docs: int, depth: int = 128, top: int = 100, q_toke
             "ms": seconds * 1e3, "gso_per_s": ops / seconds / 1e9, "steps": steps, "warmup": warmup}
 
 
+def run_dense(rows: int, width: int, depth: int, dtype: str = "f32", op: str = "dots", steps: int = 5, seed: int = 11, warmup: int = 2):
+    """One packed product (or distance matrix) of any supported element type and shape, operands resident on the device:
+    N(0,1) values generated as f32 and converted with the library's own bulk conversion."""
+    import torch
+    import numkong_b200 as nk
+    torch.manual_seed(seed)
+    a32, b32 = torch.randn(rows, depth, device="cuda"), torch.randn(width, depth, device="cuda")
+    a = a32 if dtype == "f32" else nk.cast(a32, dtype)
+    b = b32 if dtype == "f32" else nk.cast(b32, dtype)
+    if dtype in ("i8", "u8"):
+        a, b = nk.cast((a32 * 40).contiguous(), dtype), nk.cast((b32 * 40).contiguous(), dtype)
+    packed = nk.dots_pack(b, dtype)
+    fn = getattr(nk, op + "_packed")
+    out = fn(a, packed, dtype=dtype)
+    seconds = _timed(torch, lambda: fn(a, packed, out=out, dtype=dtype), steps, warmup)
+    assert nk.synchronize() == 0
+    return {"workload": f"{op}_packed {dtype} {rows} x {width} x {depth}", "ms": seconds * 1e3,
+            "gso_per_s": 2.0 * rows * width * depth / seconds / 1e9, "steps": steps, "warmup": warmup}
+
+
 def run_quantise(values: int, dtype: str = "e4m3", steps: int = 5, seed: int = 7, warmup: int = 2):
     """The step in front of `pack` when the source is f32: moments of the source (the scale comes from them) and the bulk
     conversion to the storage type. Device-resident; reports both kernels in GB/s of algorithmic traffic."""
@@ -208,7 +228,8 @@ def run_maxsim_sharded(queries: int, docs: int, depth: int = 128, top: int = 100
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("workload", choices=["nearest", "maxsim", "quantise"])
+    ap.add_argument("workload", choices=["nearest", "maxsim", "quantise", "dense"])
+    ap.add_argument("--op", default="dots", choices=["dots", "angulars", "euclideans"])
     ap.add_argument("--values", type=int, default=1 << 26)
     ap.add_argument("--queries", type=int, default=None)
     ap.add_argument("--corpus", type=int, default=65536)
@@ -220,7 +241,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--sharded", action="store_true", help="split the corpus / documents over the ranks of a torchrun launch")
     a = ap.parse_args()
-    if a.workload == "quantise":
+    if a.workload == "dense":
+        out = run_dense(a.queries or 4096, a.corpus, a.depth or 4096, a.dtype, a.op, a.steps, warmup=a.warmup)
+    elif a.workload == "quantise":
         out = run_quantise(a.values, a.dtype if a.dtype != "f16" else "e4m3", a.steps, warmup=a.warmup)
     elif a.workload == "nearest":
         fn = run_nearest_sharded if a.sharded else run_nearest
