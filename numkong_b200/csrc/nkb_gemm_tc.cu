@@ -194,21 +194,31 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
             mask[w] = bits & valid;
         }
     };
-    // Angular distances of float kinds, no zero factor in sight: a two-instruction prefilter per value. r < threshold needs
-    // dot * col_factor > (1 - threshold) / row_factor up to the rounding of the three operations behind r; with the bound
-    // lowered by 2^-18 (relative to 1 + |1 - threshold|) no value below the threshold can be missed, and the few extra ones
-    // are weeded out when pass 2 recomputes r. The sign bit of fma(-dot, col_factor, bound) is the decision; a funnel shift
-    // collects it (columns are walked downwards so that bit i ends up standing for column i).
+    // Float kinds: a two- or three-instruction prefilter per value instead of the full distance, decided by a sign bit that
+    // a funnel shift collects (columns are walked downwards so that bit i ends up standing for column i). The bound is
+    // moved so far that the roundings behind the exact distance cannot hide a value below the threshold; the few extra
+    // values that pass are weeded out when pass 2 recomputes the exact distance.
+    //   angular (no zero factor in sight): r < threshold needs dot * col_factor > (1 - threshold) / row_factor; the bound is
+    //     lowered by 2^-18 relative to 1 + |1 - threshold|; the sign of fma(-dot, col_factor, bound) decides.
+    //   euclidean: r < threshold needs |b|^2 - 2 dot < threshold^2 - |a|^2 up to 2^-21 (|a|^2 + |b|^2), and a column that
+    //     passes has |b|^2 <= 4 max(|a|^2, threshold^2) (triangle inequality), so the bound is raised by
+    //     2^-18 * 9 max(|a|^2, threshold^2) and threshold^2 by 2^-16; the sign of fma(-2, dot, |b|^2) - bound decides.
     bool prefiltered = false;
-    if constexpr (kEpi == kEpiAngular && kFloat) {
-        if (!zero_factors) {
+    if constexpr ((kEpi == kEpiAngular || kEpi == kEpiEuclidean) && kFloat) {
+        if (kEpi == kEpiEuclidean || !zero_factors) {
             prefiltered = true;
+            constexpr bool kAngular = kEpi == kEpiAngular;
+            const float pass_all = __uint_as_float(kAngular ? 0xff800000u : 0x7f800000u);
+            const float pass_none = __uint_as_float(kAngular ? 0x7f800000u : 0xff800000u);
             float bound;
-            if (my_row >= p.m) bound = __uint_as_float(0x7f800000u);             // nothing passes
-            else if (threshold == 0x7fffffff) bound = __uint_as_float(0xff800000u);  // no threshold yet: everything passes
-            else {
+            if (my_row >= p.m) bound = pass_none;
+            else if (threshold == 0x7fffffff) bound = pass_all;  // no threshold yet
+            else if constexpr (kAngular) {
                 const float b = 1.0f - __int_as_float(threshold), w = __frcp_rn(row_factor);
                 bound = fmaf(b, w, -(fabsf(b) + 1.0f) * w * 0x1p-18f);
+            } else {
+                const float t = __int_as_float(threshold), t2 = t * t;
+                bound = fmaf(t2, 1.0f + 0x1p-16f, -row_factor) + 9.0f * fmaxf(row_factor, t2) * 0x1p-18f;
             }
 #pragma unroll
             for (int w = 0; w < kCols / 32; ++w) {
@@ -218,8 +228,11 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
                     const float4 f = *reinterpret_cast<const float4 *>(colf + w * 32 + c * 4);
                     const float cf[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
-                    for (int j = 3; j >= 0; --j)
-                        bits = __funnelshift_l(__float_as_uint(fmaf(-__uint_as_float(acc[w * 32 + c * 4 + j]), cf[j], bound)), bits, 1);
+                    for (int j = 3; j >= 0; --j) {
+                        const float dot = __uint_as_float(acc[w * 32 + c * 4 + j]);
+                        const float decision = kAngular ? fmaf(-dot, cf[j], bound) : fmaf(-2.0f, dot, cf[j]) - bound;
+                        bits = __funnelshift_l(__float_as_uint(decision), bits, 1);
+                    }
                 }
                 const uint32_t first = col_base + w * 32;
                 const uint32_t valid = first >= p.n ? 0u : (p.n - first >= 32u ? 0xffffffffu : (1u << (p.n - first)) - 1u);
