@@ -241,7 +241,8 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
         }
     }
     if (!prefiltered) {
-        if (zero_factors) build_masks(std::true_type{});
+        if constexpr (kEpi == kEpiAngular && kFloat) build_masks(std::true_type{});  // only reached with a zero factor in sight
+        else if (zero_factors) build_masks(std::true_type{});
         else build_masks(std::false_type{});
     }
     uint32_t hits = 0;
