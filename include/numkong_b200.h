@@ -209,7 +209,9 @@ NKB_DECLARE_MAXSIM_FAMILY(f32)
 /* ---- run-time lookup ---------------------------------------------------------------------------
  * replaces nk_find_kernel_punned (c/numkong.c:848-913) for the kernel kinds of this path:
  * 'P' packed size, 'Q' pack, 'G' dots_packed, 'N' angulars_packed, 'E' euclideans_packed,
- * 'L' / 'l' / 'T' MaxSim size / pack / compute (capabilities.h:229-249). Unknown combinations give
+ * 'L' / 'l' / 'T' MaxSim size / pack / compute, 'y' / 'n' / 'D' the symmetric family, 'M' / 'Y' / 'p' / 'Z' the set
+ * distances of one-bit vectors, 'R' moments per element type, '-' with element type 0 the bulk conversion
+ * (capabilities.h:225-251). Unknown combinations give
  * *kernel_output = NULL and *capability_output = 0, which callers already treat as "no kernel".
  */
 #define NKB_CAPABILITY_B200 (1ull << 40)
@@ -250,6 +252,12 @@ NKB_DECLARE_MAXSIMS_FAMILY(f16)
 
 NKB_API void nkb_topk_smallest_f32(void const *scores, nk_size_t rows, nk_size_t cols, nk_size_t stride, nk_size_t top,
                                    nk_size_t id_base, void *out_values, void *out_ids);
+/* nkb_merge_topk: the cross-shard step of a sharded search. `values` (f32) and `ids` (i64) hold `parts` nearest-k lists
+ * per row, laid out [part][row][top] - what a gather of every shard's nkb_*_topk_* result delivers; slots with id < 0 are
+ * empty. out_values[rows x top] / out_ids[rows x top] receive the `top` smallest per row ordered by (value, id), empty
+ * slots as +inf / -1. parts * top (rounded up to a power of two) may not exceed 16384. Host or device pointers. */
+NKB_API void nkb_merge_topk(void const *values, void const *ids, nk_size_t parts, nk_size_t rows, nk_size_t top,
+                            void *out_values, void *out_ids);
 
 /* ---- batched angular distances without any device allocation -----------------------------------
  * No counterpart in the reference (which never allocates because it runs on the caller's CPU buffers).
@@ -269,6 +277,8 @@ NKB_API void nkb_topk_smallest_f32(void const *scores, nk_size_t rows, nk_size_t
  *    synchronous memset; make that first call (any small problem) before starting a stream capture.
  *  - All calls on one GPU share the fixed arrays: the norms are rewritten by every call, so two calls that overlap
  *    on the GPU (different streams or threads) race; run them in stream order.
+ *  - A bounded pipeline wait that gives up inside such a call leaves its code in the fixed error word; nkb_synchronize()
+ *    returns it (and clears it) without allocating anything, so check its return value after synchronising.
  */
 #define NKB_NOALLOC_MAX_ROWS 65536
 NKB_API int nkb_angulars_packed_noalloc(uint32_t dtype, void const *a, void const *b_packed, void *c, nk_size_t height,
@@ -277,20 +287,41 @@ NKB_API int nkb_angulars_packed_noalloc(uint32_t dtype, void const *a, void cons
 /* ---- additions (no counterpart in the reference) -------------------------------------------- */
 /** Last error of the calling thread, "" when the last call succeeded. The string stays valid until the next call. */
 NKB_API char const *nkb_last_error(void);
-/** Stream (a cudaStream_t) the calling thread's next calls are enqueued on. NULL selects the default stream. */
+/** Stream (a cudaStream_t) the calling thread's next calls are enqueued on. NULL selects the default stream. The library's
+ *  per-thread staging buffers pass from one call to the next, so a switch puts the new stream behind the work this thread
+ *  already enqueued on the old one (an event wait on the device; the host does not block). */
 NKB_API void nkb_set_stream(void *cuda_stream);
-/** Waits for the calling thread's stream and returns the device error word (0 = no pipeline wait ever gave up). */
+/** Waits for the calling thread's stream and returns the device error word: 0, or 0x80000000 | site << 16 | block of the
+ *  first bounded pipeline wait that gave up on this GPU since the last report (sites: 1 loader waiting for a free stage,
+ *  2 / 3 MMA issuer waiting for a drained accumulator / a loaded stage, 4 epilogue waiting for a finished accumulator,
+ *  5 / 6 the issuer's / loader's final drain). Covers the regular entry points and nkb_angulars_packed_noalloc alike,
+ *  allocates nothing, and clears the word it reports: the failure belongs to the calls enqueued before this
+ *  synchronisation (their results are not valid), later calls start clean. Calls with a host-resident operand do this
+ *  check themselves and fill their output with 0xFF. */
 NKB_API uint32_t nkb_synchronize(void);
+/** Shortens (or restores) the limit of the kernels' bounded waits. `site` as listed under nkb_synchronize, 0 = all sites;
+ *  `nanoseconds` 0 = the default of 2 s, larger values are capped there. Process-wide; for tests of the give-up path and
+ *  for callers that would rather fail fast than wait two seconds for a pipeline that will never move. */
+NKB_API void nkb_set_wait_limit_ns(int site, uint64_t nanoseconds);
+/** Test hook: stores `value` in the current GPU's error word as a wait that gave up would (which = 0: the word of the
+ *  regular entry points, created if need be; 1: the fixed word of nkb_angulars_packed_noalloc, which must have run on this
+ *  GPU before). Returns 0 on success. Nothing on the device fails. */
+NKB_API int nkb_test_set_error_word(int which, uint32_t value);
+/** Number of host-resident packed blobs whose device copies are cached right now (all GPUs). */
+NKB_API uint64_t nkb_cached_blob_count(void);
 /** Kernels launched by this library in this process so far (for launch accounting in benchmarks). */
 NKB_API uint64_t nkb_launch_count(void);
 /** Forces a GEMM tile configuration for testing/tuning: 0 = choose by shape. */
 NKB_API void nkb_set_gemm_variant(int variant);
 /** Accuracy / speed trade of the floating-point tensor-core products. The tensor cores truncate when they add into their
  *  f32 accumulators, so the depth is cut into spans of `stages` x 128 bytes that are added with round-to-nearest in
- *  registers. 0 (default): chosen by type and depth (about 12 sqrt(depth) values, at most 16 stages for bf16 and 4 for f16;
- *  16 stages for the 8-bit floats, 32 for e2m3). Shorter spans cost time (4 stages: about -12 % at depth 8192) and bring the error of bf16 / f16
- *  products of same-sign data down in proportion (measured at depth 8192, bf16: 14.5 -> 1.8 units in the last place, the
- *  reference's scalar kernel 2.9). Integer products are exact and ignore the setting. Process-wide. */
+ *  registers. 0 (default): chosen by type and depth so that the error stays within that of the reference's own kernels on the
+ *  same inputs: sqrt(depth)/16 stages for bf16 (6 at depth 8192), sqrt(depth)/11 for f16 (8 at depth 8192), 16 stages for the
+ *  8-bit floats, 32 for e2m3. Every read-out of a span keeps the tensor cores waiting for about 256 cycles (a stage takes
+ *  512), so longer spans are faster (16 stages at depth 8192: about +5 %) and less accurate in proportion (bf16, same-sign
+ *  data, depth 8192: 2.8 units in the last place at 6 stages, 14.5 at 16; the reference's scalar kernel 2.9). f16 products
+ *  carry 22 significant bits and lose some in every tensor-core addition: on same-sign f16 data even 1-stage spans leave
+ *  1.8 - 2.2 units where the reference has 0.6 - 3.0. Integer products are exact and ignore the setting. Process-wide. */
 NKB_API void nkb_set_accumulation_span(int stages);
 /** How e2m3 / e3m2 operands reach the tensor cores: 1 (default) = packed 6-bit operands with the native
  *  e2m3 / e3m2 MMA formats, 0 = recoded to the e4m3 code of the same value (exact as well). Applies to later pack AND multiply calls;

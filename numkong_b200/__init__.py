@@ -29,7 +29,7 @@ __all__ = [
     "dots_symmetric", "angulars_symmetric", "euclideans_symmetric",
     "hammings_packed", "jaccards_packed", "hammings_symmetric", "jaccards_symmetric",
     "maxsim_pack", "maxsim_packed", "maxsim", "maxsims_packed", "angulars_packed_topk", "euclideans_packed_topk",
-    "topk_smallest", "synchronize", "set_stream", "launch_count", "last_error", "dots_compact", "cast", "moments", "set_accumulation_span",
+    "topk_smallest", "merge_topk", "synchronize", "set_wait_limit_ns", "set_stream", "launch_count", "last_error", "dots_compact", "cast", "moments", "set_accumulation_span",
 ]
 
 _NUMPY_NAMES = {
@@ -570,9 +570,34 @@ def topk_smallest(scores: Any, top: int, *, id_base: int = 0):
     return vals, ids
 
 
+def merge_topk(values: Any, ids: Any, top: Optional[int] = None):
+    """Merges nearest-k lists of several shards: `values` (f32) and `ids` (i64) shaped [parts, rows, k], slots with id < 0
+    empty. Returns ([rows, top], [rows, top]) ordered by (value, id) - the cross-shard step of a sharded search, on the device."""
+    parts, rows, k = values.shape
+    top = k if top is None else int(top)
+    if top > k:
+        raise ValueError("top may not exceed the length of the lists being merged")
+    if _is_torch(values):
+        import torch
+        values, ids = values.to(torch.float32).contiguous(), ids.to(torch.int64).contiguous()
+        out_v = torch.empty((rows, k), dtype=torch.float32, device=values.device)
+        out_i = torch.empty((rows, k), dtype=torch.int64, device=values.device)
+    else:
+        values, ids = np.ascontiguousarray(values, dtype=np.float32), np.ascontiguousarray(ids, dtype=np.int64)
+        out_v, out_i = np.empty((rows, k), dtype=np.float32), np.empty((rows, k), dtype=np.int64)
+    lib.nkb_merge_topk(_ptr(values), _ptr(ids), parts, rows, k, _ptr(out_v), _ptr(out_i))
+    check("merge_topk")
+    return out_v[:, :top], out_i[:, :top]
+
+
 def synchronize() -> int:
-    """Waits for this thread's stream; returns the device error word (0 = healthy)."""
+    """Waits for this thread's stream; returns the device error word (0 = healthy) and clears what it reports."""
     return int(lib.nkb_synchronize())
+
+
+def set_wait_limit_ns(site: int, nanoseconds: int) -> None:
+    """Limit of the kernels' bounded pipeline waits (nkb_set_wait_limit_ns): site 0 = all, nanoseconds 0 = the default 2 s."""
+    lib.nkb_set_wait_limit_ns(int(site), int(nanoseconds))
 
 
 def set_stream(cuda_stream: int) -> None:

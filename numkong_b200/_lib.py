@@ -81,6 +81,12 @@ def _load() -> ctypes.CDLL:
     lib.nk_dots_compact_i8.restype, lib.nk_dots_compact_i8.argtypes = None, [vp, sz, sz, sz, vp, vp]
     lib.nkb_topk_smallest_f32.restype = None
     lib.nkb_topk_smallest_f32.argtypes = [vp, sz, sz, sz, sz, sz, vp, vp]
+    lib.nkb_merge_topk.restype, lib.nkb_merge_topk.argtypes = None, [vp, vp, sz, sz, sz, vp, vp]
+    lib.nkb_angulars_packed_noalloc.restype = ctypes.c_int
+    lib.nkb_angulars_packed_noalloc.argtypes = [ctypes.c_uint32, vp, vp, vp, sz, sz, sz, sz, sz]
+    lib.nkb_set_wait_limit_ns.restype, lib.nkb_set_wait_limit_ns.argtypes = None, [ctypes.c_int, sz]
+    lib.nkb_test_set_error_word.restype, lib.nkb_test_set_error_word.argtypes = ctypes.c_int, [ctypes.c_int, ctypes.c_uint32]
+    lib.nkb_cached_blob_count.restype, lib.nkb_cached_blob_count.argtypes = sz, []
     return lib
 
 

@@ -23,6 +23,9 @@ namespace {
 std::atomic<int> g_variant{0};
 std::atomic<int> g_fp6_native{1};
 std::atomic<uint64_t> g_nonce_counter{0};
+// Limit of every bounded wait of the tensor-core kernels, by wait site (microseconds); see nkb_set_wait_limit_ns.
+std::atomic<uint32_t> g_wait_us[kWaitSites] = {{kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs},
+                                               {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}};
 
 // ---------------------------------------------------------------- per-thread context
 struct Scratch {
@@ -43,7 +46,11 @@ struct ThreadCtx {
     int slot_set = 0;
     cudaStream_t override_stream = nullptr;
     bool use_override = false;
-    ~ThreadCtx() {}  // device memory is reclaimed with the context at process exit
+    cudaEvent_t stream_switch = nullptr;  // orders a newly selected stream behind the work already enqueued on the old one
+    // Cached device copies of host-resident blobs the current call works on: (nonce, device) pairs, pinned against eviction
+    // until this thread's next call begins.
+    std::vector<std::pair<uint64_t, int>> pins;
+    ~ThreadCtx();  // device memory is reclaimed with the context at process exit
 };
 thread_local ThreadCtx t_ctx;
 
@@ -60,11 +67,36 @@ struct CachedBlob {
     int device = -1;
     void *dev_ptr = nullptr;
     uint64_t last_use = 0;
+    int pins = 0;  // calls (of any thread) that looked this entry up and may not have enqueued their kernels yet
 };
 std::mutex g_cache_mutex;
 std::vector<CachedBlob> g_cache;
 uint64_t g_cache_clock = 0;
 constexpr size_t kCacheMaxEntries = 8;
+
+// Makes room for one more entry: frees the least recently used entry that no call has pinned. A pinned entry may belong
+// to a thread that has the pointer but has not launched yet, which the device-wide synchronisation before the free
+// would not cover; when every entry is pinned the cache grows past its nominal size instead. Caller holds g_cache_mutex.
+void evict_for_insert() {
+    if (g_cache.size() < kCacheMaxEntries) return;
+    size_t victim = g_cache.size();
+    for (size_t i = 0; i < g_cache.size(); ++i)
+        if (g_cache[i].pins == 0 && (victim == g_cache.size() || g_cache[i].last_use < g_cache[victim].last_use)) victim = i;
+    if (victim == g_cache.size()) return;
+    cudaDeviceSynchronize();  // kernels already enqueued on any stream may still read the victim
+    cudaFree(g_cache[victim].dev_ptr);
+    g_cache.erase(g_cache.begin() + victim);
+}
+
+// Drops the pins the calling thread took during its previous call.
+void release_pins() {
+    if (t_ctx.pins.empty()) return;
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    for (const auto &pin : t_ctx.pins)
+        for (auto &e : g_cache)
+            if (e.nonce == pin.first && e.device == pin.second && e.pins > 0) { --e.pins; break; }
+    t_ctx.pins.clear();
+}
 
 uint64_t fresh_nonce() {
     uint64_t t = (uint64_t)std::chrono::steady_clock::now().time_since_epoch().count();
@@ -74,6 +106,8 @@ uint64_t fresh_nonce() {
     return x ? x : 1;
 }
 
+ThreadCtx::~ThreadCtx() { release_pins(); }
+
 } // namespace
 
 // ---------------------------------------------------------------- helpers shared with other host files
@@ -82,7 +116,14 @@ void set_error(const char *fmt, const char *detail) {
     std::snprintf(buf, sizeof buf, fmt, detail ? detail : "");
     t_ctx.error = buf;
 }
-void clear_error() { t_ctx.error.clear(); }
+// Every entry point starts here: the thread's previous call has enqueued all its kernels by now, so its pins go.
+void clear_error() {
+    t_ctx.error.clear();
+    release_pins();
+}
+void wait_limits_us(uint32_t (&out)[kWaitSites]) {
+    for (int i = 0; i < kWaitSites; ++i) out[i] = g_wait_us[i].load();
+}
 cudaStream_t current_stream() { return t_ctx.use_override ? t_ctx.override_stream : t_ctx.stream; }
 int current_variant() { return g_variant.load(); }
 int fp6_native() { return g_fp6_native.load(); }
@@ -137,12 +178,31 @@ unsigned int *device_error_word() {
     return st.error_word;
 }
 
-uint32_t read_device_error() {
-    unsigned int *w = device_error_word();
-    if (!w) return 0;
+// The current device's error word if some call created it already; never allocates.
+static unsigned int *existing_error_word() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    return g_devices[dev].error_word;
+}
+
+// Reads one error word and, when it reports a failed wait, clears it again: the failure is reported once, to the caller
+// that synchronised first, and later calls start clean (the kernels of the failed call have all retired by then).
+uint32_t take_error_word(unsigned int *word) {
+    if (!word) return 0;
     unsigned int v = 0;
-    if (cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return 0xffffffffu; }
+    if (cudaMemcpy(&v, word, 4, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return 0xffffffffu; }
+    if (v != 0) { cudaMemset(word, 0, 4); cudaGetLastError(); }
     return v;
+}
+
+// Error status of the current device: the word of the regular entry points (when one of them has run) or else the fixed
+// word of the allocation-free entry point (when that has run). Allocates nothing.
+uint32_t read_device_error() {
+    const uint32_t regular = take_error_word(existing_error_word());
+    const uint32_t fixed = take_error_word(noalloc_error_word());
+    return regular ? regular : fixed;
 }
 
 void fill_error_output(void *out, MemKind kind, uint64_t rows, uint64_t row_bytes, uint64_t stride) {
@@ -184,18 +244,19 @@ const uint8_t *resident_blob(const void *blob, MemKind kind, uint32_t magic, uin
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lock(g_cache_mutex);
     for (auto &e : g_cache)
-        if (e.nonce == h.nonce && e.bytes == h.total_bytes && e.device == dev) { e.last_use = ++g_cache_clock; return static_cast<const uint8_t *>(e.dev_ptr); }
-    if (g_cache.size() >= kCacheMaxEntries) {
-        size_t victim = 0;
-        for (size_t i = 1; i < g_cache.size(); ++i) if (g_cache[i].last_use < g_cache[victim].last_use) victim = i;
-        cudaDeviceSynchronize();
-        cudaFree(g_cache[victim].dev_ptr);
-        g_cache.erase(g_cache.begin() + victim);
-    }
+        if (e.nonce == h.nonce && e.bytes == h.total_bytes && e.device == dev) {
+            e.last_use = ++g_cache_clock;
+            ++e.pins;
+            t_ctx.pins.emplace_back(e.nonce, dev);
+            return static_cast<const uint8_t *>(e.dev_ptr);
+        }
+    evict_for_insert();
     void *d = nullptr;
     if (!cuda_ok(cudaMalloc(&d, h.total_bytes), "cudaMalloc(packed blob copy)")) return nullptr;
     if (!cuda_ok(cudaMemcpyAsync(d, blob, h.total_bytes, cudaMemcpyHostToDevice, t_ctx.stream), "upload of packed blob")) { cudaFree(d); return nullptr; }
     CachedBlob e; e.nonce = h.nonce; e.bytes = h.total_bytes; e.device = dev; e.dev_ptr = d; e.last_use = ++g_cache_clock;
+    e.pins = 1;
+    t_ctx.pins.emplace_back(e.nonce, dev);
     g_cache.push_back(e);
     return static_cast<const uint8_t *>(d);
 }
@@ -204,13 +265,7 @@ void remember_blob(uint64_t nonce, uint64_t bytes, void *dev_ptr) {
     int dev = 0;
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lock(g_cache_mutex);
-    if (g_cache.size() >= kCacheMaxEntries) {
-        size_t victim = 0;
-        for (size_t i = 1; i < g_cache.size(); ++i) if (g_cache[i].last_use < g_cache[victim].last_use) victim = i;
-        cudaDeviceSynchronize();
-        cudaFree(g_cache[victim].dev_ptr);
-        g_cache.erase(g_cache.begin() + victim);
-    }
+    evict_for_insert();
     CachedBlob e; e.nonce = nonce; e.bytes = bytes; e.device = dev; e.dev_ptr = dev_ptr; e.last_use = ++g_cache_clock;
     g_cache.push_back(e);
 }
@@ -439,7 +494,7 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
             g.c = c_dev; g.c_stride = c_pitch; g.m = m; g.n = n; g.k = operand_depth(dt, k);
             g.depth_padded_bytes = h.depth_padded_bytes; g.error_word = err; g.variant = g_variant.load();
             ok = cuda_ok(launch_gemm_tc(g, stream), "tensor-core GEMM kernel");
-            g_launches += gemm_tc_launch_count(g);
+            g_launches++;
         }
     }
     if (ok && !c_direct) {
@@ -575,11 +630,42 @@ NKB_API void nk_jaccards_packed_u1(void const *v, void const *q_packed, void *re
 }
 
 NKB_API char const *nkb_last_error(void) { return t_ctx.error.c_str(); }
-NKB_API void nkb_set_stream(void *cuda_stream) { t_ctx.stream = static_cast<cudaStream_t>(cuda_stream); }
+NKB_API void nkb_set_stream(void *cuda_stream) {
+    cudaStream_t next = static_cast<cudaStream_t>(cuda_stream);
+    if (next == t_ctx.stream) return;
+    // The thread's staging buffers (row norms, re-strided operands, candidate lists) pass from call to call without
+    // ordering of their own, so the new stream is put behind everything this thread has enqueued on the old one.
+    cudaStreamCaptureStatus old_capture = cudaStreamCaptureStatusNone, new_capture = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(t_ctx.stream, &old_capture);
+    cudaStreamIsCapturing(next, &new_capture);
+    cudaGetLastError();
+    if (old_capture == cudaStreamCaptureStatusNone && new_capture == cudaStreamCaptureStatusNone) {
+        if (!t_ctx.stream_switch && cudaEventCreateWithFlags(&t_ctx.stream_switch, cudaEventDisableTiming) != cudaSuccess) t_ctx.stream_switch = nullptr;
+        if (t_ctx.stream_switch && cudaEventRecord(t_ctx.stream_switch, t_ctx.stream) == cudaSuccess)
+            cudaStreamWaitEvent(next, t_ctx.stream_switch, 0);
+        cudaGetLastError();
+    }
+    t_ctx.stream = next;
+}
 NKB_API uint32_t nkb_synchronize(void) {
     clear_error();
     if (!cuda_ok(cudaStreamSynchronize(t_ctx.stream), "nkb_synchronize")) return 0xffffffffu;
     return read_device_error();
+}
+NKB_API void nkb_set_wait_limit_ns(int site, uint64_t nanoseconds) {
+    uint64_t us = nanoseconds == 0 ? kDefaultWaitLimitUs : (nanoseconds + 999) / 1000;
+    if (us > kDefaultWaitLimitUs) us = kDefaultWaitLimitUs;
+    for (int i = 1; i < kWaitSites; ++i)
+        if (site == 0 || site == i) g_wait_us[i].store((uint32_t)us);
+}
+NKB_API int nkb_test_set_error_word(int which, uint32_t value) {
+    unsigned int *word = which == 0 ? device_error_word() : noalloc_error_word();
+    if (!word) return 1;
+    return cudaMemcpy(word, &value, 4, cudaMemcpyHostToDevice) == cudaSuccess ? 0 : 2;
+}
+NKB_API uint64_t nkb_cached_blob_count(void) {
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    return g_cache.size();
 }
 NKB_API uint64_t nkb_launch_count(void) { return g_launches.load(); }
 NKB_API void nkb_set_gemm_variant(int variant) { g_variant.store(variant); }

@@ -34,6 +34,21 @@ const Entry kTable[] = {
     {'p', NKB_DTYPE_U1, (void *)&nk_jaccards_packed_u1}, {'Z', NKB_DTYPE_U1, (void *)&nk_jaccards_symmetric_u1},
     NKB_MAXSIM_ENTRIES(bf16, NKB_DTYPE_BF16), NKB_MAXSIM_ENTRIES(f16, NKB_DTYPE_F16),
     NKB_MAXSIM_ENTRIES(f32, NKB_DTYPE_F32),
+    // Moments under kind 'R' (nk_kernel_reduce_moments_k, include/numkong/capabilities.h:225), one per element type, with the
+    // numeric values of nk_dtype_t (types.h:923-953) for the integer widths the packed families do not use.
+    {'R', NKB_DTYPE_F64, (void *)&nk_reduce_moments_f64},   {'R', NKB_DTYPE_F32, (void *)&nk_reduce_moments_f32},
+    {'R', NKB_DTYPE_F16, (void *)&nk_reduce_moments_f16},   {'R', NKB_DTYPE_BF16, (void *)&nk_reduce_moments_bf16},
+    {'R', NKB_DTYPE_E4M3, (void *)&nk_reduce_moments_e4m3}, {'R', NKB_DTYPE_E5M2, (void *)&nk_reduce_moments_e5m2},
+    {'R', NKB_DTYPE_E2M3, (void *)&nk_reduce_moments_e2m3}, {'R', NKB_DTYPE_E3M2, (void *)&nk_reduce_moments_e3m2},
+    {'R', NKB_DTYPE_I8, (void *)&nk_reduce_moments_i8},     {'R', NKB_DTYPE_U8, (void *)&nk_reduce_moments_u8},
+    {'R', 1u << 3, (void *)&nk_reduce_moments_i16},         {'R', 1u << 7, (void *)&nk_reduce_moments_u16},
+    {'R', 1u << 4, (void *)&nk_reduce_moments_i32},         {'R', 1u << 8, (void *)&nk_reduce_moments_u32},
+    {'R', 1u << 5, (void *)&nk_reduce_moments_i64},         {'R', 1u << 9, (void *)&nk_reduce_moments_u64},
+    {'R', NKB_DTYPE_I4, (void *)&nk_reduce_moments_i4},     {'R', NKB_DTYPE_U4, (void *)&nk_reduce_moments_u4},
+    {'R', NKB_DTYPE_U1, (void *)&nk_reduce_moments_u1},
+    // Bulk conversion under kind '-' with the "unknown" element type 0, which is how the reference's lookup reaches nk_cast
+    // (nk_kernel_cast_k, capabilities.h:251; c/numkong.c:897).
+    {'-', 0u, (void *)&nk_cast},
 };
 
 } // namespace

@@ -42,6 +42,7 @@ struct GemmDev {
     uint32_t int_mode;            // 0 float accumulators, 1 signed i32, 2 unsigned u32
     uint32_t flush_kblocks;       // stages per accumulation span (see the MMA issuer)
     unsigned int *error_word;
+    uint32_t wait_us[kWaitSites];  // limit of every bounded wait, by wait site (microseconds)
     // Triangular mode (A x A^T): >= 0 keeps only cells with column >= row + tri_diag (the diagonal itself reads 0 under a
     // distance epilogue), tiles wholly below that line are never computed; -1 = plain rectangular product.
     int32_t tri_diag;
@@ -126,10 +127,21 @@ __device__ __forceinline__ float column_factor(const GemmDev &p, uint32_t col) {
     return bn;
 }
 
+// True for a row or column factor that rules out the shortcuts of the distance epilogues. Angular: a zero factor calls for
+// the zero-norm rule. Both: a factor that is not finite (an Inf or NaN element, a squared norm that overflowed) goes with
+// dots that are not finite either, and only the full formula maps those the way the storing path does. With every
+// factor of a tile finite, every dot of the tile is finite too: |dot| <= |a||b| <= max(|a|^2, |b|^2).
+template <int kEpi>
+__device__ __forceinline__ bool special_factor(float f) {
+    if constexpr (kEpi == kEpiAngular) return !(f > 0.0f && f < __uint_as_float(0x7f800000u));
+    else if constexpr (kEpi == kEpiEuclidean) return !(fabsf(f) < __uint_as_float(0x7f800000u));
+    else return false;
+}
+
 // One finalised distance. Never NaN and never below -0: a NaN dot or factor falls out of fmaxf as 0.
 //   kFloat       the accumulator holds f32 bits (known at compile time for the float kinds; the integer kinds read `int_mode`)
 //   kZeroRule    apply the zero-norm rule of the angular distance; callers switch it off for a tile whose row and column
-//                factors are all non-zero, which is nearly every tile
+//                factors are all non-zero and finite, which is nearly every tile
 template <int kEpi, bool kFloat, bool kZeroRule = true>
 __device__ __forceinline__ float distance_value(uint32_t raw, uint32_t int_mode, float row_factor, float col_factor) {
     float dot;
@@ -205,7 +217,7 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
     //     2^-18 * 9 max(|a|^2, threshold^2) and threshold^2 by 2^-16; the sign of fma(-2, dot, |b|^2) - bound decides.
     bool prefiltered = false;
     if constexpr ((kEpi == kEpiAngular || kEpi == kEpiEuclidean) && kFloat) {
-        if (kEpi == kEpiEuclidean || !zero_factors) {
+        if (!zero_factors) {  // no zero and no non-finite factor in sight: every dot of the tile is finite
             prefiltered = true;
             constexpr bool kAngular = kEpi == kEpiAngular;
             const float pass_all = __uint_as_float(kAngular ? 0xff800000u : 0x7f800000u);
@@ -241,7 +253,7 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
         }
     }
     if (!prefiltered) {
-        if constexpr (kEpi == kEpiAngular && kFloat) build_masks(std::true_type{});  // only reached with a zero factor in sight
+        if constexpr (kEpi == kEpiAngular && kFloat) build_masks(std::true_type{});  // only reached with a special factor in sight
         else if (zero_factors) build_masks(std::true_type{});
         else build_masks(std::false_type{});
     }
@@ -282,7 +294,8 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
 //   colf      this tile's column factors in shared memory, indexed by column inside the tile;  colf_off  col_base inside the tile
 // Angular: max(0, 1 - dot/(|a||b|)), and for a zero norm 0 when the dot is 0 else 1 (include/numkong/spatial/serial.h:257-269).
 // Euclidean: sqrt(max(0, |a|^2 + |b|^2 - 2 dot)) (include/numkong/spatial/serial.h:272-278).
-//   zero_cols  some column factor of this tile is 0 (a zero vector, or padding past the last column)
+//   zero_cols  some column factor of this tile is special (see special_factor: a zero vector or padding past the last column
+//              under the angular epilogue, a norm that is not finite under either)
 template <int kEpi, int kCols, int kW, bool kFloat>
 __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev &p, uint32_t row_base, uint32_t col_base,
                                            uint32_t *stage, const float *colf, uint32_t colf_off, int lane, bool zero_cols) {
@@ -298,7 +311,8 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
     }
     // The angular zero-norm rule is only compiled into the path taken when this row or some column of the tile has a zero factor.
     // The predicate is uniform over the warp: the store loop below synchronises the warp.
-    const bool zero_factors = kEpi == kEpiAngular && (zero_cols || __any_sync(0xffffffffu, row_factor == 0.0f));
+    const bool zero_factors = (kEpi == kEpiAngular || kEpi == kEpiEuclidean) &&
+                              (zero_cols || __any_sync(0xffffffffu, special_factor<kEpi>(row_factor)));
     if constexpr (kEpi == kEpiAngular || kEpi == kEpiEuclidean) {
         if (p.candidates != nullptr) {
             filter_tile<kEpi, kCols, kFloat>(acc, p, my_row, col_base, row_factor, colf + colf_off, stage, lane, zero_factors);
@@ -348,7 +362,7 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
         __syncwarp();
     }
     };
-    if (zero_factors) emit(std::true_type{});
+    if (kEpi == kEpiAngular && zero_factors) emit(std::true_type{});
     else emit(std::false_type{});
 }
 
@@ -372,6 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
     auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
     auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + Plan::kBarrierOffset + 8 * (2 * kStages + 4));
+    const uint32_t drain_bar = bar_base + 8u * (2 * kStages + 5);  // the MMA issuer's "all my MMAs have retired"
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -387,6 +402,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
             mbar_init(tmem_full_bar(a), 1);
             mbar_init(tmem_empty_bar(a), kEpilogueWarps * 32);
         }
+        mbar_init(drain_bar, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -402,7 +418,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
             int stage = 0;
-            uint32_t phase = 0;
+            uint32_t phase = 0, issued = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 uint32_t mt, nt;
@@ -410,7 +426,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                 if (tile_skipped(p.tri_diag, mt * kBM, (nt + 1) * kBN)) continue;
                 const uint8_t *b_tile = p.b_payload + (uint64_t)nt * (kBN / kChunkRows) * p.kblocks * kChunkBytes;
                 for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word, p.wait_us[1])) { ok = false; break; }
                     uint32_t a_dst = smem_base + stage * Plan::kStageBytes;
                     uint32_t b_dst = a_dst + Plan::kABytes;
                     mbar_expect_tx(full_bar(stage), Plan::kStageBytes);
@@ -419,12 +435,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                     for (int j = 0; j < kBN / (int)kChunkRows; ++j)
                         bulk_load(b_dst + j * kChunkBytes, b_tile + ((uint64_t)j * p.kblocks + kb) * kChunkBytes,
                                   kChunkBytes, full_bar(stage));
+                    ++issued;
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) {
-                // Give copies that are still in flight time to land before the CTA retires.
-                for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+                // The consumer has stopped. Copies this thread issued may still be in flight, and shared memory must not
+                // be released under them: wait (bounded) until the `full` barrier of every stage issued last has
+                // counted its bytes. Stages the MMA issuer already took return at once.
+                int s = stage;
+                uint32_t ph = phase;
+                for (uint32_t i = 0; i < issued && i < (uint32_t)kStages; ++i) {
+                    if (s == 0) { s = kStages; ph ^= 1u; }
+                    --s;
+                    if (!mbar_wait(full_bar(s), ph, 6, p.error_word, p.wait_us[6])) break;
+                }
             }
         }
     } else if (warp == 1) {
@@ -445,12 +470,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                 for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
                     const uint32_t buf = seq & 1u;
                     const uint32_t buf_phase = (seq >> 1) & 1u;
-                    if (!mbar_wait(tmem_empty_bar(buf), buf_phase ^ 1u, 2, p.error_word)) { ok = false; break; }
+                    if (!mbar_wait(tmem_empty_bar(buf), buf_phase ^ 1u, 2, p.error_word, p.wait_us[2])) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + buf * kBN;
                     const uint32_t kb1 = min(kb0 + p.flush_kblocks, p.kblocks);
                     for (uint32_t kb = kb0; kb < kb1; ++kb) {
-                        if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
+                        if (!mbar_wait(full_bar(stage), phase, 3, p.error_word, p.wait_us[3])) { ok = false; break; }
                         tc_fence_after_sync();
                         const uint32_t a_src = smem_base + stage * Plan::kStageBytes;
                         const uint64_t a_desc = make_smem_desc_sw128(a_src);
@@ -466,6 +491,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                     if (ok) umma_commit(tmem_full_bar(buf));
                 }
             }
+            // TMEM and shared memory are released after the block-wide barrier below; no MMA may still be running then.
+            // On the regular path the epilogue's last wait already implies that; after a wait that gave up nothing
+            // does, so the issuer always waits (bounded) for its own last MMAs.
+            umma_commit(drain_bar);
+            mbar_wait(drain_bar, 0u, 5, p.error_word, p.wait_us[5]);
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..9)
@@ -488,7 +518,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
                 const uint32_t e = threadIdx.x - 64u;
                 const float factor = e < (uint32_t)kBN ? column_factor<kEpi>(p, nt * kBN + e) : 1.0f;
                 colf[(local_tile & 1u) * 256 + e] = factor;
-                zero_cols = epilogue_barrier_any(factor == 0.0f);
+                zero_cols = epilogue_barrier_any(special_factor<kEpi>(factor));
             }
             uint32_t acc[kColsPerThread];
 #pragma unroll
@@ -496,7 +526,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
             for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
                 const uint32_t buf = seq & 1u;
                 const uint32_t buf_phase = (seq >> 1) & 1u;
-                if (!mbar_wait(tmem_full_bar(buf), buf_phase, 4, p.error_word)) { ok = false; break; }
+                if (!mbar_wait(tmem_full_bar(buf), buf_phase, 4, p.error_word, p.wait_us[4])) { ok = false; break; }
                 tc_fence_after_sync();
                 if (kb0 == 0) {
                     // First span of a tile: nothing to add to, so every load goes straight into the accumulators and all of
@@ -569,6 +599,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
     auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
     auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kPairBarrierOffset + 8 * (2 * kStages + 4));
+    const uint32_t drain_bar = bar_base + 8u * (2 * kStages + 5);  // leader only: "all MMAs of the pair have retired"
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -588,6 +619,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
             mbar_init(tmem_full_bar(a), 1);
             mbar_init(tmem_empty_bar(a), 2 * kEpilogueWarps);  // one arrival per epilogue warp of both CTAs
         }
+        mbar_init(drain_bar, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -604,7 +636,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
         // ------------------------------------------------------------ producer (both CTAs)
         if (lane == 0) {
             int stage = 0;
-            uint32_t phase = 0;
+            uint32_t phase = 0, issued = 0;
             bool ok = true;
             for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
                 uint32_t mt, nt;
@@ -613,17 +645,33 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 const uint32_t a_row = mt * 256u + rank * 128u;
                 const uint64_t b_chunk0 = ((uint64_t)nt * 2u + rank) * p.kblocks;  // this CTA's half of the B tile
                 for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-                    if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
+                    if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, 1, p.error_word, p.wait_us[1])) { ok = false; break; }
                     const uint32_t a_dst = smem_base + stage * kPairStageBytes;
                     const uint32_t b_dst = a_dst + kBM * kBKBytes;
                     const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kPairStageBytes);
                     tma_load_2d_pair(a_dst, &a_map, (int)(kb * p.elems_per_kblock), (int)a_row, leader_full);
                     tma_load_2d_pair(b_dst, &b_map, 0, (int)((b_chunk0 + kb) * kChunkRows), leader_full);
+                    ++issued;
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
-            if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+            if (!ok) {
+                // See the single-CTA kernel. Both CTAs' copies count on the LEADER's `full` barriers, so the leader can
+                // wait for them; the follower cannot read a remote barrier and sleeps instead - its last copy was issued
+                // at least one wait limit ago, and neither CTA retires before the cluster barrier at the end.
+                if (rank == 0) {
+                    int s = stage;
+                    uint32_t ph = phase;
+                    for (uint32_t i = 0; i < issued && i < (uint32_t)kStages; ++i) {
+                        if (s == 0) { s = kStages; ph ^= 1u; }
+                        --s;
+                        if (!mbar_wait<true>(full_bar(s), ph, 6, p.error_word, p.wait_us[6])) break;
+                    }
+                } else {
+                    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+                }
+            }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -637,12 +685,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 if (tile_skipped(p.tri_diag, mt * 256u, (nt + 1) * kBN)) continue;
                 for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
                     const uint32_t buf = seq & 1u, buf_phase = (seq >> 1) & 1u;
-                    if (!mbar_wait<true>(tmem_empty_bar(buf), buf_phase ^ 1u, 2, p.error_word)) { ok = false; break; }
+                    if (!mbar_wait<true>(tmem_empty_bar(buf), buf_phase ^ 1u, 2, p.error_word, p.wait_us[2])) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + buf * kBN;
                     const uint32_t kb1 = min(kb0 + p.flush_kblocks, p.kblocks);
                     for (uint32_t kb = kb0; kb < kb1; ++kb) {
-                        if (!mbar_wait<true>(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
+                        if (!mbar_wait<true>(full_bar(stage), phase, 3, p.error_word, p.wait_us[3])) { ok = false; break; }
                         tc_fence_after_sync();
                         const uint32_t a_src = smem_base + stage * kPairStageBytes;
                         const uint64_t a_desc = make_smem_desc_sw128(a_src);
@@ -656,6 +704,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                     if (ok) umma_commit_pair(tmem_full_bar(buf), 3);
                 }
             }
+            // As in the single-CTA kernel: wait (bounded) for the pair's last MMAs before either CTA passes the final cluster barrier.
+            umma_commit_pair(drain_bar, 1);
+            mbar_wait<true>(drain_bar, 0u, 5, p.error_word, p.wait_us[5]);
         }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs): rows of this CTA's half
@@ -674,14 +725,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 const uint32_t e = threadIdx.x - 64u;
                 const float factor = column_factor<kEpi>(p, nt * kBN + e);
                 colf[(local_tile & 1u) * 256 + e] = factor;
-                zero_cols = epilogue_barrier_any(factor == 0.0f);
+                zero_cols = epilogue_barrier_any(special_factor<kEpi>(factor));
             }
             uint32_t acc[kColsPerThread];
 #pragma unroll
             for (int j = 0; j < kColsPerThread; ++j) acc[j] = 0u;
             for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
                 const uint32_t buf = seq & 1u, buf_phase = (seq >> 1) & 1u;
-                if (!mbar_wait<true>(tmem_full_bar(buf), buf_phase, 4, p.error_word)) { ok = false; break; }
+                if (!mbar_wait<true>(tmem_full_bar(buf), buf_phase, 4, p.error_word, p.wait_us[4])) { ok = false; break; }
                 tc_fence_after_sync();
                 if (kb0 == 0) {
                     // First span of a tile: nothing to add to, so every load goes straight into the accumulators and all of
@@ -850,6 +901,36 @@ cudaError_t launch_pair_by_epilogue(int epi, const CUtensorMap &a_map, const CUt
 
 } // namespace
 
+// The tensor cores truncate (toward zero) when they add products into their f32 accumulators, so one long accumulation
+// chain drifts: measured on B200, a bf16 chain of 8192 values is off by 3.7e-7 .. 7.8e-7 of sum |a||b|, ten times the error
+// of NumKong's own f32 kernels. The depth is therefore cut into spans; each span is accumulated in TMEM, read out, and the
+// spans are added in registers with round-to-nearest. A read-out keeps the tensor cores off TMEM for the ~256 cycles it
+// lasts, so spans are made as long as the reference's own error allows. Measured against every x86 back end of the
+// reference (scalar, Haswell, Skylake, Genoa, Sapphire Rapids AMX) on the same inputs, error as |c - exact| / sum |a||b|,
+// max / mean, 64 values per stage:
+//   bf16, N(0,1):           depth 1024: reference 4.0e-8 / 4.3e-9, here 2 stages 5.0e-8 / 4.8e-9, 3 stages 6.3e-8 / 6.5e-9
+//                           depth 8192: reference 5.1e-8 / 5.1e-9, here 6 stages 3.2e-8 / 4.9e-9, 8 stages 4.6e-8 / 6.6e-9
+//   bf16, all-positive:     depth 1024: reference 3.6e-7 / 7.2e-8, here 3 stages 2.7e-7 / 7.0e-8, 4 stages 3.7e-7 / 1.6e-7
+//                           depth 8192: reference 1.5e-6 / 2.7e-7, here 6 stages 5.8e-7 / 2.6e-7, 8 stages 7.9e-7 / 4.9e-7
+//   f16, N(0,1):            depth 1024: reference 1.0e-7 / 1.05e-8, here 3 stages 9.5e-8 / 1.0e-8, 4 stages 9.4e-8 / 1.3e-8
+//                           depth 8192: reference 7.6e-8 / 1.07e-8, here 8 stages 6.1e-8 / 8.9e-9, 12 stages 8.1e-8 / 1.3e-8
+// Both follow span ~ sqrt(depth): bf16 sqrt(depth)/16 stages (4 sqrt(depth) values), f16 sqrt(depth)/11 stages. (bf16 products
+// carry 16 significant bits and survive the alignment to an accumulator up to 2^8 times larger untouched, which is why its
+// all-positive error has a knee at 256 values; f16 products carry 22 bits and lose some from the first stage on: on
+// all-positive f16 data even one-stage spans leave 1.8 units in the last place where the reference has 0.6 - 1.1.)
+// The 8- and 6-bit floats sit ten times lower and level off at 1e-8: 16 stages (measured at depth 8192: the error of the
+// reference's own kernels; 32 stages double it on wide-range inputs). e2m3 products are multiples of 2^-6 of at most 56.25,
+// so 4660 of them add up exactly in f32 whatever the inputs: 32 stages (4096 values).
+uint32_t default_accumulation_span(uint32_t dtype, uint64_t depth) {
+    if (dtype == kE2M3) return 32u;
+    if (dtype != kBF16 && dtype != kF16) return 16u;
+    const double stages = sqrt((double)depth) / (dtype == kBF16 ? 16.0 : 11.0);
+    uint32_t span = (uint32_t)(stages + 0.5);
+    if (span < 1u) span = 1u;
+    if (span > 16u) span = 16u;
+    return span;
+}
+
 EncodeTiledFn get_encode_tiled() {
     static EncodeTiledFn fn = nullptr;
     if (!fn) {
@@ -861,8 +942,6 @@ EncodeTiledFn get_encode_tiled() {
     }
     return fn;
 }
-
-int gemm_tc_launch_count(const GemmArgs &) { return 1; }
 
 cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     KindInfo ki;
@@ -920,30 +999,13 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     dev.tiles_n = (uint32_t)((args.n + bn - 1) / bn);
     dev.idesc = make_idesc(ki.c_fmt, ki.ab_fmt, kBM, bn);
     dev.int_mode = ki.int_mode;
-    // Span length for float kinds. Measured on B200: one long accumulation chain has a normalised error of
-    // ~7.6e-9 * span / sqrt(depth) for 16-bit floats (truncating accumulate), e.g. 3.7e-7 at depth 8192, 3e-7 at
-    // depth 1000; the 8/6-bit kinds sit ten times lower and level off at 1e-8. Reading a 128 KiB accumulator out of
-    // TMEM stalls the MMAs for ~256 cycles, so spans are made as long as the error target (1e-7, NumKong's own f32
-    // kernels measure 3e-8..7e-8) allows: span = 12 * sqrt(depth) values for 16-bit floats, capped at 16 stages;
-    // 16 stages for the 8/6-bit kinds (measured at depth 8192: the same error as the reference's own kernels; 32 stages
-    // double it on wide-range inputs). e2m3 products are multiples of 2^-6 of at most 56.25, so up to 4660 of them add
-    // up exactly in f32 whatever the inputs: 32 stages (4096 values). Integers are exact: one span.
+    // Integers are exact in one span; floats take the span the element type and depth call for unless one is forced.
     const uint32_t forced_flush = ((uint32_t)args.variant >> 8) & 0xffu;  // nkb_set_accumulation_span
-    uint32_t auto_flush = args.dtype == kE2M3 ? 32u : 16u;
-    if (ki.kind == kKindF16) {
-        uint32_t span_values = (uint32_t)(12.0 * sqrt((double)args.k));
-        auto_flush = span_values / dev.elems_per_kblock;
-        if (auto_flush < 1u) auto_flush = 1u;
-        // On same-sign data the truncation is a downward bias of about 4.7 units in the last place per stage of the span for
-        // f16 (whose products carry 22 significant bits) and 0.9 for bf16, whatever the depth. NumKong's own test harness
-        // accepts an f16 dots kernel up to 32 units on all-positive inputs (test/test.hpp:192-196; measured at its default
-        // shape: 4 stages 25, 5 stages 28, 6 stages 34), so f16 spans stop at 4 stages; bf16 (accepted up to 256) keeps 16.
-        const uint32_t cap = args.dtype == kF16 ? 4u : 16u;
-        if (auto_flush > cap) auto_flush = cap;
-    }
+    const uint32_t auto_flush = default_accumulation_span(args.dtype, args.k);
     dev.flush_kblocks = ki.kind == kKindI8 ? dev.kblocks : (forced_flush ? forced_flush : auto_flush);
     if (dev.flush_kblocks == 0) dev.flush_kblocks = 1;
     dev.error_word = args.error_word;
+    wait_limits_us(dev.wait_us);
     dev.tri_diag = args.tri_diag;
     const bool filtering = args.candidates != nullptr && args.epilogue != kEpiDot;
     dev.threshold_bits = filtering ? args.threshold_bits : nullptr;

@@ -22,7 +22,11 @@ int current_variant();
 MemKind classify(const void *p);
 void *scratch(int slot, size_t bytes);
 unsigned int *device_error_word();
+// Error status of the current device (0 = no bounded wait gave up since the last report); a reported failure is cleared.
 uint32_t read_device_error();
+// Device address of the allocation-free entry point's fixed error word on the current device, or nullptr when that entry
+// point has not run there yet (nkb_noalloc.cu).
+unsigned int *noalloc_error_word();
 void fill_error_output(void *out, MemKind kind, uint64_t rows, uint64_t row_bytes, uint64_t stride);
 
 const uint8_t *resident_blob(const void *blob, MemKind kind, uint32_t magic, uint32_t dtype, uint64_t rows,

@@ -88,6 +88,17 @@ inline bool dtype_supported(uint32_t dt) {
 
 inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 
+// Every mbarrier wait inside the tensor-core kernels is bounded. Wait sites (the number a wait that gave up leaves in the
+// error word, 0x80000000 | site << 16 | block):
+//   1 producer waits for a free pipeline stage          2 MMA issuer waits for a drained accumulator
+//   3 MMA issuer waits for a loaded stage               4 epilogue waits for a finished accumulator
+//   5 MMA issuer waits for its last MMAs before leaving 6 producer waits for its last copies before leaving
+#ifndef NKB_WAIT_LIMIT_NS
+#define NKB_WAIT_LIMIT_NS 2000000000ull  // 2 s
+#endif
+constexpr uint32_t kDefaultWaitLimitUs = (uint32_t)(NKB_WAIT_LIMIT_NS / 1000ull);
+constexpr int kWaitSites = 8;
+
 // Sub-byte types: `depth` counts values (nibbles for i4 / u4, bits for u1), a row occupies ceil(depth / per_byte) bytes,
 // and - like the reference's kernels (include/numkong/dot/serial.h:185-215) - every value of the last byte takes part
 // even when `depth` stops inside it. On the device such a row is expanded to one i8 / u8 per value, so everything after
@@ -196,9 +207,13 @@ struct GemmArgs {
     uint32_t candidate_capacity = 0;
     uint32_t column_id_base = 0;
 };
+// Enqueues exactly one kernel.
 cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream);
-// Number of kernels launch_gemm_tc enqueues for these arguments (for launch accounting).
-int gemm_tc_launch_count(const GemmArgs &args);
+// Limits of the kernels' bounded waits, one per wait site (microseconds; see nkb_ptx.cuh), as set by nkb_set_wait_limit_ns.
+void wait_limits_us(uint32_t (&out)[kWaitSites]);
+// Accumulation span (pipeline stages of 128 bytes of depth per tensor-core accumulation chain) the GEMM uses for a
+// floating-point element type at this depth when the caller has not forced one.
+uint32_t default_accumulation_span(uint32_t dtype, uint64_t depth);
 
 // f32 x f32 -> f64 on CUDA cores. `b` is the padded row-major f32 payload.
 cudaError_t launch_gemm_f32(int epilogue, const float *a, uint64_t a_stride, const float *b, uint64_t b_stride,

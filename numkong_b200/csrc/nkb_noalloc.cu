@@ -10,6 +10,10 @@
 // nkb_angulars_packed_noalloc does the same computation with the row-norm scratch (and the error word of
 // the pipeline waits) in fixed device arrays that are part of this library's image. The price is a
 // hard limit on the number of rows per call and one shared scratch per GPU.
+//
+// How such a caller learns that a pipeline wait gave up: nkb_synchronize() reads this fixed error word as well
+// (a 4-byte copy from an address cached at set-up; it creates nothing), returns it when it is non-zero and
+// clears it. A process that only ever uses this entry point therefore never allocates device memory here.
 #include <cstdio>
 #include <mutex>
 
@@ -53,6 +57,16 @@ bool noalloc_setup(DeviceAddresses &out) {
 }
 
 } // namespace
+
+// For nkb_synchronize(): where this device's fixed error word lives, once the entry point below has set it up; nullptr
+// before that. A lookup in a table the set-up filled in - no runtime call, no allocation.
+unsigned int *noalloc_error_word() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    return g_noalloc_addresses[dev].error_word;
+}
+
 } // namespace nkb
 
 using namespace nkb;
@@ -95,6 +109,6 @@ extern "C" NKB_API int nkb_angulars_packed_noalloc(uint32_t dtype, void const *a
     args.c = c; args.c_stride = c_stride; args.m = height; args.n = width; args.k = depth;
     args.depth_padded_bytes = g.depth_padded_bytes; args.error_word = addr.error_word; args.variant = current_variant();
     if (!cuda_ok(launch_gemm_tc(args, stream), "tensor-core GEMM kernel")) return 8;
-    g_launches += gemm_tc_launch_count(args);
+    g_launches++;
     return 0;
 }

@@ -2,19 +2,16 @@
 // mbarrier, TMA (tiled and untiled bulk copies), tcgen05 (TMEM allocation, MMA,
 // commit, TMEM loads) and the descriptor encodings that go with them.
 //
-// Every wait on an mbarrier is bounded: a wait that does not complete within
-// NKB_WAIT_LIMIT_NS records an error word in global memory and returns false,
-// so a mis-programmed pipeline ends with an error status instead of a hung GPU.
+// Every wait on an mbarrier is bounded: a wait that does not complete within its limit (2 s unless
+// the host passes a shorter one for a wait site) records an error word in global memory and returns
+// false, so a mis-programmed pipeline ends with an error status instead of a hung GPU.
 #pragma once
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include "nkb_internal.h"  // wait sites and the default wait limit
 
 namespace nkb {
-
-#ifndef NKB_WAIT_LIMIT_NS
-#define NKB_WAIT_LIMIT_NS 2000000000ull  // 2 s
-#endif
 
 // Error word layout (global memory, owned by the host side): 0 = ok, otherwise
 // 0x80000000 | (site << 16) | (blockIdx.x & 0xffff) of the first wait that gave up.
@@ -71,21 +68,19 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
         : "=r"(done) : "r"(bar), "r"(parity) : "memory");
     return done != 0;
 }
-// Bounded wait. Returns false (and records `site`) when the limit runs out.
+// Bounded wait. Returns false (and records `site`) when `limit_us` microseconds have passed without the phase completing.
+// The clock is only read once the first probe has failed, and then after every failed probe (a probe that fails has itself
+// waited for a while inside the hardware, so the reads are rare).
 template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t site, unsigned int *error_word) {
-    uint32_t spins = 0;
-    uint64_t start = 0;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t site, unsigned int *error_word,
+                                          uint32_t limit_us = kDefaultWaitLimitUs) {
+    if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
     while (true) {
-        bool ok = kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity);
-        if (ok) return true;
-        if ((++spins & 0x3ffu) == 0) {
-            uint64_t now = global_timer_ns();
-            if (start == 0) start = now;
-            else if (now - start > NKB_WAIT_LIMIT_NS) {
-                atomicCAS(error_word, 0u, (site << 16) | (blockIdx.x & 0xffffu) | 0x80000000u);
-                return false;
-            }
+        if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - start > (uint64_t)limit_us * 1000ull) {
+            atomicCAS(error_word, 0u, (site << 16) | (blockIdx.x & 0xffffu) | 0x80000000u);
+            return false;
         }
     }
 }

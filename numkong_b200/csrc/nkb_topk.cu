@@ -193,6 +193,110 @@ merge_topk_kernel(float *__restrict__ run_vals, long long *__restrict__ run_ids,
     }
 }
 
+// Merges `parts` lists per row (each `top` long, any order, empty slots marked by id < 0) into the `top` smallest by
+// (value, id). Lists are laid out [part][row][top]: what a gather of per-shard results delivers. One CTA per row;
+// dynamic shared memory holds `padded` (a power of two >= parts * top) ids followed by as many 32-bit value keys.
+// Unlike merge_topk_kernel this makes no assumption about which list holds the lower ids.
+__global__ void __launch_bounds__(kTopThreads)
+merge_parts_kernel(const float *__restrict__ vals, const long long *__restrict__ ids, uint32_t parts, uint64_t rows, uint32_t top,
+                   uint32_t padded, float *__restrict__ out_vals, long long *__restrict__ out_ids) {
+    extern __shared__ unsigned long long merge_smem[];
+    long long *s_id = reinterpret_cast<long long *>(merge_smem);
+    uint32_t *s_key = reinterpret_cast<uint32_t *>(s_id + padded);
+    const uint64_t row = blockIdx.x;
+    const uint32_t total = parts * top;
+    constexpr long long kNoId = 0x7fffffffffffffffll;
+    for (uint32_t i = threadIdx.x; i < padded; i += blockDim.x) {
+        uint32_t key = 0xffffffffu;
+        long long id = kNoId;
+        if (i < total) {
+            const uint64_t at = ((uint64_t)(i / top) * rows + row) * top + i % top;
+            const long long got = ids[at];
+            if (got >= 0) { id = got; key = order_key(vals[at]); }
+        }
+        s_key[i] = key;
+        s_id[i] = id;
+    }
+    for (uint32_t size = 2; size <= padded; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (uint32_t i = threadIdx.x; i < padded / 2; i += blockDim.x) {
+                const uint32_t lo = 2 * i - (i & (stride - 1)), hi = lo + stride;
+                const bool ascending = (lo & size) == 0;
+                const uint32_t ka = s_key[lo], kb = s_key[hi];
+                const long long ia = s_id[lo], ib = s_id[hi];
+                const bool a_after_b = ka > kb || (ka == kb && ia > ib);
+                if (a_after_b == ascending) { s_key[lo] = kb; s_key[hi] = ka; s_id[lo] = ib; s_id[hi] = ia; }
+            }
+        }
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < top; i += blockDim.x) {
+        const bool empty = s_id[i] == kNoId;
+        out_vals[row * top + i] = empty ? __uint_as_float(0x7f800000u) : key_value(s_key[i]);
+        out_ids[row * top + i] = empty ? -1 : s_id[i];
+    }
+}
+
+constexpr uint32_t kMergeMaxEntries = 16384;  // parts * top, rounded up to a power of two: 192 KiB of shared memory
+
+void merge_topk_impl(const void *values, const void *ids, uint64_t parts, uint64_t rows, uint64_t top, void *out_vals, void *out_ids) {
+    clear_error();
+    if (rows == 0 || top == 0) return;
+    const MemKind v_kind = classify(out_vals), i_kind = classify(out_ids);
+    auto fail = [&]() {
+        fill_error_output(out_vals, v_kind, rows, top * 4, top * 4);
+        fill_error_output(out_ids, i_kind, rows, top * 8, top * 8);
+    };
+    if (!values || !ids || !out_vals || !out_ids) { set_error("merge_topk: null pointer%s", ""); return; }
+    uint32_t padded = 2;
+    while (padded < parts * top && padded < 2 * kMergeMaxEntries) padded <<= 1;
+    if (parts == 0 || top > kTopMax || padded > kMergeMaxEntries || rows > 0x7fffffffull) {
+        set_error("merge_topk: at most 1024 per list and 16384 entries per row (parts x top)%s", "");
+        fail();
+        return;
+    }
+    cudaStream_t stream = current_stream();
+    const uint64_t n = parts * rows * top;
+    const MemKind sv_kind = classify(values), si_kind = classify(ids);
+    const float *v_in = static_cast<const float *>(values);
+    const long long *i_in = static_cast<const long long *>(ids);
+    bool ok = true;
+    if (sv_kind == kMemHost) {
+        void *buf = scratch(kSlotA, n * 4);
+        ok = buf && cuda_ok(cudaMemcpyAsync(buf, values, n * 4, cudaMemcpyHostToDevice, stream), "upload of top-k values");
+        v_in = static_cast<const float *>(buf);
+    }
+    if (ok && si_kind == kMemHost) {
+        void *buf = scratch(kSlotC, n * 8);
+        ok = buf && cuda_ok(cudaMemcpyAsync(buf, ids, n * 8, cudaMemcpyHostToDevice, stream), "upload of top-k ids");
+        i_in = static_cast<const long long *>(buf);
+    }
+    float *v_dev = static_cast<float *>(out_vals);
+    long long *i_dev = static_cast<long long *>(out_ids);
+    if (ok && v_kind == kMemHost) { v_dev = static_cast<float *>(scratch(kSlotAux, rows * top * 4)); ok = v_dev != nullptr; }
+    if (ok && i_kind == kMemHost) { i_dev = static_cast<long long *>(scratch(kSlotAux2, rows * top * 8)); ok = i_dev != nullptr; }
+    if (ok) {
+        const size_t smem = (size_t)padded * 12;
+        static bool configured[64] = {false};
+        int d = 0;
+        cudaGetDevice(&d);
+        if (d >= 0 && d < 64 && !configured[d]) {
+            ok = cuda_ok(cudaFuncSetAttribute(merge_parts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMergeMaxEntries * 12), "merge kernel set-up");
+            configured[d] = ok;
+        }
+        if (ok) {
+            merge_parts_kernel<<<(unsigned)rows, kTopThreads, smem, stream>>>(v_in, i_in, (uint32_t)parts, rows, (uint32_t)top, padded, v_dev, i_dev);
+            g_launches++;
+            ok = cuda_ok(cudaGetLastError(), "merge kernel");
+        }
+    }
+    if (ok && v_kind == kMemHost) ok = cuda_ok(cudaMemcpyAsync(out_vals, v_dev, rows * top * 4, cudaMemcpyDeviceToHost, stream), "download of merged values");
+    if (ok && i_kind == kMemHost) ok = cuda_ok(cudaMemcpyAsync(out_ids, i_dev, rows * top * 8, cudaMemcpyDeviceToHost, stream), "download of merged ids");
+    if (ok && (v_kind == kMemHost || i_kind == kMemHost || sv_kind == kMemHost || si_kind == kMemHost)) ok = cuda_ok(cudaStreamSynchronize(stream), "merge_topk");
+    if (!ok) fail();
+}
+
 // ---- fused selection: the GEMM epilogue filters, these kernels keep the running lists -------------------
 constexpr uint32_t kFilterTopMax = 128;       // largest k the filtered path serves
 constexpr uint32_t kFilterCapacity = 512;     // candidates kept per row and panel
@@ -380,7 +484,7 @@ void spatial_topk_impl(uint32_t dt, int epilogue, const void *a, const void *b_p
         g.c = panel; g.c_stride = width * 4; g.m = m; g.n = cols; g.k = k;
         g.depth_padded_bytes = h.depth_padded_bytes; g.error_word = err; g.variant = current_variant();
         ok = cuda_ok(launch_gemm_tc(g, stream), "tensor-core GEMM kernel");
-        g_launches += gemm_tc_launch_count(g);
+        g_launches++;
         if (!ok) break;
         float *pv = p == 0 ? run_vals : new_vals;
         long long *pi = p == 0 ? run_ids : new_ids;
@@ -418,7 +522,7 @@ void spatial_topk_impl(uint32_t dt, int epilogue, const void *a, const void *b_p
             g.threshold_bits = threshold_bits; g.candidate_counts = counts; g.candidates = candidates;
             g.candidate_capacity = kFilterCapacity; g.column_id_base = 0;
             ok = cuda_ok(launch_gemm_tc(g, stream), "tensor-core GEMM kernel (filter)");
-            g_launches += gemm_tc_launch_count(g);
+            g_launches++;
             if (!ok) break;
             filter_refine_kernel<<<(unsigned)m, kTopThreads, 0, stream>>>(run_vals, run_ids, candidates, counts, threshold_bits,
                                                                          kFilterCapacity, (uint32_t)top, id_base + seen, overflow);
@@ -461,6 +565,11 @@ NKB_API nk_size_t nkb_topk_filter_fallbacks(void) { return g_filter_fallbacks.lo
 NKB_API void nkb_topk_smallest_f32(void const *scores, nk_size_t rows, nk_size_t cols, nk_size_t stride, nk_size_t top,
                                    nk_size_t id_base, void *out_values, void *out_ids) {
     topk_smallest_impl(scores, rows, cols, stride, top, id_base, out_values, out_ids);
+}
+
+NKB_API void nkb_merge_topk(void const *values, void const *ids, nk_size_t parts, nk_size_t rows, nk_size_t top,
+                            void *out_values, void *out_ids) {
+    merge_topk_impl(values, ids, parts, rows, top, out_values, out_ids);
 }
 
 #define NKB_DEFINE_TOPK(T, DT)                                                                                         \

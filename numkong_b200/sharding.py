@@ -44,26 +44,32 @@ def broadcast_bytes(buffer: torch.Tensor, src: int = 0, group=None) -> torch.Ten
     return buffer
 
 
-def merge_topk(values: torch.Tensor, ids: torch.Tensor, top: int, group=None, dst: int = 0):
-    """Merges per-rank nearest-k lists (rows x k, ascending) with ONE gather. Returns (values, ids) on `dst`
-    (None elsewhere). Ties go to the lower id; slots with id < 0 are empty."""
+def merge_topk(values: torch.Tensor, ids: torch.Tensor, top: int, group=None, dst: int = 0, merge=None):
+    """Merges per-rank nearest-k lists (rows x k, f32 distances and i64 ids, ascending) with ONE gather and the library's
+    own merge kernel (nkb_merge_topk). Returns (values, ids) on `dst` (None elsewhere). Ties go to the lower id; slots
+    with id < 0 are empty.
+
+    Every rank's lists travel as one byte record per row (k f32 values followed by k i64 ids, 12 bytes per entry), over
+    NCCL for CUDA tensors. `merge(values[parts, rows, k], ids[parts, rows, k], top)` replaces the device kernel; the
+    CPU-only tests of this host logic pass a reference merge, nothing else should."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     if world == 1:
         return values, ids
-    packed = torch.cat([values.to(torch.float64), ids.to(torch.float64)], dim=1).contiguous()  # ids < 2^53 stay exact
-    if packed.is_cuda and dist.get_backend(group) == "gloo":
-        packed = packed.cpu()  # gloo moves host memory only; the merged lists then stay on the host
-    gathered = [torch.empty_like(packed) for _ in range(world)] if rank == dst else None
-    dist.gather(packed, gathered, dst=dst, group=group)
+    rows, k = values.shape
+    record = torch.cat([values.to(torch.float32).contiguous().view(torch.uint8).reshape(rows, k * 4),
+                        ids.to(torch.int64).contiguous().view(torch.uint8).reshape(rows, k * 8)], dim=1).contiguous()
+    if record.is_cuda and dist.get_backend(group) == "gloo":
+        record = record.cpu()  # gloo moves host memory only; the library then stages the merge through the device
+    gathered = torch.empty((world, rows, k * 12), dtype=torch.uint8, device=record.device) if rank == dst else None
+    dist.gather(record, list(gathered.unbind(0)) if rank == dst else None, dst=dst, group=group)
     if rank != dst:
         return None, None
-    k = values.shape[1]
-    all_vals = torch.cat([g[:, :k] for g in gathered], dim=1)
-    all_ids = torch.cat([g[:, k:] for g in gathered], dim=1).to(torch.int64)
-    all_vals = torch.where(all_ids < 0, torch.full_like(all_vals, float("inf")), all_vals)
-    # order by (value, id): sort by id first, then a stable sort by value
-    by_id = torch.argsort(all_ids, dim=1, stable=True)
-    all_vals, all_ids = torch.gather(all_vals, 1, by_id), torch.gather(all_ids, 1, by_id)
-    by_val = torch.argsort(all_vals, dim=1, stable=True)[:, :top]
-    return torch.gather(all_vals, 1, by_val).to(values.dtype), torch.gather(all_ids, 1, by_val)
+    all_vals = gathered[:, :, :k * 4].contiguous().view(torch.float32).reshape(world, rows, k)
+    all_ids = gathered[:, :, k * 4:].contiguous().view(torch.int64).reshape(world, rows, k)
+    if merge is None:
+        from . import merge_topk as merge
+    out_vals, out_ids = merge(all_vals if all_vals.is_cuda else all_vals.numpy(), all_ids if all_ids.is_cuda else all_ids.numpy(), top)
+    if not isinstance(out_vals, torch.Tensor):
+        out_vals, out_ids = torch.from_numpy(out_vals), torch.from_numpy(out_ids)
+    return out_vals.to(values.dtype), out_ids

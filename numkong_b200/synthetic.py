@@ -125,13 +125,16 @@ def finite_codes_matrix(rows: int, cols: int, dtype: str, seed: int, max_abs: fl
     return codes[rng.integers(0, len(codes), size=(rows, cols))]
 
 
-def lognormal_matrix(rows: int, cols: int, dtype: str, seed: int) -> np.ndarray:
-    """All-positive log-normal entries, the default distribution of the reference's C++ precision tests
-    (test/test.hpp:536-549)."""
+def lognormal_matrix(rows: int, cols: int, dtype: str, seed: int, signed: bool = False) -> np.ndarray:
+    """Log-normal(0, 0.5) entries. `signed=True` gives each a random sign, which is what the reference's C++ precision
+    tests draw for signed element types (include/numkong/random.hpp:130-146, default of test/test.hpp:536-549); the
+    all-positive form is the harder case for a truncating accumulator and is kept as the default."""
     rng = np.random.default_rng(seed)
     x = rng.lognormal(0.0, 0.5, size=(rows, cols)).astype(np.float32)
+    if signed and dtype != "u8":
+        x *= rng.choice(np.array([1.0, -1.0], dtype=np.float32), size=(rows, cols))
     if dtype in ("i8", "u8"):
-        x = np.minimum(x * 16, 127)
+        x = np.clip(x * 16, -127, 127)
     return encode(x, dtype)
 
 

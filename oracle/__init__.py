@@ -18,6 +18,7 @@ _HERE = Path(__file__).resolve().parent
 _SO = _HERE / "liboracle.so"
 REF_SO = _HERE / "_ref" / "libnumkong.so"
 REF_SERIAL_SO = _HERE / "_ref" / "libnkref_serial.so"
+REF_BACKENDS_SO = _HERE / "_ref" / "libnkref_backends.so"
 
 CODES = {"i8": 1 << 2, "u8": 1 << 6, "f32": 1 << 11, "f16": 1 << 12, "bf16": 1 << 13,
          "e4m3": 1 << 14, "e5m2": 1 << 15, "e2m3": 1 << 18, "e3m2": 1 << 19, "i4": 1 << 16, "u4": 1 << 17, "u1": 1 << 1, "f64": 1 << 10}
@@ -84,11 +85,21 @@ def build(force: bool = False) -> Path:
     return _SO
 
 
-def build_ref(reference_root: str = "/root/reference") -> bool:
+def reference_root() -> Optional[Path]:
+    """Where the NumKong source tree lies: $NUMKONG_REFERENCE, else a `reference` directory beside this repository."""
+    import os
+    for candidate in (os.environ.get("NUMKONG_REFERENCE"), _HERE.parent.parent / "reference"):
+        if candidate and Path(candidate, "c", "numkong.c").exists():
+            return Path(candidate)
+    return None
+
+
+def build_ref(root: Optional[str] = None) -> bool:
     """Compiles the reference from its own sources into oracle/_ref/ when the source tree is present."""
-    if not Path(reference_root, "c", "numkong.c").exists():
+    root = Path(root) if root else reference_root()
+    if root is None or not Path(root, "c", "numkong.c").exists():
         return False
-    subprocess.run(["make", "-s", "-C", str(_HERE), "ref", f"REF={reference_root}", "-j8"], check=True)
+    subprocess.run(["make", "-s", "-C", str(_HERE), "ref", f"REF={root}", "-j8"], check=True)
     return True
 
 
@@ -333,3 +344,46 @@ def ref() -> Optional[_Ref]:
 def ref_serial() -> Optional[_Ref]:
     """The reference's scalar back end, or None when it was not compiled."""
     return _Ref(REF_SERIAL_SO, "ref_") if REF_SERIAL_SO.exists() else None
+
+
+# ---------------------------------------------------------------- every x86 back end of the 16-bit float kernels
+# Capability bits of the reference (include/numkong/capabilities.h:261-304) each back end needs.
+_BACKEND_CAPS = {"serial": 1 << 0, "haswell": 1 << 2, "skylake": 1 << 3, "genoa": 1 << 8, "sapphireamx": 1 << 18}
+_BACKENDS = {"bf16": ("serial", "haswell", "skylake", "genoa", "sapphireamx"), "f16": ("serial", "haswell", "skylake")}
+
+
+class _RefBackends:
+    """The reference's packed bf16 / f16 kernels, one back end at a time (oracle/ref_backends_shim.c): the error of the
+    WORST of them on given inputs is the envelope the device kernels are held to."""
+
+    def __init__(self, path: Path):
+        self.lib = ctypes.CDLL(str(path))
+        self.lib.refb_capabilities.restype = ctypes.c_uint64
+        self.lib.refb_configure_thread.argtypes = [ctypes.c_uint64]
+        self.caps = int(self.lib.refb_capabilities())
+        self.lib.refb_configure_thread(self.caps)  # AMX needs the kernel's permission per thread
+
+    def available(self, dtype: str):
+        return [b for b in _BACKENDS[dtype] if self.caps & _BACKEND_CAPS[b]]
+
+    def packed(self, backend: str, op: str, a: np.ndarray, b: np.ndarray, dtype: str) -> np.ndarray:
+        a, b = _as_storage(a, dtype), _as_storage(b, dtype)
+        u64, vp = ctypes.c_uint64, ctypes.c_void_p
+        self.lib.refb_configure_thread(self.caps)
+        n, k = b.shape
+        size = getattr(self.lib, f"refb_{backend}_dots_packed_size_{dtype}")
+        size.restype, size.argtypes = u64, [u64, u64]
+        blob = np.zeros(size(n, k) + 64, dtype=np.uint8)
+        pack = getattr(self.lib, f"refb_{backend}_dots_pack_{dtype}")
+        pack.restype, pack.argtypes = None, [vp, u64, u64, u64, vp]
+        pack(b.ctypes.data, n, k, _stride(b), blob.ctypes.data)
+        fn = getattr(self.lib, f"refb_{backend}_{op}_packed_{dtype}")
+        fn.restype, fn.argtypes = None, [vp, vp, vp, u64, u64, u64, u64, u64]
+        c = np.empty((a.shape[0], n), dtype=np.float32)
+        fn(a.ctypes.data, blob.ctypes.data, c.ctypes.data, a.shape[0], n, k, _stride(a), c.strides[0])
+        return c
+
+
+def ref_backends() -> Optional[_RefBackends]:
+    """Per-back-end view of the reference, or None when it was not compiled."""
+    return _RefBackends(REF_BACKENDS_SO) if REF_BACKENDS_SO.exists() else None

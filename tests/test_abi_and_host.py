@@ -78,6 +78,18 @@ def test_find_kernel_punned_contract():
     lib.nk_find_kernel_punned(ord("G"), nk.DTYPE_CODES["i8"], 0x3, ctypes.byref(fn), ctypes.byref(cap))  # capability masked out
     assert not fn.value and cap.value == 0
     assert lib.nk_configure_thread(1 << 40) == 1
+    # moments under 'R' for all nineteen element types, the bulk conversion under '-' with the "unknown" type 0
+    # (include/numkong/capabilities.h:225,251; c/numkong.c:897)
+    moment_codes = dict(nk.DTYPE_CODES, i16=1 << 3, i32=1 << 4, i64=1 << 5, u16=1 << 7, u32=1 << 8, u64=1 << 9)
+    for name in ("f64", "f32", "f16", "bf16", "e4m3", "e5m2", "e2m3", "e3m2", "i8", "u8", "i16", "u16", "i32", "u32", "i64", "u64", "i4", "u4", "u1"):
+        lib.nk_find_kernel_punned(ord("R"), moment_codes[name], 1 << 40, ctypes.byref(fn), ctypes.byref(cap))
+        assert fn.value == ctypes.cast(getattr(lib, f"nk_reduce_moments_{name}"), ctypes.c_void_p).value and cap.value == 1 << 40, name
+    lib.nk_find_kernel_punned(ord("-"), 0, (1 << 64) - 1, ctypes.byref(fn), ctypes.byref(cap))
+    assert fn.value == ctypes.cast(lib.nk_cast, ctypes.c_void_p).value and cap.value == 1 << 40
+    lib.nk_find_kernel_punned(ord("-"), nk.DTYPE_CODES["f32"], (1 << 64) - 1, ctypes.byref(fn), ctypes.byref(cap))
+    assert not fn.value and cap.value == 0   # the conversion is looked up without an element type
+    lib.nk_find_kernel_punned(ord("R"), 1 << 21, (1 << 64) - 1, ctypes.byref(fn), ctypes.byref(cap))
+    assert not fn.value and cap.value == 0   # no moments of complex types
 
 
 def test_python_mirror_argument_checks():

@@ -1,0 +1,132 @@
+"""Host-side behaviour around the kernels: cross-shard merge, non-finite inputs in the filtered nearest-k, the cache of
+host-resident packed blobs, stream switches, and run-to-run determinism of the CTA-pair kernel."""
+import numpy as np
+import pytest
+
+import numkong_b200 as nk
+from numkong_b200 import synthetic as syn
+
+pytestmark = pytest.mark.gpu
+
+
+def _stable_merge(values, ids, top):
+    parts, rows, k = values.shape
+    flat_v = np.transpose(values, (1, 0, 2)).reshape(rows, parts * k)
+    flat_i = np.transpose(ids, (1, 0, 2)).reshape(rows, parts * k)
+    flat_v = np.where(flat_i < 0, np.float32(np.inf), flat_v)
+    order = np.lexsort((flat_i, flat_v), axis=1)[:, :top]
+    out_v, out_i = np.take_along_axis(flat_v, order, axis=1), np.take_along_axis(flat_i, order, axis=1)
+    return out_v, np.where(np.isinf(out_v) & (out_i < 0), -1, out_i)
+
+
+@pytest.mark.parametrize("parts,rows,top", [(2, 33, 10), (8, 70, 100), (3, 5, 1), (8, 4, 1024), (5, 9, 7)])
+def test_merge_topk_matches_a_stable_sort_by_value_then_id(parts, rows, top):
+    """nkb_merge_topk against sorting by (value, id): ties go to the lower id wherever they sit, empty slots (id < 0) lose."""
+    import torch
+    rng = np.random.default_rng(parts * 1000 + top)
+    values = rng.standard_normal((parts, rows, top)).astype(np.float32)
+    values = np.round(values * 4) / 4 if top > 1 else values      # many exact ties across and inside the lists
+    ids = rng.permutation(parts * rows * top).reshape(parts, rows, top).astype(np.int64)   # tie order unrelated to list order
+    values[:, :, -1:] = np.where(rng.random((parts, rows, 1)) < 0.3, np.float32(0.5), values[:, :, -1:])
+    empty = rng.random((parts, rows, top)) < 0.1
+    ids[empty] = -1
+    values[0, 0, :] = np.float32(1.0)                               # one row of nothing but ties
+    want_v, want_i = _stable_merge(values, ids, top)
+    got_v, got_i = nk.merge_topk(values, ids)                       # host pointers
+    assert np.array_equal(got_i, want_i) and np.array_equal(got_v, want_v)
+    dv, di = nk.merge_topk(torch.from_numpy(values).cuda(), torch.from_numpy(ids).cuda(), top=max(1, top // 2))   # device pointers
+    assert nk.synchronize() == 0
+    assert np.array_equal(di.cpu().numpy(), want_i[:, :max(1, top // 2)]) and np.array_equal(dv.cpu().numpy(), want_v[:, :max(1, top // 2)])
+
+
+@pytest.mark.parametrize("metric", ["angulars", "euclideans"])
+def test_filtered_topk_with_non_finite_rows_equals_materialised(metric):
+    """Rows holding Inf or values whose squared norm overflows make NaN / Inf dots. The storing epilogue maps those through
+    the full formula (a NaN falls out of the clamp as distance 0); the filtered path must select exactly the same entries,
+    so tiles whose norms are not finite may not take the sign-bit prefilter."""
+    dtype, m, n, k, top = "bf16", 64, 9000, 64, 10
+    a = syn.normal_matrix(m, k, dtype, 71, normalize=True)
+    b = syn.normal_matrix(n, k, dtype, 72, normalize=True)
+    inf, big = np.uint16(0x7F80), np.uint16(0x7F00)   # +Inf and 1.7e38 as bf16 bits
+    b[4000, 3] = inf          # a corpus row with an infinite element, in a filtered panel
+    b[7000, :] = big          # a corpus row whose squared norm overflows
+    b[100, 5] = inf           # one inside the materialised bootstrap panel
+    a[7, 0] = inf             # a query row with an infinite element
+    a[9, :] = big
+    p = nk.dots_pack(b, dtype)
+    full = getattr(nk, metric + "_packed")(a, p)
+    assert not np.isnan(full).any()
+    order = np.argsort(full, axis=1, kind="stable")[:, :top]
+    nk.lib.nkb_set_topk_filter(256)
+    try:
+        dist, ids = getattr(nk, metric + "_packed_topk")(a, p, top)
+    finally:
+        nk.lib.nkb_set_topk_filter(1)
+    assert np.array_equal(ids, order)
+    assert np.array_equal(dist, np.take_along_axis(full, order, axis=1))
+
+
+def test_cache_of_host_blobs_evicts_unpinned_entries_and_stays_correct():
+    """Host-resident packed blobs are uploaded once and cached on the device, eight at a time. A ninth evicts the least
+    recently used one that no call in flight has pinned; results stay right for old and new blobs alike."""
+    nk.lib.nkb_release_caches()
+    a = syn.normal_matrix(50, 128, "i8", 1)
+    blobs, wants = [], []
+    for i in range(11):
+        b = syn.normal_matrix(40 + i, 128, "i8", 10 + i)
+        blobs.append(nk.dots_pack(b, "i8"))
+        wants.append(a.astype(np.int32) @ b.astype(np.int32).T)
+        assert nk.lib.nkb_cached_blob_count() <= 8
+    assert nk.lib.nkb_cached_blob_count() == 8
+    for i in (0, 10, 3, 1, 9, 0, 5):   # evicted ones are uploaded again, cached ones reused
+        assert np.array_equal(nk.dots_packed(a, blobs[i]), wants[i])
+        assert nk.lib.nkb_cached_blob_count() <= 8
+    nk.lib.nkb_release_caches()
+    assert nk.lib.nkb_cached_blob_count() == 0
+    assert np.array_equal(nk.dots_packed(a, blobs[2]), wants[2])
+
+
+def test_switching_streams_between_asynchronous_calls_keeps_their_scratch_ordered():
+    """Two distance calls of one thread on two different streams share the thread's row-norm scratch. The second stream is
+    put behind the first when the thread switches, so the large first call still reads its own norms."""
+    import torch
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    big_a = torch.from_numpy(syn.normal_matrix(8192, 256, "bf16", 81).view(np.int16)).cuda()
+    small_a = torch.from_numpy(syn.normal_matrix(64, 256, "bf16", 82, scale=37.0).view(np.int16)).cuda()
+    packed = nk.dots_pack(torch.from_numpy(syn.normal_matrix(4096, 256, "bf16", 83).view(np.int16)).cuda(), "bf16")
+    want_big = nk.angulars_packed(big_a, packed, dtype="bf16")
+    want_small = nk.angulars_packed(small_a, packed, dtype="bf16")
+    assert nk.synchronize() == 0
+    try:
+        for _ in range(3):
+            nk.set_stream(s1.cuda_stream)
+            got_big = nk.angulars_packed(big_a, packed, dtype="bf16")
+            nk.set_stream(s2.cuda_stream)
+            got_small = nk.angulars_packed(small_a, packed, dtype="bf16")   # rewrites the first 64 norms
+            torch.cuda.synchronize()
+            assert torch.equal(got_big, want_big) and torch.equal(got_small, want_small)
+    finally:
+        nk.set_stream(0)
+
+
+def test_cta_pair_kernel_is_deterministic_and_equals_the_single_cta_kernel():
+    """f16 at depth 8192 hands an accumulator from the MMA issuer to the epilogue warps of BOTH CTAs of a pair sixteen times
+    per tile. Twenty runs on one input must give one result, and that of the single-CTA kernel."""
+    import torch
+    m = n = 4096
+    depth = 8192
+    a = torch.from_numpy(syn.normal_matrix(m, depth, "f16", 91).view(np.int16)).cuda()
+    packed = nk.dots_pack(torch.from_numpy(syn.normal_matrix(n, depth, "f16", 92).view(np.int16)).cuda(), "f16")
+    try:
+        nk.lib.nkb_set_gemm_variant(1)
+        single = nk.dots_packed(a, packed, dtype="f16")
+        nk.lib.nkb_set_gemm_variant(3)
+        first = nk.dots_packed(a, packed, dtype="f16")
+        assert torch.equal(first, single)
+        out = torch.empty_like(first)
+        for _ in range(20):
+            nk.dots_packed(a, packed, out=out, dtype="f16")
+            assert torch.equal(out, first)
+    finally:
+        nk.lib.nkb_set_gemm_variant(0)
+    assert nk.synchronize() == 0

@@ -17,6 +17,16 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+def _reference_merge(values, ids, top):
+    """Stand-in for the device merge kernel (no GPU here): [parts, rows, k] lists -> the `top` smallest by (value, id)."""
+    parts, rows, k = values.shape
+    flat_v = np.transpose(values, (1, 0, 2)).reshape(rows, parts * k)
+    flat_i = np.transpose(ids, (1, 0, 2)).reshape(rows, parts * k)
+    flat_v = np.where(flat_i < 0, np.inf, flat_v)
+    order = np.lexsort((flat_i, flat_v), axis=1)[:, :top]
+    return np.take_along_axis(flat_v, order, axis=1), np.take_along_axis(flat_i, order, axis=1)
+
+
 def _worker(rank, world, port, out_dir):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -34,7 +44,7 @@ def _worker(rank, world, port, out_dir):
         k = 5
         order = torch.argsort(local, dim=1, stable=True)[:, :k]
         vals, ids = torch.gather(local, 1, order), order + lo
-        mv, mi = sharding.merge_topk(vals, ids, k, dst=0)
+        mv, mi = sharding.merge_topk(vals, ids, k, dst=0, merge=_reference_merge)
         if rank == 0:
             want = torch.argsort(full, dim=1, stable=True)[:, :k]
             assert torch.equal(mi, want)
