@@ -254,7 +254,8 @@ NKB_API void nkb_topk_smallest_f32(void const *scores, nk_size_t rows, nk_size_t
                                    nk_size_t id_base, void *out_values, void *out_ids);
 /* nkb_merge_topk: the cross-shard step of a sharded search. `values` (f32) and `ids` (i64) hold `parts` nearest-k lists
  * per row, laid out [part][row][top] - what a gather of every shard's nkb_*_topk_* result delivers; slots with id < 0 are
- * empty. out_values[rows x top] / out_ids[rows x top] receive the `top` smallest per row ordered by (value, id), empty
+ * empty. out_values[rows x top] / out_ids[rows x top] receive the `top` smallest per row ordered by (value, id) (-0 before
+ * +0, as in every selection of this library), empty
  * slots as +inf / -1. parts * top (rounded up to a power of two) may not exceed 16384. Host or device pointers. */
 NKB_API void nkb_merge_topk(void const *values, void const *ids, nk_size_t parts, nk_size_t rows, nk_size_t top,
                             void *out_values, void *out_ids);

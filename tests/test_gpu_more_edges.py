@@ -65,8 +65,8 @@ def test_short_depth_products_with_ragged_shapes(dtype, k):
 
 def test_accumulation_span_trades_speed_for_accuracy():
     """Same-sign bf16 data at depth 4096 (the worst case of the truncating tensor-core accumulate): shorter spans bring the
-    error down in proportion, and at 4 stages it is at the level of the reference's own scalar kernel (about 3 units in
-    the last place at this depth)."""
+    error down, and the default span (4 stages at this depth) sits at the level of the reference's own scalar kernel
+    (1.85 units in the last place on these inputs)."""
     a, b = syn.lognormal_matrix(256, 4096, "bf16", 1), syn.lognormal_matrix(512, 4096, "bf16", 2)
     exact = oracle.exact_dots_f64(a, b, "bf16")
     nearest = exact.astype(np.float32)
@@ -74,14 +74,15 @@ def test_accumulation_span_trades_speed_for_accuracy():
     packed = nk.dots_pack(b, "bf16")
     errors = {}
     try:
-        for stages in (0, 8, 4):
+        for stages in (0, 16, 8, 4):
             nk.set_accumulation_span(stages)
             c = nk.dots_packed(a, packed, dtype="bf16")
             errors[stages] = float(np.mean(np.abs(c.astype(np.float64) - nearest.astype(np.float64)) / ulp))
     finally:
         nk.set_accumulation_span(0)
-    assert errors[4] < errors[8] < errors[0]
-    assert errors[4] <= 3.0 and errors[0] <= 25.0
+    assert errors[4] < errors[8] < errors[16]
+    assert errors[0] == errors[4]            # sqrt(4096) / 16 = 4 stages is the default for bf16 at this depth
+    assert errors[4] <= 2.3 and errors[16] <= 25.0
 
 
 @pytest.mark.parametrize("dtype,limit", [("f16", 32), ("bf16", 256), ("e4m3", 4), ("e5m2", 4), ("e2m3", 4), ("e3m2", 4)])

@@ -25,7 +25,7 @@ def test_merge_topk_matches_a_stable_sort_by_value_then_id(parts, rows, top):
     import torch
     rng = np.random.default_rng(parts * 1000 + top)
     values = rng.standard_normal((parts, rows, top)).astype(np.float32)
-    values = np.round(values * 4) / 4 if top > 1 else values      # many exact ties across and inside the lists
+    values = (np.round(values * 4) / 4 + np.float32(0.0)) if top > 1 else values   # many exact ties across and inside the lists (no -0: it sorts before +0)
     ids = rng.permutation(parts * rows * top).reshape(parts, rows, top).astype(np.int64)   # tie order unrelated to list order
     values[:, :, -1:] = np.where(rng.random((parts, rows, 1)) < 0.3, np.float32(0.5), values[:, :, -1:])
     empty = rng.random((parts, rows, top)) < 0.1
