@@ -2,25 +2,33 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype bf16] [--impl reference]
 
-One "step" is one nk_dots_packed_<t> call over one batch: A (8192 x 8192) against a pre-packed B
-(8192 x 8192), the configuration the metric is quoted on (M = N = K = 8192, N(0,1) entries rounded to
-the storage type, seeded; B is packed once outside the timed region exactly as the reference's own
-benchmark does, bench/bench.hpp:245). Unit: gso/s = 2*M*N*K / seconds / 1e9 (bench/bench.hpp:257).
+One "step" is one nk_dots_packed_<t> call over the metric's configuration: A (8192 x 8192) against a pre-packed B
+(8192 x 8192), N(0,1) entries rounded to the storage type, seeded; B is packed outside the timed region exactly as the
+reference's own benchmark does (bench/bench.hpp:245). Unit: gso/s = 2*M*N*K / seconds / 1e9 (bench/bench.hpp:257).
 
-With N > 1 ranks (torchrun) every rank multiplies its own 8192-row block of A against the same packed B
-(rows of A partitioned across GPUs: weak scaling, no collective on the data path; B is packed on rank 0
-and broadcast over NCCL once during set-up). The timed region is bracketed by a barrier and a device
-synchronize; the reported time is the maximum over ranks.
+N = 1: K steps back to back, operands resident in HBM.
 
-Prints ONE JSON line (rank 0). `value` is measured with operands resident in HBM; `e2e` is the same metric
-through the C ABI with HOST buffers (pinned): every step uploads A and downloads C inside the timed region.
-`--impl reference` times the reference's own CPU kernels (compiled from its sources into oracle/_ref/) on
-this host's cores, on a bounded sample of the same workload.
+N > 1 (torchrun, one rank per GPU): STRONG scaling of the same problem. The 8192 rows of A are split into N contiguous
+blocks, one per rank - the caller-side split the reference documents for its threads (README.md:209-212,
+rust/matrix.rs:3016-3026). Packed B exists on rank 0 only when the timed region starts and is broadcast over NCCL INSIDE
+it, once, in two column blocks: every rank multiplies its rows against the first block while the second is still on its
+way (the packed rows of a column block are one contiguous byte range of the blob), then runs the remaining K - 1 steps.
+The timed region is bracketed by a barrier and a device synchronize; the reported time is the maximum over ranks and
+`value` = K * 2 * 8192^3 / that time.
+
+Prints ONE JSON line (rank 0). `value` is measured with operands resident in HBM; `e2e` is the same metric through the
+C ABI with HOST buffers (pinned): every step uploads this rank's rows of A and downloads its rows of C inside the timed
+region. The default 1-GPU run adds: every other element type at 8192^3, library 8-bit GEMMs as peak probes, a sustained
+leg of at least two seconds, the reference's CPU kernels on all host threads and on one, and the two search workloads
+(sharded twins, which also run at every N > 1). `--impl reference` times the reference's own CPU kernels (compiled from
+its sources into oracle/_ref/) on this host's cores, on a bounded sample of the same workload, without loading this
+library.
 """
 from __future__ import annotations
 
 import argparse
 import ctypes
+import importlib.util
 import json
 import os
 import subprocess
@@ -37,12 +45,21 @@ M = N = K = 8192
 METRIC, UNIT = "dots_packed_gso_per_s", "gso/s"
 STORE = {1: np.uint8, 2: np.int16}
 SEEDS = {"bf16": 1, "f16": 1, "e4m3": 2, "e5m2": 2, "e2m3": 2, "e3m2": 2, "i8": 0, "u8": 0}
+ELEMENT_BYTES = {"bf16": 2, "f16": 2, "e4m3": 1, "e5m2": 1, "e2m3": 1, "e3m2": 1, "i8": 1, "u8": 1}
 
-
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from the ncu capture summarised in
-# profiles/gemm_tc_pair_bf16_8192_dram_traffic.md (1.116e9 read + 2.52e8 written; algorithmic bytes A + packed B + C
-# are 5.37e8). Keyed by (dtype, rows of A); other configurations report null.
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, from one ncu capture of this command
+# at the full size (1.116e9 read + 2.52e8 written; the algorithmic bytes A + packed B + C are 5.37e8). Keyed by
+# (element type, rows of A per launch); other configurations report null.
 NCU_DRAM_BYTES_PER_LAUNCH = {("bf16", 8192): 1_367_000_000}
+
+
+def _synthetic():
+    """The input generators, loaded from their file so that the reference arm does not import (and thereby load the shared
+    library of) the package it is compared with."""
+    spec = importlib.util.spec_from_file_location("_nkb_synthetic", os.path.join(ROOT, "numkong_b200", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def measured_peaks():
@@ -50,18 +67,30 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return {"bf16_tflops": float(p["bf16_tflops"]), "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
-    return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+        return {"bf16_tflops": float(p["bf16_tflops"]), "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
-def gen_rows(rows: int, dtype: str, seed: int) -> np.ndarray:
-    """rows x K synthetic matrix in the storage type of `dtype`, generated in blocks to bound host memory."""
-    from numkong_b200 import synthetic as syn
-    return np.concatenate([syn.normal_matrix(min(1024, rows - r), K, dtype, seed * 100003 + r) for r in range(0, rows, 1024)])
+def gen_rows(rows: int, dtype: str, seed: int, first_row: int = 0) -> np.ndarray:
+    """Rows [first_row, first_row + rows) of the K-column synthetic matrix of `seed`, in the storage type of `dtype`. The
+    matrix is defined in blocks of 1024 rows (block b is drawn from seed * 100003 + 1024 b), so any rank can make its
+    own rows without making the others; first_row must be a multiple of 1024 unless the request fits one block."""
+    syn = _synthetic()
+    out = []
+    r = first_row
+    while r < first_row + rows:
+        block = r // 1024 * 1024
+        full = syn.normal_matrix(1024, K, dtype, seed * 100003 + block)
+        lo, hi = r - block, min(1024, first_row + rows - block)
+        out.append(full[lo:hi])
+        r = block + hi
+    return np.concatenate(out) if len(out) > 1 else out[0]
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while a timed region runs: NVML polled in-process (read-only queries, about
+    a thousand per second - the timed region of the default run lasts some 15 ms), nvidia-smi as the fall-back."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -71,8 +100,6 @@ class ClockSampler:
         self.nvml_samples, self.nvml_stop, self.nvml_thread, self.nvml_max = [], threading.Event(), None, None
 
     def _start_nvml(self) -> bool:
-        """In-process NVML polling (read-only queries, about a thousand per second): the timed region of the default run
-        lasts some 15 ms, shorter than nvidia-smi's fastest sampling period."""
         try:
             import pynvml
             import torch
@@ -151,15 +178,37 @@ def _ref_library():
     return oracle.ref()
 
 
-def time_reference(dtype: str, steps: int, warmup: int, rows_per_step: int | None = None):
-    """Times the reference's dispatched CPU kernel on a bounded sample: `rows_per_step` rows of A against the
-    full packed B, rows split evenly over all host threads (each thread configures itself once, as
-    the reference requires for AMX: include/numkong/capabilities.h:393-410)."""
+def _run_threads(ref, threads: int, work) -> float:
+    """Seconds `work(t)` takes on `threads` host threads started together (each configures itself once, as the reference
+    requires for AMX: include/numkong/capabilities.h:393-410)."""
+    barrier = threading.Barrier(threads + 1)
+
+    def body(t):
+        ref.configure_thread()
+        barrier.wait()
+        work(t)
+        barrier.wait()
+
+    pool = [threading.Thread(target=body, args=(t,)) for t in range(threads)]
+    for th in pool:
+        th.start()
+    barrier.wait()
+    t0 = time.perf_counter()
+    barrier.wait()
+    dt = time.perf_counter() - t0
+    for th in pool:
+        th.join()
+    return dt
+
+
+def time_reference(dtype: str, steps: int, warmup: int, threads: int | None = None, seconds_per_step: float = 1.0):
+    """Times the reference's dispatched CPU kernel on a bounded sample: `rows_per_step` rows of A against the full packed
+    B, rows split evenly over `threads` host threads (default: all this process may run on)."""
     ref = _ref_library()
     if ref is None:
         return None
     import oracle
-    threads = max(1, len(os.sched_getaffinity(0)))
+    threads = threads or max(1, len(os.sched_getaffinity(0)))
     b = gen_rows(N, dtype, SEEDS[dtype] + 1)
     t0 = time.perf_counter()
     blob = ref.pack(b, dtype)
@@ -172,35 +221,21 @@ def time_reference(dtype: str, steps: int, warmup: int, rows_per_step: int | Non
     def run(a: np.ndarray, c: np.ndarray) -> float:
         rows = a.shape[0]
         per = (rows + threads - 1) // threads
-        barrier = threading.Barrier(threads + 1)
 
         def work(t):
-            ref.configure_thread()
             lo, hi = t * per, min(rows, (t + 1) * per)
-            barrier.wait()
             if hi > lo:
                 fn(a[lo:hi].ctypes.data, blob.ctypes.data, c[lo:hi].ctypes.data, hi - lo, N, K, K * eb, N * 4)
-            barrier.wait()
 
-        pool = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
-        for th in pool:
-            th.start()
-        barrier.wait()
-        t0 = time.perf_counter()
-        barrier.wait()
-        dt = time.perf_counter() - t0
-        for th in pool:
-            th.join()
-        return dt
+        return _run_threads(ref, threads, work)
 
-    if rows_per_step is None:
-        # calibrate: about one second of CPU work per step
-        probe_rows = threads * 8
-        a = gen_rows(probe_rows, dtype, SEEDS[dtype])
-        c = np.zeros((probe_rows, N), dtype=oracle.out_dtype(dtype))
-        run(a, c)
-        dt = run(a, c)
-        rows_per_step = int(min(M, max(threads * 8, probe_rows * 1.0 / max(dt, 1e-4)))) // threads * threads
+    # calibrate: about `seconds_per_step` of CPU work per step
+    probe_rows = threads * 8
+    a = gen_rows(probe_rows, dtype, SEEDS[dtype])
+    c = np.zeros((probe_rows, N), dtype=oracle.out_dtype(dtype))
+    run(a, c)
+    dt = run(a, c)
+    rows_per_step = max(threads, int(min(M, max(threads * 8, probe_rows * seconds_per_step / max(dt, 1e-4)))) // threads * threads)
     a = gen_rows(rows_per_step, dtype, SEEDS[dtype])
     c = np.zeros((rows_per_step, N), dtype=oracle.out_dtype(dtype))
     for _ in range(warmup):
@@ -219,30 +254,9 @@ def time_reference_search():
     ref = _ref_library()
     if ref is None:
         return None
-    from numkong_b200 import synthetic as syn
+    syn = _synthetic()
     threads = max(1, len(os.sched_getaffinity(0)))
     u64, vp = ctypes.c_uint64, ctypes.c_void_p
-
-    def run_threads(work):
-        barrier = threading.Barrier(threads + 1)
-
-        def body(t):
-            ref.configure_thread()
-            barrier.wait()
-            work(t)
-            barrier.wait()
-
-        pool = [threading.Thread(target=body, args=(t,)) for t in range(threads)]
-        for th in pool:
-            th.start()
-        barrier.wait()
-        t0 = time.perf_counter()
-        barrier.wait()
-        dt = time.perf_counter() - t0
-        for th in pool:
-            th.join()
-        return dt
-
     out = {}
     # nearest: 1024 queries x 20,000 corpus rows x 768, f16
     q_rows, c_rows, depth = 1024, 20000, 768
@@ -259,8 +273,8 @@ def time_reference_search():
         if hi > lo:
             fn(q[lo:hi].ctypes.data, blob.ctypes.data, dist_m[lo:hi].ctypes.data, hi - lo, c_rows, depth, depth * 2, c_rows * 4)
 
-    run_threads(nearest_work)
-    dt = min(run_threads(nearest_work) for _ in range(2))
+    _run_threads(ref, threads, nearest_work)
+    dt = min(_run_threads(ref, threads, nearest_work) for _ in range(2))
     out["nearest"] = {"gso_per_s": 2.0 * q_rows * c_rows * depth / dt / 1e9, "cores": threads, "kind": "reference",
                       "sample": f"nk_angulars_packed_f16, {q_rows} queries x {c_rows} corpus rows x {depth}, distance matrix only (no selection)"}
     # MaxSim: 8 queries x 32 tokens against 256 documents of 64..300 tokens, bf16, depth 128
@@ -277,30 +291,31 @@ def time_reference_search():
             for i in range(8):
                 ms(queries[i].ctypes.data, docs[j].ctypes.data, 32, int(counts[j]), 128, scores[i, j:j + 1].ctypes.data)
 
-    run_threads(maxsim_work)
-    dt = min(run_threads(maxsim_work) for _ in range(2))
+    _run_threads(ref, threads, maxsim_work)
+    dt = min(_run_threads(ref, threads, maxsim_work) for _ in range(2))
     out["maxsim"] = {"gso_per_s": 2.0 * 8 * 32 * float(counts.sum()) * 128 / dt / 1e9, "cores": threads, "kind": "reference",
                      "sample": f"nk_maxsim_packed_bf16, 8 queries x 32 tokens vs 256 documents ({int(counts.sum())} tokens), one call per pair"}
     return out
 
 
 def reference_arm(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """The reference's own CPU implementation of the step, on all host threads, one instance whatever --gpus says (rank 0
+    runs it under torchrun, the other ranks leave at once)."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     dtype = args.dtype
     res = time_reference(dtype, args.steps, args.warmup)
     if res is None:
-        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libnumkong.so has not been built (make -C oracle ref)"}))
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libnumkong.so has not been built (make -C oracle ref REF=<NumKong tree>)"}))
         return
     line = {
-        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": dtype_arith(dtype), "data": "synthetic",
-        "config": workload_config(dtype, 1) | {"sample_rows_per_step": res["rows_per_step"]},
+        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak",
+        "vs_baseline": None, "dtype": dtype_arith(dtype), "data": "synthetic", "config": workload_config(dtype, args.gpus),
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "sample_rows_per_step": res["rows_per_step"],
+        "note": "one CPU instance on this host's cores; --gpus only selects the configuration it is compared with",
     }
     print(json.dumps(line))
 
@@ -311,10 +326,11 @@ def dtype_arith(dtype: str) -> str:
 
 
 def workload_config(dtype: str, n_gpus: int):
-    return {"workload": f"dots_packed {dtype} M=N=K=8192 per GPU (B pre-packed, N(0,1) rounded to {dtype}, seed {SEEDS[dtype]})",
-            "rows_of_A_per_gpu": M, "global_rows_of_A": M * n_gpus, "width": N, "depth": K,
-            "parallelism": f"rows of A partitioned over {n_gpus} GPU(s), packed B replicated",
-            "l2": "operands (A 8192x8192 + packed B + C = 384-512 MiB) exceed the 126 MB L2; no explicit flush"}
+    split = "all 8192 rows of A on one GPU" if n_gpus == 1 else \
+        f"the 8192 rows of A split into {n_gpus} contiguous blocks of {M // n_gpus}, one per GPU; packed B broadcast from rank 0 inside the timed region"
+    return {"workload": f"dots_packed {dtype} M=N=K=8192 (B pre-packed, N(0,1) rounded to {dtype}, seed {SEEDS[dtype]})",
+            "global_rows_of_A": M, "rows_of_A_per_gpu": M // n_gpus, "width": N, "depth": K, "parallelism": split,
+            "l2": "operands of a step (A block + packed B 128 MiB + C block) exceed the 126 MB L2; no explicit flush"}
 
 
 def time_device_steps(nk, torch, ta, packed, out, dtype, steps):
@@ -327,6 +343,77 @@ def time_device_steps(nk, torch, ta, packed, out, dtype, steps):
     return start.elapsed_time(stop) / 1e3
 
 
+def library_peak_probes(torch, peaks):
+    """Library 8-bit GEMMs at 8192^3 as PEAK PROBES for the 8-bit element types (this pool publishes a measured figure for
+    bf16 only): torch._scaled_mm on e4m3 and torch._int_mm on i8, device-resident operands in this GPU's own memory, CUDA
+    events, best of three rounds of ten. Not part of any timed region of this library."""
+    def best_of(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / 10 / 1e3)
+        return 2.0 * 8192 ** 3 / best / 1e12
+
+    out = {"assumed_8bit_tflops": 2.0 * peaks["bf16_tflops"], "assumed_note": "2 x the measured cuBLAS bf16 burst"}
+    try:
+        a = torch.randn(8192, 8192, device="cuda").to(torch.float8_e4m3fn)
+        b = torch.randn(8192, 8192, device="cuda").to(torch.float8_e4m3fn)
+        one = torch.ones((), device="cuda", dtype=torch.float32)
+        out["scaled_mm_e4m3_tflops"] = best_of(lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+        del a, b
+    except Exception as e:  # a probe that this torch build does not offer is reported, not fatal
+        out["scaled_mm_e4m3_error"] = str(e)[:200]
+    try:
+        a = torch.randint(-128, 128, (8192, 8192), device="cuda", dtype=torch.int8)
+        b = torch.randint(-128, 128, (8192, 8192), device="cuda", dtype=torch.int8)
+        out["int_mm_i8_tops"] = best_of(lambda: torch._int_mm(a, b.t()))
+        del a, b
+    except Exception as e:
+        out["int_mm_i8_error"] = str(e)[:200]
+    torch.cuda.empty_cache()
+    return out
+
+
+def sustained_leg(nk, torch, ta, packed, out, dtype, peaks, device_index, seconds=2.5):
+    """Back-to-back launches for at least `seconds`, NVML clocks sampled throughout: the figure to set beside the measured
+    SUSTAINED cuBLAS rate (a 20-step burst runs at the full boost clock, a long run settles at the power cap)."""
+    sampler = ClockSampler(device_index)
+    sampler.start()
+    time.sleep(0.2)
+    torch.cuda.synchronize()
+    wall0 = time.time()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    launches = 0
+    while True:
+        for _ in range(200):
+            nk.dots_packed(ta, packed, out=out, dtype=dtype)
+        launches += 200
+        torch.cuda.synchronize()
+        if time.time() - wall0 >= seconds:
+            break
+    stop.record()
+    torch.cuda.synchronize()
+    wall1 = time.time()
+    elapsed = start.elapsed_time(stop) / 1e3
+    clocks = sampler.stop(wall0, wall1)
+    tflops = 2.0 * ta.shape[0] * N * K * launches / elapsed / 1e12
+    ms = elapsed / launches * 1e3
+    return {"value": tflops * 1e3, "unit": UNIT, "seconds": elapsed, "launches": launches, "ms_per_step": ms,
+            "frac_of_sustained_peak": tflops / peaks["bf16_tflops_sustained"],
+            "peak": peaks["bf16_tflops_sustained"], "peak_note": f"{peaks['source']} cuBLAS bf16, seconds-long loop under the power cap",
+            "clocks": clocks, "ms_x_sm_mhz": ms * clocks["sm_mhz"] if clocks.get("sm_mhz") else None,
+            "note": "host synchronises every 200 launches (a few microseconds of idle per 150 ms)"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -334,9 +421,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-extras", action="store_true", help="skip the per-dtype table and the CPU baseline")
+    ap.add_argument("--no-extras", action="store_true", help="skip everything but the headline measurement")
     ap.add_argument("--rows", type=int, default=8192,
-                    help="rows of A per GPU; anything but 8192 is a reduced case for profiler captures, not the benchmark")
+                    help="global rows of A; anything but 8192 is a reduced case for profiler captures, not the benchmark")
     args = ap.parse_args()
     global M
     M = args.rows
@@ -348,7 +435,7 @@ def main():
     import torch
     import torch.distributed as dist
     import numkong_b200 as nk
-    from numkong_b200 import sharding
+    from numkong_b200 import sharding, workloads
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -357,31 +444,81 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dtype = args.dtype
-    nk.set_stream(torch.cuda.current_stream().cuda_stream)
+    eb = ELEMENT_BYTES[dtype]
+    compute = torch.cuda.current_stream()
+    nk.set_stream(compute.cuda_stream)
 
-    # ---- set-up (untimed): this rank's rows of A, B packed on rank 0 and broadcast
-    a_host = gen_rows(M, dtype, SEEDS[dtype] + 1000 * rank)
-    ta = torch.from_numpy(a_host.view(STORE[a_host.itemsize])).cuda()
+    # ---- set-up (untimed): this rank's rows of A on the device; B packed on rank 0
+    row0, row1 = sharding.row_shard(M, world, rank)
+    rows = row1 - row0
+    a_host = gen_rows(rows, dtype, SEEDS[dtype], first_row=row0)
+    ta = torch.from_numpy(a_host.view(STORE[eb])).cuda()
     size = nk.PackedMatrix.packed_size(N, K, dtype)
-    blob = torch.empty(size, dtype=torch.uint8, device="cuda")
+    blob = torch.zeros(size, dtype=torch.uint8, device="cuda")
     if rank == 0:
         b_host = gen_rows(N, dtype, SEEDS[dtype] + 1)
-        tb = torch.from_numpy(b_host.view(STORE[b_host.itemsize])).cuda()
-        packed0 = nk.dots_pack(tb, dtype)
-        blob.copy_(packed0.buffer)
-        del tb, packed0
+        tb = torch.from_numpy(b_host.view(STORE[eb])).cuda()
+        getattr(nk.lib, f"nk_dots_pack_{dtype}")(tb.data_ptr(), N, K, K * eb, blob.data_ptr())
+        nk.check("pack")
+        del tb
     torch.cuda.synchronize()
-    sharding.broadcast_bytes(blob, src=0)
     packed = nk.PackedMatrix(blob, dtype, N, K)
     out_dtype = torch.int32 if dtype in ("i8", "u8") else torch.float32
-    out = torch.empty((M, N), dtype=out_dtype, device="cuda")
+    out = torch.empty((rows, N), dtype=out_dtype, device="cuda")
+
+    # The broadcast of the timed region: two column blocks, each one contiguous byte range of the blob (the first carries
+    # the 128-byte header, the second the norms behind the payload). Packed rows come in blocks of 256.
+    half_cols = N // 2 // 256 * 256
+    depth_padded = (K * eb + 127) // 128 * 128
+    cut = 128 + half_cols * depth_padded
+    pieces = [(0, cut, 0, half_cols), (cut, size, half_cols, N - half_cols)]
+    comm = torch.cuda.Stream() if world > 1 else None
+
+    def broadcast_and_first_step():
+        """Rank 0 sends the packed matrix piece by piece on the communication stream; every rank multiplies a piece as soon
+        as it has arrived while the next one is still in flight."""
+        comm.wait_stream(compute)
+        arrived = []
+        with torch.cuda.stream(comm):
+            for lo, hi, _, _ in pieces:
+                dist.broadcast(blob[lo:hi], src=0)
+                ev = torch.cuda.Event()
+                ev.record(comm)
+                arrived.append(ev)
+        for ev, (_, _, first, count) in zip(arrived, pieces):
+            compute.wait_event(ev)
+            nk.dots_packed(ta, packed, out=out, dtype=dtype, columns=(first, count))
+
+    collective = None
+    if world > 1:
+        # untimed: B reaches every rank once so that the warm-up steps have data; also warms NCCL up and times the plain
+        # broadcast of the whole blob for the report
+        dist.broadcast(blob, src=0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.broadcast(blob, src=0)
+        e1.record()
+        torch.cuda.synchronize()
+        tb_ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tb_ms, op=dist.ReduceOp.MAX)
+        collective = {"op": "ncclBroadcast of packed B from rank 0, inside the timed region, once, in 2 column blocks overlapped with the first step",
+                      "bytes": int(size), "standalone_ms_whole_blob": float(tb_ms.item())}
+        broadcast_and_first_step()   # warm-up of the piecewise path
 
     for _ in range(args.warmup):
         nk.dots_packed(ta, packed, out=out, dtype=dtype)
     torch.cuda.synchronize()
     assert nk.synchronize() == 0, "device error word set during warm-up"
+    reference_rows = out[:4].clone()
+    if world > 1:
+        # the timed region must deliver B itself: every rank but the sender forgets what the warm-up left behind
+        if rank != 0:
+            blob.zero_()
+        torch.cuda.synchronize()
 
-    # ---- timed region: exactly K steps, barrier + synchronize on both sides, max over ranks
+    # ---- timed region: the broadcast (N > 1) and exactly K steps, barrier + synchronize on both sides, max over ranks
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -390,27 +527,41 @@ def main():
         dist.barrier()
     torch.cuda.synchronize()
     launches0, wall0 = nk.launch_count(), time.time()
-    seconds = time_device_steps(nk, torch, ta, packed, out, dtype, args.steps)
+    start, first_done, stop = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    start.record()
+    if world > 1:
+        broadcast_and_first_step()
+        first_done.record()
+        for _ in range(args.steps - 1):
+            nk.dots_packed(ta, packed, out=out, dtype=dtype)
+    else:
+        for _ in range(args.steps):
+            nk.dots_packed(ta, packed, out=out, dtype=dtype)
+    stop.record()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     wall1 = time.time()
     launches = nk.launch_count() - launches0
-    t = torch.tensor([seconds], dtype=torch.float64, device="cuda")
+    seconds = start.elapsed_time(stop) / 1e3
+    t = torch.tensor([seconds, start.elapsed_time(first_done) / 1e3 if world > 1 else 0.0], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    seconds = float(t.item())
+    seconds, first_step_seconds = float(t[0].item()), float(t[1].item())
     clocks = sampler.stop(wall0, wall1) if rank == 0 else None
     assert nk.synchronize() == 0, "device error word set during the timed region"
+    assert torch.equal(out[:4], reference_rows), "the timed region's result differs from the warm-up's"
+    if collective is not None:
+        collective["first_step_ms_with_broadcast"] = first_step_seconds * 1e3
+        collective["steady_ms_per_step"] = (seconds - first_step_seconds) / max(1, args.steps - 1) * 1e3
 
-    # ---- end to end through the C ABI with host buffers (pinned): upload A, multiply, download C every step
-    a_pin = torch.from_numpy(a_host.view(STORE[a_host.itemsize])).pin_memory()
-    c_pin = torch.empty((M, N), dtype=out_dtype).pin_memory()
+    # ---- end to end through the C ABI with host buffers (pinned): upload this rank's rows of A, multiply, download its C
+    a_pin = torch.from_numpy(a_host.view(STORE[eb])).pin_memory()
+    c_pin = torch.empty((rows, N), dtype=out_dtype).pin_memory()
     fn = getattr(nk.lib, f"nk_dots_packed_{dtype}")
-    eb = a_host.itemsize
 
     def e2e_step():
-        fn(a_pin.data_ptr(), blob.data_ptr(), c_pin.data_ptr(), M, N, K, K * eb, N * 4)
+        fn(a_pin.data_ptr(), blob.data_ptr(), c_pin.data_ptr(), rows, N, K, K * eb, N * 4)
 
     for _ in range(2):
         e2e_step()
@@ -428,61 +579,75 @@ def main():
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_seconds = float(te.item())
-    # spot check of the e2e result against the device-resident result
     assert torch.equal(c_pin[:4].cuda(), out[:4]), "host-buffer path and device path disagree"
+    del a_pin, c_pin
 
-    ops_per_step = 2.0 * M * N * K
-    value = ops_per_step * world * args.steps / seconds / 1e9
+    ops_per_step = 2.0 * M * N * K                     # the whole job's step: all ranks together
+    value = ops_per_step * args.steps / seconds / 1e9
     peaks = measured_peaks()
-    per_launch_s = seconds / args.steps
-    achieved_tflops = ops_per_step / per_launch_s / 1e12
-    peak = peaks["bf16_tflops"] * (1.0 if dtype in ("bf16", "f16") else 2.0)
+    # roofline of the dominant kernel: one launch = this rank's rows; duration = the steady step (all launches at N = 1)
+    launch_seconds = seconds / args.steps if world == 1 else (seconds - first_step_seconds) / max(1, args.steps - 1)
+    achieved_tflops = 2.0 * rows * N * K / launch_seconds / 1e12
+    bf16_like = dtype in ("bf16", "f16")
+    peak = peaks["bf16_tflops"] * (1.0 if bf16_like else 2.0)
 
-    extras = {}
-    search = {}
-    cpu_baseline = None
+    extras, probes, sustained, cpu_baseline, cpu_single = {}, None, None, None, None
     if rank == 0 and world == 1 and not args.no_extras:
-        del a_pin, c_pin
+        probes = library_peak_probes(torch, peaks)
+        peak8 = max(probes["assumed_8bit_tflops"], probes.get("scaled_mm_e4m3_tflops", 0.0), probes.get("int_mm_i8_tops", 0.0))
+        sustained = sustained_leg(nk, torch, ta, packed, out, dtype, peaks, local)
         for dt in ("bf16", "f16", "i8", "u8", "e4m3", "e5m2", "e2m3", "e3m2"):
+            pk = peaks["bf16_tflops"] if dt in ("bf16", "f16") else peak8
             if dt == dtype:
-                extras[dt] = {"gso_per_s": value, "frac_of_peak": achieved_tflops / peak}
+                extras[dt] = {"gso_per_s": value, "frac_of_measured_peak": achieved_tflops / pk, "peak_tflops": pk}
                 continue
-            xa = torch.from_numpy(gen_rows(M, dt, SEEDS[dt]).view(STORE[nk.DTYPE_BYTES[dt]])).cuda()
-            xb = torch.from_numpy(gen_rows(N, dt, SEEDS[dt] + 1).view(STORE[nk.DTYPE_BYTES[dt]])).cuda()
+            xa = torch.from_numpy(gen_rows(M, dt, SEEDS[dt]).view(STORE[ELEMENT_BYTES[dt]])).cuda()
+            xb = torch.from_numpy(gen_rows(N, dt, SEEDS[dt] + 1).view(STORE[ELEMENT_BYTES[dt]])).cuda()
             xp = nk.dots_pack(xb, dt)
             xo = torch.empty((M, N), dtype=torch.int32 if dt in ("i8", "u8") else torch.float32, device="cuda")
             for _ in range(3):
                 nk.dots_packed(xa, xp, out=xo, dtype=dt)
             torch.cuda.synchronize()
             s = time_device_steps(nk, torch, xa, xp, xo, dt, 10)
-            pk = peaks["bf16_tflops"] * (1.0 if dt in ("bf16", "f16") else 2.0)
-            extras[dt] = {"gso_per_s": ops_per_step * 10 / s / 1e9, "frac_of_peak": ops_per_step * 10 / s / 1e12 / pk}
+            extras[dt] = {"gso_per_s": ops_per_step * 10 / s / 1e9, "frac_of_measured_peak": ops_per_step * 10 / s / 1e12 / pk, "peak_tflops": pk}
             del xa, xb, xp, xo
         res = time_reference(dtype, steps=3, warmup=1)
         if res is not None:
             cpu_baseline = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        # The two search workloads on their small twins (BASELINE configs 4 and 5 scaled down), GPU and reference CPU.
-        from numkong_b200 import workloads
-        near = workloads.run_nearest(1024, 200000, 768, 10, "f16", steps=5)
-        late = workloads.run_maxsim(64, 20000, steps=3)
-        cpu_search = time_reference_search() or {}
-        search = {"nearest_top10_1024x200000x768_f16": {"gso_per_s": near["gso_per_s"], "ms": near["ms"], "cpu": cpu_search.get("nearest")},
-                  "maxsim_top100_64x20000_bf16": {"gso_per_s": late["gso_per_s"], "ms": late["ms"], "cpu": cpu_search.get("maxsim")}}
+            one = time_reference(dtype, steps=2, warmup=1, threads=1, seconds_per_step=2.0)
+            cpu_single = {k: one[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    # ---- the two search workloads on sharded twins, at every N: corpus rows / documents split over the ranks, every rank
+    # searches its shard, the k best per query are merged on rank 0 with one gather and the library's merge kernel; timed
+    # from "shards packed and resident" to "merged lists on rank 0", slowest rank.
+    search = {}
+    if not args.no_extras:
+        del ta, out
+        torch.cuda.empty_cache()
+        near = workloads.run_nearest_sharded(8192, 8_000_000, 768, 10, "f16", steps=2, warmup=1)
+        late = workloads.run_maxsim_sharded(256, 200_000, 128, 100, steps=2, warmup=1)
+        if rank == 0:
+            cpu_search = (time_reference_search() or {}) if world == 1 else {}
+            search = {"nearest_top10_8192x8000000x768_f16": dict(near, cpu=cpu_search.get("nearest")),
+                      "maxsim_top100_256x200000_bf16": dict(late, cpu=cpu_search.get("maxsim"))}
 
     if rank == 0:
+        note = f"peak = {peaks['source']} cuBLAS bf16 burst {peaks['bf16_tflops']} TF/s"
+        if not bf16_like:
+            note += " x 2 for 8-bit operands (see peak_probes for the library 8-bit GEMMs measured in this run)"
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": dtype_arith(dtype), "data": "synthetic", "config": workload_config(dtype, world),
+            "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "vs_baseline": None, "dtype": dtype_arith(dtype), "data": "synthetic", "config": workload_config(dtype, world),
             "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peak, "unit": "TFLOP/s", "frac": achieved_tflops / peak,
-                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((dtype, args.rows)),
-                         "note": f"peak = {peaks['source']} cuBLAS bf16 burst {peaks['bf16_tflops']} TF/s"
-                                 + ("" if dtype in ("bf16", "f16") else " x 2 for 8-bit operands (no measured 8-bit figure on this pool)")},
-            "cpu_baseline": cpu_baseline,
-            "e2e": {"value": ops_per_step * world * e2e_steps / e2e_seconds / 1e9, "unit": UNIT,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((dtype, rows)), "note": note,
+                         "launch": f"{rows} x {N} x {K}, mean duration {launch_seconds * 1e3:.4f} ms (CUDA events on the launching stream)"},
+            "cpu_baseline": cpu_baseline, "cpu_baseline_single_thread": cpu_single,
+            "e2e": {"value": ops_per_step * e2e_steps / e2e_seconds / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": M * K * eb, "d2h_bytes_per_step": M * N * 4, "steps": e2e_steps,
                     "ms_per_step": e2e_seconds / e2e_steps * 1e3},
-            "gpu_launches": int(launches), "clocks": clocks, "per_dtype": extras, "search_workloads": search,
+            "gpu_launches": int(launches), "clocks": clocks, "collective": collective, "sustained": sustained,
+            "peak_probes": probes, "per_dtype": extras, "search_workloads": search,
         }
         print(json.dumps(line))
     if world > 1:

@@ -260,6 +260,16 @@ NKB_API void nkb_topk_smallest_f32(void const *scores, nk_size_t rows, nk_size_t
 NKB_API void nkb_merge_topk(void const *values, void const *ids, nk_size_t parts, nk_size_t rows, nk_size_t top,
                             void *out_values, void *out_ids);
 
+/* nkb_dots_packed_columns: nk_dots_packed_<t> (element type by its code) restricted to the columns
+ * [first_column, first_column + column_count) of the result, i.e. to that range of packed rows; first_column must be a
+ * multiple of 256. `c` points at cell (0, 0) of the full height x width result, of which only those columns are written.
+ * For callers that receive the packed matrix piecewise (a broadcast in column blocks: the packed rows of a block are one
+ * contiguous byte range of the blob, 256 rows = 256 * depth_padded bytes from offset 128 on) and want to multiply the
+ * blocks that have arrived while the others are still on their way. No counterpart in the reference. */
+NKB_API void nkb_dots_packed_columns(uint32_t dtype, void const *a, void const *b_packed, void *c, nk_size_t height,
+                                     nk_size_t width, nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride,
+                                     nk_size_t first_column, nk_size_t column_count);
+
 /* ---- batched angular distances without any device allocation -----------------------------------
  * No counterpart in the reference (which never allocates because it runs on the caller's CPU buffers).
  *
@@ -295,7 +305,8 @@ NKB_API void nkb_set_stream(void *cuda_stream);
 /** Waits for the calling thread's stream and returns the device error word: 0, or 0x80000000 | site << 16 | block of the
  *  first bounded pipeline wait that gave up on this GPU since the last report (sites: 1 loader waiting for a free stage,
  *  2 / 3 MMA issuer waiting for a drained accumulator / a loaded stage, 4 epilogue waiting for a finished accumulator,
- *  5 / 6 the issuer's / loader's final drain). Covers the regular entry points and nkb_angulars_packed_noalloc alike,
+ *  5 / 6 the issuer's / loader's final drain, 7 epilogue waiting for the other half of a tile whose depth two CTA pairs
+ *  share). Covers the regular entry points and nkb_angulars_packed_noalloc alike,
  *  allocates nothing, and clears the word it reports: the failure belongs to the calls enqueued before this
  *  synchronisation (their results are not valid), later calls start clean. Calls with a host-resident operand do this
  *  check themselves and fill their output with 0xFF. */

@@ -234,7 +234,7 @@ def _out_matrix(v: _View, width: int, out: Any, dtype_name: str):
     return None, 0, 0
 
 
-def _packed_call(op: str, a: Any, packed: PackedMatrix, out: Any, dtype: Optional[str]):
+def _packed_call(op: str, a: Any, packed: PackedMatrix, out: Any, dtype: Optional[str], columns: Optional[Tuple[int, int]] = None):
     if not isinstance(packed, PackedMatrix) or packed.kind != "dots":
         raise TypeError("second argument must be a PackedMatrix produced by dots_pack")
     v = _view_like(a, dtype, packed.dtype)
@@ -252,14 +252,22 @@ def _packed_call(op: str, a: Any, packed: PackedMatrix, out: Any, dtype: Optiona
             ndt = np.float64 if t in ("f32", "f64") else (_OUT_NUMPY.get(t, np.float32) if _integer_cells(t, op) else np.float32)
             obj = np.empty((v.rows, packed.width), dtype=ndt)
             ptr, stride = obj.ctypes.data, packed.width * obj.itemsize
-    getattr(lib, f"nk_{op}_packed_{t}")(v.ptr, _ptr(packed.buffer), ptr, v.rows, packed.width, v.depth, v.stride, stride)
+    if columns is not None:
+        if op != "dots":
+            raise ValueError("a column range is available for dots_packed only")
+        lib.nkb_dots_packed_columns(DTYPE_CODES[t], v.ptr, _ptr(packed.buffer), ptr, v.rows, packed.width, v.depth, v.stride, stride,
+                                    int(columns[0]), int(columns[1]))
+    else:
+        getattr(lib, f"nk_{op}_packed_{t}")(v.ptr, _ptr(packed.buffer), ptr, v.rows, packed.width, v.depth, v.stride, stride)
     check(f"{op}_packed")
     return obj
 
 
-def dots_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Optional[str] = None):
-    """C = A . B^T with widening accumulation (i8->i32, u8->u32, f32->f64, else f32). Mirrors nk.dots_packed."""
-    return _packed_call("dots", a, packed, out, dtype)
+def dots_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Optional[str] = None, columns: Optional[Tuple[int, int]] = None):
+    """C = A . B^T with widening accumulation (i8->i32, u8->u32, f32->f64, else f32). Mirrors nk.dots_packed.
+    `columns=(first, count)` (an addition; first a multiple of 256) computes only that range of columns of C and leaves
+    the rest of `out` untouched (nkb_dots_packed_columns)."""
+    return _packed_call("dots", a, packed, out, dtype, columns)
 
 
 def angulars_packed(a: Any, packed: PackedMatrix, *, out: Any = None, dtype: Optional[str] = None):

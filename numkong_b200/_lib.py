@@ -82,6 +82,8 @@ def _load() -> ctypes.CDLL:
     lib.nkb_topk_smallest_f32.restype = None
     lib.nkb_topk_smallest_f32.argtypes = [vp, sz, sz, sz, sz, sz, vp, vp]
     lib.nkb_merge_topk.restype, lib.nkb_merge_topk.argtypes = None, [vp, vp, sz, sz, sz, vp, vp]
+    lib.nkb_dots_packed_columns.restype = None
+    lib.nkb_dots_packed_columns.argtypes = [ctypes.c_uint32, vp, vp, vp, sz, sz, sz, sz, sz, sz, sz]
     lib.nkb_angulars_packed_noalloc.restype = ctypes.c_int
     lib.nkb_angulars_packed_noalloc.argtypes = [ctypes.c_uint32, vp, vp, vp, sz, sz, sz, sz, sz]
     lib.nkb_set_wait_limit_ns.restype, lib.nkb_set_wait_limit_ns.argtypes = None, [ctypes.c_int, sz]

@@ -399,9 +399,15 @@ bool ensure_pipe_streams() {
 
 // One packed call on `stream` without the final synchronisation: stages A and C as needed, launches the
 // kernels, copies C back. Returns false (error text set) on failure.
+// `first_column` (a multiple of 256) selects the packed rows [first_column, first_column + n) of the blob; `c` then points at
+// the cell of the first of those columns.
 bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const uint8_t *blob, const PackedHeader &h,
                  unsigned int *err, void *c, MemKind c_kind, uint64_t m, uint64_t n, uint64_t k, uint64_t a_stride,
-                 uint64_t c_stride, cudaStream_t stream) {
+                 uint64_t c_stride, cudaStream_t stream, uint64_t first_column = 0) {
+    // Packed rows are stored in blocks of 128 (tensor-core types: one chunk column of depth_padded_bytes / 128 chunks per
+    // block) or one after the other (f32 / f64), so a column range is a byte offset into the payload and the norms.
+    const uint8_t *payload = blob + h.payload_offset + first_column * h.depth_padded_bytes;
+    const uint8_t *norms = blob + h.norms_offset + first_column * norm_bytes(dt);
     const uint32_t out_bytes = dot_out_bytes(dt);
     const uint64_t c_row_bytes = n * out_bytes;
     // Output: in place when it is device memory with 4-byte aligned rows, else a dense device copy.
@@ -432,14 +438,14 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
         }
         if (ok && dt == kF32) {
             ok = cuda_ok(launch_gemm_f32(epilogue, static_cast<const float *>(a_dev), a_pitch,
-                                         reinterpret_cast<const float *>(blob + h.payload_offset), h.depth_padded_bytes,
-                                         reinterpret_cast<const double *>(blob + h.norms_offset), a_norms,
+                                         reinterpret_cast<const float *>(payload), h.depth_padded_bytes,
+                                         reinterpret_cast<const double *>(norms), a_norms,
                                          reinterpret_cast<double *>(c_dev), c_pitch, m, n, k, stream), "f32 GEMM kernel");
             g_launches++;
         } else if (ok) {
             ok = cuda_ok(launch_gemm_f64(epilogue, static_cast<const double *>(a_dev), a_pitch,
-                                         reinterpret_cast<const double *>(blob + h.payload_offset), h.depth_padded_bytes,
-                                         reinterpret_cast<const double *>(blob + h.norms_offset), a_norms,
+                                         reinterpret_cast<const double *>(payload), h.depth_padded_bytes,
+                                         reinterpret_cast<const double *>(norms), a_norms,
                                          reinterpret_cast<double *>(c_dev), c_pitch, m, n, k, stream), "f64 GEMM kernel");
             g_launches++;
         }
@@ -490,7 +496,7 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
         if (ok) {
             GemmArgs g;
             g.dtype = operand_dtype(dt); g.epilogue = epilogue; g.a = a_dev; g.a_stride = a_pitch;
-            g.b_payload = blob + h.payload_offset; g.b_norms = blob + h.norms_offset; g.a_norms = a_norms;
+            g.b_payload = payload; g.b_norms = norms; g.a_norms = a_norms;
             g.c = c_dev; g.c_stride = c_pitch; g.m = m; g.n = n; g.k = operand_depth(dt, k);
             g.depth_padded_bytes = h.depth_padded_bytes; g.error_word = err; g.variant = g_variant.load();
             ok = cuda_ok(launch_gemm_tc(g, stream), "tensor-core GEMM kernel");
@@ -504,10 +510,21 @@ bool packed_core(uint32_t dt, int epilogue, const void *a, MemKind a_kind, const
     return ok;
 }
 
+// `first_column` / `column_count` restrict the call to a range of packed rows (columns of the result); `c` always points at
+// cell (0, 0) of the full result. column_count == ~0 means "all of them".
 void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed, void *c, uint64_t m, uint64_t n,
-                 uint64_t k, uint64_t a_stride, uint64_t c_stride) {
+                 uint64_t k, uint64_t a_stride, uint64_t c_stride, uint64_t first_column = 0, uint64_t column_count = ~0ull) {
     clear_error();
     const uint32_t out_bytes = dot_out_bytes(dt);  // distances share the cell width of the dots
+    const uint64_t width = n;  // packed rows in the blob
+    if (column_count != ~0ull) {
+        if (first_column % kRowPad || first_column > n || column_count > n - first_column) {
+            set_error("packed columns: the first column must be a multiple of 256 and the range must lie inside the packed matrix%s", "");
+            return;
+        }
+        n = column_count;
+        c = c ? static_cast<uint8_t *>(c) + first_column * out_bytes : c;
+    }
     const uint64_t c_row_bytes = n * out_bytes;
     if (m == 0 || n == 0) return;
     const MemKind c_kind = classify(c);
@@ -519,7 +536,7 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
     const MemKind a_kind = classify(a), b_kind = classify(b_packed);
 
     PackedHeader h;
-    const uint8_t *blob = resident_blob(b_packed, b_kind, kMagicDots, dt, n, k, &h);
+    const uint8_t *blob = resident_blob(b_packed, b_kind, kMagicDots, dt, width, k, &h);
     if (!blob) { fail(); return; }
     unsigned int *err = device_error_word();
     if (!err) { set_error("could not allocate the device error word%s", ""); fail(); return; }
@@ -543,7 +560,7 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
             t_ctx.use_override = true;
             t_ctx.override_stream = t_ctx.pipe[block & 1];
             ok = packed_core(dt, epilogue, static_cast<const uint8_t *>(a) + r0 * a_stride, a_kind, blob, h, err,
-                             static_cast<uint8_t *>(c) + r0 * c_stride, c_kind, rows, n, k, a_stride, c_stride, t_ctx.pipe[block & 1]);
+                             static_cast<uint8_t *>(c) + r0 * c_stride, c_kind, rows, n, k, a_stride, c_stride, t_ctx.pipe[block & 1], first_column);
         }
         t_ctx.slot_set = 0;
         t_ctx.use_override = false;
@@ -553,7 +570,7 @@ void packed_impl(uint32_t dt, int epilogue, const void *a, const void *b_packed,
             ok = ok && joined;
         }
     } else {
-        ok = packed_core(dt, epilogue, a, a_kind, blob, h, err, c, c_kind, m, n, k, a_stride, c_stride, stream);
+        ok = packed_core(dt, epilogue, a, a_kind, blob, h, err, c, c_kind, m, n, k, a_stride, c_stride, stream, first_column);
     }
     const bool must_sync = a_kind == kMemHost || b_kind == kMemHost || c_kind == kMemHost;
     if (ok && must_sync) {
@@ -627,6 +644,13 @@ NKB_API void nk_hammings_packed_u1(void const *v, void const *q_packed, void *re
 NKB_API void nk_jaccards_packed_u1(void const *v, void const *q_packed, void *result, nk_size_t rows, nk_size_t cols, nk_size_t d,
                                    nk_size_t v_stride, nk_size_t r_stride) {
     packed_impl(kU1, kEpiJaccard, v, q_packed, result, rows, cols, d, v_stride, r_stride);
+}
+
+NKB_API void nkb_dots_packed_columns(uint32_t dtype, void const *a, void const *b_packed, void *c, nk_size_t height, nk_size_t width,
+                                     nk_size_t depth, nk_size_t a_stride, nk_size_t c_stride, nk_size_t first_column,
+                                     nk_size_t column_count) {
+    if (!dtype_supported(dtype)) { clear_error(); set_error("packed columns: unsupported element type%s", ""); return; }
+    packed_impl(dtype, kEpiDot, a, b_packed, c, height, width, depth, a_stride, c_stride, first_column, column_count);
 }
 
 NKB_API char const *nkb_last_error(void) { return t_ctx.error.c_str(); }

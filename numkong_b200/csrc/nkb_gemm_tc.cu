@@ -12,7 +12,9 @@
 //               two of them, so reading one out overlaps the MMAs that fill the other
 //   warps 2..9  epilogue: tcgen05.ld of their 32-lane quarter and column half, f32/i32 summation of the
 //               accumulation spans in registers, finalisation, global stores
+#include <atomic>
 #include <cmath>
+#include <mutex>
 #include <type_traits>
 #include "nkb_internal.h"
 #include "nkb_ptx.cuh"
@@ -52,6 +54,9 @@ struct GemmDev {
     uint2 *candidates;
     uint32_t candidate_capacity;
     uint32_t column_id_base;
+    // Split mode of the CTA-pair kernel (see PairWork): hand-over flags of this launch and the value that marks them set.
+    uint32_t *split_flags;   // nullptr = whole tiles
+    uint32_t split_epoch;
 };
 
 // Epilogue scratch after the barriers: column factors (2 x 256 f32) + eight staging blocks of 32 rows x (W + 4) words,
@@ -296,9 +301,13 @@ __device__ __forceinline__ void filter_tile(uint32_t (&acc)[kCols], const GemmDe
 // Euclidean: sqrt(max(0, |a|^2 + |b|^2 - 2 dot)) (include/numkong/spatial/serial.h:272-278).
 //   zero_cols  some column factor of this tile is special (see special_factor: a zero vector or padding past the last column
 //              under the angular epilogue, a norm that is not finite under either)
-template <int kEpi, int kCols, int kW, bool kFloat>
+//   kAccum     (raw dots only) add the values to what the cells already hold instead of overwriting them: the second half of a
+//              tile whose depth was split between two CTA pairs
+template <int kEpi, int kCols, int kW, bool kFloat, bool kAccum = false>
 __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev &p, uint32_t row_base, uint32_t col_base,
                                            uint32_t *stage, const float *colf, uint32_t colf_off, int lane, bool zero_cols) {
+    static_assert(!kAccum || kEpi == kEpiDot, "only raw dots can be added up across depth ranges");
+    auto plus = [](uint32_t x, uint32_t y) { return kFloat ? __float_as_uint(__uint_as_float(x) + __uint_as_float(y)) : x + y; };
     constexpr int kPitch = kW + 4;          // words per staged row (keeps 16-byte accesses aligned and conflict-free)
     constexpr int kQuads = kW / 4;          // 16-byte pieces per staged row
     constexpr int kRowsPerStore = 32 / kQuads;
@@ -342,20 +351,26 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
 #pragma unroll
         for (int it = 0; it < kQuads; ++it) {
             const uint32_t r = it * kRowsPerStore + (uint32_t)lane / kQuads, q = (uint32_t)lane % kQuads;
-            const uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kPitch + q * 4);
+            uint4 v = *reinterpret_cast<const uint4 *>(stage + r * kPitch + q * 4);
             const uint32_t row = row_base + r, col = col0 + q * 4;
             // Triangular mode: the first column this row keeps (0 when the product is rectangular).
             const uint32_t keep_from = p.tri_diag >= 0 ? row + (uint32_t)p.tri_diag : 0u;
             if (row < p.m && col < p.n && col + 4 > keep_from) {
                 uint32_t *dst = reinterpret_cast<uint32_t *>(p.c + (uint64_t)row * p.c_stride) + col;
-                if (col + 4 <= p.n && col >= keep_from + (kEpi != kEpiDot ? 1u : 0u) && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0)
+                if (col + 4 <= p.n && col >= keep_from + (kEpi != kEpiDot ? 1u : 0u) && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                    if constexpr (kAccum) {
+                        const uint4 old = *reinterpret_cast<const uint4 *>(dst);
+                        v = make_uint4(plus(v.x, old.x), plus(v.y, old.y), plus(v.z, old.z), plus(v.w, old.w));
+                    }
                     *reinterpret_cast<uint4 *>(dst) = v;
-                else {
+                } else {
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        if (col + j < p.n && col + j >= keep_from)
-                            dst[j] = (kEpi != kEpiDot && p.tri_diag >= 0 && col + j == keep_from) ? 0u : w[j];  // distance to itself
+                        if (col + j < p.n && col + j >= keep_from) {
+                            if constexpr (kAccum) dst[j] = plus(w[j], dst[j]);
+                            else dst[j] = (kEpi != kEpiDot && p.tri_diag >= 0 && col + j == keep_from) ? 0u : w[j];  // distance to itself
+                        }
                 }
             }
         }
@@ -582,6 +597,65 @@ constexpr int kPairStageBytes = kBM * kBKBytes + (kPairBN / 2) * kBKBytes;  // 1
 constexpr int kPairBarrierOffset = kPairStages * kPairStageBytes;
 constexpr int kPairSmemTotal = kPairBarrierOffset + 256 + kEpiSmemBytesDecl + 1024;
 
+// The work of one CTA pair. Whole-tile mode: tiles pair, pair + P, pair + 2 P, ... Split mode: the pipeline stages of all tiles
+// are numbered tile by tile and dealt out in P equal contiguous shares, so that every pair is busy for the same time even when
+// the tiles do not fill a whole number of waves (1024 x 8192 makes 128 tiles for 74 pairs: 1.73 waves, 2 with whole tiles). A
+// share may begin in the middle of one tile and end in the middle of another. Shares are at least one tile long (the launcher
+// sees to that), so a tile is shared by at most two pairs: the one whose share BEGINS inside it computes the later depth range
+// first thing and stores it as a partial result; the one whose share ENDS inside it computes the earlier depth range last and
+// adds it to the stored partial (a + b = b + a: the result does not depend on timing). Flags in global memory order the two.
+struct PairWork {
+    uint32_t tile, k0, k1;  // current item: depth stages [k0, k1) of `tile`
+    uint32_t next_tile, stride, num_tiles, kblocks;
+    uint64_t unit, unit_end;
+    bool split;
+    __device__ PairWork(const GemmDev &p, uint32_t pair, uint32_t num_pairs, uint32_t tiles)
+        : tile(0), k0(0), k1(0), next_tile(pair), stride(num_pairs), num_tiles(tiles), kblocks(p.kblocks), unit(0), unit_end(0),
+          split(p.split_flags != nullptr) {
+        if (split) {
+            const uint64_t total = (uint64_t)tiles * kblocks;
+            unit = total * pair / num_pairs;
+            unit_end = total * (pair + 1) / num_pairs;
+        }
+    }
+    __device__ bool next() {
+        if (!split) {
+            if (next_tile >= num_tiles) return false;
+            tile = next_tile; k0 = 0; k1 = kblocks;
+            next_tile += stride;
+            return true;
+        }
+        if (unit >= unit_end) return false;
+        tile = (uint32_t)(unit / kblocks);
+        k0 = (uint32_t)(unit - (uint64_t)tile * kblocks);
+        const uint64_t left = unit_end - unit;
+        k1 = left < (uint64_t)(kblocks - k0) ? k0 + (uint32_t)left : kblocks;
+        unit += k1 - k0;
+        return true;
+    }
+};
+
+// Sixteen flags per shared tile, one per epilogue warp of the pair that stored the partial result.
+__device__ __forceinline__ void publish_partial(uint32_t *flag, uint32_t epoch) {
+    __threadfence();
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+}
+// All lanes of a warp call this; returns false (recording wait site 7) when the flags do not show up within the limit.
+__device__ __forceinline__ bool await_partial(const uint32_t *flags, uint32_t epoch, int lane, unsigned int *error_word, uint32_t limit_us) {
+    const uint64_t start = global_timer_ns();
+    while (true) {
+        uint32_t v = epoch;
+        if (lane < 2 * kEpilogueWarps) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
+        if (__all_sync(0xffffffffu, v == epoch)) return true;
+        const bool expired = __shfl_sync(0xffffffffu, (uint32_t)(global_timer_ns() - start > (uint64_t)limit_us * 1000ull), 0) != 0;
+        if (expired) {
+            if (lane == 0) atomicCAS(error_word, 0u, (7u << 16) | (blockIdx.x & 0xffffu) | 0x80000000u);
+            return false;
+        }
+        __nanosleep(200);
+    }
+}
+
 template <int kKind, int kEpi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map, const GemmDev p) {
@@ -638,13 +712,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
             int stage = 0;
             uint32_t phase = 0, issued = 0;
             bool ok = true;
-            for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+            for (PairWork work(p, pair, num_pairs, num_tiles); ok && work.next();) {
                 uint32_t mt, nt;
-                tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+                tile_coords(work.tile, p.tiles_m, p.tiles_n, mt, nt);
                 if (tile_skipped(p.tri_diag, mt * 256u, (nt + 1) * kBN)) continue;
                 const uint32_t a_row = mt * 256u + rank * 128u;
                 const uint64_t b_chunk0 = ((uint64_t)nt * 2u + rank) * p.kblocks;  // this CTA's half of the B tile
-                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                for (uint32_t kb = work.k0; kb < work.k1; ++kb) {
                     if (!mbar_wait<true>(empty_bar(stage), phase ^ 1u, 1, p.error_word, p.wait_us[1])) { ok = false; break; }
                     const uint32_t a_dst = smem_base + stage * kPairStageBytes;
                     const uint32_t b_dst = a_dst + kBM * kBKBytes;
@@ -679,16 +753,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
             int stage = 0;
             uint32_t phase = 0, seq = 0;
             bool ok = true;
-            for (uint32_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+            for (PairWork work(p, pair, num_pairs, num_tiles); ok && work.next();) {
                 uint32_t mt, nt;
-                tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+                tile_coords(work.tile, p.tiles_m, p.tiles_n, mt, nt);
                 if (tile_skipped(p.tri_diag, mt * 256u, (nt + 1) * kBN)) continue;
-                for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
+                for (uint32_t kb0 = work.k0; kb0 < work.k1 && ok; kb0 += p.flush_kblocks, ++seq) {
                     const uint32_t buf = seq & 1u, buf_phase = (seq >> 1) & 1u;
                     if (!mbar_wait<true>(tmem_empty_bar(buf), buf_phase ^ 1u, 2, p.error_word, p.wait_us[2])) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + buf * kBN;
-                    const uint32_t kb1 = min(kb0 + p.flush_kblocks, p.kblocks);
+                    const uint32_t kb1 = min(kb0 + p.flush_kblocks, work.k1);
                     for (uint32_t kb = kb0; kb < kb1; ++kb) {
                         if (!mbar_wait<true>(full_bar(stage), phase, 3, p.error_word, p.wait_us[3])) { ok = false; break; }
                         tc_fence_after_sync();
@@ -716,9 +790,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
         uint32_t *epi_stage = reinterpret_cast<uint32_t *>(smem_gen + kPairBarrierOffset + 256 + kEpiColfBytes) + (warp - 2) * kEpiStageWords;
         uint32_t seq = 0, local_tile = 0;
         bool ok = true;
-        for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs) {  // keeps walking after a failed wait, see above
+        for (PairWork work(p, pair, num_pairs, num_tiles); work.next();) {  // keeps walking after a failed wait, see above
             uint32_t mt, nt;
-            tile_coords(tile, p.tiles_m, p.tiles_n, mt, nt);
+            tile_coords(work.tile, p.tiles_m, p.tiles_n, mt, nt);
             if (tile_skipped(p.tri_diag, mt * 256u, (nt + 1) * kBN)) continue;
             bool zero_cols = false;
             if constexpr (kEpi != kEpiDot) {
@@ -730,11 +804,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
             uint32_t acc[kColsPerThread];
 #pragma unroll
             for (int j = 0; j < kColsPerThread; ++j) acc[j] = 0u;
-            for (uint32_t kb0 = 0; kb0 < p.kblocks && ok; kb0 += p.flush_kblocks, ++seq) {
+            for (uint32_t kb0 = work.k0; kb0 < work.k1 && ok; kb0 += p.flush_kblocks, ++seq) {
                 const uint32_t buf = seq & 1u, buf_phase = (seq >> 1) & 1u;
                 if (!mbar_wait<true>(tmem_full_bar(buf), buf_phase, 4, p.error_word, p.wait_us[4])) { ok = false; break; }
                 tc_fence_after_sync();
-                if (kb0 == 0) {
+                if (kb0 == work.k0) {
                     // First span of a tile: nothing to add to, so every load goes straight into the accumulators and all of
                     // them are in flight before the one wait.
 #pragma unroll
@@ -761,9 +835,30 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
                 if (lane == 0) mbar_arrive_cluster_addr(map_to_cta(tmem_empty_bar(buf), 0));
             }
             if (!ok) continue;
+            if constexpr (kEpi == kEpiDot) {
+                if (work.k1 < p.kblocks) {
+                    // The earlier depth range of a tile shared with the next pair, which stored the later range long ago (it was
+                    // that pair's first item, this is our last): wait for its sixteen warps' flags, then add to what they stored.
+                    if (!await_partial(p.split_flags + (uint64_t)pair * (2 * kEpilogueWarps), p.split_epoch, lane, p.error_word, p.wait_us[7])) {
+                        ok = false;
+                        continue;
+                    }
+                    store_tile<kEpi, kColsPerThread, 16, kKind != kKindI8, true>(acc, p, mt * 256u + rank * 128u + quarter * 32u, nt * kBN + half * kColsPerThread,
+                                                                                 epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane, zero_cols);
+                    ++local_tile;
+                    continue;
+                }
+            }
             store_tile<kEpi, kColsPerThread, 16, kKind != kKindI8>(acc, p, mt * 256u + rank * 128u + quarter * 32u, nt * kBN + half * kColsPerThread,
                                                                    epi_stage, colf + (local_tile & 1u) * 256, half * kColsPerThread, lane, zero_cols);
             ++local_tile;
+            if constexpr (kEpi == kEpiDot) {
+                if (work.k0 > 0) {
+                    // The later depth range of a tile shared with the previous pair: tell it that this warp's cells are in place.
+                    __syncwarp();
+                    if (lane == 0) publish_partial(p.split_flags + (uint64_t)(pair - 1) * (2 * kEpilogueWarps) + rank * kEpilogueWarps + (warp - 2), p.split_epoch);
+                }
+            }
         }
     }
 
@@ -853,8 +948,32 @@ cudaError_t launch_by_epilogue(int epi, int bn, bool wide_store, const CUtensorM
     }
 }
 
+// Hand-over flags of the split mode: a ring of 64 launches x 128 pairs x 16 flags per GPU, allocated on the first launch
+// that splits and never cleared - every launch marks its flags with its own number. Only raw-dot products split, so the
+// entry points that promise not to allocate (distance epilogues) never come here.
+constexpr uint32_t kSplitRing = 64, kSplitPairsMax = 128, kSplitFlagsPerLaunch = kSplitPairsMax * 2 * kEpilogueWarps;
+std::atomic<uint32_t> g_split_epoch{0};
+uint32_t *split_flag_ring() {
+    static std::mutex mutex;
+    static uint32_t *ring[64] = {nullptr};
+    int d = 0;
+    cudaGetDevice(&d);
+    if (d < 0 || d >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!ring[d]) {
+        void *ptr = nullptr;
+        const size_t bytes = (size_t)kSplitRing * kSplitFlagsPerLaunch * sizeof(uint32_t);
+        if (cudaMalloc(&ptr, bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        if (cudaMemset(ptr, 0, bytes) != cudaSuccess) { cudaGetLastError(); cudaFree(ptr); return nullptr; }
+        ring[d] = static_cast<uint32_t *>(ptr);
+    }
+    return ring[d];
+}
+
+// `split`: 0 = whole tiles, 1 = split the depth when whole tiles would leave more than 5 % of the pairs' time idle,
+// 2 = split whenever the shape allows it (testing).
 template <int kKind, int kEpi>
-cudaError_t launch_pair(const CUtensorMap &a_map, const CUtensorMap &b_map, const GemmDev &dev, cudaStream_t stream) {
+cudaError_t launch_pair(const CUtensorMap &a_map, const CUtensorMap &b_map, GemmDev dev, cudaStream_t stream, int split) {
     auto kernel = gemm_tc_pair_kernel<kKind, kEpi>;
     static int max_pairs[64] = {0};
     int d = 0;
@@ -879,21 +998,37 @@ cudaError_t launch_pair(const CUtensorMap &a_map, const CUtensorMap &b_map, cons
     }
     uint32_t tiles = dev.tiles_m * dev.tiles_n;
     uint32_t pairs = tiles < (uint32_t)max_pairs[d] ? tiles : (uint32_t)max_pairs[d];
+    dev.split_flags = nullptr;
+    dev.split_epoch = 0;
+    if (kEpi == kEpiDot && split != 0 && dev.tri_diag < 0 && tiles > pairs && pairs <= kSplitPairsMax) {
+        // Every share is at least one tile long (tiles > pairs), so no tile is shared by more than two pairs.
+        const uint32_t rounds = (tiles + pairs - 1) / pairs;
+        const bool unbalanced = (uint64_t)tiles * 100 < (uint64_t)rounds * pairs * 95;
+        if (split == 2 || unbalanced) {
+            uint32_t *ring = split_flag_ring();
+            if (ring) {
+                uint32_t epoch = g_split_epoch.fetch_add(1) + 1;
+                if (epoch == 0) epoch = g_split_epoch.fetch_add(1) + 1;  // 0 is what untouched flags hold
+                dev.split_flags = ring + (size_t)(epoch % kSplitRing) * kSplitFlagsPerLaunch;
+                dev.split_epoch = epoch;
+            }
+        }
+    }
     kernel<<<2 * pairs, kThreads, kPairSmemTotal, stream>>>(a_map, b_map, dev);
     return cudaGetLastError();
 }
 
 template <int kKind>
-cudaError_t launch_pair_by_epilogue(int epi, const CUtensorMap &a_map, const CUtensorMap &b_map, const GemmDev &dev, cudaStream_t stream) {
+cudaError_t launch_pair_by_epilogue(int epi, const CUtensorMap &a_map, const CUtensorMap &b_map, const GemmDev &dev, cudaStream_t stream, int split) {
     switch (epi) {
-    case kEpiDot: return launch_pair<kKind, kEpiDot>(a_map, b_map, dev, stream);
-    case kEpiAngular: return launch_pair<kKind, kEpiAngular>(a_map, b_map, dev, stream);
-    case kEpiEuclidean: return launch_pair<kKind, kEpiEuclidean>(a_map, b_map, dev, stream);
+    case kEpiDot: return launch_pair<kKind, kEpiDot>(a_map, b_map, dev, stream, split);
+    case kEpiAngular: return launch_pair<kKind, kEpiAngular>(a_map, b_map, dev, stream, 0);
+    case kEpiEuclidean: return launch_pair<kKind, kEpiEuclidean>(a_map, b_map, dev, stream, 0);
     case kEpiHamming:
-        if constexpr (kKind == kKindI8) return launch_pair<kKind, kEpiHamming>(a_map, b_map, dev, stream);
+        if constexpr (kKind == kKindI8) return launch_pair<kKind, kEpiHamming>(a_map, b_map, dev, stream, 0);
         else return cudaErrorInvalidValue;
     case kEpiJaccard:
-        if constexpr (kKind == kKindI8) return launch_pair<kKind, kEpiJaccard>(a_map, b_map, dev, stream);
+        if constexpr (kKind == kKindI8) return launch_pair<kKind, kEpiJaccard>(a_map, b_map, dev, stream, 0);
         else return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
     }
@@ -961,7 +1096,9 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     const uint64_t pair_tiles = ((args.m + 255) / 256) * ((args.n + 255) / 256);
     const bool pair_by_shape = (args.variant & 0xff) == 0 && args.depth_padded_bytes / kBKBytes >= 8 &&
                                pair_tiles >= (uint64_t)device_sm_count() / 2;
-    const bool use_pair = ((args.variant & 0xff) == 3 || pair_by_shape) && chunk_rows_total < 0x7fffffffull;
+    // Variant 5 = CTA pairs with the depth split between pairs whenever the shape allows; variant 3 = CTA pairs, whole tiles.
+    const bool use_pair = ((args.variant & 0xff) == 3 || (args.variant & 0xff) == 5 || pair_by_shape) && chunk_rows_total < 0x7fffffffull;
+    const int split = (args.variant & 0xff) == 5 ? 2 : (args.variant & 0xff) == 0 ? 1 : 0;
     int bn = 256;
     if ((args.variant & 0xff) == 1 || (args.variant & 0xff) == 4) bn = 256;
     else if ((args.variant & 0xff) == 2) bn = 128;
@@ -1013,6 +1150,8 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
     dev.candidates = filtering ? args.candidates : nullptr;
     dev.candidate_capacity = args.candidate_capacity;
     dev.column_id_base = args.column_id_base;
+    dev.split_flags = nullptr;
+    dev.split_epoch = 0;
 
     if (use_pair) {
         // The packed payload seen as rows of 128 bytes: one 16 KiB chunk = 128 consecutive rows, copied verbatim
@@ -1029,9 +1168,9 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
         dev.tiles_n = (uint32_t)((args.n + 255) / 256);
         dev.idesc = make_idesc(ki.c_fmt, ki.ab_fmt, 256, 256);
         switch (ki.kind) {
-        case kKindF16: return launch_pair_by_epilogue<kKindF16>(args.epilogue, map, b_map, dev, stream);
-        case kKindF8F6F4: return launch_pair_by_epilogue<kKindF8F6F4>(args.epilogue, map, b_map, dev, stream);
-        default: return launch_pair_by_epilogue<kKindI8>(args.epilogue, map, b_map, dev, stream);
+        case kKindF16: return launch_pair_by_epilogue<kKindF16>(args.epilogue, map, b_map, dev, stream, split);
+        case kKindF8F6F4: return launch_pair_by_epilogue<kKindF8F6F4>(args.epilogue, map, b_map, dev, stream, split);
+        default: return launch_pair_by_epilogue<kKindI8>(args.epilogue, map, b_map, dev, stream, split);
         }
     }
     switch (ki.kind) {

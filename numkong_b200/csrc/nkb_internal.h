@@ -93,6 +93,7 @@ inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 //   1 producer waits for a free pipeline stage          2 MMA issuer waits for a drained accumulator
 //   3 MMA issuer waits for a loaded stage               4 epilogue waits for a finished accumulator
 //   5 MMA issuer waits for its last MMAs before leaving 6 producer waits for its last copies before leaving
+//   7 epilogue waits for the partial tile another CTA pair stored (depth split between pairs)
 #ifndef NKB_WAIT_LIMIT_NS
 #define NKB_WAIT_LIMIT_NS 2000000000ull  // 2 s
 #endif

@@ -145,8 +145,24 @@ def run_quantise(values: int, dtype: str = "e4m3", steps: int = 5, seed: int = 7
             "cast_ms": s_cast * 1e3, "cast_gbs": (values * 4 + out.numel()) / s_cast / 1e9}
 
 
+class _SingleProcess:
+    """Stands in for torch.distributed when the script runs as one plain process (one GPU, no launcher)."""
+    ReduceOp = type("ReduceOp", (), {"MAX": None})
+
+    @staticmethod
+    def barrier():
+        pass
+
+    @staticmethod
+    def all_reduce(tensor, op=None):
+        return tensor
+
+
 def _distributed(torch):
+    """(communication module, rank, world size): torch.distributed under a launcher, a stand-in for a single process."""
     import os
+    if "RANK" not in os.environ or int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        return _SingleProcess, 0, 1
     import torch.distributed as dist
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -255,7 +271,8 @@ def main():
         print(json.dumps(out))
     if a.sharded:
         import torch.distributed as dist
-        dist.destroy_process_group()
+        if dist.is_initialized():
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":

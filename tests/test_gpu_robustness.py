@@ -130,3 +130,67 @@ def test_cta_pair_kernel_is_deterministic_and_equals_the_single_cta_kernel():
     finally:
         nk.lib.nkb_set_gemm_variant(0)
     assert nk.synchronize() == 0
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "i8", "f32", "i4"])
+def test_column_ranges_of_a_packed_product_tile_the_full_result(dtype):
+    """nkb_dots_packed_columns: the product computed in column blocks (as a caller does that receives the packed matrix
+    piecewise) equals the product computed at once, bit for bit, and each call writes its own columns only."""
+    import torch
+    m, n, k = 300, 1000, 512
+    a, b = syn.normal_matrix(m, k // (2 if dtype == "i4" else 1), "u8" if dtype == "i4" else dtype, 61), syn.normal_matrix(n, k // (2 if dtype == "i4" else 1), "u8" if dtype == "i4" else dtype, 62)
+    packed = nk.dots_pack(b, dtype)
+    whole = nk.dots_packed(a, packed, dtype=dtype)
+    out = np.full_like(whole, 7)
+    for first, count in ((512, 256), (0, 512), (768, n - 768)):
+        nk.dots_packed(a, packed, out=out, dtype=dtype, columns=(first, count))
+    assert np.array_equal(out, whole)
+    ta = torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda()
+    tp = nk.dots_pack(torch.from_numpy(b.view(np.int16) if b.dtype == np.uint16 else b).cuda(), dtype)
+    dev = torch.full((m, n), 7, dtype=torch.from_numpy(whole[:1]).dtype, device="cuda")
+    nk.dots_packed(ta, tp, out=dev, dtype=dtype, columns=(256, 512))
+    assert nk.synchronize() == 0
+    got = dev.cpu().numpy()
+    assert np.array_equal(got[:, 256:768], whole[:, 256:768]) and np.all(got[:, :256] == 7) and np.all(got[:, 768:] == 7)
+    with pytest.raises(RuntimeError, match="multiple of 256"):
+        nk.dots_packed(a, packed, out=out, dtype=dtype, columns=(100, 200))
+
+
+@pytest.mark.parametrize("dtype,m,n,k", [("bf16", 1024, 8192, 2048), ("i8", 1000, 8100, 1024), ("f16", 2304, 4096, 1536), ("e4m3", 1024, 8192, 4096)])
+def test_depth_split_between_cta_pairs_matches_whole_tiles(dtype, m, n, k):
+    """Shapes whose 256 x 256 tiles do not fill a whole number of waves (1024 x 8192: 128 tiles for 74 CTA pairs) are dealt
+    out by pipeline stages instead, so a tile's depth may be shared by two pairs whose partial results are added in global
+    memory. Integers: bit-identical to the whole-tile kernel. Floats: the two halves are rounded once more when they meet,
+    so the result may differ from the whole-tile kernel in the last place but not from one run to the next."""
+    import torch
+    import oracle
+    a, b = syn.normal_matrix(m, k, dtype, 31), syn.normal_matrix(n, k, dtype, 32)
+    store = np.int16 if a.dtype == np.uint16 else a.dtype
+    ta, tb = torch.from_numpy(a.view(store)).cuda(), torch.from_numpy(b.view(store)).cuda()
+    packed = nk.dots_pack(tb, dtype)
+    try:
+        nk.lib.nkb_set_gemm_variant(3)
+        whole = nk.dots_packed(ta, packed, dtype=dtype)
+        nk.lib.nkb_set_gemm_variant(5)
+        split = nk.dots_packed(ta, packed, dtype=dtype)
+        again = torch.empty_like(split)
+        for _ in range(5):
+            nk.dots_packed(ta, packed, out=again, dtype=dtype)
+            assert torch.equal(again, split)
+        nk.lib.nkb_set_gemm_variant(0)
+        auto = nk.dots_packed(ta, packed, dtype=dtype)
+    finally:
+        nk.lib.nkb_set_gemm_variant(0)
+    assert nk.synchronize() == 0
+    if dtype == "i8":
+        assert torch.equal(split, whole) and torch.equal(auto, whole)
+        rows = np.r_[0:2, m - 2:m]
+        assert np.array_equal(split.cpu().numpy()[rows], oracle.dots(a[rows], b, dtype))
+    else:
+        assert not torch.equal(split, whole) or k <= 1024   # some tile was really shared
+        rows = np.r_[0:8, 250:260, m - 8:m]
+        exact = oracle.exact_dots_f64(a[rows], b, dtype)
+        scale = np.abs(oracle.decode(a[rows], dtype).astype(np.float64)) @ np.abs(oracle.decode(b, dtype).astype(np.float64)).T
+        for got in (split, auto):
+            assert np.max(np.abs(got.cpu().numpy()[rows] - exact) / scale) <= 1.0e-7
+        assert torch.equal(auto, split)   # the shape-driven choice is the split one for these shapes
