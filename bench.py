@@ -485,9 +485,14 @@ def main():
                 ev = torch.cuda.Event()
                 ev.record(comm)
                 arrived.append(ev)
-        for ev, (_, _, first, count) in zip(arrived, pieces):
+        # The products of the pieces leave sixteen SMs to the broadcast kernel, which otherwise would not run before they end.
+        nk.lib.nkb_set_sm_budget(132)
+        for ev, (_, _, first, count) in zip(arrived[:-1], pieces[:-1]):
             compute.wait_event(ev)
             nk.dots_packed(ta, packed, out=out, dtype=dtype, columns=(first, count))
+        nk.lib.nkb_set_sm_budget(0)
+        compute.wait_event(arrived[-1])
+        nk.dots_packed(ta, packed, out=out, dtype=dtype, columns=(pieces[-1][2], pieces[-1][3]))
 
     collective = None
     if world > 1:

@@ -335,6 +335,11 @@ NKB_API void nkb_set_gemm_variant(int variant);
  *  carry 22 significant bits and lose some in every tensor-core addition: on same-sign f16 data even 1-stage spans leave
  *  1.8 - 2.2 units where the reference has 0.6 - 3.0. Integer products are exact and ignore the setting. Process-wide. */
 NKB_API void nkb_set_accumulation_span(int stages);
+/** SMs the persistent GEMM kernels may occupy; 0 (default) = all. These kernels put one CTA on every SM for as long as they
+ *  run, so a collective that should progress at the same time on another stream (its kernel needs a few SMs of its own)
+ *  only does so when some are left free: a caller that overlaps a broadcast of the packed matrix with the products of the
+ *  parts that have arrived sets e.g. 132 of 148 for those products and 0 again afterwards. Process-wide. */
+NKB_API void nkb_set_sm_budget(int sms);
 /** How e2m3 / e3m2 operands reach the tensor cores: 1 (default) = packed 6-bit operands with the native
  *  e2m3 / e3m2 MMA formats, 0 = recoded to the e4m3 code of the same value (exact as well). Applies to later pack AND multiply calls;
  *  a blob packed under one setting must be multiplied under the same one. */

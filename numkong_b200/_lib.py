@@ -89,6 +89,7 @@ def _load() -> ctypes.CDLL:
     lib.nkb_set_wait_limit_ns.restype, lib.nkb_set_wait_limit_ns.argtypes = None, [ctypes.c_int, sz]
     lib.nkb_test_set_error_word.restype, lib.nkb_test_set_error_word.argtypes = ctypes.c_int, [ctypes.c_int, ctypes.c_uint32]
     lib.nkb_cached_blob_count.restype, lib.nkb_cached_blob_count.argtypes = sz, []
+    lib.nkb_set_sm_budget.restype, lib.nkb_set_sm_budget.argtypes = None, [ctypes.c_int]
     return lib
 
 

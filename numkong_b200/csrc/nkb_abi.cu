@@ -23,6 +23,7 @@ namespace {
 std::atomic<int> g_variant{0};
 std::atomic<int> g_fp6_native{1};
 std::atomic<uint64_t> g_nonce_counter{0};
+std::atomic<int> g_sm_budget{0};
 // Limit of every bounded wait of the tensor-core kernels, by wait site (microseconds); see nkb_set_wait_limit_ns.
 std::atomic<uint32_t> g_wait_us[kWaitSites] = {{kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs},
                                                {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}};
@@ -127,6 +128,7 @@ void wait_limits_us(uint32_t (&out)[kWaitSites]) {
 cudaStream_t current_stream() { return t_ctx.use_override ? t_ctx.override_stream : t_ctx.stream; }
 int current_variant() { return g_variant.load(); }
 int fp6_native() { return g_fp6_native.load(); }
+int sm_budget() { return g_sm_budget.load(); }
 
 bool cuda_ok(cudaError_t e, const char *what) {
     if (e == cudaSuccess) return true;
@@ -698,6 +700,7 @@ NKB_API void nkb_set_accumulation_span(int stages) {
     g_variant.store((g_variant.load() & ~0xff00) | (span << 8));
 }
 NKB_API void nkb_set_fp6_native(int native) { g_fp6_native.store(native ? 1 : 0); }
+NKB_API void nkb_set_sm_budget(int sms) { g_sm_budget.store(sms < 0 ? 0 : sms); }
 NKB_API void nkb_release_caches(void) {
     cudaDeviceSynchronize();
     {

@@ -920,7 +920,9 @@ cudaError_t launch_one(const CUtensorMap &map, const GemmDev &dev, cudaStream_t 
         configured[d] = true;
     }
     uint32_t tiles = dev.tiles_m * dev.tiles_n;
-    uint32_t grid = tiles < (uint32_t)device_sm_count() ? tiles : (uint32_t)device_sm_count();
+    uint32_t sms = (uint32_t)device_sm_count();
+    if (sm_budget() > 0 && (uint32_t)sm_budget() < sms) sms = (uint32_t)sm_budget();
+    uint32_t grid = tiles < sms ? tiles : sms;
     kernel<<<grid, kThreads, Plan::kTotal, stream>>>(map, dev);
     return cudaGetLastError();
 }
@@ -997,7 +999,9 @@ cudaError_t launch_pair(const CUtensorMap &a_map, const CUtensorMap &b_map, Gemm
         max_pairs[d] = n;
     }
     uint32_t tiles = dev.tiles_m * dev.tiles_n;
-    uint32_t pairs = tiles < (uint32_t)max_pairs[d] ? tiles : (uint32_t)max_pairs[d];
+    uint32_t most = (uint32_t)max_pairs[d];
+    if (sm_budget() > 1 && (uint32_t)sm_budget() / 2 < most) most = (uint32_t)sm_budget() / 2;
+    uint32_t pairs = tiles < most ? tiles : most;
     dev.split_flags = nullptr;
     dev.split_epoch = 0;
     if (kEpi == kEpiDot && split != 0 && dev.tri_diag < 0 && tiles > pairs && pairs <= kSplitPairsMax) {

@@ -210,6 +210,8 @@ struct GemmArgs {
 };
 // Enqueues exactly one kernel.
 cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream);
+// SMs the persistent tensor-core kernels may occupy (0 = all of them), as set by nkb_set_sm_budget.
+int sm_budget();
 // Limits of the kernels' bounded waits, one per wait site (microseconds; see nkb_ptx.cuh), as set by nkb_set_wait_limit_ns.
 void wait_limits_us(uint32_t (&out)[kWaitSites]);
 // Accumulation span (pipeline stages of 128 bytes of depth per tensor-core accumulation chain) the GEMM uses for a

@@ -9,10 +9,15 @@
 // over query tokens is carried in f64.
 //
 // One kernel serves both the single (query, document) call of the reference API and the all-pairs
-// batch (many queries x many ragged documents packed back to back): a CTA owns one tile of 128 query
-// tokens and one contiguous run of whole documents, walks that run 256 document tokens at a time
-// with the same producer / MMA / epilogue warp roles as the packed GEMM, and adds each finished
-// (query, document) sum into the output with one atomic per warp.
+// batch (many queries x many ragged documents packed back to back). A CTA owns one tile of 128 query
+// tokens and one contiguous run of whole documents. The run is cut into FOUR STREAMS of whole
+// documents (equal shares of its tokens), and every stream has its own 128-column accumulator in
+// TMEM: the MMA issuer goes round the streams, one 128-token document tile each, while sixteen
+// epilogue warps - one per TMEM lane quarter and stream - read their stream's tile. A warp therefore
+// sees every document of its stream from its first token to its last: the running maximum of a
+// document never leaves the warp's registers, no two warps ever have to merge partial maxima, and
+// the per-(query, document) sum is finished by the one warp that holds the query's 32 rows (a plain
+// store; only queries that straddle warps or tiles add their parts atomically - two parts commute).
 #include <cstdio>
 #include <cstring>
 #include "nkb_internal.h"
@@ -24,31 +29,34 @@ namespace nkb {
 
 namespace {
 
-constexpr int kMsBM = 128;
-constexpr int kMsBN = 256;
-constexpr int kMsStages = 3;
-constexpr int kMsEpilogueWarps = 16;
+constexpr int kMsBM = 128;                 // query tokens per CTA = TMEM lanes
+constexpr int kMsBN = 128;                 // document tokens per tile = one 128-row block of the packed payload
+constexpr int kMsStreams = 4;              // document streams per CTA = accumulators in TMEM (4 x 128 columns)
+constexpr int kMsEpilogueWarps = 4 * kMsStreams;
 constexpr int kMsThreads = 64 + 32 * kMsEpilogueWarps;
-constexpr int kMsABytes = kMsBM * 128;
-constexpr int kMsBBytes = kMsBN * 128;
-constexpr int kMsStageBytes = kMsABytes + kMsBBytes;
-constexpr int kMsBarrierOffset = kMsStages * kMsStageBytes;
+// Shared memory: the query tile stays resident when it is at most four depth blocks long (depth <= 256 for 16-bit types:
+// every late-interaction model in use), and only document chunks stream through the ring; deeper queries stream through the
+// ring with the documents (half as many, twice as large stages).
+constexpr int kMsResidentBlocks = 4;
+constexpr int kMsResidentBytes = kMsResidentBlocks * (int)kChunkBytes;   // 64 KiB
+constexpr int kMsRingBytes = 6 * (int)kChunkBytes;                       // 96 KiB: 6 document stages, or 3 query + document stages
+constexpr int kMsRingOffset = kMsResidentBytes;
+constexpr int kMsBarrierOffset = kMsRingOffset + kMsRingBytes;
+constexpr int kMsMaxStages = 6;
 // The epilogue warps run alone on their SM sub-partitions, so every global load they wait for is dead time. The
 // inverse norms of the document tokens a CTA walks and the ends of its documents are therefore copied into shared
 // memory once per CTA (lookups beyond these windows fall back to global memory).
-constexpr int kMsInvCache = 36 * kMsBN;   // tokens (a run is about 32 tiles plus one document)
+constexpr int kMsInvCache = 72 * kMsBN;   // tokens (a run is about 64 tiles plus one document)
 constexpr int kMsEndCache = 256;          // documents
 constexpr int kMsCacheOffset = kMsBarrierOffset + 256;
-constexpr int kMsPartialOffset = kMsCacheOffset + kMsInvCache * 4 + kMsEndCache * 4;
-constexpr int kMsPartialBytes = 2 * 4 * 4 * 32 * 8;  // (max, argmax) of 3 partner warps x 4 quarters, two documents deep
-constexpr int kMsSmemTotal = kMsPartialOffset + kMsPartialBytes + 1024;
+constexpr int kMsSmemTotal = kMsCacheOffset + kMsInvCache * 4 + kMsEndCache * 4 + 1024;
 
 struct MaxsimDev {
     const uint8_t *q_payload, *d_payload;
     const float *q_inv, *d_inv;          // inverse norms per token
     const uint64_t *q_offsets, *d_offsets;  // token offsets per query / document (device), length count+1
     const uint32_t *q_token_query;       // query index of every query token (filled by maxsim_prepare_kernel)
-    const uint64_t *segment_bounds;      // first document of every segment, length segments+1 (same kernel)
+    const uint64_t *stream_bounds;       // first document of every stream, 4 per segment plus one closing entry (same kernel)
     uint64_t n_queries, n_docs;
     uint64_t q_tokens, d_tokens;
     uint32_t kblocks;
@@ -71,16 +79,30 @@ __device__ __forceinline__ uint64_t lower_bound_offsets(const uint64_t *offsets,
     return lo;
 }
 
-// Runs once before maxsim_kernel: the query each query token belongs to, and the first document of every segment
-// (a segment = the documents whose first token falls into its equal share of all document tokens).
+// Runs once before maxsim_kernel: the query each query token belongs to, and the first document of every stream. A segment
+// is the run of documents whose first token falls into its equal share of all document tokens; its four streams are the
+// documents whose first token falls into each quarter of the segment's own tokens.
 __global__ void maxsim_prepare_kernel(const uint64_t *q_offsets, uint64_t n_queries, uint64_t q_tokens, uint32_t *q_token_query,
                                       const uint64_t *d_offsets, uint64_t n_docs, uint64_t d_tokens, uint32_t segments,
-                                      uint64_t *segment_bounds) {
+                                      uint64_t *stream_bounds) {
     const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < q_tokens) q_token_query[i] = (uint32_t)(lower_bound_offsets(q_offsets, n_queries, i + 1) - 1);
-    if (i <= segments) {
+    if (i <= (uint64_t)segments * kMsStreams) {
         const uint64_t per_seg = (d_tokens + segments - 1) / segments;
-        segment_bounds[i] = i == segments ? n_docs : lower_bound_offsets(d_offsets, n_docs, i * per_seg);
+        const uint64_t seg = i / kMsStreams, part = i % kMsStreams;
+        uint64_t bound = n_docs;
+        if (seg < segments) {
+            const uint64_t first = lower_bound_offsets(d_offsets, n_docs, seg * per_seg);
+            bound = first;
+            if (part != 0) {
+                const uint64_t last = seg + 1 == segments ? n_docs : lower_bound_offsets(d_offsets, n_docs, (seg + 1) * per_seg);
+                const uint64_t t0 = d_offsets[first], t1 = d_offsets[last];
+                bound = lower_bound_offsets(d_offsets, n_docs, t0 + (t1 - t0) * part / kMsStreams);
+                if (bound < first) bound = first;
+                if (bound > last) bound = last;
+            }
+        }
+        stream_bounds[i] = bound;
     }
 }
 
@@ -90,28 +112,41 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-// Largest value of a 32-column chunk held in registers and, on request, its FIRST position. Column j counts when bit j
-// of `inside` is set (kFull: every column counts); the others read as the lowest float.
-//   chunk_maximum()   four group maxima (8 columns each, three-input max) and their maximum: 18 instructions per chunk
-//   chunk_position()  first column equal to the maximum: the first group whose maximum matches is selected into eight
-//                     values and scanned from the back. Only needed when the chunk beats the running maximum of some row.
-// Equal dots resolve to the lower column, like a left-to-right scan with `>` does.
-template <bool kFull>
-__device__ __forceinline__ float chunk_value(const uint32_t (&v)[32], uint32_t inside, int j) {
-    return (kFull || ((inside >> j) & 1u)) ? __uint_as_float(v[j]) : -3.402823466e+38f;
+constexpr float kLowest = -3.402823466e+38f;
+
+// Largest value of a 32-column chunk held in registers and, on request, its FIRST position.
+//   chunk_maximum()         four group maxima (8 columns each, three-input max) and their maximum: 18 instructions
+//   chunk_maximum_masked()  the same when only the columns whose bit is set in `inside` count. The mask is the same for every
+//                           thread of the warp (document boundaries), so whole groups inside or outside it cost no selects.
+//   chunk_position()        first column equal to the maximum: the first group whose maximum matches is selected into eight
+//                           values and scanned from the back. Only needed when the chunk beats the running maximum of some row.
+// Equal dots resolve to the lower column, like a left-to-right scan with `>` does. A column outside the mask reads as the
+// lowest float and can only "win" when every column inside holds that very value, which finite dots never do.
+__device__ __forceinline__ float group_maximum(const uint32_t (&v)[32], int g) {
+    return max3(max3(__uint_as_float(v[8 * g]), __uint_as_float(v[8 * g + 1]), __uint_as_float(v[8 * g + 2])),
+                max3(__uint_as_float(v[8 * g + 3]), __uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5])),
+                fmaxf(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7])));
 }
-template <bool kFull>
-__device__ __forceinline__ float chunk_maximum(const uint32_t (&v)[32], uint32_t inside, float (&group)[4]) {
+__device__ __forceinline__ float chunk_maximum(const uint32_t (&v)[32], float (&group)[4]) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) group[g] = group_maximum(v, g);
+    return fmaxf(max3(group[0], group[1], group[2]), group[3]);
+}
+__device__ __forceinline__ float chunk_maximum_masked(const uint32_t (&v)[32], uint32_t inside, float (&group)[4]) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-        float x[8];
+        const uint32_t bits = (inside >> (8 * g)) & 0xffu;
+        if (bits == 0xffu) group[g] = group_maximum(v, g);
+        else if (bits == 0u) group[g] = kLowest;
+        else {
+            float x[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = chunk_value<kFull>(v, inside, 8 * g + i);
-        group[g] = max3(max3(x[0], x[1], x[2]), max3(x[3], x[4], x[5]), fmaxf(x[6], x[7]));
+            for (int i = 0; i < 8; ++i) x[i] = ((bits >> i) & 1u) ? __uint_as_float(v[8 * g + i]) : kLowest;
+            group[g] = max3(max3(x[0], x[1], x[2]), max3(x[3], x[4], x[5]), fmaxf(x[6], x[7]));
+        }
     }
     return fmaxf(max3(group[0], group[1], group[2]), group[3]);
 }
-template <bool kFull>
 __device__ __forceinline__ uint32_t chunk_position(const uint32_t (&v)[32], uint32_t inside, const float (&group)[4], float top) {
     const bool in0 = group[0] == top, in1 = group[1] == top, in2 = group[2] == top;
     const uint32_t first = in0 ? 0u : in1 ? 8u : in2 ? 16u : 24u;
@@ -120,7 +155,7 @@ __device__ __forceinline__ uint32_t chunk_position(const uint32_t (&v)[32], uint
 #pragma unroll
     for (int i = 6; i >= 0; --i) {
         const uint32_t raw = in0 ? v[i] : in1 ? v[8 + i] : in2 ? v[16 + i] : v[24 + i];
-        const float w = (kFull || ((group_inside >> i) & 1u)) ? __uint_as_float(raw) : -3.402823466e+38f;
+        const float w = ((group_inside >> i) & 1u) ? __uint_as_float(raw) : kLowest;
         at = w == top ? (uint32_t)i : at;
     }
     return first + at;
@@ -128,16 +163,18 @@ __device__ __forceinline__ uint32_t chunk_position(const uint32_t (&v)[32], uint
 
 template <int kKind>
 __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p) {
-    constexpr int kTmemCols = 2 * kMsBN;
+    constexpr int kTmemCols = kMsStreams * kMsBN;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + kMsBarrierOffset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kMsStages + s); };
-    auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kMsStages + a); };
-    auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMsStages + 2 + a); };
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kMsBarrierOffset + 8 * (2 * kMsStages + 4));
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kMsMaxStages + s); };
+    auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kMsMaxStages + a); };
+    auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMsMaxStages + kMsStreams + a); };
+    const uint32_t query_bar = bar_base + 8u * (2 * kMsMaxStages + 2 * kMsStreams);      // resident query tile has landed
+    const uint32_t drain_bar = query_bar + 8u;                                            // all MMAs have retired
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kMsBarrierOffset + 8 * (2 * kMsMaxStages + 2 * kMsStreams + 2));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -149,30 +186,35 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
     const uint32_t segment = (blockIdx.x % per_group) / p.q_group;
     if (q_tile >= p.q_tiles) return;  // padding blocks of the last group (nothing allocated yet)
 
+    const bool resident = p.kblocks <= (uint32_t)kMsResidentBlocks;
+    const int stages = resident ? 6 : 3;
+    const uint32_t stage_bytes = resident ? kChunkBytes : 2u * kChunkBytes;
+
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kMsStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), kMsEpilogueWarps * 32); }
+        for (int s = 0; s < kMsMaxStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < kMsStreams; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), 4 * 32); }
+        mbar_init(query_bar, 1);
+        mbar_init(drain_bar, 1);
         fence_mbar_init();
     }
     if (warp == 1) {
         tmem_alloc<1>(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
         tmem_relinquish<1>();
     }
-    // This CTA's run of whole documents (bounds computed by maxsim_prepare_kernel).
-    const uint64_t doc_begin = p.segment_bounds[segment], doc_end = p.segment_bounds[segment + 1];
+    // This CTA's run of whole documents and its four streams (bounds computed by maxsim_prepare_kernel).
+    const uint64_t *bounds = p.stream_bounds + (uint64_t)segment * kMsStreams;
+    const uint64_t doc_begin = bounds[0], doc_end = bounds[kMsStreams];
     const bool has_work = doc_begin < doc_end;
     const uint64_t tok_begin = has_work ? p.d_offsets[doc_begin] : 0;
     const uint64_t tok_end = has_work ? p.d_offsets[doc_end] : 0;
-    const uint64_t tile_begin = tok_begin / kMsBN;
-    const uint64_t tile_end = has_work ? (tok_end + kMsBN - 1) / kMsBN : tile_begin;  // empty documents only -> no tiles
-    // Shared-memory copies of what the epilogue looks up per document.
+    // Shared-memory copies of what the epilogue looks up per document. Everything the epilogue indexes with is kept
+    // relative to the first 128-token block the CTA touches / to its first document, in 32 bits (a run of 2^32 tokens or
+    // documents would take hours): 64-bit compares cost the epilogue's busiest pipe twice as much.
     float *inv_cache = reinterpret_cast<float *>(smem_gen + kMsCacheOffset);
-    // Everything the epilogue indexes with is kept relative to the CTA's first tile / first document, in 32 bits (a run
-    // of 2^32 tokens or documents would take hours): 64-bit compares cost the epilogue's busiest pipe twice as much.
     uint32_t *end_cache = reinterpret_cast<uint32_t *>(smem_gen + kMsCacheOffset + kMsInvCache * 4);
-    const uint64_t cache_base = tile_begin * kMsBN;  // first token held in inv_cache = origin of relative token positions
-    const uint32_t run_lo = (uint32_t)(tok_begin - cache_base), run_hi = (uint32_t)(tok_end - cache_base);
-    const uint32_t run_docs = (uint32_t)(doc_end - doc_begin), run_tiles = (uint32_t)(tile_end - tile_begin);
+    const uint64_t cache_base = tok_begin / kMsBN * kMsBN;  // first token held in inv_cache = origin of relative token positions
+    const uint32_t run_hi = (uint32_t)(tok_end - cache_base);
+    const uint32_t run_docs = (uint32_t)(doc_end - doc_begin);
     if (has_work) {
         for (uint32_t i = threadIdx.x; i < (uint32_t)kMsInvCache; i += blockDim.x)
             inv_cache[i] = cache_base + i < p.d_tokens ? __ldg(p.d_inv + cache_base + i) : 0.0f;
@@ -190,63 +232,101 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
     auto end_of_doc = [&](uint32_t doc) {
         return doc < (uint32_t)kMsEndCache ? end_cache[doc] : (uint32_t)(p.d_offsets[doc_begin + doc + 1] - cache_base);
     };
+    // Stream `s`: documents [first, last) of the run, tokens [lo, hi) relative to cache_base, and the 128-token blocks that
+    // hold them (a block at the border between two streams is multiplied for both; each keeps its own documents' columns).
+    struct Stream { uint32_t first_doc, last_doc, lo, hi, first_block, blocks; };
+    auto stream_of = [&](int s) {
+        Stream st;
+        st.first_doc = (uint32_t)(bounds[s] - doc_begin);
+        st.last_doc = (uint32_t)(bounds[s + 1] - doc_begin);
+        st.lo = st.first_doc == 0 ? (uint32_t)(tok_begin - cache_base) : end_of_doc(st.first_doc - 1);
+        st.hi = st.last_doc == 0 ? st.lo : end_of_doc(st.last_doc - 1);
+        st.first_block = st.lo / kMsBN;
+        st.blocks = st.hi > st.lo ? (st.hi + kMsBN - 1) / kMsBN - st.first_block : 0u;
+        return st;
+    };
 
     if (warp == 0) {
-        if (lane == 0) {
+        if (lane == 0 && has_work) {
+            Stream st[kMsStreams];
+            uint32_t rounds = 0;
+            for (int s = 0; s < kMsStreams; ++s) { st[s] = stream_of(s); rounds = st[s].blocks > rounds ? st[s].blocks : rounds; }
+            const uint8_t *a_tile = p.q_payload + (uint64_t)q_tile * p.kblocks * kChunkBytes;
+            if (resident) {
+                mbar_expect_tx(query_bar, p.kblocks * kChunkBytes);
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb)
+                    bulk_load(smem_base + kb * kChunkBytes, a_tile + (uint64_t)kb * kChunkBytes, kChunkBytes, query_bar);
+            }
+            int stage = 0;
+            uint32_t phase = 0, issued = 0;
+            bool ok = true;
+            for (uint32_t r = 0; r < rounds && ok; ++r) {
+                for (int s = 0; s < kMsStreams && ok; ++s) {
+                    if (r >= st[s].blocks) continue;
+                    const uint8_t *b_tile = p.d_payload + (cache_base / kMsBN + st[s].first_block + r) * (uint64_t)p.kblocks * kChunkBytes;
+                    for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                        if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
+                        const uint32_t dst = smem_base + kMsRingOffset + stage * stage_bytes;
+                        mbar_expect_tx(full_bar(stage), stage_bytes);
+                        if (!resident) bulk_load(dst + kChunkBytes, a_tile + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
+                        bulk_load(dst, b_tile + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
+                        ++issued;
+                        if (++stage == stages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+            if (!ok) {
+                // Copies issued last may still be in flight: wait (bounded) until their stages' barriers have counted them.
+                int s = stage;
+                uint32_t ph = phase;
+                for (uint32_t i = 0; i < issued && i < (uint32_t)stages; ++i) {
+                    if (s == 0) { s = stages; ph ^= 1u; }
+                    --s;
+                    if (!mbar_wait(full_bar(s), ph, 6, p.error_word)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && has_work) {
+            Stream st[kMsStreams];
+            uint32_t rounds = 0;
+            for (int s = 0; s < kMsStreams; ++s) { st[s] = stream_of(s); rounds = st[s].blocks > rounds ? st[s].blocks : rounds; }
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            const uint8_t *a_tile = p.q_payload + (uint64_t)q_tile * p.kblocks * kChunkBytes;
-            for (uint64_t t = tile_begin; t < tile_end && ok; ++t) {
-                const uint8_t *b_tile = p.d_payload + t * (kMsBN / kChunkRows) * p.kblocks * kChunkBytes;
-                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
-                    uint32_t a_dst = smem_base + stage * kMsStageBytes;
-                    mbar_expect_tx(full_bar(stage), kMsStageBytes);
-                    bulk_load(a_dst, a_tile + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
-#pragma unroll
-                    for (int j = 0; j < kMsBN / (int)kChunkRows; ++j)
-                        bulk_load(a_dst + kMsABytes + j * kChunkBytes, b_tile + ((uint64_t)j * p.kblocks + kb) * kChunkBytes,
-                                  kChunkBytes, full_bar(stage));
-                    if (++stage == kMsStages) { stage = 0; phase ^= 1u; }
-                }
-            }
-            if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0, local = 0;
-            bool ok = true;
-            for (uint64_t t = tile_begin; t < tile_end && ok; ++t, ++local) {
-                const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
-                if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, 2, p.error_word)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + acc * kMsBN;
-                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
+            if (resident && !mbar_wait(query_bar, 0u, 3, p.error_word)) ok = false;
+            for (uint32_t r = 0; r < rounds && ok; ++r) {
+                for (int s = 0; s < kMsStreams && ok; ++s) {
+                    if (r >= st[s].blocks) continue;
+                    // Stream s's accumulator was handed out r times before: wait until its four warps have read round r - 1.
+                    if (!mbar_wait(tmem_empty_bar(s), (r & 1u) ^ 1u, 2, p.error_word)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t a_src = smem_base + stage * kMsStageBytes;
-                    const uint64_t a_desc = make_smem_desc_sw128(a_src);
-                    const uint64_t b_desc = make_smem_desc_sw128(a_src + kMsABytes);
+                    const uint32_t d_tmem = tmem_base + s * kMsBN;
+                    for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                        if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        const uint32_t b_src = smem_base + kMsRingOffset + stage * stage_bytes;
+                        const uint32_t a_src = resident ? smem_base + kb * kChunkBytes : b_src + kChunkBytes;
+                        const uint64_t a_desc = make_smem_desc_sw128(a_src);
+                        const uint64_t b_desc = make_smem_desc_sw128(b_src);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma<kKind, 1>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb | (uint32_t)k) != 0u);
-                    umma_commit(empty_bar(stage));
-                    if (++stage == kMsStages) { stage = 0; phase ^= 1u; }
+                        for (int k = 0; k < 4; ++k)
+                            umma<kKind, 1>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb | (uint32_t)k) != 0u);
+                        umma_commit(empty_bar(stage));
+                        if (++stage == stages) { stage = 0; phase ^= 1u; }
+                    }
+                    if (ok) umma_commit(tmem_full_bar(s));
                 }
-                if (ok) umma_commit(tmem_full_bar(acc));
             }
+            // No MMA may still be running when TMEM and shared memory are released below.
+            umma_commit(drain_bar);
+            mbar_wait(drain_bar, 0u, 5, p.error_word);
         }
-    } else {
+    } else if (has_work) {
         // ------------------------------------------------------------ epilogue (warps 2..17)
-        // Sixteen warps: four per TMEM lane quarter (= 32 query tokens), each scanning its own 64 of the tile's 256
-        // columns. One warp per scheduler could not hide the latency of its dependent compare/select chains (measured:
-        // 32 % issue utilisation); four do. The four warps of a quarter keep partial (max, argmax) pairs per document
-        // and combine them when a document ends: partners park their pair in shared memory, meet at a named barrier,
-        // and the first warp merges (larger dot wins, equal dots go to the lower token), normalises and accumulates.
-        const uint32_t quarter = warp & 3u;
-        const uint32_t sub = (uint32_t)(warp - 2) >> 2;  // which 64-column slice of every tile
+        const uint32_t quarter = warp & 3u;                 // TMEM lanes 32 * quarter .. + 31 = 32 query tokens
+        const int s = (warp - 2) >> 2;                      // the stream this warp follows
+        const Stream st = stream_of(s);
         const uint64_t row = (uint64_t)q_tile * kMsBM + quarter * 32u + lane;
         const bool row_ok = row < p.q_tokens;
         const float q_inv = row_ok ? p.q_inv[row] : 0.0f;
@@ -261,105 +341,97 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             const uint32_t other_q = __shfl_down_sync(0xffffffffu, qid, 1u << b);
             if (lane + (1 << b) < 32 && other_q == qid) joins |= 1u << b;
         }
-        // Where this query's scores of the run's documents go (segment heads of the all-pairs call only).
+        // Where this query's scores of the run's documents go (segment heads of the all-pairs call only), and whether this
+        // warp holds ALL of the query's tokens (then the sum is final and stored; otherwise the parts are added atomically).
         float *score_row = segment_head && p.scores_f32 ? p.scores_f32 + (uint64_t)qid * p.score_stride + doc_begin : nullptr;
-        float *part_val = reinterpret_cast<float *>(smem_gen + kMsPartialOffset);
-        uint32_t *part_arg = reinterpret_cast<uint32_t *>(smem_gen + kMsPartialOffset + kMsPartialBytes / 2);
+        bool whole_query = false;
+        if (segment_head) {
+            const uint64_t warp_row0 = (uint64_t)q_tile * kMsBM + quarter * 32u;
+            whole_query = p.q_offsets[qid] >= warp_row0 && p.q_offsets[qid + 1] <= warp_row0 + 32u;
+        }
 
-        uint32_t cur_doc = 0;                                    // number of the current document within the run
-        uint32_t cur_end = has_work ? end_of_doc(0) : 0;         // its end, relative
-        uint32_t docs_done = 0;
-        float run = -3.402823466e+38f;
-        uint32_t arg = 0;                                        // relative position of the running winner
+        uint32_t cur_doc = st.first_doc;                          // number of the current document within the run
+        uint32_t cur_end = st.blocks ? end_of_doc(cur_doc) : 0u;  // its end, relative
+        float run = kLowest;
+        uint32_t arg = 0;                                         // relative position of the running winner
 
-        // Closes the current document for this quarter. Called by all four warps of the quarter, in the same order.
+        // Closes the current document: normalise the winner, add the query's tokens up (f64, segmented by query), write.
         auto finish_doc = [&]() {
-            const uint32_t slot = (((docs_done & 1u) * 4u + quarter) * 4u + sub) * 32u + lane;
-            if (sub != 0) { part_val[slot] = run; part_arg[slot] = arg; }
-            asm volatile("bar.sync %0, 128;" ::"r"(1u + quarter) : "memory");
-            if (sub == 0) {
-#pragma unroll
-                for (uint32_t s = 1; s < 4; ++s) {
-                    const float v = part_val[slot + s * 32u];
-                    const uint32_t a = part_arg[slot + s * 32u];
-                    if (v > run || (v == run && a < arg)) { run = v; arg = a; }
-                }
-                float angular = 0.0f;
-                if (row_ok) {
-                    const float cosine = run * q_inv * inverse_norm_of(arg);
-                    angular = 1.0f - cosine;
-                    if (!(angular > 0.0f)) angular = angular < 0.0f ? 0.0f : angular;  // clamp, keep NaN
-                }
-                double sum = (double)angular;
-#pragma unroll
-                for (int b = 0; b < 5; ++b) {
-                    const double other = __shfl_down_sync(0xffffffffu, sum, 1u << b);
-                    if ((joins >> b) & 1u) sum += other;
-                }
-                if (segment_head) {
-                    if (p.total_f64) atomicAdd(p.total_f64, sum);
-                    else atomicAdd(score_row + cur_doc, (float)sum);
-                }
+            float angular = 0.0f;
+            if (row_ok) {
+                const float cosine = run * q_inv * inverse_norm_of(arg);
+                angular = 1.0f - cosine;
+                if (!(angular > 0.0f)) angular = angular < 0.0f ? 0.0f : angular;  // clamp, keep NaN
             }
-            ++docs_done;
-            run = -3.402823466e+38f;
+            double sum = (double)angular;
+#pragma unroll
+            for (int b = 0; b < 5; ++b) {
+                const double other = __shfl_down_sync(0xffffffffu, sum, 1u << b);
+                if ((joins >> b) & 1u) sum += other;
+            }
+            if (segment_head) {
+                if (p.total_f64) atomicAdd(p.total_f64, sum);
+                else if (whole_query) score_row[cur_doc] = (float)sum;
+                else atomicAdd(score_row + cur_doc, (float)sum);
+            }
+            run = kLowest;
             arg = 0;
         };
-
-        bool ok = true;
-        // After a wait has given up (`ok` false) a warp stops waiting but keeps walking tiles and documents: the four
-        // warps of a quarter meet at a named barrier per document, and one that left early would strand its partners.
-        for (uint32_t local = 0; local < run_tiles; ++local) {
-            const uint32_t acc = local & 1u, acc_phase = (local >> 1) & 1u;
-            if (ok && !mbar_wait(tmem_full_bar(acc), acc_phase, 4, p.error_word)) ok = false;
-            tc_fence_after_sync();
-            const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + acc * kMsBN + sub * 64u;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t v[32];
-                tmem_ld_32x32(t_addr + half * 32, v);
-                tmem_ld_wait_for(v);
-                const uint32_t c0 = local * kMsBN + sub * 64u + (uint32_t)half * 32u;  // relative position of column 0
-                float group[4];
-                if (c0 >= run_lo && c0 + 32u <= cur_end) {
-                    // The whole chunk lies inside the current document (documents end inside the run).
-                    const float best = chunk_maximum<true>(v, 0xffffffffu, group);
-                    if (best > run) { run = best; arg = c0 + chunk_position<true>(v, 0xffffffffu, group, best); }
-                } else {
-                    // Document boundaries (or an end of the run) fall inside or before the chunk: walk it piece by piece,
-                    // masking the columns outside the piece. Boundaries are the same for every thread.
-                    const uint32_t hi = c0 + 32u < run_hi ? c0 + 32u : run_hi;
-                    uint32_t pos = c0 > run_lo ? c0 : run_lo;
-                    while (pos < hi) {
-                        while (pos >= cur_end) {
-                            finish_doc();
-                            ++cur_doc;
-                            cur_end = end_of_doc(cur_doc);
-                        }
-                        const uint32_t piece_end = cur_end < hi ? cur_end : hi;
-                        const uint32_t j0 = pos - c0, j1 = piece_end - c0;  // 0 <= j0 < j1 <= 32
-                        const uint32_t inside = (0xffffffffu >> (32u - j1)) & (0xffffffffu << j0);
-                        const float best = chunk_maximum<false>(v, inside, group);
-                        if (best > run) { run = best; arg = c0 + chunk_position<false>(v, inside, group, best); }
-                        pos = piece_end;
-                    }
+        // One 32-column chunk whose column 0 sits at relative position c0.
+        auto scan_chunk = [&](const uint32_t (&v)[32], uint32_t c0) {
+            float group[4];
+            if (c0 >= st.lo && c0 + 32u <= cur_end) {
+                // The whole chunk lies inside the current document.
+                const float best = chunk_maximum(v, group);
+                if (best > run) { run = best; arg = c0 + chunk_position(v, 0xffffffffu, group, best); }
+                return;
+            }
+            // Document boundaries (or an end of the stream) fall inside or before the chunk: walk it piece by piece, masking
+            // the columns outside the piece. Boundaries are the same for every thread.
+            const uint32_t hi = c0 + 32u < st.hi ? c0 + 32u : st.hi;
+            uint32_t pos = c0 > st.lo ? c0 : st.lo;
+            while (pos < hi) {
+                while (pos >= cur_end) {
+                    finish_doc();
+                    ++cur_doc;
+                    cur_end = end_of_doc(cur_doc);
                 }
+                const uint32_t piece_end = cur_end < hi ? cur_end : hi;
+                const uint32_t j0 = pos - c0, j1 = piece_end - c0;  // 0 <= j0 < j1 <= 32
+                const uint32_t inside = (0xffffffffu >> (32u - j1)) & (0xffffffffu << j0);
+                const float best = chunk_maximum_masked(v, inside, group);
+                if (best > run) { run = best; arg = c0 + chunk_position(v, inside, group, best); }
+                pos = piece_end;
             }
+        };
+
+        for (uint32_t r = 0; r < st.blocks; ++r) {
+            if (!mbar_wait(tmem_full_bar(s), r & 1u, 4, p.error_word)) break;  // nothing else waits for this warp
+            tc_fence_after_sync();
+            const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + s * kMsBN;
+            const uint32_t tile_c0 = (st.first_block + r) * kMsBN;  // relative position of the tile's column 0
+            // Two chunks in flight: the next one is on its way from TMEM while the current one is scanned.
+            uint32_t v0[32], v1[32];
+            tmem_ld_32x32(t_addr, v0);
+            tmem_ld_wait_for(v0);
+            tmem_ld_32x32(t_addr + 32, v1);
+            scan_chunk(v0, tile_c0);
+            tmem_ld_wait_for(v1);
+            tmem_ld_32x32(t_addr + 64, v0);
+            scan_chunk(v1, tile_c0 + 32u);
+            tmem_ld_wait_for(v0);
+            tmem_ld_32x32(t_addr + 96, v1);
+            scan_chunk(v0, tile_c0 + 64u);
+            tmem_ld_wait_for(v1);
             tc_fence_before_sync();
-            mbar_arrive(tmem_empty_bar(acc));
-            // Documents that end inside this tile are complete for every warp of the quarter once it gets here.
-            const uint32_t tile_hi = (local + 1u) * kMsBN < run_hi ? (local + 1u) * kMsBN : run_hi;
-            while (cur_doc < run_docs && cur_end <= tile_hi) {
+            mbar_arrive(tmem_empty_bar(s));   // everything this warp needs of the tile is in registers
+            scan_chunk(v1, tile_c0 + 96u);
+            // Documents that end inside this tile are complete.
+            const uint32_t tile_hi = tile_c0 + kMsBN < st.hi ? tile_c0 + kMsBN : st.hi;
+            while (cur_doc < st.last_doc && cur_end <= tile_hi) {
                 finish_doc();
                 ++cur_doc;
-                cur_end = cur_doc < run_docs ? end_of_doc(cur_doc) : 0u;  // 0: no chunk is "inside" once the run is done
-            }
-        }
-        // Normally nothing is left here: every document of the run ends inside one of its tiles.
-        if (has_work) {
-            while (cur_doc < run_docs) {
-                finish_doc();
-                ++cur_doc;
+                cur_end = cur_doc < st.last_doc ? end_of_doc(cur_doc) : 0u;  // 0: no chunk is "inside" once the stream is done
             }
         }
     }
@@ -419,28 +491,30 @@ cudaError_t launch_maxsim_tc(uint32_t dt, const MaxsimDev &dev_in, cudaStream_t 
     dev.q_group = group;
     uint64_t grid = (uint64_t)((dev.q_tiles + group - 1) / group) * group * dev.segments;
     if (grid == 0 || grid > 0x7fffffffull || dev.q_tokens > 0xffffffffull) return cudaErrorInvalidValue;
-    // Look-up tables for the main kernel: token -> query, segment -> first document.
+    // Look-up tables for the main kernel: token -> query, stream -> first document (four streams per segment).
     const uint64_t map_bytes = round_up(dev.q_tokens * 4, 16);
-    uint8_t *tables = static_cast<uint8_t *>(scratch(kSlotNorms, map_bytes + ((uint64_t)dev.segments + 1) * 8));
+    const uint64_t bound_count = (uint64_t)dev.segments * kMsStreams + 1;
+    uint8_t *tables = static_cast<uint8_t *>(scratch(kSlotNorms, map_bytes + bound_count * 8));
     if (!tables) return cudaErrorMemoryAllocation;
     uint32_t *token_query = reinterpret_cast<uint32_t *>(tables);
     uint64_t *bounds = reinterpret_cast<uint64_t *>(tables + map_bytes);
-    const uint64_t items = dev.q_tokens > (uint64_t)dev.segments + 1 ? dev.q_tokens : (uint64_t)dev.segments + 1;
+    const uint64_t items = dev.q_tokens > bound_count ? dev.q_tokens : bound_count;
     maxsim_prepare_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(dev.q_offsets, dev.n_queries, dev.q_tokens, token_query,
                                                                              dev.d_offsets, dev.n_docs, dev.d_tokens, dev.segments, bounds);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     g_launches++;
     dev.q_token_query = token_query;
-    dev.segment_bounds = bounds;
+    dev.stream_bounds = bounds;
     maxsim_kernel<kKindF16><<<(unsigned)grid, kMsThreads, kMsSmemTotal, stream>>>(dev);
     return cudaGetLastError();
 }
 
 uint32_t pick_segments(uint64_t d_tokens, uint32_t q_tiles) {
-    // Runs of about 32 document tiles per CTA, but at least two CTAs per SM when the work allows it.
+    // Runs of about 64 document tiles (8192 tokens, some 45 documents of late-interaction size: eleven per stream) per CTA,
+    // but at least two CTAs per SM when the work allows it.
     uint64_t tiles = (d_tokens + kMsBN - 1) / kMsBN;
-    uint64_t seg = (tiles + 31) / 32;
+    uint64_t seg = (tiles + 63) / 64;
     const uint64_t min_ctas = 2 * 148;
     if ((uint64_t)q_tiles * seg < min_ctas) {
         uint64_t want = (min_ctas + q_tiles - 1) / q_tiles;
