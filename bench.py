@@ -11,8 +11,9 @@ N = 1: K steps back to back, operands resident in HBM.
 N > 1 (torchrun, one rank per GPU): STRONG scaling of the same problem. The 8192 rows of A are split into N contiguous
 blocks, one per rank - the caller-side split the reference documents for its threads (README.md:209-212,
 rust/matrix.rs:3016-3026). Packed B exists on rank 0 only when the timed region starts and is broadcast over NCCL INSIDE
-it, once, in two column blocks: every rank multiplies its rows against the first block while the second is still on its
-way (the packed rows of a column block are one contiguous byte range of the blob), then runs the remaining K - 1 steps.
+it, once; then every rank runs its K steps. (--broadcast-pieces 2 sends it in two column blocks and multiplies the first
+while the second is still on its way - the packed rows of a column block are one contiguous byte range of the blob -
+which measured no faster: the broadcast kernel and the persistent GEMM compete for the same SMs.)
 The timed region is bracketed by a barrier and a device synchronize; the reported time is the maximum over ranks and
 `value` = K * 2 * 8192^3 / that time.
 
@@ -422,6 +423,10 @@ def main():
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip everything but the headline measurement")
+    ap.add_argument("--broadcast-pieces", type=int, default=1, choices=[1, 2],
+                    help="N > 1: 1 = broadcast the packed matrix whole, then multiply (default); 2 = broadcast it in two column blocks "
+                         "and multiply the first while the second is in flight (measured on two B200s: 0.73-0.77 ms for the first step "
+                         "against 0.74-0.76 ms whole - the broadcast kernel and the persistent GEMM compete for SMs, so nothing is won)")
     ap.add_argument("--rows", type=int, default=8192,
                     help="global rows of A; anything but 8192 is a reduced case for profiler captures, not the benchmark")
     args = ap.parse_args()
@@ -472,6 +477,8 @@ def main():
     depth_padded = (K * eb + 127) // 128 * 128
     cut = 128 + half_cols * depth_padded
     pieces = [(0, cut, 0, half_cols), (cut, size, half_cols, N - half_cols)]
+    if args.broadcast_pieces == 1:
+        pieces = [(0, size, 0, N)]
     comm = torch.cuda.Stream() if world > 1 else None
 
     def broadcast_and_first_step():
@@ -485,8 +492,9 @@ def main():
                 ev = torch.cuda.Event()
                 ev.record(comm)
                 arrived.append(ev)
-        # The products of the pieces leave sixteen SMs to the broadcast kernel, which otherwise would not run before they end.
-        nk.lib.nkb_set_sm_budget(132)
+        # The products of all pieces but the last leave 32 SMs to the broadcast kernel (NCCL runs 32 channels here), which
+        # otherwise would not run before they end.
+        nk.lib.nkb_set_sm_budget(116)
         for ev, (_, _, first, count) in zip(arrived[:-1], pieces[:-1]):
             compute.wait_event(ev)
             nk.dots_packed(ta, packed, out=out, dtype=dtype, columns=(first, count))
@@ -508,7 +516,7 @@ def main():
         torch.cuda.synchronize()
         tb_ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
         dist.all_reduce(tb_ms, op=dist.ReduceOp.MAX)
-        collective = {"op": "ncclBroadcast of packed B from rank 0, inside the timed region, once, in 2 column blocks overlapped with the first step",
+        collective = {"op": "ncclBroadcast of packed B from rank 0, inside the timed region, once" + (", in 2 column blocks overlapped with the first step" if len(pieces) == 2 else ", ahead of the first step"),
                       "bytes": int(size), "standalone_ms_whole_blob": float(tb_ms.item())}
         broadcast_and_first_step()   # warm-up of the piecewise path
 

@@ -223,7 +223,7 @@ struct SumSq<kU1> {  // a bit squared is the bit: the "norm" of a bit row is its
     static __device__ __forceinline__ void add(Acc &acc, const uint8_t *p) { acc += (unsigned long long)__popc((unsigned)*p); }
 };
 
-// One warp per row; 16-byte vector loads when the row start allows it.
+// One warp per row; 16-byte vector loads, four per lane in flight, when the row start allows it.
 template <uint32_t kDtype>
 __global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, uint64_t depth, uint64_t stride,
                                  void *__restrict__ out, int out_mode /*0 native, 1 f32*/, int inverse) {
@@ -237,9 +237,24 @@ __global__ void row_sumsq_kernel(const uint8_t *__restrict__ x, uint64_t rows, u
         Acc acc = 0;
         uint64_t done = 0;
         if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
-            uint64_t vecs = depth / per16;
-            for (uint64_t v = lane; v < vecs; v += 32) {
-                uint4 q = __ldg(reinterpret_cast<const uint4 *>(p) + v);
+            const uint64_t vecs = depth / per16;
+            const uint4 *pv = reinterpret_cast<const uint4 *>(p);
+            uint64_t v = lane;
+            // Four independent 16-byte loads per lane in flight (2 KiB per warp): one load at a time left the kernel waiting
+            // on memory latency at two thirds of the copy rate.
+            for (; v + 96 < vecs; v += 128) {
+                uint4 q[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) q[u] = __ldg(pv + v + 32 * u);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint8_t *qb = reinterpret_cast<const uint8_t *>(&q[u]);
+#pragma unroll
+                    for (uint32_t e = 0; e < per16; ++e) SumSq<kDtype>::add(acc, qb + e * eb);
+                }
+            }
+            for (; v < vecs; v += 32) {
+                uint4 q = __ldg(pv + v);
                 const uint8_t *qb = reinterpret_cast<const uint8_t *>(&q);
 #pragma unroll
                 for (uint32_t e = 0; e < per16; ++e) SumSq<kDtype>::add(acc, qb + e * eb);
