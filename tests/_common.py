@@ -12,12 +12,12 @@ MINIFLOATS = ("e4m3", "e5m2", "e2m3", "e3m2")
 # Odd shapes in the spirit of the reference's Python suite (test/test_base.py:36-95): (height, width, depth)
 SMALL_SHAPES = [(1, 1, 1), (1, 8, 3), (3, 1, 7), (7, 5, 3), (33, 17, 65), (17, 63, 127), (129, 257, 129), (130, 300, 1000)]
 
-# Tolerance for floating-point dots, stated as  max |c - c_exact| / sum_l |a_l||b_l|  where c_exact is the
-# f64 accumulation of the exactly decoded inputs (the statistic recommended for signed inputs, because plain
-# relative error explodes near zero). The reference's own kernels measure 2e-8..7e-8 (16-bit floats) and
-# 0..1.3e-8 (8/6-bit floats) on N(0,1) inputs at depth 1024..8192; the bounds below leave a factor of ~4.
-# The tensor cores truncate instead of rounding, so even a 3-term dot can be off by one f32 ulp of the result
-# (1.2e-7 in this statistic); long dots measure 1e-8 (8/6-bit) to 9e-8 (16-bit) thanks to span-wise accumulation.
+# Sanity bound for floating-point dots on odd shapes, stated as  max |c - c_exact| / sum_l |a_l||b_l|  where c_exact is the
+# f64 accumulation of the exactly decoded inputs (the statistic recommended for signed inputs, because plain relative
+# error explodes near zero). This is NOT the acceptance gate: that is tests/test_gpu_error_envelope.py, which holds bf16 /
+# f16 products and distances to the error of the reference's own worst back end on the same inputs. The bound here only
+# has to cover the worst single cell of tiny problems: the tensor cores truncate instead of rounding, so even a 3-term dot
+# can be off by one f32 ulp of the result (1.2e-7 in this statistic); long dots measure 1e-8 (8/6-bit) to 5e-8 (16-bit).
 DOT_TOLERANCE = {"bf16": 2.5e-7, "f16": 2.5e-7, "e4m3": 1.5e-7, "e5m2": 1.5e-7, "e2m3": 1.5e-7, "e3m2": 1.5e-7, "f32": 1e-15}
 
 # Batched distances: absolute tolerance on the result (angular lives in [0, 2], so this is ~4 ulp of 1.0),
