@@ -10,9 +10,9 @@
 //
 // One kernel serves both the single (query, document) call of the reference API and the all-pairs
 // batch (many queries x many ragged documents packed back to back). A CTA owns one tile of 128 query
-// tokens and one contiguous run of whole documents. The run is cut into TWO STREAMS of whole
-// documents (equal shares of its tokens), and every stream has two 128-column accumulators in
-// TMEM: the MMA issuer goes round the streams, one 128-token document tile each, while the
+// tokens and one contiguous run of whole documents. The run is cut into FOUR STREAMS of whole
+// documents (equal shares of its tokens), and every stream has its own 128-column accumulator in
+// TMEM: the MMA issuer goes round the streams, one 128-token document tile each, while sixteen
 // epilogue warps - one per TMEM lane quarter and stream - read their stream's tile. A warp therefore
 // sees every document of its stream from its first token to its last: the running maximum of a
 // document never leaves the warp's registers, no two warps ever have to merge partial maxima, and
@@ -31,8 +31,7 @@ namespace {
 
 constexpr int kMsBM = 128;                 // query tokens per CTA = TMEM lanes
 constexpr int kMsBN = 128;                 // document tokens per tile = one 128-row block of the packed payload
-constexpr int kMsStreams = 2;              // document streams per CTA
-constexpr int kMsBuffers = 2;              // accumulators per stream in TMEM (2 x 2 x 128 = all 512 columns)
+constexpr int kMsStreams = 4;              // document streams per CTA = accumulators in TMEM (4 x 128 columns)
 constexpr int kMsEpilogueWarps = 4 * kMsStreams;
 constexpr int kMsThreads = 64 + 32 * kMsEpilogueWarps;
 // Shared memory: the query tile stays resident when it is at most four depth blocks long (depth <= 256 for 16-bit types:
@@ -57,7 +56,7 @@ struct MaxsimDev {
     const float *q_inv, *d_inv;          // inverse norms per token
     const uint64_t *q_offsets, *d_offsets;  // token offsets per query / document (device), length count+1
     const uint32_t *q_token_query;       // query index of every query token (filled by maxsim_prepare_kernel)
-    const uint64_t *stream_bounds;       // first document of every stream, kMsStreams per segment plus one closing entry (same kernel)
+    const uint64_t *stream_bounds;       // first document of every stream, 4 per segment plus one closing entry (same kernel)
     uint64_t n_queries, n_docs;
     uint64_t q_tokens, d_tokens;
     uint32_t kblocks;
@@ -81,8 +80,8 @@ __device__ __forceinline__ uint64_t lower_bound_offsets(const uint64_t *offsets,
 }
 
 // Runs once before maxsim_kernel: the query each query token belongs to, and the first document of every stream. A segment
-// is the run of documents whose first token falls into its equal share of all document tokens; its streams are the
-// documents whose first token falls into each equal part of the segment's own tokens.
+// is the run of documents whose first token falls into its equal share of all document tokens; its four streams are the
+// documents whose first token falls into each quarter of the segment's own tokens.
 __global__ void maxsim_prepare_kernel(const uint64_t *q_offsets, uint64_t n_queries, uint64_t q_tokens, uint32_t *q_token_query,
                                       const uint64_t *d_offsets, uint64_t n_docs, uint64_t d_tokens, uint32_t segments,
                                       uint64_t *stream_bounds) {
@@ -164,19 +163,18 @@ __device__ __forceinline__ uint32_t chunk_position(const uint32_t (&v)[32], uint
 
 template <int kKind>
 __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p) {
-    constexpr int kTmemCols = kMsStreams * kMsBuffers * kMsBN;
+    constexpr int kTmemCols = kMsStreams * kMsBN;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + kMsBarrierOffset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kMsMaxStages + s); };
-    constexpr int kAccs = kMsStreams * kMsBuffers;  // accumulator `s * kMsBuffers + b`: buffer b of stream s
     auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kMsMaxStages + a); };
-    auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMsMaxStages + kAccs + a); };
-    const uint32_t query_bar = bar_base + 8u * (2 * kMsMaxStages + 2 * kAccs);           // resident query tile has landed
+    auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMsMaxStages + kMsStreams + a); };
+    const uint32_t query_bar = bar_base + 8u * (2 * kMsMaxStages + 2 * kMsStreams);      // resident query tile has landed
     const uint32_t drain_bar = query_bar + 8u;                                            // all MMAs have retired
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kMsBarrierOffset + 8 * (2 * kMsMaxStages + 2 * kAccs + 2));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kMsBarrierOffset + 8 * (2 * kMsMaxStages + 2 * kMsStreams + 2));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -194,7 +192,7 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMsMaxStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < kAccs; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), 4 * 32); }
+        for (int a = 0; a < kMsStreams; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), 4 * 32); }
         mbar_init(query_bar, 1);
         mbar_init(drain_bar, 1);
         fence_mbar_init();
@@ -203,7 +201,7 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
         tmem_alloc<1>(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
         tmem_relinquish<1>();
     }
-    // This CTA's run of whole documents and its streams (bounds computed by maxsim_prepare_kernel).
+    // This CTA's run of whole documents and its four streams (bounds computed by maxsim_prepare_kernel).
     const uint64_t *bounds = p.stream_bounds + (uint64_t)segment * kMsStreams;
     const uint64_t doc_begin = bounds[0], doc_end = bounds[kMsStreams];
     const bool has_work = doc_begin < doc_end;
@@ -300,11 +298,10 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             for (uint32_t r = 0; r < rounds && ok; ++r) {
                 for (int s = 0; s < kMsStreams && ok; ++s) {
                     if (r >= st[s].blocks) continue;
-                    // Buffer r % 2 of stream s was handed out r / 2 times before: wait until its four warps have read that round.
-                    const int acc = s * kMsBuffers + (int)(r & 1u);
-                    if (!mbar_wait(tmem_empty_bar(acc), ((r >> 1) & 1u) ^ 1u, 2, p.error_word)) { ok = false; break; }
+                    // Stream s's accumulator was handed out r times before: wait until its four warps have read round r - 1.
+                    if (!mbar_wait(tmem_empty_bar(s), (r & 1u) ^ 1u, 2, p.error_word)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + acc * kMsBN;
+                    const uint32_t d_tmem = tmem_base + s * kMsBN;
                     for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
                         if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
                         tc_fence_after_sync();
@@ -318,7 +315,7 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                         umma_commit(empty_bar(stage));
                         if (++stage == stages) { stage = 0; phase ^= 1u; }
                     }
-                    if (ok) umma_commit(tmem_full_bar(acc));
+                    if (ok) umma_commit(tmem_full_bar(s));
                 }
             }
             // No MMA may still be running when TMEM and shared memory are released below.
@@ -409,32 +406,26 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
         };
 
         for (uint32_t r = 0; r < st.blocks; ++r) {
-            const int acc = s * kMsBuffers + (int)(r & 1u);
-            if (!mbar_wait(tmem_full_bar(acc), (r >> 1) & 1u, 4, p.error_word)) break;  // nothing else waits for this warp
+            if (!mbar_wait(tmem_full_bar(s), r & 1u, 4, p.error_word)) break;  // nothing else waits for this warp
             tc_fence_after_sync();
-            const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + acc * kMsBN;
+            const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + s * kMsBN;
             const uint32_t tile_c0 = (st.first_block + r) * kMsBN;  // relative position of the tile's column 0
-            // The whole tile goes into registers at once and the accumulator back to the MMA issuer: TMEM is held for the
-            // duration of the loads only, and the four chunk scans below are independent instruction streams.
-            uint32_t v[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_addr + c * 32, v[c]);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_wait_for(v[c]);
+            // Two chunks in flight: the next one is on its way from TMEM while the current one is scanned.
+            uint32_t v0[32], v1[32];
+            tmem_ld_32x32(t_addr, v0);
+            tmem_ld_wait_for(v0);
+            tmem_ld_32x32(t_addr + 32, v1);
+            scan_chunk(v0, tile_c0);
+            tmem_ld_wait_for(v1);
+            tmem_ld_32x32(t_addr + 64, v0);
+            scan_chunk(v1, tile_c0 + 32u);
+            tmem_ld_wait_for(v0);
+            tmem_ld_32x32(t_addr + 96, v1);
+            scan_chunk(v0, tile_c0 + 64u);
+            tmem_ld_wait_for(v1);
             tc_fence_before_sync();
-            mbar_arrive(tmem_empty_bar(acc));
-            if (tile_c0 >= st.lo && tile_c0 + kMsBN <= cur_end) {
-                // The whole tile lies inside the current document: four maximum trees side by side, then the updates in order.
-                float group[4][4], best[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) best[c] = chunk_maximum(v[c], group[c]);
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    if (best[c] > run) { run = best[c]; arg = tile_c0 + 32u * c + chunk_position(v[c], 0xffffffffu, group[c], best[c]); }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) scan_chunk(v[c], tile_c0 + 32u * c);
-            }
+            mbar_arrive(tmem_empty_bar(s));   // everything this warp needs of the tile is in registers
+            scan_chunk(v1, tile_c0 + 96u);
             // Documents that end inside this tile are complete.
             const uint32_t tile_hi = tile_c0 + kMsBN < st.hi ? tile_c0 + kMsBN : st.hi;
             while (cur_doc < st.last_doc && cur_end <= tile_hi) {
@@ -500,7 +491,7 @@ cudaError_t launch_maxsim_tc(uint32_t dt, const MaxsimDev &dev_in, cudaStream_t 
     dev.q_group = group;
     uint64_t grid = (uint64_t)((dev.q_tiles + group - 1) / group) * group * dev.segments;
     if (grid == 0 || grid > 0x7fffffffull || dev.q_tokens > 0xffffffffull) return cudaErrorInvalidValue;
-    // Look-up tables for the main kernel: token -> query, stream -> first document (kMsStreams streams per segment).
+    // Look-up tables for the main kernel: token -> query, stream -> first document (four streams per segment).
     const uint64_t map_bytes = round_up(dev.q_tokens * 4, 16);
     const uint64_t bound_count = (uint64_t)dev.segments * kMsStreams + 1;
     uint8_t *tables = static_cast<uint8_t *>(scratch(kSlotNorms, map_bytes + bound_count * 8));
