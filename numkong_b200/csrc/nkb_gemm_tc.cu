@@ -597,7 +597,8 @@ constexpr int kPairStageBytes = kBM * kBKBytes + (kPairBN / 2) * kBKBytes;  // 1
 constexpr int kPairBarrierOffset = kPairStages * kPairStageBytes;
 constexpr int kPairSmemTotal = kPairBarrierOffset + 256 + kEpiSmemBytesDecl + 1024;
 
-// The work of one CTA pair. Whole-tile mode: tiles pair, pair + P, pair + 2 P, ... Split mode: the pipeline stages of all tiles
+// The work of one CTA pair. Whole-tile mode (the default): tiles pair, pair + P, pair + 2 P, ... Split mode (opt-in, see
+// launch_pair for why it is not the default): the pipeline stages of all tiles
 // are numbered tile by tile and dealt out in P equal contiguous shares, so that every pair is busy for the same time even when
 // the tiles do not fill a whole number of waves (1024 x 8192 makes 128 tiles for 74 pairs: 1.73 waves, 2 with whole tiles). A
 // share may begin in the middle of one tile and end in the middle of another. Shares are at least one tile long (the launcher
@@ -972,8 +973,12 @@ uint32_t *split_flag_ring() {
     return ring[d];
 }
 
-// `split`: 0 = whole tiles, 1 = split the depth when whole tiles would leave more than 5 % of the pairs' time idle,
-// 2 = split whenever the shape allows it (testing).
+// `split`: 0 = whole tiles (the default for every shape), 2 = split the depth between pairs whenever the shape allows it
+// (nkb_set_gemm_variant(5)). Splitting by itself whenever whole tiles leave pairs idle was measured and withdrawn: at
+// 1024 x 8192 x 8192 (bf16) 135 us against 114 us with whole tiles, at 2048 rows 272 against 221 - pairs that start at
+// different depths no longer fetch the same A and B chunks at the same time, and the L2 sharing that the lock-step sweep
+// gives is worth more than the idle tail of the last wave. It would also make the bits of a row depend on how many rows
+// are multiplied with it, which the reference's row-slicing callers may not see.
 template <int kKind, int kEpi>
 cudaError_t launch_pair(const CUtensorMap &a_map, const CUtensorMap &b_map, GemmDev dev, cudaStream_t stream, int split) {
     auto kernel = gemm_tc_pair_kernel<kKind, kEpi>;
@@ -1006,9 +1011,7 @@ cudaError_t launch_pair(const CUtensorMap &a_map, const CUtensorMap &b_map, Gemm
     dev.split_epoch = 0;
     if (kEpi == kEpiDot && split != 0 && dev.tri_diag < 0 && tiles > pairs && pairs <= kSplitPairsMax) {
         // Every share is at least one tile long (tiles > pairs), so no tile is shared by more than two pairs.
-        const uint32_t rounds = (tiles + pairs - 1) / pairs;
-        const bool unbalanced = (uint64_t)tiles * 100 < (uint64_t)rounds * pairs * 95;
-        if (split == 2 || unbalanced) {
+        if (split == 2) {
             uint32_t *ring = split_flag_ring();
             if (ring) {
                 uint32_t epoch = g_split_epoch.fetch_add(1) + 1;
@@ -1102,7 +1105,7 @@ cudaError_t launch_gemm_tc(const GemmArgs &args, cudaStream_t stream) {
                                pair_tiles >= (uint64_t)device_sm_count() / 2;
     // Variant 5 = CTA pairs with the depth split between pairs whenever the shape allows; variant 3 = CTA pairs, whole tiles.
     const bool use_pair = ((args.variant & 0xff) == 3 || (args.variant & 0xff) == 5 || pair_by_shape) && chunk_rows_total < 0x7fffffffull;
-    const int split = (args.variant & 0xff) == 5 ? 2 : (args.variant & 0xff) == 0 ? 1 : 0;
+    const int split = (args.variant & 0xff) == 5 ? 2 : 0;
     int bn = 256;
     if ((args.variant & 0xff) == 1 || (args.variant & 0xff) == 4) bn = 256;
     else if ((args.variant & 0xff) == 2) bn = 128;
