@@ -379,6 +379,24 @@ def library_peak_probes(torch, peaks):
         del a, b
     except Exception as e:
         out["int_mm_i8_error"] = str(e)[:200]
+    try:
+        # f64 library GEMM at 4096^3: the denominator for the f32 -> f64 product, which runs on the FP64 CUDA cores
+        a = torch.randn(4096, 4096, device="cuda", dtype=torch.float64)
+        b = torch.randn(4096, 4096, device="cuda", dtype=torch.float64)
+        fn = lambda: torch.matmul(a, b)
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out["matmul_f64_tflops"] = 2.0 * 4096 ** 3 * 3 / (e0.elapsed_time(e1) / 1e3) / 1e12
+        del a, b
+    except Exception as e:
+        out["matmul_f64_error"] = str(e)[:200]
     torch.cuda.empty_cache()
     return out
 
@@ -520,22 +538,28 @@ def main():
                       "bytes": int(size), "standalone_ms_whole_blob": float(tb_ms.item())}
         broadcast_and_first_step()   # warm-up of the piecewise path
 
+    # The clock sampler starts ahead of the warm-up, so that nothing idles between the warm-up and the timed region (NVLink
+    # and the SM clocks drop to a lower state within a fraction of a second of idling).
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
     for _ in range(args.warmup):
         nk.dots_packed(ta, packed, out=out, dtype=dtype)
     torch.cuda.synchronize()
     assert nk.synchronize() == 0, "device error word set during warm-up"
     reference_rows = out[:4].clone()
     if world > 1:
-        # the timed region must deliver B itself: every rank but the sender forgets what the warm-up left behind
+        # the timed region must deliver B itself: every rank but the sender forgets what the warm-up left behind; one
+        # more untimed broadcast (of a scratch buffer the size of the blob) is the communication path's own warm-up
         if rank != 0:
             blob.zero_()
+        scratch = torch.empty_like(blob)
+        dist.broadcast(scratch, src=0)
+        del scratch
         torch.cuda.synchronize()
 
     # ---- timed region: the broadcast (N > 1) and exactly K steps, barrier + synchronize on both sides, max over ranks
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -624,6 +648,17 @@ def main():
             s = time_device_steps(nk, torch, xa, xp, xo, dt, 10)
             extras[dt] = {"gso_per_s": ops_per_step * 10 / s / 1e9, "frac_of_measured_peak": ops_per_step * 10 / s / 1e12 / pk, "peak_tflops": pk}
             del xa, xb, xp, xo
+        # f32 inputs: f64 accumulation on the FP64 CUDA cores (the reference's numerics demand it), against the f64 library GEMM
+        xa, xb = torch.randn(M, K, device="cuda"), torch.randn(N, K, device="cuda")
+        xp = nk.dots_pack(xb, "f32")
+        xo = torch.empty((M, N), dtype=torch.float64, device="cuda")
+        nk.dots_packed(xa, xp, out=xo, dtype="f32")
+        torch.cuda.synchronize()
+        s = time_device_steps(nk, torch, xa, xp, xo, "f32", 3)
+        pk = probes.get("matmul_f64_tflops")
+        extras["f32"] = {"gso_per_s": ops_per_step * 3 / s / 1e9, "frac_of_measured_peak": (ops_per_step * 3 / s / 1e12 / pk) if pk else None,
+                         "peak_tflops": pk, "note": "f64 accumulation on CUDA cores; peak = the f64 library GEMM timed in this run"}
+        del xa, xb, xp, xo
         res = time_reference(dtype, steps=3, warmup=1)
         if res is not None:
             cpu_baseline = {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")}

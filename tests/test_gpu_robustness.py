@@ -195,3 +195,21 @@ def test_depth_split_between_cta_pairs_matches_whole_tiles(dtype, m, n, k):
         exact = oracle.exact_dots_f64(a[rows], b, dtype)
         scale = np.abs(oracle.decode(a[rows], dtype).astype(np.float64)) @ np.abs(oracle.decode(b, dtype).astype(np.float64)).T
         assert np.max(np.abs(split.cpu().numpy()[rows] - exact) / scale) <= 1.5e-7
+
+
+def test_sm_budget_changes_the_grid_not_the_result():
+    """nkb_set_sm_budget caps how many SMs the persistent GEMM kernels occupy (so that a collective on another stream finds
+    room); tiles are dealt to fewer CTAs, every tile is computed the same way."""
+    import torch
+    a = torch.from_numpy(syn.normal_matrix(2048, 1024, "bf16", 51).view(np.int16)).cuda()
+    packed = nk.dots_pack(torch.from_numpy(syn.normal_matrix(6144, 1024, "bf16", 52).view(np.int16)).cuda(), "bf16")
+    want = nk.dots_packed(a, packed, dtype="bf16")
+    want_angular = nk.angulars_packed(a[:300], packed, dtype="bf16")
+    try:
+        for budget in (132, 64, 3, 2):
+            nk.lib.nkb_set_sm_budget(budget)
+            assert torch.equal(nk.dots_packed(a, packed, dtype="bf16"), want), budget
+            assert torch.equal(nk.angulars_packed(a[:300], packed, dtype="bf16"), want_angular), budget
+    finally:
+        nk.lib.nkb_set_sm_budget(0)
+    assert nk.synchronize() == 0
