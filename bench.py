@@ -10,10 +10,13 @@ N = 1: K steps back to back, operands resident in HBM.
 
 N > 1 (torchrun, one rank per GPU): STRONG scaling of the same problem. The 8192 rows of A are split into N contiguous
 blocks, one per rank - the caller-side split the reference documents for its threads (README.md:209-212,
-rust/matrix.rs:3016-3026). Packed B exists on rank 0 only when the timed region starts and is broadcast over NCCL INSIDE
-it, once; then every rank runs its K steps. (--broadcast-pieces 2 sends it in two column blocks and multiplies the first
-while the second is still on its way - the packed rows of a column block are one contiguous byte range of the blob -
-which measured no faster: the broadcast kernel and the persistent GEMM compete for the same SMs.)
+rust/matrix.rs:3016-3026). Packed B exists on rank 0 only when the timed region starts and reaches the other ranks INSIDE
+it, once; then every rank runs its K steps. By default rank 0 stores the blob once through the NVSwitch's multicast
+mapping with the library's own kernels (multimem.st + a flag barrier: numkong_b200.sharding.SwitchBroadcast);
+--broadcast nccl uses ncclBroadcast instead, and is what runs where the GPUs have no multicast mapping. (--broadcast nccl
+--broadcast-pieces 2 sends it in two column blocks and multiplies the first while the second is still on its way - the
+packed rows of a column block are one contiguous byte range of the blob - which measured no faster: the broadcast kernel
+and the persistent GEMM compete for the same SMs.)
 The timed region is bracketed by a barrier and a device synchronize; the reported time is the maximum over ranks and
 `value` = K * 2 * 8192^3 / that time.
 
@@ -445,6 +448,10 @@ def main():
                     help="N > 1: 1 = broadcast the packed matrix whole, then multiply (default); 2 = broadcast it in two column blocks "
                          "and multiply the first while the second is in flight (measured on two B200s: 0.73-0.77 ms for the first step "
                          "against 0.74-0.76 ms whole - the broadcast kernel and the persistent GEMM compete for SMs, so nothing is won)")
+    ap.add_argument("--broadcast", default="switch", choices=["switch", "nccl"],
+                    help="N > 1: how packed B reaches the ranks inside the timed region. switch (default) = rank 0 stores it once "
+                         "through the NVSwitch multicast mapping with the library's own kernels (numkong_b200.sharding.SwitchBroadcast); "
+                         "nccl = ncclBroadcast. Without a multicast mapping switch falls back to nccl and says so.")
     ap.add_argument("--rows", type=int, default=8192,
                     help="global rows of A; anything but 8192 is a reduced case for profiler captures, not the benchmark")
     args = ap.parse_args()
@@ -477,11 +484,20 @@ def main():
     a_host = gen_rows(rows, dtype, SEEDS[dtype], first_row=row0)
     ta = torch.from_numpy(a_host.view(STORE[eb])).cuda()
     size = nk.PackedMatrix.packed_size(N, K, dtype)
-    blob = torch.zeros(size, dtype=torch.uint8, device="cuda")
+    # `blob` is what every rank multiplies with. Through the switch it is this rank's copy of a symmetric buffer that rank 0's
+    # multicast stores fill on all GPUs at once (rank 0's own copy included), and rank 0 packs into a buffer of its own.
+    channel = None
+    if world > 1 and args.broadcast == "switch":
+        channel = sharding.SwitchBroadcast(size)
+        if not channel.available:
+            channel.close()
+            channel = None
+    blob = channel.buffer[:size] if channel is not None else torch.zeros(size, dtype=torch.uint8, device="cuda")
+    packed_on_sender = torch.zeros(size, dtype=torch.uint8, device="cuda") if (channel is not None and rank == 0) else blob
     if rank == 0:
         b_host = gen_rows(N, dtype, SEEDS[dtype] + 1)
         tb = torch.from_numpy(b_host.view(STORE[eb])).cuda()
-        getattr(nk.lib, f"nk_dots_pack_{dtype}")(tb.data_ptr(), N, K, K * eb, blob.data_ptr())
+        getattr(nk.lib, f"nk_dots_pack_{dtype}")(tb.data_ptr(), N, K, K * eb, packed_on_sender.data_ptr())
         nk.check("pack")
         del tb
     torch.cuda.synchronize()
@@ -500,8 +516,13 @@ def main():
     comm = torch.cuda.Stream() if world > 1 else None
 
     def broadcast_and_first_step():
-        """Rank 0 sends the packed matrix piece by piece on the communication stream; every rank multiplies a piece as soon
-        as it has arrived while the next one is still in flight."""
+        """Through the switch: rank 0's multicast stores, a flag barrier, the first product. Over NCCL: rank 0 sends the packed
+        matrix piece by piece on the communication stream; every rank multiplies a piece as soon as it has arrived while the
+        next one is still in flight."""
+        if channel is not None:
+            channel.send(packed_on_sender if rank == 0 else None, src=0, blocks=128)
+            nk.dots_packed(ta, packed, out=out, dtype=dtype)
+            return
         comm.wait_stream(compute)
         arrived = []
         with torch.cuda.stream(comm):
@@ -524,19 +545,33 @@ def main():
     if world > 1:
         # untimed: B reaches every rank once so that the warm-up steps have data; also warms NCCL up and times the plain
         # broadcast of the whole blob for the report
-        dist.broadcast(blob, src=0)
-        torch.cuda.synchronize()
-        dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        dist.broadcast(blob, src=0)
-        e1.record()
-        torch.cuda.synchronize()
-        tb_ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tb_ms, op=dist.ReduceOp.MAX)
-        collective = {"op": "ncclBroadcast of packed B from rank 0, inside the timed region, once" + (", in 2 column blocks overlapped with the first step" if len(pieces) == 2 else ", ahead of the first step"),
-                      "bytes": int(size), "standalone_ms_whole_blob": float(tb_ms.item())}
-        broadcast_and_first_step()   # warm-up of the piecewise path
+        def standalone_ms(send):
+            send()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            send()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            return float(ms.item())
+
+        nccl_scratch = torch.empty(size, dtype=torch.uint8, device="cuda") if channel is not None else blob
+        nccl_ms = standalone_ms(lambda: dist.broadcast(nccl_scratch, src=0))
+        if channel is not None:
+            del nccl_scratch
+            switch_ms = standalone_ms(lambda: channel.send(packed_on_sender if rank == 0 else None, src=0, blocks=128))
+            collective = {"op": "packed B stored once by rank 0 through the NVSwitch multicast mapping (multimem.st, the library's "
+                                "nkb_multicast_store) and a flag barrier between the GPUs (nkb_peer_barrier), inside the timed region, "
+                                "once, ahead of the first step",
+                          "bytes": int(size), "standalone_ms_whole_blob": switch_ms, "standalone_ms_ncclBroadcast": nccl_ms}
+        else:
+            collective = {"op": "ncclBroadcast of packed B from rank 0, inside the timed region, once" + (", in 2 column blocks overlapped with the first step" if len(pieces) == 2 else ", ahead of the first step")
+                                + (" (no multicast mapping on these GPUs)" if args.broadcast == "switch" else ""),
+                          "bytes": int(size), "standalone_ms_whole_blob": nccl_ms}
+        broadcast_and_first_step()   # warm-up of the timed path
 
     # The clock sampler starts ahead of the warm-up, so that nothing idles between the warm-up and the timed region (NVLink
     # and the SM clocks drop to a lower state within a fraction of a second of idling).
@@ -552,11 +587,14 @@ def main():
     if world > 1:
         # the timed region must deliver B itself: every rank but the sender forgets what the warm-up left behind; one
         # more untimed broadcast (of a scratch buffer the size of the blob) is the communication path's own warm-up
-        if rank != 0:
+        if rank != 0 or channel is not None:
             blob.zero_()
-        scratch = torch.empty_like(blob)
-        dist.broadcast(scratch, src=0)
-        del scratch
+        if channel is None:
+            scratch = torch.empty_like(blob)
+            dist.broadcast(scratch, src=0)
+            del scratch
+        else:
+            channel.barrier()
         torch.cuda.synchronize()
 
     # ---- timed region: the broadcast (N > 1) and exactly K steps, barrier + synchronize on both sides, max over ranks
@@ -699,6 +737,9 @@ def main():
         }
         print(json.dumps(line))
     if world > 1:
+        if channel is not None:
+            del packed, blob
+            channel.close()
         dist.destroy_process_group()
 
 

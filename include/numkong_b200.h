@@ -306,7 +306,8 @@ NKB_API void nkb_set_stream(void *cuda_stream);
  *  first bounded pipeline wait that gave up on this GPU since the last report (sites: 1 loader waiting for a free stage,
  *  2 / 3 MMA issuer waiting for a drained accumulator / a loaded stage, 4 epilogue waiting for a finished accumulator,
  *  5 / 6 the issuer's / loader's final drain, 7 epilogue waiting for the other half of a tile whose depth two CTA pairs
- *  share). Covers the regular entry points and nkb_angulars_packed_noalloc alike,
+ *  share, 8 nkb_peer_barrier waiting for another GPU - the low bits then name that peer). Covers the regular entry points
+ *  and nkb_angulars_packed_noalloc alike,
  *  allocates nothing, and clears the word it reports: the failure belongs to the calls enqueued before this
  *  synchronisation (their results are not valid), later calls start clean. Calls with a host-resident operand do this
  *  check themselves and fill their output with 0xFF. */
@@ -340,6 +341,25 @@ NKB_API void nkb_set_accumulation_span(int stages);
  *  only does so when some are left free: a caller that overlaps a broadcast of the packed matrix with the products of the
  *  parts that have arrived sets e.g. 132 of 148 for those products and 0 again afterwards. Process-wide. */
 NKB_API void nkb_set_sm_budget(int sms);
+/** One-to-all delivery of `bytes` bytes (a packed matrix, typically) through the NVSwitch: `multicast_dst` is the MULTICAST
+ *  address of a buffer that exists on every GPU of the group (an NVLink multicast mapping, e.g. the `multicast_ptr` of a
+ *  torch.distributed._symmetric_memory buffer, plus the offset inside it); `src` is ordinary device memory of the calling
+ *  GPU. Every 16 bytes are issued once with `multimem.st` and written into all GPUs' copies by the switch, the sender's
+ *  included, so the sender's link carries the data once whatever the number of receivers (a ring broadcast forwards it hop by
+ *  hop). Enqueued on the calling thread's stream; the caller orders the receivers behind it (a barrier across the group on
+ *  their streams). Addresses and size must be multiples of 16. `blocks` = CTAs to use (0: 64). Stands where the reference's
+ *  callers hand "the full packed B" to every worker (README.md:199-212). Returns 0, or non-zero with nkb_last_error() set.
+ *  An address that is not a multicast mapping is undefined behaviour, as for any store through a bad pointer. */
+NKB_API int nkb_multicast_store(void *multicast_dst, void const *src, nk_size_t bytes, int blocks);
+/** Barrier between the GPUs of a group, enqueued on the calling thread's stream: work enqueued behind it on any of them
+ *  starts only after every GPU has reached it - e.g. after the sender's nkb_multicast_store has finished. `peer_flags` is a
+ *  HOST array of `world` device addresses: entry p is GPU p's flag buffer (at least `world` 32-bit words, zero before the
+ *  first barrier, used for nothing else) as mapped into this process - the `buffer_ptrs` of a symmetric-memory buffer.
+ *  Every GPU writes `epoch` into its own slot of every peer's buffer and waits until all slots of its own buffer have reached
+ *  `epoch`; callers pass 1, 2, 3, ... in step on all GPUs. The wait is bounded like every other wait of this library (site 8,
+ *  nkb_set_wait_limit_ns): when a peer does not show up the kernel records the error word and returns, nkb_synchronize()
+ *  reports it, and what was ordered behind the barrier must be treated as not ordered. `world` <= 16. */
+NKB_API int nkb_peer_barrier(void *const *peer_flags, int world, int rank, uint32_t epoch);
 /** How e2m3 / e3m2 operands reach the tensor cores: 1 (default) = packed 6-bit operands with the native
  *  e2m3 / e3m2 MMA formats, 0 = recoded to the e4m3 code of the same value (exact as well). Applies to later pack AND multiply calls;
  *  a blob packed under one setting must be multiplied under the same one. */

@@ -90,6 +90,9 @@ def _load() -> ctypes.CDLL:
     lib.nkb_test_set_error_word.restype, lib.nkb_test_set_error_word.argtypes = ctypes.c_int, [ctypes.c_int, ctypes.c_uint32]
     lib.nkb_cached_blob_count.restype, lib.nkb_cached_blob_count.argtypes = sz, []
     lib.nkb_set_sm_budget.restype, lib.nkb_set_sm_budget.argtypes = None, [ctypes.c_int]
+    lib.nkb_multicast_store.restype, lib.nkb_multicast_store.argtypes = ctypes.c_int, [vp, vp, sz, ctypes.c_int]
+    lib.nkb_peer_barrier.restype = ctypes.c_int
+    lib.nkb_peer_barrier.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_uint32]
     return lib
 
 

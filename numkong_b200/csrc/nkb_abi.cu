@@ -26,7 +26,8 @@ std::atomic<uint64_t> g_nonce_counter{0};
 std::atomic<int> g_sm_budget{0};
 // Limit of every bounded wait of the tensor-core kernels, by wait site (microseconds); see nkb_set_wait_limit_ns.
 std::atomic<uint32_t> g_wait_us[kWaitSites] = {{kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs},
-                                               {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}};
+                                               {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs}, {kDefaultWaitLimitUs},
+                                               {kDefaultWaitLimitUs}};
 
 // ---------------------------------------------------------------- per-thread context
 struct Scratch {

@@ -94,11 +94,12 @@ inline uint64_t round_up(uint64_t x, uint64_t m) { return (x + m - 1) / m * m; }
 //   3 MMA issuer waits for a loaded stage               4 epilogue waits for a finished accumulator
 //   5 MMA issuer waits for its last MMAs before leaving 6 producer waits for its last copies before leaving
 //   7 epilogue waits for the partial tile another CTA pair stored (depth split between pairs)
+//   8 a GPU waits for the other GPUs of its group at nkb_peer_barrier (the low 16 bits then name the missing peer)
 #ifndef NKB_WAIT_LIMIT_NS
 #define NKB_WAIT_LIMIT_NS 2000000000ull  // 2 s
 #endif
 constexpr uint32_t kDefaultWaitLimitUs = (uint32_t)(NKB_WAIT_LIMIT_NS / 1000ull);
-constexpr int kWaitSites = 8;
+constexpr int kWaitSites = 9;
 
 // Sub-byte types: `depth` counts values (nibbles for i4 / u4, bits for u1), a row occupies ceil(depth / per_byte) bytes,
 // and - like the reference's kernels (include/numkong/dot/serial.h:185-215) - every value of the last byte takes part

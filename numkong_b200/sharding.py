@@ -4,7 +4,8 @@ The path shards by rows, exactly like the reference's callers split rows of A ac
 (README.md:199-212 of the reference): every rank multiplies its own rows against the same packed B, or
 scores the queries against its own slice of the corpus / documents. The only exchanges are a broadcast
 of the packed operand that every rank needs and, for nearest-k searches, one gather of each rank's k best
-followed by a merge. Collectives run on NCCL for CUDA tensors and on gloo for CPU tensors (tests).
+followed by a merge. Collectives run on NCCL for CUDA tensors and on gloo for CPU tensors (tests); the packed operand
+can instead travel through the NVSwitch's multicast with the library's own copy and barrier kernels (SwitchBroadcast).
 """
 from __future__ import annotations
 
@@ -42,6 +43,86 @@ def broadcast_bytes(buffer: torch.Tensor, src: int = 0, group=None) -> torch.Ten
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.broadcast(buffer, src=src, group=group)
     return buffer
+
+
+class SwitchBroadcast:
+    """One-to-all delivery of a byte buffer (a packed matrix) through the NVSwitch's multicast: the sender issues every
+    16 bytes once (`multimem.st`, nkb_multicast_store) and the switch writes them into every GPU's copy, so the sender's
+    link carries the data once whatever the group size; a bounded flag barrier between the GPUs (nkb_peer_barrier) orders
+    the receivers' streams behind the copy. Receivers run no kernel but the barrier.
+
+        channel = SwitchBroadcast(nbytes)        # set-up, collective: symmetric buffer + multicast mapping
+        blob = channel.send(blob_on_src, src=0)  # every rank calls it; returns this rank's copy (a view of the buffer)
+
+    `available` is False where the GPUs have no multicast mapping (no NVSwitch fabric, one GPU): `send` then falls back to
+    the group's ordinary broadcast (NCCL) into the same buffer. Ranks must leave together (`close`) - a process that exits
+    while its memory is still bound to the multicast object disturbs the others.
+    """
+
+    def __init__(self, nbytes: int, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = (int(nbytes) + 15) // 16 * 16
+        self.buffer = symm.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self._handle = symm.rendezvous(self.buffer, self.group)
+        self._flags = symm.empty(64, dtype=torch.int32, device=device)
+        self._flags.zero_()
+        self._flag_handle = symm.rendezvous(self._flags, self.group)
+        self._epoch = 0
+        base = int(self._handle.buffer_ptrs[self.rank])
+        inside = self.buffer.data_ptr() - base
+        multicast = int(self._handle.multicast_ptr)
+        self.available = multicast != 0 and self.world <= 16 and 0 <= inside and inside + self.nbytes <= int(self._handle.buffer_size)
+        self._multicast = multicast + inside if self.available else 0
+        flag_base = int(self._flag_handle.buffer_ptrs[self.rank])
+        flag_inside = self._flags.data_ptr() - flag_base
+        import ctypes
+        self._peer_flags = (ctypes.c_void_p * self.world)(*[int(ptr) + flag_inside for ptr in self._flag_handle.buffer_ptrs])
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)  # every rank's flags are zero before anyone's first barrier
+
+    def barrier(self) -> None:
+        """Orders everything enqueued behind it on any rank's current stream after everything enqueued before it on all."""
+        from . import _lib
+        self._epoch += 1
+        _lib.lib.nkb_set_stream(torch.cuda.current_stream().cuda_stream)
+        if _lib.lib.nkb_peer_barrier(self._peer_flags, self.world, self.rank, self._epoch) != 0:
+            raise RuntimeError("peer barrier: " + _lib.last_error())
+
+    def send(self, source: torch.Tensor = None, src: int = 0, blocks: int = 0) -> torch.Tensor:
+        """`source` (uint8, on `src` only; other ranks may pass None) lands in every rank's buffer; returns that buffer's
+        first `source.numel()` bytes - on every rank the size of the buffer when `source` is None."""
+        from . import _lib
+        count = self.nbytes if source is None else int(source.numel())
+        if not self.available:
+            view = self.buffer[:count]
+            if self.rank == src:
+                view.copy_(source.reshape(-1).view(torch.uint8))
+            dist.broadcast(view, src=src, group=self.group)
+            return view
+        self.barrier()  # nobody still reads what the buffer held before
+        if self.rank == src:
+            flat = source.reshape(-1).view(torch.uint8)
+            padded = (count + 15) // 16 * 16
+            if padded != count or flat.data_ptr() % 16:
+                staged = torch.zeros(padded, dtype=torch.uint8, device=flat.device)
+                staged[:count] = flat
+                flat = staged
+            _lib.lib.nkb_set_stream(torch.cuda.current_stream().cuda_stream)
+            if _lib.lib.nkb_multicast_store(self._multicast, flat.data_ptr(), padded, blocks) != 0:
+                raise RuntimeError("multicast store: " + _lib.last_error())
+        self.barrier()
+        return self.buffer[:count]
+
+    def close(self) -> None:
+        """Collective: all ranks drop their mapping together, with nothing in flight."""
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        self._handle = self._flag_handle = None
+        self.buffer = self._flags = None
 
 
 def merge_topk(values: torch.Tensor, ids: torch.Tensor, top: int, group=None, dst: int = 0, merge=None):
