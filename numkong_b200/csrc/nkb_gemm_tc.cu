@@ -87,6 +87,9 @@ __device__ __forceinline__ void tile_coords(uint32_t tile, uint32_t tiles_m, uin
     uint32_t in_group = tile % per_group;
     mt = first_m + in_group % group_rows;
     nt = in_group / group_rows;
+    // Odd groups walk the column tiles backwards: the packed rows the previous group touched last are still in L2 when the
+    // next group begins with them.
+    if (group & 1u) nt = tiles_n - 1u - nt;
 }
 
 // True when no cell of a tile (first row, one past its last column) survives the triangular mask. Every warp role asks
@@ -362,7 +365,9 @@ __device__ __forceinline__ void store_tile(uint32_t (&acc)[kCols], const GemmDev
                         const uint4 old = *reinterpret_cast<const uint4 *>(dst);
                         v = make_uint4(plus(v.x, old.x), plus(v.y, old.y), plus(v.z, old.z), plus(v.w, old.w));
                     }
-                    *reinterpret_cast<uint4 *>(dst) = v;
+                    // Streaming store: result cells are written once and not read here again, so they should be the first
+                    // lines L2 gives up - ahead of the operand chunks that other tiles are about to ask for.
+                    __stcs(reinterpret_cast<uint4 *>(dst), v);
                 } else {
                     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
