@@ -486,12 +486,19 @@ def main():
     size = nk.PackedMatrix.packed_size(N, K, dtype)
     # `blob` is what every rank multiplies with. Through the switch it is this rank's copy of a symmetric buffer that rank 0's
     # multicast stores fill on all GPUs at once (rank 0's own copy included), and rank 0 packs into a buffer of its own.
-    channel = None
+    channel, switch_note = None, None
     if world > 1 and args.broadcast == "switch":
-        channel = sharding.SwitchBroadcast(size)
-        if not channel.available:
-            channel.close()
+        # Every rank must take the same road: one that cannot map the buffer (or has no multicast address) sends all to NCCL.
+        try:
+            channel = sharding.SwitchBroadcast(size)
+            usable = channel.available
+        except Exception as exc:  # no symmetric memory in this build of torch, no fabric, ...
+            usable, switch_note = False, f"{type(exc).__name__}: {exc}"[:200]
+        agreed = torch.tensor([1.0 if usable else 0.0], device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if agreed.item() == 0.0:
             channel = None
+            switch_note = switch_note or "no multicast mapping on these GPUs"
     blob = channel.buffer[:size] if channel is not None else torch.zeros(size, dtype=torch.uint8, device="cuda")
     packed_on_sender = torch.zeros(size, dtype=torch.uint8, device="cuda") if (channel is not None and rank == 0) else blob
     if rank == 0:
@@ -563,13 +570,20 @@ def main():
         if channel is not None:
             del nccl_scratch
             switch_ms = standalone_ms(lambda: channel.send(packed_on_sender if rank == 0 else None, src=0, blocks=128))
+            # every rank's copy must be rank 0's blob, bit for bit, before anything is timed with it
+            digest = blob[: size // 8 * 8].view(torch.int64).sum().reshape(1)
+            lowest, highest = digest.clone(), digest.clone()
+            dist.all_reduce(lowest, op=dist.ReduceOp.MIN)
+            dist.all_reduce(highest, op=dist.ReduceOp.MAX)
+            sender = packed_on_sender[: size // 8 * 8].view(torch.int64).sum().reshape(1) if rank == 0 else digest
+            assert lowest.item() == highest.item() == sender.item(), "the switch delivered different bytes to different ranks"
             collective = {"op": "packed B stored once by rank 0 through the NVSwitch multicast mapping (multimem.st, the library's "
                                 "nkb_multicast_store) and a flag barrier between the GPUs (nkb_peer_barrier), inside the timed region, "
                                 "once, ahead of the first step",
                           "bytes": int(size), "standalone_ms_whole_blob": switch_ms, "standalone_ms_ncclBroadcast": nccl_ms}
         else:
             collective = {"op": "ncclBroadcast of packed B from rank 0, inside the timed region, once" + (", in 2 column blocks overlapped with the first step" if len(pieces) == 2 else ", ahead of the first step")
-                                + (" (no multicast mapping on these GPUs)" if args.broadcast == "switch" else ""),
+                                + (f" (switch delivery not used: {switch_note})" if switch_note else ""),
                           "bytes": int(size), "standalone_ms_whole_blob": nccl_ms}
         broadcast_and_first_step()   # warm-up of the timed path
 

@@ -558,16 +558,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const GemmDev p) {
 #pragma unroll
                     for (int c = 0; c < kColsPerThread / 32; ++c) tmem_ld_wait_for(*reinterpret_cast<uint32_t(*)[32]>(&acc[c * 32]));
                 } else {
+                    // Later spans are added to the running sums eight columns at a time, two loads deep: while the values of
+                    // one load are added, the next load is on its way from TMEM (no more registers than one 16-column load).
+                    const uint32_t span_addr = tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread;
+                    uint32_t va[8], vb[8];
+                    auto add8 = [&](int c8, const uint32_t (&v)[8]) {
 #pragma unroll
-                    for (int c = 0; c < kColsPerThread / 16; ++c) {
-                        uint32_t v[16];
-                        tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 16, v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if constexpr (kKind == kKindI8) acc[c * 16 + j] += v[j];
-                            else acc[c * 16 + j] = __float_as_uint(__uint_as_float(acc[c * 16 + j]) + __uint_as_float(v[j]));
+                        for (int j = 0; j < 8; ++j) {
+                            if constexpr (kKind == kKindI8) acc[c8 * 8 + j] += v[j];
+                            else acc[c8 * 8 + j] = __float_as_uint(__uint_as_float(acc[c8 * 8 + j]) + __uint_as_float(v[j]));
                         }
+                    };
+                    tmem_ld_32x8(span_addr, va);
+#pragma unroll
+                    for (int c8 = 0; c8 < kColsPerThread / 8; c8 += 2) {
+                        tmem_ld_wait_for(va);
+                        tmem_ld_32x8(span_addr + (c8 + 1) * 8, vb);
+                        add8(c8, va);
+                        tmem_ld_wait_for(vb);
+                        if (c8 + 2 < kColsPerThread / 8) tmem_ld_32x8(span_addr + (c8 + 2) * 8, va);
+                        add8(c8 + 1, vb);
                     }
                 }
                 tc_fence_before_sync();
@@ -824,16 +834,26 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
 #pragma unroll
                     for (int c = 0; c < kColsPerThread / 32; ++c) tmem_ld_wait_for(*reinterpret_cast<uint32_t(*)[32]>(&acc[c * 32]));
                 } else {
+                    // Later spans are added to the running sums eight columns at a time, two loads deep: while the values of
+                    // one load are added, the next load is on its way from TMEM (no more registers than one 16-column load).
+                    const uint32_t span_addr = tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread;
+                    uint32_t va[8], vb[8];
+                    auto add8 = [&](int c8, const uint32_t (&v)[8]) {
 #pragma unroll
-                    for (int c = 0; c < kColsPerThread / 16; ++c) {
-                        uint32_t v[16];
-                        tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + buf * kBN + half * kColsPerThread + c * 16, v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if constexpr (kKind == kKindI8) acc[c * 16 + j] += v[j];
-                            else acc[c * 16 + j] = __float_as_uint(__uint_as_float(acc[c * 16 + j]) + __uint_as_float(v[j]));
+                        for (int j = 0; j < 8; ++j) {
+                            if constexpr (kKind == kKindI8) acc[c8 * 8 + j] += v[j];
+                            else acc[c8 * 8 + j] = __float_as_uint(__uint_as_float(acc[c8 * 8 + j]) + __uint_as_float(v[j]));
                         }
+                    };
+                    tmem_ld_32x8(span_addr, va);
+#pragma unroll
+                    for (int c8 = 0; c8 < kColsPerThread / 8; c8 += 2) {
+                        tmem_ld_wait_for(va);
+                        tmem_ld_32x8(span_addr + (c8 + 1) * 8, vb);
+                        add8(c8, va);
+                        tmem_ld_wait_for(vb);
+                        if (c8 + 2 < kColsPerThread / 8) tmem_ld_32x8(span_addr + (c8 + 2) * 8, va);
+                        add8(c8 + 1, vb);
                     }
                 }
                 tc_fence_before_sync();
