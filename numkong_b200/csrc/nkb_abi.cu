@@ -166,6 +166,13 @@ void *scratch(int slot, size_t bytes) {
     return p;
 }
 
+size_t scratch_capacity(int slot) {
+    const Scratch &s = t_ctx.slots[slot + t_ctx.slot_set * kSlotsPerSet];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return s.ptr && s.device == dev ? s.bytes : 0;
+}
+
 unsigned int *device_error_word() {
     int dev = 0;
     cudaGetDevice(&dev);

@@ -21,6 +21,8 @@ int current_variant();
 // Device/managed memory is used in place; everything else is treated as host memory.
 MemKind classify(const void *p);
 void *scratch(int slot, size_t bytes);
+// Bytes the calling thread's staging buffer `slot` already holds on the current device (0: none yet).
+size_t scratch_capacity(int slot);
 unsigned int *device_error_word();
 // Error status of the current device (0 = no bounded wait gave up since the last report); a reported failure is cleared.
 uint32_t read_device_error();

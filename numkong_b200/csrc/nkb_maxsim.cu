@@ -62,7 +62,8 @@ struct MaxsimDev {
     uint32_t kblocks;
     uint32_t q_tiles, segments;
     uint32_t q_group;                    // query tiles that walk the same document segment side by side
-    uint32_t idesc;
+    uint32_t idesc;        // M = 128, N = 128: one stream's tile
+    uint32_t idesc_pair;   // M = 128, N = 256: the tiles of two neighbouring streams in one instruction
     float *scores_f32;                   // batch: n_queries x n_docs
     uint64_t score_stride;               // in floats
     double *total_f64;                   // single pair: one accumulator
@@ -187,8 +188,13 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
     if (q_tile >= p.q_tiles) return;  // padding blocks of the last group (nothing allocated yet)
 
     const bool resident = p.kblocks <= (uint32_t)kMsResidentBlocks;
-    const int stages = resident ? 6 : 3;
-    const uint32_t stage_bytes = resident ? kChunkBytes : 2u * kChunkBytes;
+    // A stage is two chunks. Query tile streamed (deep queries): a document chunk and the query chunk of the same depth block.
+    // Query tile resident: the chunks of the SAME round of two neighbouring streams (0 and 1, or 2 and 3), back to back, so
+    // that one N = 256 instruction multiplies both - half as many instructions for the issuing thread, and the query chunk is
+    // read from shared memory once per 256 columns instead of once per 128 (at N = 128 an instruction reads 8 KiB per 64
+    // cycles, all the 128 bytes per cycle that shared memory delivers, while the copies of the next stages write into it).
+    const int stages = 3;
+    const uint32_t stage_bytes = 2u * kChunkBytes;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMsMaxStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -260,15 +266,35 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             int stage = 0;
             uint32_t phase = 0, issued = 0;
             bool ok = true;
+            auto tile_of = [&](int s, uint32_t r) {
+                return p.d_payload + (cache_base / kMsBN + st[s].first_block + r) * (uint64_t)p.kblocks * kChunkBytes;
+            };
             for (uint32_t r = 0; r < rounds && ok; ++r) {
+                if (resident) {
+                    for (int s = 0; s < kMsStreams && ok; s += 2) {
+                        const bool have0 = r < st[s].blocks, have1 = r < st[s + 1].blocks;
+                        if (!have0 && !have1) continue;
+                        const uint8_t *tile0 = tile_of(s, r), *tile1 = tile_of(s + 1, r);
+                        for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
+                            const uint32_t dst = smem_base + kMsRingOffset + stage * stage_bytes;
+                            mbar_expect_tx(full_bar(stage), ((uint32_t)have0 + (uint32_t)have1) * kChunkBytes);
+                            if (have0) bulk_load(dst, tile0 + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
+                            if (have1) bulk_load(dst + kChunkBytes, tile1 + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
+                            ++issued;
+                            if (++stage == stages) { stage = 0; phase ^= 1u; }
+                        }
+                    }
+                    continue;
+                }
                 for (int s = 0; s < kMsStreams && ok; ++s) {
                     if (r >= st[s].blocks) continue;
-                    const uint8_t *b_tile = p.d_payload + (cache_base / kMsBN + st[s].first_block + r) * (uint64_t)p.kblocks * kChunkBytes;
+                    const uint8_t *b_tile = tile_of(s, r);
                     for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
                         if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
                         const uint32_t dst = smem_base + kMsRingOffset + stage * stage_bytes;
                         mbar_expect_tx(full_bar(stage), stage_bytes);
-                        if (!resident) bulk_load(dst + kChunkBytes, a_tile + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
+                        bulk_load(dst + kChunkBytes, a_tile + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
                         bulk_load(dst, b_tile + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
                         ++issued;
                         if (++stage == stages) { stage = 0; phase ^= 1u; }
@@ -296,6 +322,34 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             bool ok = true;
             if (resident && !mbar_wait(query_bar, 0u, 3, p.error_word)) ok = false;
             for (uint32_t r = 0; r < rounds && ok; ++r) {
+                if (resident) {
+                    for (int s = 0; s < kMsStreams && ok; s += 2) {
+                        const bool have0 = r < st[s].blocks, have1 = r < st[s + 1].blocks;
+                        if (!have0 && !have1) continue;
+                        // A stream's accumulator was handed out r times before: wait until its four warps have read round r - 1.
+                        if (have0 && !mbar_wait(tmem_empty_bar(s), (r & 1u) ^ 1u, 2, p.error_word)) { ok = false; break; }
+                        if (have1 && !mbar_wait(tmem_empty_bar(s + 1), (r & 1u) ^ 1u, 2, p.error_word)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        // Both streams: one instruction over their 256 neighbouring columns; one of them left: its 128 alone.
+                        const uint32_t d_tmem = tmem_base + (have0 ? s : s + 1) * kMsBN;
+                        const uint32_t idesc = have0 && have1 ? p.idesc_pair : p.idesc;
+                        for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                            if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
+                            tc_fence_after_sync();
+                            const uint32_t b_src = smem_base + kMsRingOffset + stage * stage_bytes + (have0 ? 0u : kChunkBytes);
+                            const uint64_t a_desc = make_smem_desc_sw128(smem_base + kb * kChunkBytes);
+                            const uint64_t b_desc = make_smem_desc_sw128(b_src);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                umma<kKind, 1>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | (uint32_t)k) != 0u);
+                            umma_commit(empty_bar(stage));
+                            if (++stage == stages) { stage = 0; phase ^= 1u; }
+                        }
+                        if (ok && have0) umma_commit(tmem_full_bar(s));
+                        if (ok && have1) umma_commit(tmem_full_bar(s + 1));
+                    }
+                    continue;
+                }
                 for (int s = 0; s < kMsStreams && ok; ++s) {
                     if (r >= st[s].blocks) continue;
                     // Stream s's accumulator was handed out r times before: wait until its four warps have read round r - 1.
@@ -306,7 +360,7 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                         if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
                         tc_fence_after_sync();
                         const uint32_t b_src = smem_base + kMsRingOffset + stage * stage_bytes;
-                        const uint32_t a_src = resident ? smem_base + kb * kChunkBytes : b_src + kChunkBytes;
+                        const uint32_t a_src = b_src + kChunkBytes;
                         const uint64_t a_desc = make_smem_desc_sw128(a_src);
                         const uint64_t b_desc = make_smem_desc_sw128(b_src);
 #pragma unroll
@@ -398,6 +452,13 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
                 }
                 const uint32_t piece_end = cur_end < hi ? cur_end : hi;
                 const uint32_t j0 = pos - c0, j1 = piece_end - c0;  // 0 <= j0 < j1 <= 32
+                if (j0 == 0u && j1 == 32u) {
+                    // The chunk begins a document and lies inside it (every document's first chunk once documents sit on
+                    // 32-token boundaries): no column is masked.
+                    const float best = chunk_maximum(v, group);
+                    if (best > run) { run = best; arg = c0 + chunk_position(v, 0xffffffffu, group, best); }
+                    return;
+                }
                 const uint32_t inside = (0xffffffffu >> (32u - j1)) & (0xffffffffu << j0);
                 const float best = chunk_maximum_masked(v, inside, group);
                 if (best > run) { run = best; arg = c0 + chunk_position(v, inside, group, best); }
@@ -473,9 +534,126 @@ __global__ void maxsim_f32_kernel(const float *__restrict__ q, const float *__re
 
 __global__ void iota_offsets_kernel(uint64_t *out, uint64_t a, uint64_t b) { out[0] = a; out[1] = b; }
 
+// ---- documents re-laid on 32-token boundaries (batch form) ------------------------------------------------------------
+// The epilogue scans the similarity tile 32 columns at a time. A document boundary inside such a chunk costs it several times
+// a plain chunk (two masked maxima, two position searches, the close of a document in mid-chunk), and with documents of
+// 64 - 300 tokens every fifth or sixth chunk holds one: measured, treating every chunk as plain makes the kernel 38 % faster.
+// So the batch call first copies the documents into a scratch blob in which every document starts on a multiple of 32 tokens:
+// the tail of its last chunk repeats the document's LAST token. A repeated token can tie with the real one but never beat it,
+// and ties go to the lower position, so maxima, winners and sums are the same bits as on the caller's layout; inverse norms
+// are repeated alongside. Costs one pass over the packed documents (read + write at HBM rate, about 3 % of the call at depth
+// 128), 9 % more columns on average for documents of late-interaction size, and the scratch.
+constexpr int kPadScanBlock = 1024;
+__device__ __forceinline__ uint64_t padded_length(const uint64_t *offsets, uint64_t doc) {
+    return (offsets[doc + 1] - offsets[doc] + 31u) & ~(uint64_t)31u;
+}
+// (a) sum of the padded lengths of every block of 1024 documents
+__global__ void __launch_bounds__(kPadScanBlock) pad_block_sums_kernel(const uint64_t *offsets, uint64_t n_docs, uint64_t *block_sums) {
+    __shared__ uint64_t warp_sums[kPadScanBlock / 32];
+    const uint64_t doc = (uint64_t)blockIdx.x * kPadScanBlock + threadIdx.x;
+    uint64_t v = doc < n_docs ? padded_length(offsets, doc) : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        uint64_t w = warp_sums[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) w += __shfl_down_sync(0xffffffffu, w, o);
+        if (threadIdx.x == 0) block_sums[blockIdx.x] = w;
+    }
+}
+// (b) exclusive scan of the block sums, in place, by one thread block; the grand total goes behind the last entry
+__global__ void __launch_bounds__(kPadScanBlock) pad_scan_blocks_kernel(uint64_t *block_sums, uint64_t blocks) {
+    __shared__ uint64_t warp_sums[kPadScanBlock / 32];
+    __shared__ uint64_t carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (uint64_t base = 0; base < blocks; base += kPadScanBlock) {
+        const uint64_t i = base + threadIdx.x;
+        const uint64_t own = i < blocks ? block_sums[i] : 0;
+        uint64_t v = own;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint64_t up = __shfl_up_sync(0xffffffffu, v, o);
+            if ((threadIdx.x & 31) >= o) v += up;
+        }
+        if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = v;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            uint64_t w = warp_sums[threadIdx.x];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint64_t up = __shfl_up_sync(0xffffffffu, w, o);
+                if (threadIdx.x >= o) w += up;
+            }
+            warp_sums[threadIdx.x] = w;  // inclusive over warps
+        }
+        __syncthreads();
+        const uint64_t before = carry + ((threadIdx.x >> 5) ? warp_sums[(threadIdx.x >> 5) - 1] : 0) + v - own;
+        if (i < blocks) block_sums[i] = before;
+        __syncthreads();
+        if (threadIdx.x == kPadScanBlock - 1) carry = before + own;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) block_sums[blocks] = carry;
+}
+// (c) the padded offsets: exclusive scan inside every block of 1024 documents plus the block's base
+__global__ void __launch_bounds__(kPadScanBlock) pad_offsets_kernel(const uint64_t *offsets, uint64_t n_docs, const uint64_t *block_bases,
+                                                                  uint64_t *padded_offsets) {
+    __shared__ uint64_t warp_sums[kPadScanBlock / 32];
+    const uint64_t doc = (uint64_t)blockIdx.x * kPadScanBlock + threadIdx.x;
+    const uint64_t own = doc < n_docs ? padded_length(offsets, doc) : 0;
+    uint64_t v = own;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint64_t up = __shfl_up_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) >= o) v += up;
+    }
+    if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        uint64_t w = warp_sums[threadIdx.x];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint64_t up = __shfl_up_sync(0xffffffffu, w, o);
+            if (threadIdx.x >= o) w += up;
+        }
+        warp_sums[threadIdx.x] = w;
+    }
+    __syncthreads();
+    const uint64_t before = block_bases[blockIdx.x] + ((threadIdx.x >> 5) ? warp_sums[(threadIdx.x >> 5) - 1] : 0) + v - own;
+    if (doc < n_docs) padded_offsets[doc] = before;
+    if (doc + 1 == n_docs) padded_offsets[n_docs] = before + own;
+}
+// One warp per document: its rows (128 bytes per depth block, eight 16-byte pieces stored at piece ^ (row & 7) inside the
+// 128-row chunk of their depth block) move to their new row numbers, the last row is repeated up to the next multiple of 32.
+__global__ void __launch_bounds__(256) maxsim_pad_rows_kernel(const uint4 *__restrict__ src, const float *__restrict__ src_inv,
+                                                             const uint64_t *__restrict__ offsets, const uint64_t *__restrict__ padded_offsets,
+                                                             uint64_t n_docs, uint32_t kblocks, uint4 *__restrict__ dst, float *__restrict__ dst_inv) {
+    const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const uint32_t pieces_per_row = kblocks * 8u;
+    for (uint64_t doc = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); doc < n_docs; doc += warps) {
+        const uint64_t from = offsets[doc], length = offsets[doc + 1] - from, to = padded_offsets[doc];
+        const uint64_t padded = padded_offsets[doc + 1] - to;
+        if (length == 0) continue;
+        for (uint64_t x = lane; x < padded * pieces_per_row; x += 32) {
+            const uint64_t j = x / pieces_per_row;
+            const uint32_t pc = (uint32_t)(x % pieces_per_row), kb = pc >> 3, piece = pc & 7u;
+            const uint64_t s_row = from + (j < length ? j : length - 1), d_row = to + j;
+            const uint64_t s_at = ((s_row >> 7) * kblocks + kb) * 1024u + (s_row & 127u) * 8u + (piece ^ (uint32_t)(s_row & 7u));
+            const uint64_t d_at = ((d_row >> 7) * kblocks + kb) * 1024u + (d_row & 127u) * 8u + (piece ^ (uint32_t)(d_row & 7u));
+            dst[d_at] = src[s_at];
+        }
+        for (uint64_t j = lane; j < padded; j += 32) dst_inv[to + j] = src_inv[from + (j < length ? j : length - 1)];
+    }
+}
+
 cudaError_t launch_maxsim_tc(uint32_t dt, const MaxsimDev &dev_in, cudaStream_t stream) {
     MaxsimDev dev = dev_in;
     dev.idesc = make_idesc(1, dt == kBF16 ? 1 : 0, kMsBM, kMsBN);
+    dev.idesc_pair = make_idesc(1, dt == kBF16 ? 1 : 0, kMsBM, 2 * kMsBN);
     static bool configured[64] = {false};
     int d = 0;
     cudaGetDevice(&d);
@@ -663,7 +841,43 @@ void maxsims_batch_impl(uint32_t dt, const void *q_packed, const void *q_offsets
         dev.n_queries = n_queries; dev.n_docs = n_docs; dev.q_tokens = q_tokens; dev.d_tokens = d_tokens;
         dev.kblocks = (uint32_t)(qh.depth_padded_bytes / kChunkRowBytes);
         dev.q_tiles = (uint32_t)((q_tokens + kMsBM - 1) / kMsBM);
-        dev.segments = pick_segments(d_tokens, dev.q_tiles);
+        // Documents on 32-token boundaries (see maxsim_pad_rows_kernel), unless switched off for comparisons (bit 24 of the
+        // variant word), the scratch would take more than half of the free device memory, or they sit on such boundaries already.
+        if ((((uint32_t)current_variant() >> 24) & 1u) == 0u) {
+            const uint64_t blocks = (n_docs + kPadScanBlock - 1) / kPadScanBlock;
+            const uint64_t bound_rows = round_up(d_tokens + 31 * n_docs, kRowPad);
+            const uint64_t offsets_bytes = round_up((n_docs + 1) * 8, 256), sums_bytes = round_up((blocks + 1) * 8, 256);
+            const uint64_t inv_bytes = round_up(bound_rows * 4, 256), payload_bytes = bound_rows * dh.depth_padded_bytes;
+            const uint64_t need = offsets_bytes + sums_bytes + inv_bytes + payload_bytes;
+            size_t free_bytes = 0, total_bytes = 0;
+            if (cudaMemGetInfo(&free_bytes, &total_bytes) != cudaSuccess) { cudaGetLastError(); free_bytes = 0; }
+            uint8_t *pad = need <= free_bytes / 2 || scratch_capacity(kSlotA) >= need ? static_cast<uint8_t *>(scratch(kSlotA, need)) : nullptr;
+            if (pad) {
+                uint64_t *padded_offsets = reinterpret_cast<uint64_t *>(pad), *sums = reinterpret_cast<uint64_t *>(pad + offsets_bytes);
+                float *padded_inv = reinterpret_cast<float *>(pad + offsets_bytes + sums_bytes);
+                uint4 *padded_payload = reinterpret_cast<uint4 *>(pad + offsets_bytes + sums_bytes + inv_bytes);
+                pad_block_sums_kernel<<<(unsigned)blocks, kPadScanBlock, 0, stream>>>(d_off_dev, n_docs, sums);
+                pad_scan_blocks_kernel<<<1, kPadScanBlock, 0, stream>>>(sums, blocks);
+                pad_offsets_kernel<<<(unsigned)blocks, kPadScanBlock, 0, stream>>>(d_off_dev, n_docs, sums, padded_offsets);
+                uint64_t padded_tokens = 0;
+                ok = cuda_ok(cudaGetLastError(), "padded offsets") &&
+                     cuda_ok(cudaMemcpyAsync(&padded_tokens, padded_offsets + n_docs, 8, cudaMemcpyDeviceToHost, stream), "read padded size") &&
+                     cuda_ok(cudaStreamSynchronize(stream), "read padded size");
+                g_launches += 3;
+                if (ok && padded_tokens != d_tokens && padded_tokens <= bound_rows) {
+                    const uint64_t warps_wanted = n_docs < 148 * 64 ? n_docs : 148 * 64;
+                    maxsim_pad_rows_kernel<<<(unsigned)((warps_wanted + 7) / 8), 256, 0, stream>>>(
+                        reinterpret_cast<const uint4 *>(dev.d_payload), dev.d_inv, d_off_dev, padded_offsets, n_docs, dev.kblocks, padded_payload, padded_inv);
+                    ok = cuda_ok(cudaGetLastError(), "document re-layout kernel");
+                    g_launches++;
+                    dev.d_payload = reinterpret_cast<const uint8_t *>(padded_payload);
+                    dev.d_inv = padded_inv;
+                    dev.d_offsets = padded_offsets;
+                    dev.d_tokens = padded_tokens;
+                }
+            }
+        }
+        dev.segments = pick_segments(dev.d_tokens, dev.q_tiles);
         dev.scores_f32 = s_dev; dev.score_stride = s_pitch / 4; dev.total_f64 = nullptr; dev.error_word = err;
         ok = cuda_ok(launch_maxsim_tc(dt, dev, stream), "MaxSim kernel");
         g_launches++;

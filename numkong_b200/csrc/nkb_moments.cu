@@ -169,8 +169,22 @@ template <> struct Moments<kE4M3> : FloatMoments<1, false> {
         for (int i = 0; i < 4; ++i) s.squares += (double)large_squares[i] * kScaleSquared;
     }
 };
+// An e5m2 code is the high byte of a binary16 value: two codes become a binary16 pair with one byte permutation and are
+// then added in f64 in the same order as the one-by-one path (the sums are the same bits; squares of e5m2 values span 60
+// binades, so no f32 partial sum of them is exact).
 template <> struct Moments<kE5M2> : FloatMoments<1, false> {
     static __device__ __forceinline__ void add(State &s, unsigned long long bits) { add_value(s, (double)decode_bits<kE5M2>((uint32_t)bits)); }
+    static __device__ __forceinline__ void add_vector(State &s, const uint32_t (&w)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                const uint32_t bits = __byte_perm(w[i], 0u, p ? 0x3424u : 0x1404u);  // the two codes in the high bytes of the two halves
+                const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&bits));
+                add_value(s, (double)v.x);
+                add_value(s, (double)v.y);
+            }
+    }
 };
 template <typename Format>
 struct Fp6Moments : FloatMoments<1, false> {
