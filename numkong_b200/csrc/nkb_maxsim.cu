@@ -11,13 +11,23 @@
 // One kernel serves both the single (query, document) call of the reference API and the all-pairs
 // batch (many queries x many ragged documents packed back to back). A CTA owns one tile of 128 query
 // tokens and one contiguous run of whole documents. The run is cut into FOUR STREAMS of whole
-// documents (equal shares of its tokens), and every stream has its own 128-column accumulator in
-// TMEM: the MMA issuer goes round the streams, one 128-token document tile each, while sixteen
-// epilogue warps - one per TMEM lane quarter and stream - read their stream's tile. A warp therefore
-// sees every document of its stream from its first token to its last: the running maximum of a
-// document never leaves the warp's registers, no two warps ever have to merge partial maxima, and
-// the per-(query, document) sum is finished by the one warp that holds the query's 32 rows (a plain
-// store; only queries that straddle warps or tiles add their parts atomically - two parts commute).
+// documents (equal shares of its tokens) and sixteen epilogue warps - one per TMEM lane quarter and
+// stream - follow them. A warp therefore sees every document of its stream from its first token to
+// its last: the running maximum of a document never leaves the warp's registers, no two warps ever
+// have to merge partial maxima, and the per-(query, document) sum is finished by the one warp that
+// holds the query's 32 rows (a plain store; only queries that straddle warps or tiles add their parts
+// atomically - two parts commute).
+//
+// With the query tile resident in shared memory (depth <= 256 for 16-bit types) the four streams
+// advance in lock-step, 64 tokens each per step: their four half chunks sit back to back in one
+// stage, ONE N = 256 instruction per 32 bytes of depth multiplies all four, and TMEM holds two such
+// 256-column buffers. A warp pulls its stream's 64 columns into registers, hands the buffer back at
+// once and scans from registers while the tensor cores fill the other buffer, so no MMA waits for a
+// scan. Deeper queries stream through the ring with the documents; the streams then own one
+// 128-column accumulator each and take turns.
+//
+// The batch form first re-lays the documents on 32-token boundaries (maxsim_pad_rows_kernel), so
+// that no 32-column chunk of the scan holds a document boundary.
 #include <cstdio>
 #include <cstring>
 #include "nkb_internal.h"
@@ -31,7 +41,7 @@ namespace {
 
 constexpr int kMsBM = 128;                 // query tokens per CTA = TMEM lanes
 constexpr int kMsBN = 128;                 // document tokens per tile = one 128-row block of the packed payload
-constexpr int kMsStreams = 4;              // document streams per CTA = accumulators in TMEM (4 x 128 columns)
+constexpr int kMsStreams = 4;              // document streams per CTA (TMEM: 2 buffers x 4 x 64 columns, or 4 x 128 for deep queries)
 constexpr int kMsEpilogueWarps = 4 * kMsStreams;
 constexpr int kMsThreads = 64 + 32 * kMsEpilogueWarps;
 // Shared memory: the query tile stays resident when it is at most four depth blocks long (depth <= 256 for 16-bit types:
@@ -39,7 +49,7 @@ constexpr int kMsThreads = 64 + 32 * kMsEpilogueWarps;
 // ring with the documents (half as many, twice as large stages).
 constexpr int kMsResidentBlocks = 4;
 constexpr int kMsResidentBytes = kMsResidentBlocks * (int)kChunkBytes;   // 64 KiB
-constexpr int kMsRingBytes = 6 * (int)kChunkBytes;                       // 96 KiB: 6 document stages, or 3 query + document stages
+constexpr int kMsRingBytes = 6 * (int)kChunkBytes;                       // 96 KiB: three stages of 32 KiB
 constexpr int kMsRingOffset = kMsResidentBytes;
 constexpr int kMsBarrierOffset = kMsRingOffset + kMsRingBytes;
 constexpr int kMsMaxStages = 6;
@@ -188,17 +198,24 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
     if (q_tile >= p.q_tiles) return;  // padding blocks of the last group (nothing allocated yet)
 
     const bool resident = p.kblocks <= (uint32_t)kMsResidentBlocks;
-    // A stage is two chunks. Query tile streamed (deep queries): a document chunk and the query chunk of the same depth block.
-    // Query tile resident: the chunks of the SAME round of two neighbouring streams (0 and 1, or 2 and 3), back to back, so
-    // that one N = 256 instruction multiplies both - half as many instructions for the issuing thread, and the query chunk is
-    // read from shared memory once per 256 columns instead of once per 128 (at N = 128 an instruction reads 8 KiB per 64
-    // cycles, all the 128 bytes per cycle that shared memory delivers, while the copies of the next stages write into it).
+    // A stage is 32 KiB. Query tile streamed (deep queries): a document chunk and the query chunk of the same depth block; every
+    // stream then has one 128-column accumulator and the streams take turns (N = 128 instructions).
+    // Query tile resident (the regular case): the four streams advance in LOCK-STEP, 64 tokens each per step. A stage holds
+    // the four 64-token half chunks (8 KiB each) of one depth block back to back = 256 rows, and ONE N = 256 instruction
+    // multiplies all four - a quarter of the instructions for the issuing thread, and the query chunk is read from shared
+    // memory once per 256 columns (at N = 128 an instruction reads 8 KiB per 64 cycles: all the 128 bytes per cycle shared
+    // memory delivers, while the copies of the next stages write into it). TMEM holds two such 256-column buffers; stream s owns
+    // columns 64 s .. 64 s + 63 of either. An epilogue warp pulls its 64 columns into registers, hands the buffer back at once
+    // and scans from registers while the tensor cores fill the other buffer: no MMA ever waits for a scan.
     const int stages = 3;
     const uint32_t stage_bytes = 2u * kChunkBytes;
+    constexpr uint32_t kHalf = kMsBN / 2;                          // tokens per stream and step in lock-step mode
+    constexpr uint32_t kHalfBytes = kHalf * kChunkRowBytes;        // 8 KiB: 64 rows of one depth block
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMsMaxStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < kMsStreams; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), 4 * 32); }
+        // lock-step mode uses barriers 0 and 1 (one per buffer; every epilogue warp reports once per step)
+        for (int a = 0; a < kMsStreams; ++a) { mbar_init(tmem_full_bar(a), 1); mbar_init(tmem_empty_bar(a), resident ? 4 * kMsStreams : 4 * 32); }
         mbar_init(query_bar, 1);
         mbar_init(drain_bar, 1);
         fence_mbar_init();
@@ -240,7 +257,7 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
     };
     // Stream `s`: documents [first, last) of the run, tokens [lo, hi) relative to cache_base, and the 128-token blocks that
     // hold them (a block at the border between two streams is multiplied for both; each keeps its own documents' columns).
-    struct Stream { uint32_t first_doc, last_doc, lo, hi, first_block, blocks; };
+    struct Stream { uint32_t first_doc, last_doc, lo, hi, first_block, blocks, first_half, halves; };
     auto stream_of = [&](int s) {
         Stream st;
         st.first_doc = (uint32_t)(bounds[s] - doc_begin);
@@ -249,6 +266,8 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
         st.hi = st.last_doc == 0 ? st.lo : end_of_doc(st.last_doc - 1);
         st.first_block = st.lo / kMsBN;
         st.blocks = st.hi > st.lo ? (st.hi + kMsBN - 1) / kMsBN - st.first_block : 0u;
+        st.first_half = st.lo / kHalf;                                                   // 64-token half blocks (lock-step mode)
+        st.halves = st.hi > st.lo ? (st.hi + kHalf - 1) / kHalf - st.first_half : 0u;
         return st;
     };
 
@@ -269,24 +288,29 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             auto tile_of = [&](int s, uint32_t r) {
                 return p.d_payload + (cache_base / kMsBN + st[s].first_block + r) * (uint64_t)p.kblocks * kChunkBytes;
             };
-            for (uint32_t r = 0; r < rounds && ok; ++r) {
-                if (resident) {
-                    for (int s = 0; s < kMsStreams && ok; s += 2) {
-                        const bool have0 = r < st[s].blocks, have1 = r < st[s + 1].blocks;
-                        if (!have0 && !have1) continue;
-                        const uint8_t *tile0 = tile_of(s, r), *tile1 = tile_of(s + 1, r);
-                        for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-                            if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
-                            const uint32_t dst = smem_base + kMsRingOffset + stage * stage_bytes;
-                            mbar_expect_tx(full_bar(stage), ((uint32_t)have0 + (uint32_t)have1) * kChunkBytes);
-                            if (have0) bulk_load(dst, tile0 + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
-                            if (have1) bulk_load(dst + kChunkBytes, tile1 + (uint64_t)kb * kChunkBytes, kChunkBytes, full_bar(stage));
-                            ++issued;
-                            if (++stage == stages) { stage = 0; phase ^= 1u; }
+            if (resident) {
+                uint32_t steps = 0;
+                for (int s = 0; s < kMsStreams; ++s) steps = st[s].halves > steps ? st[s].halves : steps;
+                for (uint32_t t = 0; t < steps && ok; ++t) {
+                    uint32_t active = 0;
+                    for (int s = 0; s < kMsStreams; ++s) active += t < st[s].halves ? 1u : 0u;
+                    for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                        if (!mbar_wait(empty_bar(stage), phase ^ 1u, 1, p.error_word)) { ok = false; break; }
+                        const uint32_t dst = smem_base + kMsRingOffset + stage * stage_bytes;
+                        mbar_expect_tx(full_bar(stage), active * kHalfBytes);
+                        for (int s = 0; s < kMsStreams; ++s) {
+                            if (t >= st[s].halves) continue;  // this stream is done: its rows of the stage keep what they held
+                            const uint64_t token = cache_base + (uint64_t)(st[s].first_half + t) * kHalf;
+                            const uint8_t *src = p.d_payload + ((token >> 7) * p.kblocks + kb) * (uint64_t)kChunkBytes + (token & 64u) * kChunkRowBytes;
+                            bulk_load(dst + s * kHalfBytes, src, kHalfBytes, full_bar(stage));
                         }
+                        ++issued;
+                        if (++stage == stages) { stage = 0; phase ^= 1u; }
                     }
-                    continue;
                 }
+                rounds = 0;  // nothing left for the stream-by-stream loop below
+            }
+            for (uint32_t r = 0; r < rounds && ok; ++r) {
                 for (int s = 0; s < kMsStreams && ok; ++s) {
                     if (r >= st[s].blocks) continue;
                     const uint8_t *b_tile = tile_of(s, r);
@@ -321,35 +345,31 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             uint32_t phase = 0;
             bool ok = true;
             if (resident && !mbar_wait(query_bar, 0u, 3, p.error_word)) ok = false;
-            for (uint32_t r = 0; r < rounds && ok; ++r) {
-                if (resident) {
-                    for (int s = 0; s < kMsStreams && ok; s += 2) {
-                        const bool have0 = r < st[s].blocks, have1 = r < st[s + 1].blocks;
-                        if (!have0 && !have1) continue;
-                        // A stream's accumulator was handed out r times before: wait until its four warps have read round r - 1.
-                        if (have0 && !mbar_wait(tmem_empty_bar(s), (r & 1u) ^ 1u, 2, p.error_word)) { ok = false; break; }
-                        if (have1 && !mbar_wait(tmem_empty_bar(s + 1), (r & 1u) ^ 1u, 2, p.error_word)) { ok = false; break; }
+            if (resident) {
+                uint32_t steps = 0;
+                for (int s = 0; s < kMsStreams; ++s) steps = st[s].halves > steps ? st[s].halves : steps;
+                for (uint32_t t = 0; t < steps && ok; ++t) {
+                    // Buffer t & 1 was handed out t / 2 times before: wait until all sixteen warps have pulled step t - 2 out of it.
+                    const uint32_t buf = t & 1u;
+                    if (!mbar_wait(tmem_empty_bar(buf), ((t >> 1) & 1u) ^ 1u, 2, p.error_word)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + buf * (2u * kMsBN);
+                    for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                        if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
                         tc_fence_after_sync();
-                        // Both streams: one instruction over their 256 neighbouring columns; one of them left: its 128 alone.
-                        const uint32_t d_tmem = tmem_base + (have0 ? s : s + 1) * kMsBN;
-                        const uint32_t idesc = have0 && have1 ? p.idesc_pair : p.idesc;
-                        for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
-                            if (!mbar_wait(full_bar(stage), phase, 3, p.error_word)) { ok = false; break; }
-                            tc_fence_after_sync();
-                            const uint32_t b_src = smem_base + kMsRingOffset + stage * stage_bytes + (have0 ? 0u : kChunkBytes);
-                            const uint64_t a_desc = make_smem_desc_sw128(smem_base + kb * kChunkBytes);
-                            const uint64_t b_desc = make_smem_desc_sw128(b_src);
+                        const uint64_t a_desc = make_smem_desc_sw128(smem_base + kb * kChunkBytes);
+                        const uint64_t b_desc = make_smem_desc_sw128(smem_base + kMsRingOffset + stage * stage_bytes);
 #pragma unroll
-                            for (int k = 0; k < 4; ++k)
-                                umma<kKind, 1>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | (uint32_t)k) != 0u);
-                            umma_commit(empty_bar(stage));
-                            if (++stage == stages) { stage = 0; phase ^= 1u; }
-                        }
-                        if (ok && have0) umma_commit(tmem_full_bar(s));
-                        if (ok && have1) umma_commit(tmem_full_bar(s + 1));
+                        for (int k = 0; k < 4; ++k)
+                            umma<kKind, 1>(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc_pair, (kb | (uint32_t)k) != 0u);
+                        umma_commit(empty_bar(stage));
+                        if (++stage == stages) { stage = 0; phase ^= 1u; }
                     }
-                    continue;
+                    if (ok) umma_commit(tmem_full_bar(buf));
                 }
+                rounds = 0;
+            }
+            for (uint32_t r = 0; r < rounds && ok; ++r) {
                 for (int s = 0; s < kMsStreams && ok; ++s) {
                     if (r >= st[s].blocks) continue;
                     // Stream s's accumulator was handed out r times before: wait until its four warps have read round r - 1.
@@ -466,7 +486,41 @@ __global__ void __launch_bounds__(kMsThreads, 1) maxsim_kernel(const MaxsimDev p
             }
         };
 
-        for (uint32_t r = 0; r < st.blocks; ++r) {
+        if (resident) {
+            // Lock-step mode: every warp walks all steps (the buffer goes back when all sixteen have reported), a warp whose
+            // stream is done just reports.
+            uint32_t steps = 0;
+            for (int i = 0; i < kMsStreams; ++i) { const uint32_t h = stream_of(i).halves; steps = h > steps ? h : steps; }
+            for (uint32_t t = 0; t < steps; ++t) {
+                const uint32_t buf = t & 1u;
+                if (!mbar_wait(tmem_full_bar(buf), (t >> 1) & 1u, 4, p.error_word)) break;  // the issuer's own bounded wait ends the others
+                tc_fence_after_sync();
+                const bool mine = t < st.halves;
+                uint32_t v0[32], v1[32];
+                if (mine) {
+                    const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + buf * (2u * kMsBN) + (uint32_t)s * kHalf;
+                    tmem_ld_32x32(t_addr, v0);
+                    tmem_ld_32x32(t_addr + 32, v1);
+                    tmem_ld_wait_for(v0);
+                    tmem_ld_wait_for(v1);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty_bar(buf));   // both chunks are in registers: the buffer can be refilled
+                if (!mine) continue;
+                const uint32_t c0 = (st.first_half + t) * kHalf;   // relative position of the step's column 0
+                scan_chunk(v0, c0);
+                scan_chunk(v1, c0 + 32u);
+                // Documents that end inside this step are complete.
+                const uint32_t step_hi = c0 + kHalf < st.hi ? c0 + kHalf : st.hi;
+                while (cur_doc < st.last_doc && cur_end <= step_hi) {
+                    finish_doc();
+                    ++cur_doc;
+                    cur_end = cur_doc < st.last_doc ? end_of_doc(cur_doc) : 0u;  // 0: no chunk is "inside" once the stream is done
+                }
+            }
+        }
+        for (uint32_t r = 0; r < (resident ? 0u : st.blocks); ++r) {
             if (!mbar_wait(tmem_full_bar(s), r & 1u, 4, p.error_word)) break;  // nothing else waits for this warp
             tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + ((quarter * 32u) << 16) + s * kMsBN;
