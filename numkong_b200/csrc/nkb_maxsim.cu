@@ -56,7 +56,10 @@ constexpr int kMsMaxStages = 6;
 // The epilogue warps run alone on their SM sub-partitions, so every global load they wait for is dead time. The
 // inverse norms of the document tokens a CTA walks and the ends of its documents are therefore copied into shared
 // memory once per CTA (lookups beyond these windows fall back to global memory).
-constexpr int kMsInvCache = 72 * kMsBN;   // tokens (a run is about 64 tiles plus one document)
+constexpr int kMsRunTiles = 112;          // 128-token tiles per CTA: the set-up of a CTA (TMEM, barriers, query tile, these caches)
+                                          // overlaps with nothing, so runs are as long as the caches below allow (measured:
+                                          // 64 -> 128 tiles per run +5 %)
+constexpr int kMsInvCache = (kMsRunTiles + 8) * kMsBN;   // tokens (a run plus one long document)
 constexpr int kMsEndCache = 256;          // documents
 constexpr int kMsCacheOffset = kMsBarrierOffset + 256;
 constexpr int kMsSmemTotal = kMsCacheOffset + kMsInvCache * 4 + kMsEndCache * 4 + 1024;
@@ -743,10 +746,10 @@ cudaError_t launch_maxsim_tc(uint32_t dt, const MaxsimDev &dev_in, cudaStream_t 
 }
 
 uint32_t pick_segments(uint64_t d_tokens, uint32_t q_tiles) {
-    // Runs of about 64 document tiles (8192 tokens, some 45 documents of late-interaction size: eleven per stream) per CTA,
-    // but at least two CTAs per SM when the work allows it.
+    // Runs of about kMsRunTiles document tiles (14,336 tokens, some 80 documents of late-interaction size: twenty per stream)
+    // per CTA, but at least two CTAs per SM when the work allows it.
     uint64_t tiles = (d_tokens + kMsBN - 1) / kMsBN;
-    uint64_t seg = (tiles + 63) / 64;
+    uint64_t seg = (tiles + kMsRunTiles - 1) / kMsRunTiles;
     const uint64_t min_ctas = 2 * 148;
     if ((uint64_t)q_tiles * seg < min_ctas) {
         uint64_t want = (min_ctas + q_tiles - 1) / q_tiles;
