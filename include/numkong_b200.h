@@ -231,6 +231,11 @@ NKB_API int nk_configure_thread(uint64_t caps);    /* capabilities.h:909: nothin
  *   all documents back to back (one nk_maxsim_pack_<t> call each); q_offsets[n_queries+1] and
  *   d_offsets[n_documents+1] (u64, ascending, starting at 0) delimit them; every document needs at least
  *   one vector. scores[q * score_stride/4 + d] receives what nk_maxsim_packed_<t> returns for that pair.
+ *   For the duration of the call the documents are copied onto 32-token boundaries (every document's last vector repeated
+ *   up to the next multiple of 32: the same scores, bit for bit, and a scan without document boundaries inside its
+ *   32-column chunks); the copy lives in the calling thread's staging memory (about 1.1 x the packed documents, kept for the
+ *   next call and returned by nkb_release_caches()) and is skipped when it would take more than half of the free device
+ *   memory. (Allocating it per call was measured: a stream-ordered allocation of 10 GB per call costs more than the call.)
  * nkb_topk_smallest_f32: per row of a score matrix, the `top` smallest values and their columns + id_base.
  */
 #define NKB_DECLARE_TOPK_FAMILY(T)                                                                                     \
