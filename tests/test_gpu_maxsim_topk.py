@@ -69,6 +69,31 @@ def test_all_pairs_batch_is_bit_identical_from_run_to_run():
     assert nk.synchronize() == 0
 
 
+@pytest.mark.parametrize("depth", [128, 96, 320])
+def test_all_pairs_batch_is_the_same_on_the_callers_layout_and_on_32_token_boundaries(depth):
+    """The batch form scans a copy of the documents in which every document starts on a multiple of 32 tokens and its last
+    token is repeated up to the next one (bit 24 of the tuning word switches the copy off). A repeated token ties with the
+    real one and ties go to the lower position, so both layouts must give the same bits - for ragged lengths, one-token
+    documents, documents that already are multiples of 32, queries that straddle row groups, and (depth 320) the deep-query
+    pipeline."""
+    import torch
+    rng = np.random.default_rng(23)
+    q_counts = [32, 32, 7, 40, 32, 19]
+    d_counts = list(rng.integers(1, 301, size=300)) + [1, 32, 64, 31, 33, 256, 255, 257]
+    q_off = np.concatenate([[0], np.cumsum(q_counts)]).astype(np.int64)
+    d_off = np.concatenate([[0], np.cumsum(d_counts)]).astype(np.int64)
+    tq = nk.maxsim_pack(torch.from_numpy(syn.normal_matrix(int(q_off[-1]), depth, "bf16", 221).view(np.int16)).cuda(), "bf16")
+    td = nk.maxsim_pack(torch.from_numpy(syn.normal_matrix(int(d_off[-1]), depth, "bf16", 222).view(np.int16)).cuda(), "bf16")
+    try:
+        nk.lib.nkb_set_gemm_variant(1 << 24)
+        plain = nk.maxsims_packed(tq, q_off, td, d_off).clone()
+    finally:
+        nk.lib.nkb_set_gemm_variant(0)
+    padded = nk.maxsims_packed(tq, q_off, td, d_off)
+    assert nk.synchronize() == 0
+    assert torch.equal(plain, padded)
+
+
 def test_maxsim_of_identical_sides_is_zero():
     """test/test_maxsim.py:169-175 of the reference."""
     x = np.ones((8, 64), dtype=np.float32)
