@@ -11,9 +11,10 @@ N = 1: K steps back to back, operands resident in HBM.
 N > 1 (torchrun, one rank per GPU): STRONG scaling of the same problem. The 8192 rows of A are split into N contiguous
 blocks, one per rank - the caller-side split the reference documents for its threads (README.md:209-212,
 rust/matrix.rs:3016-3026). Packed B exists on rank 0 only when the timed region starts and reaches the other ranks INSIDE
-it, once; then every rank runs its K steps. By default rank 0 stores the blob once through the NVSwitch's multicast
-mapping with the library's own kernels (multimem.st + a flag barrier: numkong_b200.sharding.SwitchBroadcast);
---broadcast nccl uses ncclBroadcast instead, and is what runs where the GPUs have no multicast mapping. (--broadcast nccl
+it, once; then every rank runs its K steps. Two ways: rank 0 stores the blob once through the NVSwitch's multicast
+mapping with the library's own kernels (multimem.st + a flag barrier: numkong_b200.sharding.SwitchBroadcast), or
+ncclBroadcast; by default the set-up times both and the timed region uses the faster (the switch from four GPUs on, NCCL on
+two; --broadcast switch / nccl force one), and NCCL is what runs where the GPUs have no multicast mapping. (--broadcast nccl
 --broadcast-pieces 2 sends it in two column blocks and multiplies the first while the second is still on its way - the
 packed rows of a column block are one contiguous byte range of the blob - which measured no faster: the broadcast kernel
 and the persistent GEMM compete for the same SMs.)
@@ -448,10 +449,11 @@ def main():
                     help="N > 1: 1 = broadcast the packed matrix whole, then multiply (default); 2 = broadcast it in two column blocks "
                          "and multiply the first while the second is in flight (measured on two B200s: 0.73-0.77 ms for the first step "
                          "against 0.74-0.76 ms whole - the broadcast kernel and the persistent GEMM compete for SMs, so nothing is won)")
-    ap.add_argument("--broadcast", default="switch", choices=["switch", "nccl"],
-                    help="N > 1: how packed B reaches the ranks inside the timed region. switch (default) = rank 0 stores it once "
-                         "through the NVSwitch multicast mapping with the library's own kernels (numkong_b200.sharding.SwitchBroadcast); "
-                         "nccl = ncclBroadcast. Without a multicast mapping switch falls back to nccl and says so.")
+    ap.add_argument("--broadcast", default="auto", choices=["auto", "switch", "nccl"],
+                    help="N > 1: how packed B reaches the ranks inside the timed region. switch = rank 0 stores it once through the "
+                         "NVSwitch multicast mapping with the library's own kernels (numkong_b200.sharding.SwitchBroadcast); nccl = "
+                         "ncclBroadcast; auto (default) = whichever of the two delivered the blob faster in the set-up (the switch "
+                         "from four GPUs on, NCCL on two). Without a multicast mapping switch falls back to nccl and says so.")
     ap.add_argument("--rows", type=int, default=8192,
                     help="global rows of A; anything but 8192 is a reduced case for profiler captures, not the benchmark")
     args = ap.parse_args()
@@ -487,7 +489,7 @@ def main():
     # `blob` is what every rank multiplies with. Through the switch it is this rank's copy of a symmetric buffer that rank 0's
     # multicast stores fill on all GPUs at once (rank 0's own copy included), and rank 0 packs into a buffer of its own.
     channel, switch_note = None, None
-    if world > 1 and args.broadcast == "switch":
+    if world > 1 and args.broadcast in ("switch", "auto"):
         # Every rank must take the same road: one that cannot map the buffer (or has no multicast address) sends all to NCCL.
         try:
             channel = sharding.SwitchBroadcast(size)
@@ -526,7 +528,7 @@ def main():
         """Through the switch: rank 0's multicast stores, a flag barrier, the first product. Over NCCL: rank 0 sends the packed
         matrix piece by piece on the communication stream; every rank multiplies a piece as soon as it has arrived while the
         next one is still in flight."""
-        if channel is not None:
+        if use_switch:
             channel.send(packed_on_sender if rank == 0 else None, src=0, blocks=128)
             nk.dots_packed(ta, packed, out=out, dtype=dtype)
             return
@@ -549,6 +551,7 @@ def main():
         nk.dots_packed(ta, packed, out=out, dtype=dtype, columns=(pieces[-1][2], pieces[-1][3]))
 
     collective = None
+    use_switch = channel is not None
     if world > 1:
         # untimed: B reaches every rank once so that the warm-up steps have data; also warms NCCL up and times the plain
         # broadcast of the whole blob for the report
@@ -577,10 +580,19 @@ def main():
             dist.all_reduce(highest, op=dist.ReduceOp.MAX)
             sender = packed_on_sender[: size // 8 * 8].view(torch.int64).sum().reshape(1) if rank == 0 else digest
             assert lowest.item() == highest.item() == sender.item(), "the switch delivered different bytes to different ranks"
-            collective = {"op": "packed B stored once by rank 0 through the NVSwitch multicast mapping (multimem.st, the library's "
-                                "nkb_multicast_store) and a flag barrier between the GPUs (nkb_peer_barrier), inside the timed region, "
-                                "once, ahead of the first step",
-                          "bytes": int(size), "standalone_ms_whole_blob": switch_ms, "standalone_ms_ncclBroadcast": nccl_ms}
+            use_switch = args.broadcast == "switch" or switch_ms <= nccl_ms   # the same numbers on every rank (reduced above)
+            if use_switch:
+                collective = {"op": "packed B stored once by rank 0 through the NVSwitch multicast mapping (multimem.st, the library's "
+                                    "nkb_multicast_store) and a flag barrier between the GPUs (nkb_peer_barrier), inside the timed "
+                                    "region, once, ahead of the first step",
+                              "bytes": int(size), "standalone_ms_whole_blob": switch_ms, "standalone_ms_ncclBroadcast": nccl_ms}
+            else:
+                # NCCL was faster here (two GPUs): rank 0's copy of the symmetric buffer becomes the sender's blob
+                if rank == 0:
+                    blob.copy_(packed_on_sender)
+                collective = {"op": "ncclBroadcast of packed B from rank 0, inside the timed region, once, ahead of the first step "
+                                    "(chosen over the switch delivery by the set-up's timings)",
+                              "bytes": int(size), "standalone_ms_whole_blob": nccl_ms, "standalone_ms_switch": switch_ms}
         else:
             collective = {"op": "ncclBroadcast of packed B from rank 0, inside the timed region, once" + (", in 2 column blocks overlapped with the first step" if len(pieces) == 2 else ", ahead of the first step")
                                 + (f" (switch delivery not used: {switch_note})" if switch_note else ""),
@@ -601,9 +613,9 @@ def main():
     if world > 1:
         # the timed region must deliver B itself: every rank but the sender forgets what the warm-up left behind; one
         # more untimed broadcast (of a scratch buffer the size of the blob) is the communication path's own warm-up
-        if rank != 0 or channel is not None:
+        if rank != 0 or use_switch:
             blob.zero_()
-        if channel is None:
+        if not use_switch:
             scratch = torch.empty_like(blob)
             dist.broadcast(scratch, src=0)
             del scratch
