@@ -329,7 +329,12 @@ NKB_API int nkb_test_set_error_word(int which, uint32_t value);
 NKB_API uint64_t nkb_cached_blob_count(void);
 /** Kernels launched by this library in this process so far (for launch accounting in benchmarks). */
 NKB_API uint64_t nkb_launch_count(void);
-/** Forces a GEMM tile configuration for testing/tuning: 0 = choose by shape. */
+/** Tuning word for tests and A/B measurements; 0 = the library chooses everything. Bits 0-7 force a GEMM tile configuration
+ *  (1: 128 x 256 tiles per CTA, 2: 128 x 128, 3: CTA pairs on 256 x 256 tiles, 4: the four-stage 128 x 256 kernel, 5: CTA
+ *  pairs with the depth of the last tiles split between pairs - the one setting under which a row's bits depend on how many
+ *  rows are multiplied with it); bits 8-15 are the accumulation span (nkb_set_accumulation_span writes them); bits 16-23 the
+ *  number of query tiles of the all-pairs MaxSim that walk a document segment side by side (0: eight); bit 24 keeps that call
+ *  on the caller's document layout instead of the copy on 32-token boundaries. Process-wide. */
 NKB_API void nkb_set_gemm_variant(int variant);
 /** Accuracy / speed trade of the floating-point tensor-core products. The tensor cores truncate when they add into their
  *  f32 accumulators, so the depth is cut into spans of `stages` x 128 bytes that are added with round-to-nearest in
