@@ -196,10 +196,14 @@ def run_nearest_sharded(queries: int, corpus: int, depth: int, top: int, dtype: 
     from numkong_b200 import search, sharding
     dist, rank, world = _distributed(torch)
     lo, hi = sharding.row_shard(corpus, world, rank)
-    tq = _device_rows(torch, queries, depth, dtype, seed)          # same seed everywhere = replicated queries
+    tq = _device_rows(torch, queries, depth, dtype, seed)          # the queries live on rank 0 ...
+    if rank != 0:
+        tq.zero_()
     packed = nk.dots_pack(_device_rows(torch, hi - lo, depth, dtype, seed + 1 + rank), dtype)
 
     def step():
+        if world > 1:
+            dist.broadcast(tq, src=0)                              # ... and reach the other ranks inside every timed step
         d, i = search.nearest_in_shard(tq, packed, top, id_base=lo, dtype=dtype)
         sharding.merge_topk(d, i, top)
 
@@ -225,9 +229,13 @@ def run_maxsim_sharded(queries: int, docs: int, depth: int = 128, top: int = 100
     d0, d1 = sharding.token_balanced_shards(torch.from_numpy(d_off), world)[rank]
     local_off = torch.from_numpy(d_off[d0:d1 + 1] - d_off[d0]).cuda()
     tq = nk.maxsim_pack(_device_rows(torch, queries * q_tokens, depth, "bf16", seed + 1), "bf16")
+    if rank != 0:
+        tq.buffer.zero_()                                          # the packed queries live on rank 0 ...
     td = nk.maxsim_pack(_device_rows(torch, int(d_off[d1] - d_off[d0]), depth, "bf16", seed + 2 + rank), "bf16")
 
     def step():
+        if world > 1:
+            dist.broadcast(tq.buffer, src=0)                       # ... and are broadcast inside every timed step (position independent)
         scores = nk.maxsims_packed(tq, q_off, td, local_off)
         vals, ids = nk.topk_smallest(scores, min(top, d1 - d0), id_base=d0)
         sharding.merge_topk(vals, ids, min(top, d1 - d0))
